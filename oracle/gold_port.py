@@ -1,0 +1,315 @@
+"""Python face of the CPU oracle (oracle/qc_oracle.c): functions with the names, signatures and
+output layouts of the reference's gold recipes, computed on CPU tensors by the C restatement.
+
+THIS IS TEST INFRASTRUCTURE.  Only tests/, the smoke check and the CPU-baseline leg of the benchmark
+may import it; the product package must never do so.
+
+Reference functions mirrored (quant_cast_bench/quant_cast_gold/recipes.py = "G"):
+  float8_tensorwise_scale G:1179-1183, float8_tensorwise_f G:1186-1191, rowwise_fp8_f G:301-307,
+  rowwise_precalc_scale G:389-393, rowwise_precalc_f G:396-399, colwise_fp8_f G:339-349,
+  mxfp8_f G:561-568, mxfp8_swizzle_f G:1051-1053, mxfp8_dim_m_f G:656-671,
+  mxfp8_dim_m_swizzle_f G:1092-1094, mxfp8_dim_km_f G:701-719, mxfp8_dim_km_swizzle_f G:1134-1139,
+  nvfp4_gs_scale G:1243-1246, nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266,
+  nvfp4_gs_swizzle_sr_f G:1409-1426, _to_blocked_4d G:1000-1037.
+Extensions without a reference counterpart take `fmt="e5m2"`, `mode="floor"`, or a Philox key.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+FMT = {"e4m3": 0, "e5m2": 1}
+FP8_DTYPE = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+ROWWISE, COLWISE, SWIZZLE, FLOOR, SR = 1, 2, 4, 8, 16
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        _lib = ctypes.CDLL(path)
+        _lib.qco_mxfp8.restype = ctypes.c_int
+        _lib.qco_nvfp4.restype = ctypes.c_int
+        _lib.qco_nvfp4_t.restype = ctypes.c_int
+        _lib.qco_num_threads.restype = ctypes.c_int
+    return _lib
+
+
+def num_threads() -> int:
+    return lib().qco_num_threads()
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _i64(v):
+    return ctypes.c_int64(int(v))
+
+
+def _u64(v):
+    return ctypes.c_uint64(int(v) & 0xFFFFFFFFFFFFFFFF)
+
+
+def _check_x(x):
+    assert x.device.type == "cpu" and x.dtype == torch.bfloat16 and x.is_contiguous(), "oracle wants contiguous CPU bf16"
+    return x
+
+
+def _cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def blocked_shape(rows, cols):
+    return (_cdiv(rows, 128), _cdiv(cols, 4), 32, 16)
+
+
+def key_words(key):
+    """(seed, offset) of a Philox key given as a 2-element uint64 tensor, a (seed, offset) pair or an int."""
+    if isinstance(key, torch.Tensor):
+        k = key.reshape(-1).cpu().view(torch.int64).tolist()
+        return k[0], (k[1] if len(k) > 1 else 0)
+    if isinstance(key, (tuple, list)):
+        return int(key[0]), int(key[1])
+    return int(key), 0
+
+
+# ------------------------------------------------------------------ scalar helpers (for KATs)
+def f32_to_fp8(v, fmt="e4m3"):
+    v = v.contiguous().float()
+    out = torch.empty(v.shape, dtype=torch.uint8)
+    lib().qco_f32_to_fp8(_p(v), _i64(v.numel()), FMT[fmt], _p(out))
+    return out
+
+
+def f32_to_e2m1(v):
+    v = v.contiguous().float()
+    out = torch.empty(v.shape, dtype=torch.uint8)
+    lib().qco_f32_to_e2m1(_p(v), _i64(v.numel()), _p(out))
+    return out
+
+
+def e4m3_to_f32(b):
+    b = b.contiguous().view(torch.uint8)
+    out = torch.empty(b.shape, dtype=torch.float32)
+    lib().qco_e4m3_to_f32(_p(b), _i64(b.numel()), _p(out))
+    return out
+
+
+def amax_to_e8m0(amax, mode="rceil"):
+    a = amax.contiguous().float()
+    out = torch.empty(a.shape, dtype=torch.uint8)
+    lib().qco_amax_to_e8m0(_p(a), _i64(a.numel()), int(mode == "floor"), _p(out))
+    return out
+
+
+def e8m0_to_recip(b, mode="rceil"):
+    b = b.contiguous().view(torch.uint8)
+    out = torch.empty(b.shape, dtype=torch.float32)
+    lib().qco_e8m0_to_recip(_p(b), _i64(b.numel()), int(mode == "floor"), _p(out))
+    return out
+
+
+def philox4x32_10(ctr, key):
+    c = (ctypes.c_uint32 * 4)(*ctr)
+    k = (ctypes.c_uint32 * 2)(*key)
+    o = (ctypes.c_uint32 * 4)()
+    lib().qco_philox4x32_10(c, k, o)
+    return list(o)
+
+
+def sr_dither22(first, n, key):
+    seed, off = key_words(key)
+    out = torch.empty(n, dtype=torch.int32)
+    lib().qco_sr_dither22(_i64(first), _i64(n), _u64(seed), _u64(off), _p(out))
+    return out
+
+
+def to_blocked_4d(scale):
+    """G:1000-1037: (H, W) one-byte scales -> (ceil(H/128), ceil(W/4), 32, 16), padding 0."""
+    H, W = scale.shape
+    s = scale.contiguous().view(torch.uint8)
+    out = torch.empty(blocked_shape(H, W), dtype=torch.uint8)
+    lib().qco_to_blocked(_p(s), _i64(H), _i64(W), _p(out))
+    return out.view(scale.dtype)
+
+
+# ------------------------------------------------------------------ amax / per-tensor scales
+def amax_bf16(x):
+    _check_x(x)
+    out = torch.empty((), dtype=torch.float32)
+    lib().qco_amax_bf16(_p(x), _i64(x.numel()), _p(out))
+    return out
+
+
+def float8_tensorwise_scale(x, fmt="e4m3"):
+    _check_x(x)
+    out = torch.empty((), dtype=torch.float32)
+    lib().qco_fp8_tensorwise_scale(_p(x), _i64(x.numel()), FMT[fmt], _p(out))
+    return out
+
+
+def fp8_scale_from_amax(amax, fmt="e4m3"):
+    out = torch.empty((), dtype=torch.float32)
+    lib().qco_fp8_scale_from_amax(ctypes.c_float(float(amax)), FMT[fmt], _p(out))
+    return out
+
+
+def nvfp4_gs_scale(x):
+    _check_x(x)
+    out = torch.empty((), dtype=torch.float32)
+    lib().qco_nvfp4_gs_scale(_p(x), _i64(x.numel()), _p(out))
+    return out
+
+
+def nvfp4_scale_from_amax(amax):
+    out = torch.empty((), dtype=torch.float32)
+    lib().qco_nvfp4_scale_from_amax(ctypes.c_float(float(amax)), _p(out))
+    return out
+
+
+# ------------------------------------------------------------------ fp8
+def float8_tensorwise_f(x, scale, fmt="e4m3", **kwargs):
+    _check_x(x)
+    s = scale.detach().reshape(-1)[:1].float().contiguous()
+    q = torch.empty(x.shape, dtype=torch.uint8)
+    lib().qco_fp8_tensorwise_cast(_p(x), _i64(x.numel()), _p(s), FMT[fmt], _p(q))
+    return (q.view(FP8_DTYPE[fmt]),)
+
+
+def rowwise_fp8_f(x, fmt="e4m3", **kwargs):
+    _check_x(x)
+    M, N = x.shape
+    q = torch.empty((M, N), dtype=torch.uint8)
+    s = torch.empty((M, 1), dtype=torch.float32)
+    lib().qco_fp8_rowwise(_p(x), _i64(M), _i64(N), FMT[fmt], _p(q), _p(s))
+    return q.view(FP8_DTYPE[fmt]), s
+
+
+def rowwise_precalc_scale(x, fmt="e4m3"):
+    _check_x(x)
+    M, N = x.shape
+    s = torch.empty((M, 1), dtype=torch.float32)
+    lib().qco_fp8_rowwise_scale(_p(x), _i64(M), _i64(N), FMT[fmt], _p(s))
+    return s
+
+
+def rowwise_precalc_f(x, scale, fmt="e4m3", **kwargs):
+    _check_x(x)
+    M, N = x.shape
+    s = scale.float().contiguous()
+    assert s.numel() == M
+    q = torch.empty((M, N), dtype=torch.uint8)
+    lib().qco_fp8_rowwise_precalc(_p(x), _i64(M), _i64(N), _p(s), FMT[fmt], _p(q))
+    return (q.view(FP8_DTYPE[fmt]),)
+
+
+def colwise_fp8_f(x, fmt="e4m3", **kwargs):
+    _check_x(x)
+    M, N = x.shape
+    q = torch.empty((N, M), dtype=torch.uint8)
+    s = torch.empty((N, 1), dtype=torch.float32)
+    lib().qco_fp8_colwise(_p(x), _i64(M), _i64(N), FMT[fmt], _p(q), _p(s))
+    return q.view(FP8_DTYPE[fmt]), s
+
+
+# ------------------------------------------------------------------ mxfp8
+def _mxfp8(x, flags):
+    _check_x(x)
+    M, N = x.shape
+    swz = bool(flags & SWIZZLE)
+    qk = sk = qm = sm = None
+    if flags & ROWWISE:
+        qk = torch.empty((M, N), dtype=torch.uint8)
+        sk = torch.empty(blocked_shape(M, N // 32) if swz else (M, N // 32), dtype=torch.uint8)
+    if flags & COLWISE:
+        qm = torch.empty((N, M), dtype=torch.uint8)
+        sm = torch.empty(blocked_shape(N, M // 32) if swz else (N, M // 32), dtype=torch.uint8)
+    rc = lib().qco_mxfp8(_p(x), _i64(M), _i64(N), flags, _p(qk), _p(sk), _p(qm), _p(sm))
+    assert rc == 0, "mxfp8: rowwise needs N % 32 == 0, colwise needs M % 32 == 0"
+    outs = []
+    if flags & ROWWISE:
+        outs += [qk.view(torch.float8_e4m3fn), sk.view(torch.float8_e8m0fnu)]
+    if flags & COLWISE:
+        outs += [qm.view(torch.float8_e4m3fn), sm.view(torch.float8_e8m0fnu)]
+    return tuple(outs)
+
+
+def _mode(mode):
+    return FLOOR if mode == "floor" else 0
+
+
+def mxfp8_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, ROWWISE | _mode(mode))
+
+
+def mxfp8_swizzle_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, ROWWISE | SWIZZLE | _mode(mode))
+
+
+def mxfp8_dim_m_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, COLWISE | _mode(mode))
+
+
+def mxfp8_dim_m_swizzle_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, COLWISE | SWIZZLE | _mode(mode))
+
+
+def mxfp8_dim_km_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, ROWWISE | COLWISE | _mode(mode))
+
+
+def mxfp8_dim_km_swizzle_f(x, mode="rceil", **kwargs):
+    return _mxfp8(x, ROWWISE | COLWISE | SWIZZLE | _mode(mode))
+
+
+# ------------------------------------------------------------------ nvfp4
+def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
+    _check_x(x)
+    M, N = x.shape
+    o = outer_scale.detach().float().contiguous().reshape(-1)
+    per_row = int(outer_scale.ndim == 2)
+    if per_row:
+        assert o.numel() == M and not transposed
+    seed, off = key_words(key) if key is not None else (0, 0)
+    swz = bool(flags & SWIZZLE)
+    if transposed:
+        q = torch.empty((N, M // 2), dtype=torch.uint8)
+        s = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=torch.uint8)
+        rc = lib().qco_nvfp4_t(_p(x), _i64(M), _i64(N), _p(o), flags, _u64(seed), _u64(off), _p(q), _p(s))
+    else:
+        q = torch.empty((M, N // 2), dtype=torch.uint8)
+        s = torch.empty(blocked_shape(M, N // 16) if swz else (M, N // 16), dtype=torch.uint8)
+        rc = lib().qco_nvfp4(_p(x), _i64(M), _i64(N), _p(o), per_row, flags, _u64(seed), _u64(off), _p(q), _p(s))
+    assert rc == 0, "nvfp4: the blocked dim must be a multiple of 16"
+    return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
+
+
+def nvfp4_gs_f(x, outer_scale, **kwargs):
+    return _nvfp4(x, outer_scale, 0)
+
+
+def nvfp4_gs_swizzle_f(x, outer_scale, **kwargs):
+    return _nvfp4(x, outer_scale, SWIZZLE)
+
+
+def nvfp4_gs_swizzle_sr_f(x, outer_scale, key, **kwargs):
+    return _nvfp4(x, outer_scale, SWIZZLE | SR, key=key)
+
+
+def nvfp4_gs_t_f(x, outer_scale, **kwargs):
+    """== nvfp4_gs_f(x.t().contiguous(), outer_scale)"""
+    return _nvfp4(x, outer_scale, 0, transposed=True)
+
+
+def nvfp4_gs_swizzle_t_f(x, outer_scale, **kwargs):
+    """== nvfp4_gs_swizzle_f(x.t().contiguous(), outer_scale) (test/test_quant_cast_gold.py:104)"""
+    return _nvfp4(x, outer_scale, SWIZZLE, transposed=True)
+
+
+def nvfp4_gs_swizzle_t_sr_f(x, outer_scale, key, **kwargs):
+    return _nvfp4(x, outer_scale, SWIZZLE | SR, key=key, transposed=True)

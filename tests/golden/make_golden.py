@@ -1,0 +1,145 @@
+"""Generate tests/golden/gold_vectors.npz by running the REFERENCE's gold recipes on CPU.
+
+Run in a checkout where the reference project is available:
+    python tests/golden/make_golden.py --reference /path/to/quant_cast_bench_checkout
+The reference imports `torch.func._random` (a module of newer PyTorch builds) at import time; it is
+only used by the stochastic-rounding recipes, which are not part of the stored vectors, so an empty
+stand-in module is registered before the import.  Nothing from the reference is copied: only the
+inputs fed to it and the bytes it returned are stored.
+
+Stored per case `<shape>_<seed>`: the bf16 input bits and, for every gold recipe on the hot path,
+the raw bytes of each output (fp8 / e8m0 / packed fp4 as uint8, fp32 scales as their int32 bits).
+Also stored: scalar known-answer tables for PyTorch's fp32->e4m3/e5m2 casts, the reference's fp4
+encoder, its e8m0 RCEIL rounding and reciprocal, and its blocked-layout permutation.
+"""
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def import_gold(ref_root):
+    stub = types.ModuleType("torch.func._random")
+    stub.uniform = None
+    stub.key = None
+    sys.modules["torch.func._random"] = stub
+    sys.path.insert(0, ref_root)
+    from quant_cast_bench.quant_cast_gold import recipes as G
+    from quant_cast_bench.quant_cast_gold import utils as GU
+    return G, GU
+
+
+def make_input(M, N, seed, spread=10.0, outlier_p=1e-3, outlier_mul=100.0, zero_row_p=0.01):
+    """Same distribution family as the benchmark configs: N(0,1) * 2^U(-spread, spread) per row,
+    sparse outliers, some all-zero rows."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, N, generator=g)
+    x = x * torch.exp2((torch.rand(M, 1, generator=g) * 2 - 1) * spread)
+    x = torch.where(torch.rand(M, N, generator=g) < outlier_p, x * outlier_mul, x)
+    x[torch.rand(M, generator=g) < zero_row_p] = 0
+    x[M // 2] = 0  # at least one all-zero row in every case
+    return x.to(torch.bfloat16)
+
+
+def raw(t):
+    if t.dtype == torch.float32:
+        return t.contiguous().view(torch.int32).numpy()
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.int16).numpy()
+    return t.contiguous().view(torch.uint8).numpy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--out", default=os.path.join(HERE, "gold_vectors.npz"))
+    args = ap.parse_args()
+    G, GU = import_gold(args.reference)
+    out = {}
+
+    cases = [(128, 128, 0), (96, 160, 1), (128, 160, 2), (160, 320, 4)]
+    names = []
+    for M, N, seed in cases:
+        x = make_input(M, N, seed)
+        tag = f"{M}x{N}_s{seed}"
+        names.append(tag)
+        out[f"{tag}/x"] = raw(x)
+        s = G.float8_tensorwise_scale(x)
+        out[f"{tag}/float8_tensorwise_scale/0"] = raw(s.reshape(1))
+        out[f"{tag}/float8_tensorwise_f/0"] = raw(G.float8_tensorwise_f(x, s)[0])
+        ps = G.rowwise_precalc_scale(x)
+        out[f"{tag}/rowwise_precalc_scale/0"] = raw(ps)
+        out[f"{tag}/rowwise_precalc_f/0"] = raw(G.rowwise_precalc_f(x, ps)[0])
+        for fn in ("rowwise_fp8_f", "colwise_fp8_f", "mxfp8_f", "mxfp8_swizzle_f", "mxfp8_dim_m_f",
+                   "mxfp8_dim_m_swizzle_f", "mxfp8_dim_km_f", "mxfp8_dim_km_swizzle_f"):
+            for i, o in enumerate(getattr(G, fn)(x)):
+                out[f"{tag}/{fn}/{i}"] = raw(o)
+        gs = G.nvfp4_gs_scale(x)
+        out[f"{tag}/nvfp4_gs_scale/0"] = raw(gs.reshape(1))
+        for fn in ("nvfp4_gs_f", "nvfp4_gs_swizzle_f"):
+            for i, o in enumerate(getattr(G, fn)(x, gs)):
+                out[f"{tag}/{fn}/{i}"] = raw(o)
+        # transposed variant = the same recipe on x.t().contiguous() (test/test_quant_cast_gold.py:104)
+        for i, o in enumerate(G.nvfp4_gs_swizzle_f(x.t().contiguous(), gs)):
+            out[f"{tag}/nvfp4_gs_swizzle_t_f/{i}"] = raw(o)
+        for i, o in enumerate(G.nvfp4_gs_f(x.t().contiguous(), gs)):
+            out[f"{tag}/nvfp4_gs_t_f/{i}"] = raw(o)
+        pt = G.nvfp4_gs_per_token_scale(x).clamp(min=2.0 ** -100)
+        out[f"{tag}/nvfp4_per_token_scale/0"] = raw(pt)
+        for i, o in enumerate(G.nvfp4_gs_f(x, pt)):
+            out[f"{tag}/nvfp4_gs_f_per_token/{i}"] = raw(o)
+    out["cases"] = np.array(names)
+
+    # ---- scalar known-answer tables -------------------------------------------------------------
+    g = torch.Generator().manual_seed(1234)
+    bits = torch.randint(0, 2 ** 32, (20000,), generator=g, dtype=torch.int64)
+    # every e4m3 / e5m2 / e2m1 grid point and midpoint, and their fp32 neighbours
+    grid = []
+    for dt in (torch.float8_e4m3fn, torch.float8_e5m2):
+        vals = torch.arange(256, dtype=torch.uint8).view(dt).float()
+        vals = vals[torch.isfinite(vals)].unique()
+        mids = (vals[1:] + vals[:-1]) / 2
+        grid += [vals, mids]
+    grid.append(torch.tensor([0.0, 0.25, 0.5, 0.75, 1.0, 1.25, 1.5, 1.75, 2.0, 2.5, 3.0, 3.5, 4.0, 5.0, 6.0, 7.0]))
+    grid = torch.cat(grid)
+    grid = torch.cat([grid, -grid])
+    gb = grid.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    near = torch.cat([gb - 1, gb, gb + 1]) & 0xFFFFFFFF
+    allbits = torch.cat([bits, near])
+    allbits = torch.where(allbits >= 2 ** 31, allbits - 2 ** 32, allbits).to(torch.int32)
+    v = allbits.view(torch.float32)
+    v = v[torch.isfinite(v)]
+    v4 = v[v.abs() <= 464.0]
+    out["kat/e4m3_in"] = raw(v4)
+    out["kat/e4m3_out"] = raw(v4.to(torch.float8_e4m3fn))
+    v5 = v[v.abs() < 61440.0]
+    out["kat/e5m2_in"] = raw(v5)
+    out["kat/e5m2_out"] = raw(v5.to(torch.float8_e5m2))
+    small = torch.cat([v, torch.empty(8000).uniform_(-8, 8, generator=g)])
+    out["kat/e2m1_in"] = raw(small)
+    out["kat/e2m1_out"] = raw(GU.f32_to_f4_unpacked(small.clone()))
+    codes = torch.arange(256, dtype=torch.uint8)
+    dec = codes.view(torch.float8_e4m3fn).float()
+    out["kat/e4m3_decode"] = raw(dec)
+    am = v[v >= 0]
+    am = torch.cat([am, torch.tensor([448.0 * 2.0 ** k for k in range(-126, 120)])])
+    out["kat/rceil_in"] = raw(am)
+    out["kat/rceil_out"] = raw(G._amax_to_e8m0_rceil(am))
+    out["kat/recip_out"] = raw(G._e8m0_scale_to_reciprocal_fp32(codes.view(torch.float8_e8m0fnu)))
+    for H, W in ((128, 4), (96, 5), (300, 9)):
+        sc = torch.randint(0, 256, (H, W), generator=g, dtype=torch.uint8)
+        out[f"kat/blocked_{H}x{W}_in"] = raw(sc)
+        out[f"kat/blocked_{H}x{W}_out"] = raw(G._to_blocked_4d(sc))
+    out["kat/bf16_clamp_min"] = raw(torch.zeros(1, dtype=torch.bfloat16).clamp(min=1e-12))
+
+    np.savez_compressed(args.out, **out)
+    print(f"wrote {args.out}: {len(out)} arrays, {os.path.getsize(args.out)/1e6:.2f} MB, torch {torch.__version__}")
+
+
+if __name__ == "__main__":
+    main()
