@@ -1,0 +1,398 @@
+"""Benchmark of the quantization-cast hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one mxfp8 two-direction cast with blocked (32x4x4) scales -- the gold recipe
+`mxfp8_dim_km_swizzle` -- of a bf16 [16384, 16384] matrix (rowwise + transposed e4m3 outputs and both
+E8M0 scale grids from one read of x).  The metric is achieved GB/s over the algorithmic bytes
+(sum of numel * element_size over the inputs and outputs of the gold signature, as the reference's
+benchmarks/benchmark.py:35-38 counts them).  With N > 1 every rank casts its own [16384, 16384] row
+shard of a (N * 16384, 16384) matrix (no collective on this path: weak scaling) and `value` is the
+whole-job rate, bytes of all ranks over the slowest rank's time.
+
+Printed: ONE JSON line (rank 0).  Besides the base keys it carries
+  roofline      the dominant kernel against the measured HBM copy rate (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (oracle/qc_oracle.c, OpenMP) on the same workload on the host cores
+  e2e           the same cast through the host-buffer API (pinned host in, pinned host out)
+  casts         per-cast GB/s of the other casts of the benchmark configurations, same run
+  clocks        SM clock / throttle reasons sampled while the GPU was under load
+`--impl reference` times the CPU implementation alone (the reference is a PyTorch-eager recipe that
+cannot travel to the GPU box; its C restatement, pinned to the reference by golden vectors, runs here).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_STEP, N_STEP = 16384, 16384
+WORKLOAD = "mxfp8_dim_km_swizzle bf16[16384,16384] (config 2: N(0,1)*2^U(-10,10) per row, 0.1% outliers x100, 1% zero rows)"
+
+
+def algorithmic_bytes(M, N, kind):
+    """Bytes of the gold signature's inputs + outputs."""
+    e = M * N
+    if kind == "mxfp8_dim_km":
+        return 2 * e + e + e + 2 * (e // 32)
+    if kind in ("mxfp8", "mxfp8_dim_m"):
+        return 2 * e + e + e // 32
+    if kind == "nvfp4":
+        return 2 * e + 4 + e // 2 + e // 16
+    if kind == "fp8_tensorwise":
+        return 2 * e + 4 + e
+    if kind == "fp8_rowwise":
+        return 2 * e + e + 4 * M
+    if kind == "amax":
+        return 2 * e + 4
+    raise KeyError(kind)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def device_input(M, N, seed, device, spread=10.0, outlier_p=1e-3, outlier_mul=100.0, zero_row_p=0.01):
+    """Config-2 style input generated on the device (same distribution as workloads.make_input)."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    rows = 2048
+    for r0 in range(0, M, rows):
+        r1 = min(M, r0 + rows)
+        t = torch.randn(r1 - r0, N, generator=g, device=device)
+        if spread > 0:
+            t *= torch.exp2((torch.rand(r1 - r0, 1, generator=g, device=device) * 2 - 1) * spread)
+        if outlier_p > 0:
+            t = torch.where(torch.rand(r1 - r0, N, generator=g, device=device) < outlier_p, t * outlier_mul, t)
+        if zero_row_p > 0:
+            t[torch.rand(r1 - r0, generator=g, device=device) < zero_row_p] = 0
+        x[r0:r1] = t.to(torch.bfloat16)
+    return x
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) from a thread."""
+
+    def __init__(self, index):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                util = nv.nvmlDeviceGetUtilizationRates(self.h).gpu
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((mhz, util))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        mhz = [m for m, _ in self.samples]
+        return {
+            "sm_mhz": statistics.median(mhz) if mhz else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(mhz),
+        }
+
+
+def cpu_reference_step(x_cpu):
+    from oracle import gold_port as O
+    return O.mxfp8_dim_km_swizzle_f(x_cpu)
+
+
+def run_reference(args):
+    """CPU arm: the oracle's mxfp8_dim_km_swizzle on the host cores, all OpenMP threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import gold_port as O
+    from quant_cast_bench_b200.workloads import make_input
+    rows = 4096  # bounded sample: a quarter of the 16384-row workload per step
+    x = make_input(rows, N_STEP, seed=0)
+    nbytes = algorithmic_bytes(rows, N_STEP, "mxfp8_dim_km")
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_step(x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(x)
+    dt = time.perf_counter() - t0
+    gbs = nbytes * args.steps / dt / 1e9
+    cores = O.num_threads()
+    line = {
+        "impl": "reference", "metric": "achieved_GBps_mxfp8_dim_km_swizzle", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->e4m3+e8m0 (fp32 scale math)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": f"{rows} of {M_STEP} rows per step"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{rows}x{N_STEP} rows of the workload per step, {args.steps} steps"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def time_kernel(fn, iters, warmup=3):
+    """Average device time of fn() in ms: CUDA events on the launching (current) stream, one pair per launch."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = [a.elapsed_time(b) for a, b in evs]
+    return sum(ts) / len(ts), min(ts)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: quant_cast_cuda has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from quant_cast_bench_b200 import quant_cast_cuda as Q
+    from quant_cast_bench_b200.quant_cast_cuda import _lib as L
+    from quant_cast_bench_b200.quant_cast_cuda.host_api import HostMxfp8Caster
+
+    # this rank's [16384, 16384] row shard of the (world * 16384, 16384) matrix
+    x = device_input(M_STEP, N_STEP, seed=1000 + rank, device=dev)
+    nbytes = algorithmic_bytes(M_STEP, N_STEP, "mxfp8_dim_km")
+
+    def step():
+        return Q.mxfp8_dim_km_swizzle_cuda(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    barrier()
+    torch.cuda.synchronize()
+    L.launch_count = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    launches = L.launch_count
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    value = nbytes * world * args.steps / (ms_total * 1e-3) / 1e9
+
+    # per-launch duration of the dominant kernel, measured live (x is 512 MiB > L2, outputs 528 MiB)
+    k_avg, k_min = time_kernel(step, iters=max(args.steps, 20))
+    peak, peak_kind = measured_peak()
+    achieved = nbytes / (k_avg * 1e-3) / 1e9
+
+    # end to end through the host-buffer API: pinned host x in, pinned host outputs back, every step
+    caster = HostMxfp8Caster(M_STEP, N_STEP, dev, swizzle=True)
+    x_host = torch.empty((M_STEP, N_STEP), dtype=torch.bfloat16, pin_memory=True)
+    x_host.copy_(x)
+    for _ in range(2):
+        caster.cast(x_host)
+    torch.cuda.synchronize()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        outs_host = caster.cast(x_host)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = nbytes * world * e2e_steps / float(te.item()) / 1e9
+    h2d = x_host.numel() * 2
+    d2h = sum(o.numel() * o.element_size() for o in outs_host)
+
+    casts = {}
+    cpu = None
+    if rank == 0:
+        casts = bench_other_casts(Q, x, dev, peak)
+        clocks = sampler.stop()
+        cpu = cpu_baseline()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "achieved_GBps_mxfp8_dim_km_swizzle", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / 4987.5,
+        "dtype": "bf16->e4m3+e8m0 (fp32 scale math)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": M_STEP, "cols": N_STEP, "bytes_per_step_per_gpu": nbytes,
+                   "l2": "inputs (512 MiB) and outputs (528 MiB) exceed the 126 MB L2; no flush between iterations",
+                   "vs_baseline_ref": "reference CuTe kernel on B200, 4987.5 GB/s (benchmarks/bench_results.csv:34)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "mxfp8_tile_kernel<1,1,swizzle,rceil>",
+                     "launch_ms_avg": k_avg, "launch_ms_min": k_min, "frac_of_8TBps": achieved / 8000.0},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "casts": casts,
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline():
+    """The CPU oracle on a bounded sample of the same workload, all host threads (rank 0, N = 1 leg)."""
+    import torch
+    from oracle import gold_port as O
+    from quant_cast_bench_b200.workloads import make_input
+    rows = 4096
+    x = make_input(rows, N_STEP, seed=0)
+    cpu_reference_step(x)
+    reps = 3
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_reference_step(x)
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": algorithmic_bytes(rows, N_STEP, "mxfp8_dim_km") / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(),
+            "kind": "port", "sample": f"{rows} of {M_STEP} rows x {N_STEP} cols, mean of {reps} after 1 warm-up",
+            "host_cpus": os.cpu_count()}
+
+
+def bench_other_casts(Q, x, dev, peak):
+    """Per-cast GB/s of the other casts (same run, CUDA events per launch, inputs larger than L2 or an
+    L2 flush write in between)."""
+    import torch
+    out = {}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def timed(fn, nbytes, flush_l2=False, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            if flush_l2:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ms = statistics.median(ts)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "GBps": gbs, "frac_measured_peak": gbs / peak, "frac_8TBps": gbs / 8000.0}
+
+    M, N = x.shape
+    for mode in ("rceil", "floor"):
+        sfx = "" if mode == "rceil" else "_floor"
+        out["mxfp8" + sfx] = timed(lambda: Q.mxfp8_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8"))
+        out["mxfp8_swizzle" + sfx] = timed(lambda: Q.mxfp8_swizzle_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8"))
+        out["mxfp8_dim_m" + sfx] = timed(lambda: Q.mxfp8_dim_m_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_m"))
+        out["mxfp8_dim_m_swizzle" + sfx] = timed(lambda: Q.mxfp8_dim_m_swizzle_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_m"))
+        out["mxfp8_dim_km" + sfx] = timed(lambda: Q.mxfp8_dim_km_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_km"))
+        out["mxfp8_dim_km_swizzle" + sfx] = timed(lambda: Q.mxfp8_dim_km_swizzle_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_km"))
+    # reference shape for the fp8 / nvfp4 rows as well (16384^2), then the smaller configurations
+    s = Q.float8_tensorwise_scale_cuda(x)
+    gs = Q.nvfp4_gs_scale_cuda(x)
+    out["amax_16384"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x), algorithmic_bytes(M, N, "amax"))
+    out["fp8_tensorwise_16384"] = timed(lambda: Q.float8_tensorwise_cuda(x, s), algorithmic_bytes(M, N, "fp8_tensorwise"))
+    out["fp8_rowwise_16384"] = timed(lambda: Q.rowwise_fp8_cuda(x), algorithmic_bytes(M, N, "fp8_rowwise"))
+    out["nvfp4_16384"] = timed(lambda: Q.nvfp4_gs_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
+    out["nvfp4_swizzle_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
+    out["nvfp4_swizzle_t_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_t_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
+    key = Q.philox_key(0, device=dev)
+    out["nvfp4_swizzle_sr_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key), algorithmic_bytes(M, N, "nvfp4") + 16)
+    x1 = x[:4096, :4096].contiguous()          # config 1 shape (fits L2: flush between iterations)
+    s1 = Q.float8_tensorwise_scale_cuda(x1)
+    out["c1_fp8_tensorwise_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
+    out["c1_fp8_tensorwise_e5m2_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1, "e5m2"), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
+    out["c1_fp8_rowwise_4096"] = timed(lambda: Q.rowwise_fp8_cuda(x1), algorithmic_bytes(4096, 4096, "fp8_rowwise"), True)
+    out["c1_amax_4096"] = timed(lambda: Q.float8_tensorwise_scale_cuda(x1), algorithmic_bytes(4096, 4096, "amax"), True)
+    x3 = x[:8192, :8192].contiguous()          # config 3 shape (128 MiB input)
+    gs3 = Q.nvfp4_gs_scale_cuda(x3)
+    out["c3_nvfp4_amax_8192"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x3), algorithmic_bytes(8192, 8192, "amax"), True)
+    out["c3_nvfp4_8192"] = timed(lambda: Q.nvfp4_gs_cuda(x3, gs3), algorithmic_bytes(8192, 8192, "nvfp4"), True)
+    out["c3_nvfp4_swizzle_8192"] = timed(lambda: Q.nvfp4_gs_swizzle_cuda(x3, gs3), algorithmic_bytes(8192, 8192, "nvfp4"), True)
+    out["c3_nvfp4_swizzle_t_8192"] = timed(lambda: Q.nvfp4_gs_swizzle_t_cuda(x3, gs3), algorithmic_bytes(8192, 8192, "nvfp4"), True)
+    x5 = x[:8192, :].contiguous()              # config 5 shape
+    out["c5_nvfp4_sr_8192x16384"] = timed(lambda: Q.nvfp4_gs_swizzle_sr_cuda(x5, gs, key), algorithmic_bytes(8192, 16384, "nvfp4") + 16)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,148 @@
+/*
+ * quant_cast_cuda -- C ABI of the sm_100a quantization-cast kernels.
+ *
+ * Every entry point takes plain device pointers and sizes plus the CUDA stream to launch on
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).  Nothing here allocates device
+ * memory, synchronises the device, or keeps mutable host state: outputs and scratch are supplied
+ * by the caller and launches are asynchronous.
+ *
+ * Return value: 0 on success; a negative QCC_ERR_* for a rejected argument (nothing was launched);
+ * a positive value is the cudaError_t of a failed launch.
+ *
+ * Each function replaces the body of one gold recipe of vkuzo/quant_cast_bench; the citation gives
+ * the reference definition ("G" = quant_cast_bench/quant_cast_gold/recipes.py).  A backend recipe
+ * file in the style of quant_cast_bench/quant_cast_triton/recipes.py:48-65 binds these through
+ * ctypes (see quant_cast_bench_b200/quant_cast_cuda/recipes.py).
+ *
+ * Common conventions: x is a contiguous row-major (M, N) bf16 matrix; pointers must be 16-byte
+ * aligned; outputs are contiguous; one-byte scales are raw bytes (e8m0 / e4m3 bit patterns); the
+ * "blocked" scale layout is the (ceil(H/128), ceil(W/4), 32, 16) grid of G:1000-1037 with padding
+ * written as zero.
+ */
+#ifndef QUANT_CAST_CUDA_H
+#define QUANT_CAST_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element formats of the fp8 casts */
+#define QCC_FMT_E4M3 0 /* torch.float8_e4m3fn, max 448 */
+#define QCC_FMT_E5M2 1 /* torch.float8_e5m2, max 57344 (not in the reference; same recipe, other dtype) */
+
+/* flags of the block-scaled casts */
+#define QCC_ROWWISE 1  /* blocks along the last dim; outputs in the frame of x                       */
+#define QCC_COLWISE 2  /* blocks down the rows; outputs in the transposed (N, M) frame               */
+#define QCC_SWIZZLE 4  /* block scales in the blocked 32x4x4 layout instead of plain row-major      */
+#define QCC_FLOOR 8    /* mxfp8: FLOOR scale mode (OCP MX v1.0) instead of RCEIL                     */
+#define QCC_SR 16      /* nvfp4: stochastic rounding of the fp4 values, Philox4x32-10 keyed          */
+
+/* what qcc_amax_finalize writes */
+#define QCC_AMAX_RAW 0        /* the amax itself, fp32                                   */
+#define QCC_AMAX_FP8_SCALE 1  /* max(amax, bf16(1e-12)) / fp8_max     G:1179-1183        */
+#define QCC_AMAX_NVFP4_SCALE 2 /* amax / (448 * 6)                    G:1243-1246        */
+
+/* argument errors */
+#define QCC_ERR_SHAPE -1     /* a dimension violates the divisibility the cast needs */
+#define QCC_ERR_ALIGN -2     /* a pointer is not 16-byte aligned                     */
+#define QCC_ERR_ARG -3       /* NULL pointer, unknown format or flag combination     */
+#define QCC_ERR_WORKSPACE -4 /* scratch buffer too small                             */
+#define QCC_ERR_DRIVER -5    /* the CUDA driver entry point for tensor maps is missing */
+
+/* Library version (major * 100 + minor). */
+int qcc_version(void);
+
+/* Reads and clears the device-side error word of the current device (non-zero means a kernel gave
+ * up a bounded wait on a TMA barrier).  Synchronises the device; meant for tests. */
+int qcc_device_error(unsigned int *out);
+
+/* Number of SMs of the current device (cached per device). */
+int qcc_sm_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * amax and per-tensor scales
+ * ------------------------------------------------------------------------------------------- */
+
+/* Bytes of scratch qcc_amax_bf16 needs (independent of n). */
+size_t qcc_amax_workspace_bytes(void);
+
+/*
+ * out[0] = f(max |x[i]|) over n bf16 values, f selected by `mode` (QCC_AMAX_*), `fmt` used by
+ * QCC_AMAX_FP8_SCALE only.  Two launches: per-CTA partial maxima into `workspace`, then a
+ * one-CTA finish.  The maximum is exact (a bf16 magnitude), so any partition of x gives the same
+ * result.  Replaces float8_tensorwise_scale (G:1179-1183) and nvfp4_gs_scale (G:1243-1246).
+ */
+int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace,
+                  size_t workspace_bytes, void *stream);
+
+/* out[0] = f(amax[0]) for an amax that is already reduced (e.g. after an all-reduce over shards);
+ * same `mode` / `fmt` as above.  One tiny launch. */
+int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * fp8 casts
+ * ------------------------------------------------------------------------------------------- */
+
+/* q[i] = fp8(float(x[i]) * (1 / scale[0])), saturating.  float8_tensorwise_f, G:1186-1191. */
+int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream);
+
+/* One scale per row: scale[r] = max(amax_r, bf16(1e-12)) / fp8_max, q = fp8(x * (1 / scale[r])).
+ * rowwise_fp8_f, G:301-307.  q may be NULL to get the scales only (rowwise_precalc_scale,
+ * G:389-393). */
+int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *stream);
+
+/* q = fp8(float(x) / scale[r]) with a caller-supplied per-row scale; a true division.
+ * rowwise_precalc_f, G:396-399. */
+int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q,
+                            void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * mxfp8: 32-element blocks, e8m0 scales, e4m3 elements
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * flags & QCC_ROWWISE: qk (M, N) e4m3 and sk, the (M, N/32) scales      mxfp8_f            G:561-568
+ * flags & QCC_COLWISE: qm (N, M) e4m3 and sm, the (N, M/32) scales      mxfp8_dim_m_f      G:656-671
+ * both:                one read of x, four outputs                      mxfp8_dim_km_f     G:701-719
+ * flags & QCC_SWIZZLE: sk / sm in the blocked layout                    G:1051-1053, G:1092-1094,
+ *                                                                       G:1134-1139
+ * flags & QCC_FLOOR:   FLOOR scale mode (extension, not in the reference)
+ * Needs N % 32 == 0, and M % 32 == 0 when QCC_COLWISE is set.  Outputs of a direction that is not
+ * requested may be NULL.
+ */
+int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
+              void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * nvfp4: 16-element blocks, e4m3 block scales relative to an fp32 outer scale, e2m1 elements
+ * packed two per byte (even element in the low nibble)
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * Rowwise: q (M, N/2) bytes, s the (M, N/16) e4m3 scales (plain or blocked).
+ *   nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266, nvfp4_gs_swizzle_sr_f G:1409-1426.
+ * outer: device fp32; outer_per_row == 0 -> one value for the tensor, != 0 -> one per row (the
+ * per-token form of G:1567-1571).  philox_key: device uint64[2] = {seed, offset}, read only when
+ * QCC_SR is set; element (r, c) uses counter ((r * N + c) >> 2) + offset, output word (r * N + c) & 3,
+ * and its low 22 bits as the dither of G:1401-1405.  Needs N % 16 == 0.
+ */
+int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
+              const uint64_t *philox_key, void *q, void *s, void *stream);
+
+/*
+ * Transposed: the outputs that the rowwise cast gives on x.t().contiguous() (the call of
+ * test/test_quant_cast_gold.py:104), without materialising the transpose: q (N, M/2), s over the
+ * (N, M/16) frame.  The stochastic-rounding stream is indexed in the transposed frame.
+ * Needs M % 32 == 0 (output rows of M/2 bytes must be 16-byte multiples for the TMA store) and
+ * N % 8 == 0; outer is a single value.
+ */
+int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
+                         const uint64_t *philox_key, void *q, void *s, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUANT_CAST_CUDA_H */

@@ -1,0 +1,295 @@
+// Shared device helpers for the sm_100a quantization-cast kernels: packed conversions (PTX cvt),
+// e8m0 / e4m3 scale arithmetic in integer bit math, the 32x4x4 blocked scale layout, Philox4x32-10,
+// and thin wrappers over the TMA / mbarrier PTX used by the tiled kernels.
+//
+// Numerics follow the gold recipes of vkuzo/quant_cast_bench
+// (quant_cast_bench/quant_cast_gold/recipes.py = "G", quant_cast_gold/utils.py = "GU").
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/quant_cast_cuda.h"
+
+namespace qcc {
+
+// ---------------------------------------------------------------------------------------------
+// bit helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float u2f(uint32_t u) { return __uint_as_float(u); }
+__device__ __forceinline__ uint32_t f2u(float f) { return __float_as_uint(f); }
+
+// bf16x2 word -> the two fp32 values (low half = even element)
+__device__ __forceinline__ float bf16lo(uint32_t w) { return u2f(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return u2f(w & 0xFFFF0000u); }
+
+// |a|, |b| packed maximum of two bf16x2 words (magnitudes), result is a non-negative bf16x2
+__device__ __forceinline__ uint32_t absmax2(uint32_t acc, uint32_t w)
+{
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&acc);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&w);
+    __nv_bfloat162 r = __hmax2(__habs2(a), __habs2(b));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+// max of the two halves of a non-negative bf16x2, widened to fp32 (exact)
+__device__ __forceinline__ float hmax_halves_f32(uint32_t acc)
+{
+    uint32_t lo = acc << 16, hi = acc & 0xFFFF0000u;   // non-negative floats order like integers
+    return u2f(lo > hi ? lo : hi);
+}
+
+// ---------------------------------------------------------------------------------------------
+// packed conversions
+// ---------------------------------------------------------------------------------------------
+// two fp32 -> two fp8 in a 16-bit word; `lo` lands in the low byte.  RNE, saturate to max finite.
+template <int FMT>
+__device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi)
+{
+    uint16_t r;
+    if (FMT == QCC_FMT_E5M2)
+        asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    else
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// four fp32 -> four fp8 bytes in one word, element 0 in the lowest byte
+template <int FMT>
+__device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d)
+{
+    return cvt_fp8x2<FMT>(a, b) | (cvt_fp8x2<FMT>(c, d) << 16);
+}
+// e4m3 byte -> fp32 (exact)
+__device__ __forceinline__ float e4m3_to_f32(uint32_t byte)
+{
+    uint32_t h2;
+    uint16_t b = (uint16_t)byte;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(b));
+    __half lo = __ushort_as_half((unsigned short)(h2 & 0xFFFFu));
+    return __half2float(lo);
+}
+// eight fp32 -> eight fp4 e2m1 nibbles in one word, element 0 in the lowest nibble (GU:87-92).
+// RNE, saturating at +-6; a negative value that rounds to zero keeps its sign (GU:52-56).
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float v[8])
+{
+    uint32_t r;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n"
+        "}\n"
+        : "=r"(r)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// scale arithmetic
+// ---------------------------------------------------------------------------------------------
+// fp32(1/448) exactly as PyTorch rounds the Python double 1.0/448 to fp32 (G:503)
+#define QCC_INV448_BITS 0x3B124925u
+
+// amax (>= 0, an exact bf16 magnitude widened to fp32) -> e8m0 byte, RCEIL.  G:494-528:
+// descale = amax * fp32(1/448); byte = biased exponent, +1 if any mantissa bit is set (for an
+// fp32 subnormal: only above 2^-127); Inf/NaN -> 255.
+__device__ __forceinline__ uint32_t e8m0_rceil(float amax)
+{
+    uint32_t b = f2u(__fmul_rn(amax, u2f(QCC_INV448_BITS)));
+    uint32_t add = b < 0x00800000u ? 0x3FFFFFu : 0x7FFFFFu;
+    return min((b + add) >> 23, 255u);
+}
+// FLOOR mode (OCP MX v1.0 6.3, not in the reference): exponent field of amax minus emax(e4m3)=8,
+// clamped at 0; Inf/NaN -> 255.
+__device__ __forceinline__ uint32_t e8m0_floor(float amax)
+{
+    uint32_t e = (f2u(amax) >> 23) & 0xFFu;
+    return e == 0xFFu ? 255u : (e > 8u ? e - 8u : 0u);
+}
+// e8m0 byte -> fp32 reciprocal 2^(127-byte).  G:538-558: byte 254 -> subnormal 2^-127, 255 -> NaN.
+// FLOOR clamps the scale to the smallest normal first (byte 0 behaves as byte 1).
+template <bool FLOOR>
+__device__ __forceinline__ float e8m0_recip(uint32_t byte)
+{
+    if (FLOOR) byte = max(byte, 1u);
+    uint32_t r = (254u - byte) & 0xFFu;
+    uint32_t bits = r << 23;
+    bits = r == 0u ? 0x00400000u : bits;
+    bits = r == 255u ? 0x7F800001u : bits;
+    return u2f(bits);
+}
+template <bool FLOOR>
+__device__ __forceinline__ uint32_t e8m0_from_amax(float amax)
+{
+    return FLOOR ? e8m0_floor(amax) : e8m0_rceil(amax);
+}
+
+// fp8 per-tensor / per-row scale from an amax: clamp at bf16(1e-12) (the clamp happens in bf16 in
+// the reference, G:304, G:1182), then an IEEE division by the format maximum.
+template <int FMT>
+__device__ __forceinline__ float fp8_scale_from_amax(float amax)
+{
+    float a = fmaxf(amax, u2f(0x2B8D0000u));
+    return __fdiv_rn(a, FMT == QCC_FMT_E5M2 ? 57344.0f : 448.0f);
+}
+
+// nvfp4 inner (per-16) scale byte and the data multiplier.  G:1505-1513:
+// inner = e4m3(clamp((amax / 6) / outer, 2^-6, 448)); recip = (1 / outer) / fp32(inner).
+__device__ __forceinline__ uint32_t nvfp4_inner(float amax, float outer, float inv_outer, float &recip)
+{
+    float f = __fdiv_rn(__fdiv_rn(amax, 6.0f), outer);
+    f = fminf(fmaxf(f, 0.015625f), 448.0f);
+    uint32_t byte = cvt_fp8x2<QCC_FMT_E4M3>(f, 0.0f) & 0xFFu;
+    recip = __fdiv_rn(inv_outer, e4m3_to_f32(byte));
+    return byte;
+}
+
+// Offset of block scale (r, c) in the 32x4x4 blocked layout with `ncb` column blocks (G:1000-1037)
+__device__ __forceinline__ size_t blocked_offset(uint32_t r, uint32_t c, uint32_t ncb)
+{
+    uint32_t br = r >> 7, rr = r & 127u, bc = c >> 2, c4 = c & 3u;
+    return ((size_t)br * ncb + bc) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u + c4;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Philox4x32-10 and the stochastic-rounding dither
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1)
+{
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return c;
+}
+// the four 32-bit words for elements [4g, 4g+4) of the flat stream (g = flat index >> 2)
+__device__ __forceinline__ uint4 sr_words(uint64_t g, uint64_t seed, uint64_t offset)
+{
+    g += offset;
+    return philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), 0u, 0u), (uint32_t)seed,
+                         (uint32_t)(seed >> 32));
+}
+// G:1401-1405: add a 22-bit dither into the mantissa bits fp4 discards, then truncate them
+__device__ __forceinline__ float sr_dither(float d, uint32_t word)
+{
+    return u2f((f2u(d) + (word & 0x3FFFFFu)) & 0xFFC00000u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// device-side error word (bounded waits record a code here instead of hanging)
+// ---------------------------------------------------------------------------------------------
+// One copy per translation unit; qcc_device_error() collects them.
+static __device__ unsigned int g_qcc_error = 0;
+
+static inline int read_clear_device_error(unsigned int *out)
+{
+    unsigned int v = 0, zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_qcc_error, sizeof(v));
+    if (e != cudaSuccess) return (int)e;
+    if (v) {
+        e = cudaMemcpyToSymbol(g_qcc_error, &zero, sizeof(zero));
+        if (e != cudaSuccess) return (int)e;
+    }
+    *out = v;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMA / mbarrier wrappers (cluster size 1, no multicast)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Wait for phase `parity` with an iteration cap; on timeout record the code and carry on (the caller
+// then works on whatever is in shared memory, but never hangs).
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, unsigned int err_code)
+{
+    uint32_t a = smem_u32(bar);
+    for (uint32_t it = 0; it < (1u << 24); it++) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return;
+    }
+    atomicMax(&g_qcc_error, err_code);
+}
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *src, int x, int y, int z)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void named_barrier(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// 16-byte vector access
+__device__ __forceinline__ uint4 ld_nc_v4(const void *p)
+{
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr)
+{
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr)
+{
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+}  // namespace qcc

@@ -1,0 +1,376 @@
+// fp8 casts and the tensor-wide amax, sm_100a.
+//
+// All kernels here are HBM-bound streams: 128-bit coalesced loads, packed cvt.rn.satfinite stores,
+// grids sized from the SM count.  Numerics follow G = quant_cast_bench/quant_cast_gold/recipes.py of
+// vkuzo/quant_cast_bench: float8_tensorwise_scale G:1179-1183, float8_tensorwise_f G:1186-1191,
+// rowwise_fp8_f G:301-307, rowwise_precalc_f G:396-399, nvfp4_gs_scale G:1243-1246.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace qcc {
+
+// ---------------------------------------------------------------------------------------------
+// amax: per-CTA partial maxima, then a one-CTA finish
+// ---------------------------------------------------------------------------------------------
+constexpr int AMAX_THREADS = 256;
+constexpr int AMAX_MAX_CTAS = 2048;
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+// partial[blockIdx.x] = max |x| over this CTA's grid-stride share, as fp32 bits
+__global__ void __launch_bounds__(AMAX_THREADS) amax_partial_kernel(const uint16_t *__restrict__ x, int64_t n,
+                                                                   uint32_t *__restrict__ partial)
+{
+    const int64_t nvec = n >> 3;  // 16-byte chunks
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint32_t acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
+    const int64_t stride = (int64_t)gridDim.x * AMAX_THREADS;
+    int64_t i = (int64_t)blockIdx.x * AMAX_THREADS + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        uint4 a = ld_nc_v4(xv + i), b = ld_nc_v4(xv + i + stride), c = ld_nc_v4(xv + i + 2 * stride),
+              d = ld_nc_v4(xv + i + 3 * stride);
+        acc0 = absmax2(absmax2(acc0, a.x), a.y); acc1 = absmax2(absmax2(acc1, a.z), a.w);
+        acc2 = absmax2(absmax2(acc2, b.x), b.y); acc3 = absmax2(absmax2(acc3, b.z), b.w);
+        acc0 = absmax2(absmax2(acc0, c.x), c.y); acc1 = absmax2(absmax2(acc1, c.z), c.w);
+        acc2 = absmax2(absmax2(acc2, d.x), d.y); acc3 = absmax2(absmax2(acc3, d.z), d.w);
+    }
+    for (; i < nvec; i += stride) {
+        uint4 a = ld_nc_v4(xv + i);
+        acc0 = absmax2(absmax2(acc0, a.x), a.y); acc1 = absmax2(absmax2(acc1, a.z), a.w);
+    }
+    uint32_t acc = absmax2(absmax2(acc0, acc1), absmax2(acc2, acc3));
+    uint32_t m = f2u(hmax_halves_f32(acc));
+    // scalar tail (n % 8 elements), handled by the first thread of the grid
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (int64_t t = nvec << 3; t < n; t++) m = max(m, ((uint32_t)x[t] & 0x7FFFu) << 16);
+    m = warp_max_u32(m);
+    __shared__ uint32_t s[AMAX_THREADS / 32];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < AMAX_THREADS / 32 ? s[threadIdx.x] : 0u;
+        m = warp_max_u32(m);
+        if (threadIdx.x == 0) partial[blockIdx.x] = m;
+    }
+}
+
+__device__ __forceinline__ float amax_finish(float amax, int mode, int fmt)
+{
+    if (mode == QCC_AMAX_FP8_SCALE)
+        return fmt == QCC_FMT_E5M2 ? fp8_scale_from_amax<QCC_FMT_E5M2>(amax) : fp8_scale_from_amax<QCC_FMT_E4M3>(amax);
+    if (mode == QCC_AMAX_NVFP4_SCALE) return __fdiv_rn(amax, 2688.0f);
+    return amax;
+}
+
+__global__ void __launch_bounds__(AMAX_THREADS) amax_finish_kernel(const uint32_t *__restrict__ partial, int count,
+                                                                  int mode, int fmt, float *__restrict__ out)
+{
+    uint32_t m = 0;
+    for (int i = threadIdx.x; i < count; i += AMAX_THREADS) m = max(m, partial[i]);
+    m = warp_max_u32(m);
+    __shared__ uint32_t s[AMAX_THREADS / 32];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < AMAX_THREADS / 32 ? s[threadIdx.x] : 0u;
+        m = warp_max_u32(m);
+        if (threadIdx.x == 0) out[0] = amax_finish(u2f(m), mode, fmt);
+    }
+}
+
+__global__ void scale_from_amax_kernel(const float *__restrict__ amax, int mode, int fmt, float *__restrict__ out)
+{
+    out[0] = amax_finish(amax[0], mode, fmt);
+}
+
+// ---------------------------------------------------------------------------------------------
+// tensorwise cast: 16 elements per thread per step (two 16-byte loads, one 16-byte store)
+// ---------------------------------------------------------------------------------------------
+template <int FMT>
+__device__ __forceinline__ uint4 cast16(uint4 a, uint4 b, float inv)
+{
+    uint4 o;
+    o.x = cvt_fp8x4<FMT>(bf16lo(a.x) * inv, bf16hi(a.x) * inv, bf16lo(a.y) * inv, bf16hi(a.y) * inv);
+    o.y = cvt_fp8x4<FMT>(bf16lo(a.z) * inv, bf16hi(a.z) * inv, bf16lo(a.w) * inv, bf16hi(a.w) * inv);
+    o.z = cvt_fp8x4<FMT>(bf16lo(b.x) * inv, bf16hi(b.x) * inv, bf16lo(b.y) * inv, bf16hi(b.y) * inv);
+    o.w = cvt_fp8x4<FMT>(bf16lo(b.z) * inv, bf16hi(b.z) * inv, bf16lo(b.w) * inv, bf16hi(b.w) * inv);
+    return o;
+}
+template <int FMT>
+__device__ __forceinline__ uint2 cast8(uint4 a, float inv)
+{
+    uint2 o;
+    o.x = cvt_fp8x4<FMT>(bf16lo(a.x) * inv, bf16hi(a.x) * inv, bf16lo(a.y) * inv, bf16hi(a.y) * inv);
+    o.y = cvt_fp8x4<FMT>(bf16lo(a.z) * inv, bf16hi(a.z) * inv, bf16lo(a.w) * inv, bf16hi(a.w) * inv);
+    return o;
+}
+
+constexpr int TW_THREADS = 256;
+constexpr int TW_UNROLL = 2;  // independent 16-element groups per thread
+
+template <int FMT>
+__global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16_t *__restrict__ x, int64_t n,
+                                                                   const float *__restrict__ scale,
+                                                                   uint8_t *__restrict__ q)
+{
+    const float inv = __fdiv_rn(1.0f, __ldg(scale));
+    const int64_t ngrp = n >> 4;  // groups of 16 elements
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint4 *qv = reinterpret_cast<uint4 *>(q);
+    const int64_t base = (int64_t)blockIdx.x * (TW_THREADS * TW_UNROLL) + threadIdx.x;
+    uint4 a[TW_UNROLL], b[TW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < TW_UNROLL; u++) {
+        int64_t g = base + (int64_t)u * TW_THREADS;
+        if (g < ngrp) { a[u] = ld_nc_v4(xv + 2 * g); b[u] = ld_nc_v4(xv + 2 * g + 1); }
+    }
+#pragma unroll
+    for (int u = 0; u < TW_UNROLL; u++) {
+        int64_t g = base + (int64_t)u * TW_THREADS;
+        if (g < ngrp) __stcs(qv + g, cast16<FMT>(a[u], b[u], inv));
+    }
+    // scalar tail: the last n % 16 elements
+    if (blockIdx.x == 0 && threadIdx.x < (n & 15)) {
+        int64_t t = (ngrp << 4) + threadIdx.x;
+        q[t] = (uint8_t)cvt_fp8x2<FMT>(u2f((uint32_t)x[t] << 16) * inv, 0.0f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rowwise cast: TPR threads share a row and keep it in registers (CH 16-byte chunks each), so x is
+// read from HBM exactly once.  PRECALC: per-row scale supplied, true division.
+// ---------------------------------------------------------------------------------------------
+constexpr int RW_THREADS = 256;
+
+template <int FMT, int TPR, int CH, bool PRECALC>
+__global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_kernel(const uint16_t *__restrict__ x, int64_t M, int64_t N,
+                                                                const float *__restrict__ scale_in,
+                                                                uint8_t *__restrict__ q, float *__restrict__ scale_out)
+{
+    constexpr int ROWS = RW_THREADS / TPR;
+    const int tr = threadIdx.x % TPR;
+    const int lr = threadIdx.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * ROWS + lr;
+    const bool row_ok = row < M;
+    const int64_t nchunk = N >> 3;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + (row_ok ? row : 0) * N);
+    uint4 v[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        int64_t k = tr + (int64_t)c * TPR;
+        v[c] = (row_ok && k < nchunk) ? ld_nc_v4(xr + k) : make_uint4(0, 0, 0, 0);
+    }
+    float s;
+    if (PRECALC) {
+        s = row_ok ? __ldg(scale_in + row) : 1.0f;
+    } else {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int c = 0; c < CH; c++) acc = absmax2(absmax2(absmax2(absmax2(acc, v[c].x), v[c].y), v[c].z), v[c].w);
+        uint32_t m = f2u(hmax_halves_f32(acc));
+        constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+        for (int o = W / 2; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        if (TPR > 32) {
+            __shared__ uint32_t sm[RW_THREADS / 32];
+            if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+            __syncthreads();
+            constexpr int WPR = TPR / 32 > 0 ? TPR / 32 : 1;
+            m = 0;
+#pragma unroll
+            for (int w = 0; w < WPR; w++) m = max(m, sm[lr * WPR + w]);
+        }
+        s = fp8_scale_from_amax<FMT>(u2f(m));
+        if (row_ok && tr == 0) scale_out[row] = s;
+    }
+    if (q == nullptr || !row_ok) return;
+    uint2 *qr = reinterpret_cast<uint2 *>(q + row * N);
+    if (PRECALC) {
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            int64_t k = tr + (int64_t)c * TPR;
+            if (k < nchunk) {
+                uint4 a = v[c];
+                uint2 o;
+                o.x = cvt_fp8x4<FMT>(__fdiv_rn(bf16lo(a.x), s), __fdiv_rn(bf16hi(a.x), s), __fdiv_rn(bf16lo(a.y), s),
+                                     __fdiv_rn(bf16hi(a.y), s));
+                o.y = cvt_fp8x4<FMT>(__fdiv_rn(bf16lo(a.z), s), __fdiv_rn(bf16hi(a.z), s), __fdiv_rn(bf16lo(a.w), s),
+                                     __fdiv_rn(bf16hi(a.w), s));
+                __stcs(qr + k, o);
+            }
+        }
+    } else {
+        const float inv = __fdiv_rn(1.0f, s);
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            int64_t k = tr + (int64_t)c * TPR;
+            if (k < nchunk) __stcs(qr + k, cast8<FMT>(v[c], inv));
+        }
+    }
+}
+
+// Any N (also N % 8 != 0 or rows longer than the register-resident variants): one CTA per row, two
+// passes over the row (the second pass is served by L2).
+template <int FMT, bool PRECALC>
+__global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_generic_kernel(const uint16_t *__restrict__ x, int64_t M,
+                                                                        int64_t N, const float *__restrict__ scale_in,
+                                                                        uint8_t *__restrict__ q,
+                                                                        float *__restrict__ scale_out)
+{
+    const int64_t row = blockIdx.x;
+    const uint16_t *xr = x + row * N;
+    float s;
+    __shared__ uint32_t sm[RW_THREADS / 32];
+    if (PRECALC) {
+        s = __ldg(scale_in + row);
+    } else {
+        uint32_t m = 0;
+        for (int64_t c = threadIdx.x; c < N; c += RW_THREADS) m = max(m, ((uint32_t)xr[c] & 0x7FFFu) << 16);
+        m = warp_max_u32(m);
+        if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+        __syncthreads();
+        m = 0;
+#pragma unroll
+        for (int w = 0; w < RW_THREADS / 32; w++) m = max(m, sm[w]);
+        s = fp8_scale_from_amax<FMT>(u2f(m));
+        if (threadIdx.x == 0) scale_out[row] = s;
+    }
+    if (q == nullptr) return;
+    const float inv = __fdiv_rn(1.0f, s);
+    for (int64_t c = threadIdx.x; c < N; c += RW_THREADS) {
+        float f = u2f((uint32_t)xr[c] << 16);
+        float d = PRECALC ? __fdiv_rn(f, s) : f * inv;
+        q[row * N + c] = (uint8_t)cvt_fp8x2<FMT>(d, 0.0f);
+    }
+}
+
+template <int FMT, bool PRECALC>
+static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scale_in, void *q, float *scale_out,
+                          cudaStream_t st)
+{
+    const uint16_t *xp = (const uint16_t *)x;
+    uint8_t *qp = (uint8_t *)q;
+#define QCC_RW(TPR, CH)                                                                                      \
+    do {                                                                                                     \
+        constexpr int ROWS = RW_THREADS / (TPR);                                                             \
+        unsigned grid = (unsigned)((M + ROWS - 1) / ROWS);                                                   \
+        fp8_rowwise_kernel<FMT, TPR, CH, PRECALC><<<grid, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out); \
+        return (int)cudaGetLastError();                                                                      \
+    } while (0)
+    if (N % 8 == 0 && N <= 16384 && M <= 0x7FFFFFFF) {
+        const int64_t chunks = N / 8;
+        if (chunks <= 32) QCC_RW(32, 1);
+        if (chunks <= 64) QCC_RW(32, 2);
+        if (chunks <= 128) QCC_RW(32, 4);
+        if (chunks <= 256) QCC_RW(64, 4);
+        if (chunks <= 512) QCC_RW(128, 4);
+        if (chunks <= 1024) QCC_RW(256, 4);
+        QCC_RW(256, 8);
+    }
+#undef QCC_RW
+    if (M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    fp8_rowwise_generic_kernel<FMT, PRECALC><<<(unsigned)M, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace qcc
+
+using namespace qcc;
+
+// per-translation-unit error words of the tiled kernels
+extern "C" int qcc_mxfp8_device_error(unsigned int *out);
+extern "C" int qcc_nvfp4_device_error(unsigned int *out);
+
+extern "C" {
+
+int qcc_version(void) { return 100; }
+
+int qcc_device_error(unsigned int *out)
+{
+    unsigned int a = 0, b = 0, c = 0;
+    int e = read_clear_device_error(&a);
+    if (e) return e;
+    if ((e = qcc_mxfp8_device_error(&b)) != 0) return e;
+    if ((e = qcc_nvfp4_device_error(&c)) != 0) return e;
+    if (out) *out = a > b ? (a > c ? a : c) : (b > c ? b : c);
+    return 0;
+}
+
+int qcc_sm_count(void) { return sm_count(); }
+
+size_t qcc_amax_workspace_bytes(void) { return (size_t)AMAX_MAX_CTAS * sizeof(uint32_t); }
+
+int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace, size_t workspace_bytes,
+                  void *stream)
+{
+    if (!x || !out || !workspace || n < 0) return QCC_ERR_ARG;
+    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
+        return QCC_ERR_ARG;
+    if (!aligned16(x)) return QCC_ERR_ALIGN;
+    if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    int64_t want = ((n >> 3) + AMAX_THREADS * 4 - 1) / (AMAX_THREADS * 4);
+    int64_t cap = (int64_t)sm_count() * 8;
+    if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
+    int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    amax_partial_kernel<<<grid, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, (uint32_t *)workspace);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>((const uint32_t *)workspace, grid, mode, fmt, out);
+    return (int)cudaGetLastError();
+}
+
+int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *stream)
+{
+    if (!amax || !out) return QCC_ERR_ARG;
+    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
+        return QCC_ERR_ARG;
+    scale_from_amax_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(amax, mode, fmt, out);
+    return (int)cudaGetLastError();
+}
+
+int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream)
+{
+    if (!x || !scale || !q || n < 0) return QCC_ERR_ARG;
+    if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t per_cta = (int64_t)TW_THREADS * TW_UNROLL * 16;
+    int64_t grid = (n + per_cta - 1) / per_cta;
+    if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    if (fmt == QCC_FMT_E5M2)
+        fp8_tensorwise_kernel<QCC_FMT_E5M2><<<(unsigned)grid, TW_THREADS, 0, st>>>((const uint16_t *)x, n, scale, (uint8_t *)q);
+    else
+        fp8_tensorwise_kernel<QCC_FMT_E4M3><<<(unsigned)grid, TW_THREADS, 0, st>>>((const uint16_t *)x, n, scale, (uint8_t *)q);
+    return (int)cudaGetLastError();
+}
+
+int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *stream)
+{
+    if (!x || !scale || M < 0 || N < 0) return QCC_ERR_ARG;
+    if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (N % 8 == 0 && (!aligned16(x) || (q && !aligned16(q)))) return QCC_ERR_ALIGN;
+    if (M == 0 || N == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, st)
+                               : launch_rowwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, st);
+}
+
+int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
+{
+    if (!x || !scale || !q || M < 0 || N < 0) return QCC_ERR_ARG;
+    if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (N % 8 == 0 && (!aligned16(x) || !aligned16(q))) return QCC_ERR_ALIGN;
+    if (M == 0 || N == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, st)
+                               : launch_rowwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, st);
+}
+
+}  // extern "C"

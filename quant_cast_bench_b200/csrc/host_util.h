@@ -1,0 +1,63 @@
+// Host-side helpers shared by the launchers: device properties, alignment checks and the tensor-map
+// encoder obtained from the driver at run time (no link-time dependency on libcuda).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qcc {
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// SM count of the current device, cached per device ordinal.
+inline int sm_count()
+{
+    static int cache[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline encode_tiled_fn get_encode_tiled()
+{
+    static encode_tiled_fn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+        tried = true;
+    }
+    return fn;
+}
+
+// Tensor map over a row-major tensor of up to 3 dims (dim 0 contiguous).  strides[i] = byte stride of
+// dim i+1.  Returns 0, QCC_ERR_DRIVER, or 1000 + CUresult.
+inline int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const uint64_t *dims,
+                           const uint64_t *strides, const uint32_t *box, CUtensorMapSwizzle swz)
+{
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return -5;
+    cuuint64_t gd[3];
+    cuuint64_t gs[2];
+    cuuint32_t bx[3];
+    cuuint32_t es[3] = {1, 1, 1};
+    for (int i = 0; i < rank; i++) { gd[i] = dims[i]; bx[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; i++) gs[i] = strides[i];
+    CUresult r = enc(map, dt, (cuuint32_t)rank, const_cast<void *>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+}  // namespace qcc

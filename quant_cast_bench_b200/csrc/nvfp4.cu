@@ -1,0 +1,360 @@
+// nvfp4 (1x16 blocks, e4m3 block scales under an fp32 outer scale, e2m1 elements packed two per
+// byte) for sm_100a.
+//
+//  * rowwise: a flat stream -- a thread owns one 16-element block (two 16-byte loads, one 8-byte
+//    store of packed nibbles, one scale byte); x, q and the plain scales are addressed by the flat
+//    block index, only the blocked scale layout and per-row outer scales need (row, column).
+//  * transposed: a TMA tile kernel.  A CTA owns 256 rows x 128 columns of x, fetched as 64-column x
+//    32-row boxes with 128-byte swizzle, one mbarrier per 32-row slab.  Warp b quantises slab b down
+//    the rows (lane = four adjacent columns, two 16x1 blocks each) and writes 16 packed bytes per
+//    column into a swizzled staging tile whose rows are output rows; the tile leaves through rank-3
+//    TMA stores over the (column / 4, column % 4, m / 2) view of the (N, M/2) output.
+//
+// Numerics: G = quant_cast_bench/quant_cast_gold/recipes.py, GU = quant_cast_gold/utils.py of
+// vkuzo/quant_cast_bench.  nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266,
+// nvfp4_gs_swizzle_sr_f G:1392-1426, fp4 encode GU:15-57, nibble order GU:87-92, blocked layout
+// G:1000-1037; the transposed cast is nvfp4_gs_swizzle_f(x.t().contiguous(), s) of
+// test/test_quant_cast_gold.py:104.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace qcc {
+
+// n / d for n < 2^32 by multiply-shift (d >= 1)
+struct FastDiv {
+    uint32_t d, mul, shift;
+    __host__ void init(uint32_t div)
+    {
+        d = div;
+        shift = 0;
+        while ((1ull << shift) < div) shift++;
+        mul = (uint32_t)(((1ull << 32) * ((1ull << shift) - div)) / div + 1);
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return (uint32_t)(((uint64_t)__umulhi(n, mul) + n) >> shift); }
+};
+
+// One block: 16 bf16 in two uint4 -> 8 packed bytes and the inner scale byte.
+template <bool SR>
+__device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer, float inv_outer, uint64_t flat0,
+                                                 uint64_t seed, uint64_t offset, uint2 &packed)
+{
+    uint32_t acc = absmax2(absmax2(absmax2(absmax2(0u, a.x), a.y), absmax2(a.z, a.w)),
+                           absmax2(absmax2(b.x, b.y), absmax2(b.z, b.w)));
+    float recip;
+    const uint32_t byte = nvfp4_inner(hmax_halves_f32(acc), outer, inv_outer, recip);
+    float v[16] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w),
+                   bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] *= recip;
+    // the clamp to +-6 of G:1513 is what the saturating conversion does; it only has to be explicit
+    // ahead of the dither
+    if (SR) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = fminf(fmaxf(v[i], -6.0f), 6.0f);
+#pragma unroll
+        for (int g4 = 0; g4 < 4; g4++) {
+            uint4 w = sr_words((flat0 >> 2) + g4, seed, offset);
+            v[4 * g4 + 0] = sr_dither(v[4 * g4 + 0], w.x);
+            v[4 * g4 + 1] = sr_dither(v[4 * g4 + 1], w.y);
+            v[4 * g4 + 2] = sr_dither(v[4 * g4 + 2], w.z);
+            v[4 * g4 + 3] = sr_dither(v[4 * g4 + 3], w.w);
+        }
+    }
+    packed.x = cvt_e2m1x8(v);
+    packed.y = cvt_e2m1x8(v + 8);
+    return byte;
+}
+
+constexpr int NV_THREADS = 256;
+constexpr int NV_UNROLL = 2;
+
+template <bool SWZ, bool SR, bool PER_ROW>
+__global__ void __launch_bounds__(NV_THREADS)
+nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv div_nb,
+                     const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
+                     uint8_t *__restrict__ s)
+{
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint2 *qv = reinterpret_cast<uint2 *>(q);
+    uint64_t seed = 0, offset = 0;
+    if (SR) { seed = key[0]; offset = key[1]; }
+    float o_all = 0.f, inv_all = 0.f;
+    if (!PER_ROW) { o_all = __ldg(outer); inv_all = __fdiv_rn(1.0f, o_all); }
+    const uint32_t base = blockIdx.x * (NV_THREADS * NV_UNROLL) + threadIdx.x;
+    uint4 a[NV_UNROLL], b[NV_UNROLL];
+#pragma unroll
+    for (int u = 0; u < NV_UNROLL; u++) {
+        const uint32_t bi = base + u * NV_THREADS;
+        if (bi < nblocks) { a[u] = ld_nc_v4(xv + 2 * (size_t)bi); b[u] = ld_nc_v4(xv + 2 * (size_t)bi + 1); }
+    }
+#pragma unroll
+    for (int u = 0; u < NV_UNROLL; u++) {
+        const uint32_t bi = base + u * NV_THREADS;
+        if (bi >= nblocks) continue;
+        uint32_t row = 0, cb = 0;
+        if (SWZ || PER_ROW) { row = div_nb.div(bi); cb = bi - row * nb; }
+        float o = o_all, inv = inv_all;
+        if (PER_ROW) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
+        uint2 packed;
+        const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, (uint64_t)bi * 16u, seed, offset, packed);
+        __stcs(qv + bi, packed);
+        s[SWZ ? blocked_offset(row, cb, (nb + 3) >> 2) : (size_t)bi] = (uint8_t)byte;
+    }
+}
+
+// Zero the padding of a blocked scale grid that the rowwise stream does not visit: rows M..ceil128(M)
+// and scale columns nb..ceil4(nb).
+__global__ void nvfp4_zero_pad_kernel(uint8_t *__restrict__ s, uint32_t M, uint32_t nb)
+{
+    const uint32_t Hp = ((M + 127) >> 7) << 7, Wp = ((nb + 3) >> 2) << 2, ncb = Wp >> 2;
+    const uint64_t total = (uint64_t)Hp * Wp;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / Wp), c = (uint32_t)(i % Wp);
+        if (r >= M || c >= nb) s[blocked_offset(r, c, ncb)] = 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// transposed cast: TMA tile kernel
+// ---------------------------------------------------------------------------------------------
+constexpr int NVT_TILE_M = 256;
+constexpr int NVT_PANEL_BYTES = NVT_TILE_M * 128;  // one 64-column panel: 256 rows x 128 B
+constexpr int NVT_SLAB_BYTES = 32 * 128;
+constexpr int NVT_X_OFF = 0;
+constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 rows x 128 B
+constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * NVT_SLAB_BYTES;  // 128 columns x 16 block scales
+constexpr int NVT_BAR_OFF = NVT_S_OFF + 2048;
+constexpr int NVT_BYTES = NVT_BAR_OFF + 8 * 8;
+constexpr int NVT_ALLOC = NVT_BYTES + 1024;
+
+template <bool SWZ, bool SR>
+__global__ void __launch_bounds__(256)
+nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
+                        const float *__restrict__ outer_p, const uint64_t *__restrict__ key, uint8_t *__restrict__ s, int M,
+                        int N)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sbase + NVT_BAR_OFF);
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            mbar_expect_tx(&bars[i], 2 * NVT_SLAB_BYTES);
+            uint8_t *dst = sbase + NVT_X_OFF + i * NVT_SLAB_BYTES;
+            tma_load_2d(dst, &tm_x, &bars[i], tile_n * 128, tile_m * NVT_TILE_M + i * 32);
+            tma_load_2d(dst + NVT_PANEL_BYTES, &tm_x, &bars[i], tile_n * 128 + 64, tile_m * NVT_TILE_M + i * 32);
+        }
+    }
+    const float outer = __ldg(outer_p);
+    const float inv_outer = __fdiv_rn(1.0f, outer);
+    uint64_t seed = 0, offset = 0;
+    if (SR) { seed = key[0]; offset = key[1]; }
+    const int mb16 = M >> 4;  // scale columns of the transposed frame
+
+    mbar_wait(&bars[b], 0, 2u);
+
+    const uint32_t pbase = base + NVT_X_OFF + (lane >> 4) * NVT_PANEL_BYTES + (b * 32) * 128 + (lane & 1) * 8;
+    const uint32_t j = (lane & 15) >> 1;
+    uint4 outw[4];  // per column: 32 rows -> 16 packed bytes
+    uint32_t sc[4][2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint2 w[16];
+        uint32_t a0 = 0, a1 = 0;
+#pragma unroll
+        for (int r = 0; r < 16; r++) {
+            const int rr = 16 * h + r;
+            w[r] = lds_v2(pbase + rr * 128 + ((j ^ (rr & 7)) << 4));
+            a0 = absmax2(a0, w[r].x);
+            a1 = absmax2(a1, w[r].y);
+        }
+        const float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            float recip;
+            sc[k][h] = nvfp4_inner(am[k], outer, inv_outer, recip);
+            float v[16];
+#pragma unroll
+            for (int r = 0; r < 16; r++) {
+                const uint32_t word = (k < 2) ? w[r].x : w[r].y;
+                const float f = (k & 1) ? bf16hi(word) : bf16lo(word);
+                v[r] = f * recip;
+            }
+            if (SR) {
+#pragma unroll
+                for (int r = 0; r < 16; r++) v[r] = fminf(fmaxf(v[r], -6.0f), 6.0f);
+                // flat index in the transposed frame: column * M + m
+                const uint64_t col = (uint64_t)tile_n * 128 + 4 * lane + k;
+                const uint64_t flat0 = col * (uint64_t)M + (uint64_t)tile_m * NVT_TILE_M + b * 32 + 16 * h;
+#pragma unroll
+                for (int g4 = 0; g4 < 4; g4++) {
+                    uint4 rw = sr_words((flat0 >> 2) + g4, seed, offset);
+                    v[4 * g4 + 0] = sr_dither(v[4 * g4 + 0], rw.x);
+                    v[4 * g4 + 1] = sr_dither(v[4 * g4 + 1], rw.y);
+                    v[4 * g4 + 2] = sr_dither(v[4 * g4 + 2], rw.z);
+                    v[4 * g4 + 3] = sr_dither(v[4 * g4 + 3], rw.w);
+                }
+            }
+            const uint32_t p0 = cvt_e2m1x8(v), p1 = cvt_e2m1x8(v + 8);
+            if (h == 0) { outw[k].x = p0; outw[k].y = p1; } else { outw[k].z = p0; outw[k].w = p1; }
+        }
+    }
+    const uint32_t key7 = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+        sts_v4(base + NVT_Q_OFF + k * NVT_SLAB_BYTES + lane * 128 + ((b ^ key7) << 4), outw[k]);
+    // block scales of this slab -> staging, zero outside the matrix
+    uint8_t *ss = sbase + NVT_S_OFF;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int c = 4 * lane + k;
+        const bool col_ok = tile_n * 128 + c < N;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int blk = 2 * b + h;                       // 0..15 inside the tile
+            const bool ok = col_ok && (tile_m * 16 + blk < mb16);
+            const int off = SWZ ? ((blk >> 2) * 512 + (c & 31) * 16 + (c >> 5) * 4 + (blk & 3)) : (c * 16 + blk);
+            ss[off] = ok ? (uint8_t)sc[k][h] : (uint8_t)0;
+        }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (b < 4 && lane == 0) {
+        tma_store_3d(&tm_q, sbase + NVT_Q_OFF + b * NVT_SLAB_BYTES, tile_m * (NVT_TILE_M / 2), b, tile_n * 32);
+        tma_commit();
+    }
+    if (threadIdx.x < 128) {
+        const int t = threadIdx.x;
+        const uint4 v = *reinterpret_cast<const uint4 *>(ss + t * 16);
+        if (SWZ) {
+            // four consecutive 512-byte atoms (row block = tile_n, column blocks 4 tile_m .. 4 tile_m + 3)
+            const uint32_t ncb = (mb16 + 3) >> 2;
+            const uint32_t atom = t >> 5;
+            if ((uint32_t)tile_m * 4 + atom < ncb) {
+                const size_t off = ((size_t)tile_n * ncb + tile_m * 4 + atom) * 512u + (t & 31) * 16u;
+                *reinterpret_cast<uint4 *>(s + off) = v;
+            }
+        } else {
+            const int Cn = tile_n * 128 + t;
+            if (Cn < N) {
+                uint8_t *dst = s + (size_t)Cn * mb16 + tile_m * 16;
+                if ((mb16 & 15) == 0) {
+                    *reinterpret_cast<uint4 *>(dst) = v;
+                } else {
+                    const uint8_t *src = ss + t * 16;
+                    for (int kk = 0; kk < 16; kk++)
+                        if (tile_m * 16 + kk < mb16) dst[kk] = src[kk];
+                }
+            }
+        }
+    }
+    if (b < 4 && lane == 0) tma_wait_read_all();
+}
+
+}  // namespace qcc
+
+using namespace qcc;
+
+extern "C" int qcc_nvfp4_device_error(unsigned int *out) { return read_clear_device_error(out); }
+
+extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
+                         const uint64_t *philox_key, void *q, void *s, void *stream)
+{
+    if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
+    if (M < 0 || N < 0 || N % 16 != 0) return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
+    if (M == 0 || N == 0) return 0;
+    const int64_t nb = N / 16;
+    if (M * nb >= (1ll << 32) - 2 * NV_THREADS * NV_UNROLL || nb > 0x7FFFFFFF || M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t nblocks = (uint32_t)(M * nb);
+    FastDiv dv;
+    dv.init((uint32_t)nb);
+    const unsigned grid = (nblocks + NV_THREADS * NV_UNROLL - 1) / (NV_THREADS * NV_UNROLL);
+    const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row != 0;
+    const uint16_t *xp = (const uint16_t *)x;
+    uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
+    if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
+        nvfp4_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(sp, (uint32_t)M, (uint32_t)nb);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+#define QCC_NV(SWZ_, SR_, PR_) \
+    nvfp4_rowwise_kernel<SWZ_, SR_, PR_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp)
+    if (swz) {
+        if (sr) { if (pr) QCC_NV(true, true, true); else QCC_NV(true, true, false); }
+        else    { if (pr) QCC_NV(true, false, true); else QCC_NV(true, false, false); }
+    } else {
+        if (sr) { if (pr) QCC_NV(false, true, true); else QCC_NV(false, true, false); }
+        else    { if (pr) QCC_NV(false, false, true); else QCC_NV(false, false, false); }
+    }
+#undef QCC_NV
+    return (int)cudaGetLastError();
+}
+
+template <bool SWZ, bool SR>
+static int launch_nvt(const CUtensorMap &tx, const CUtensorMap &tq, const float *outer, const uint64_t *key, uint8_t *s,
+                      int M, int N, cudaStream_t st)
+{
+    auto kern = nvfp4_transposed_kernel<SWZ, SR>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, NVT_ALLOC);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + NVT_TILE_M - 1) / NVT_TILE_M));
+    kern<<<grid, 256, NVT_ALLOC, st>>>(tx, tq, outer, key, s, M, N);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
+                                    const uint64_t *philox_key, void *q, void *s, void *stream)
+{
+    if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
+    if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
+    // M / 2 bytes per output row must be a multiple of 16 for the TMA store: M % 32 == 0
+    if (M % 32 != 0 || N % 8 != 0) return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
+    if (M == 0 || N == 0) return 0;
+    if ((M + NVT_TILE_M - 1) / NVT_TILE_M > 65535) return QCC_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    CUtensorMap tx, tq;
+    {
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        uint64_t strides[1] = {(uint64_t)N * 2};
+        uint32_t box[2] = {64, 32};
+        int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (e) return e;
+    }
+    {
+        // (N, M/2) bytes seen as (column / 4, column % 4, byte): a box is 32 columns of equal residue
+        uint64_t dims[3] = {(uint64_t)M / 2, 4, ((uint64_t)N + 3) / 4};
+        uint64_t strides[2] = {(uint64_t)M / 2, (uint64_t)M * 2};
+        uint32_t box[3] = {128, 1, 32};
+        if (N % 4 != 0) return QCC_ERR_SHAPE;
+        dims[2] = (uint64_t)N / 4;
+        int e = make_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (e) return e;
+    }
+    const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR;
+    uint8_t *sp = (uint8_t *)s;
+    if (swz) return sr ? launch_nvt<true, true>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st)
+                       : launch_nvt<true, false>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st);
+    return sr ? launch_nvt<false, true>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st)
+              : launch_nvt<false, false>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st);
+}

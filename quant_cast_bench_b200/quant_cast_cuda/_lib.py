@@ -1,0 +1,67 @@
+"""ctypes binding of libquant_cast_cuda.so (the C ABI declared in include/quant_cast_cuda.h).
+
+There is no fallback: if the library has not been built, or no CUDA device is present, every cast
+raises.  Build with `python -m quant_cast_bench_b200.build`.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libquant_cast_cuda.so")
+
+# constants of include/quant_cast_cuda.h
+FMT_E4M3, FMT_E5M2 = 0, 1
+ROWWISE, COLWISE, SWIZZLE, FLOOR, SR = 1, 2, 4, 8, 16
+AMAX_RAW, AMAX_FP8_SCALE, AMAX_NVFP4_SCALE = 0, 1, 2
+ERRORS = {
+    -1: "shape: a dimension violates the divisibility this cast needs",
+    -2: "alignment: a tensor is not 16-byte aligned",
+    -3: "argument: missing tensor, unknown format or flag combination",
+    -4: "workspace too small",
+    -5: "the CUDA driver does not provide cuTensorMapEncodeTiled",
+}
+
+_vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+SIGNATURES = {
+    "qcc_version": (_int, []),
+    "qcc_device_error": (_int, [ctypes.POINTER(ctypes.c_uint)]),
+    "qcc_sm_count": (_int, []),
+    "qcc_amax_workspace_bytes": (_sz, []),
+    "qcc_amax_bf16": (_int, [_vp, _i64, _int, _int, _vp, _vp, _sz, _vp]),
+    "qcc_scale_from_amax": (_int, [_vp, _int, _int, _vp, _vp]),
+    "qcc_fp8_tensorwise": (_int, [_vp, _i64, _vp, _int, _vp, _vp]),
+    "qcc_fp8_rowwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "qcc_fp8_rowwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
+    "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "qcc_nvfp4": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp]),
+    "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
+}
+
+_lib = None
+launch_count = 0  # kernels launched through this binding (the benchmark resets and reads it)
+
+
+def load():
+    """Load the shared library and declare every entry point; raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: the CUDA library has not been built "
+                "(python -m quant_cast_bench_b200.build). quant_cast_cuda has no CPU fallback."
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the .so does not export a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc, what):
+    if rc == 0:
+        return
+    if rc < 0:
+        raise ValueError(f"{what}: {ERRORS.get(rc, rc)}")
+    raise RuntimeError(f"{what}: CUDA error {rc}")

@@ -1,0 +1,379 @@
+"""CUDA implementations of the quant_cast_gold recipes.
+
+Mirrors the backend recipe files of vkuzo/quant_cast_bench (quant_cast_triton/recipes.py:48-65,
+:1796-1835): every `<name>_cuda(*inputs, **kwargs) -> tuple[Tensor, ...]` takes the positional inputs
+of the gold `pt_ref_fn` of the same recipe (quant_cast_gold/recipes.py), accepts and ignores the
+tile kwargs `global_row / global_col / num_col`, allocates its outputs with torch.empty on x.device,
+returns the gold shapes and dtype views, reads scalar aux inputs on the device (no host sync), and
+launches on the current CUDA stream.  `ALL_RECIPES` lists `(gold recipe name, QuantCastCudaRecipe)`.
+
+Functions without a gold counterpart are marked "extension": e5m2 (`fmt="e5m2"`), the FLOOR scale
+mode (`mode="floor"`), the transposed nvfp4 cast, and Philox-keyed stochastic rounding.
+"""
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from . import _lib as L
+
+_FMT = {"e4m3": L.FMT_E4M3, "e5m2": L.FMT_E5M2, torch.float8_e4m3fn: L.FMT_E4M3, torch.float8_e5m2: L.FMT_E5M2}
+_FP8_DTYPE = {L.FMT_E4M3: torch.float8_e4m3fn, L.FMT_E5M2: torch.float8_e5m2}
+
+
+def _fmt(fmt):
+    if fmt not in _FMT:
+        raise ValueError(f"unknown fp8 format {fmt!r}; use 'e4m3' or 'e5m2'")
+    return _FMT[fmt]
+
+
+def _mode(mode):
+    if mode not in ("rceil", "floor"):
+        raise ValueError(f"unknown mxfp8 scale mode {mode!r}; use 'rceil' or 'floor'")
+    return L.FLOOR if mode == "floor" else 0
+
+
+def _check_x(x, name="x"):
+    if not (isinstance(x, torch.Tensor) and x.is_cuda):
+        raise ValueError(f"{name} must be a CUDA tensor (quant_cast_cuda has no CPU path)")
+    assert x.dtype == torch.bfloat16, f"{name} must be bfloat16, got {x.dtype}"
+    assert x.is_contiguous() and x.dim() == 2, f"{name} must be a contiguous 2-D tensor"
+    return x
+
+
+def _p(t):
+    return t.data_ptr() if t is not None else None
+
+
+def _stream(x):
+    return torch.cuda.current_stream(x.device).cuda_stream
+
+
+def _cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def blocked_shape(rows, cols):
+    """Shape of the 32x4x4 blocked scale grid of a (rows, cols) block-scale matrix (gold G:1000-1037)."""
+    return (_cdiv(rows, 128), _cdiv(cols, 4), 32, 16)
+
+
+def philox_key(seed, offset=0, device="cuda"):
+    """A Philox4x32-10 key as the stochastic-rounding casts take it: uint64 [seed, offset] on the device."""
+    t = torch.tensor([int(seed) & 0x7FFFFFFFFFFFFFFF, int(offset)], dtype=torch.int64, device=device)
+    return t.view(torch.uint64)
+
+
+# --------------------------------------------------------------------------------------------
+# amax and per-tensor scales
+# --------------------------------------------------------------------------------------------
+def _amax(x, mode, fmt=L.FMT_E4M3):
+    lib = L.load()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    out = torch.empty((), dtype=torch.float32, device=x.device)
+    ws_bytes = lib.qcc_amax_workspace_bytes()
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
+    L.launch_count += 2
+    return out
+
+
+def amax_cuda(x):
+    """max |x| as a 0-dim fp32 tensor (exact: a bf16 magnitude)."""
+    return _amax(x, L.AMAX_RAW)
+
+
+def scale_from_amax_cuda(amax, kind, fmt="e4m3"):
+    """Per-tensor scale from an already reduced amax: kind 'fp8' -> max(amax, bf16(1e-12)) / fp8_max,
+    kind 'nvfp4' -> amax / 2688.  Used after the all-reduce of per-shard amaxes."""
+    lib = L.load()
+    mode = {"fp8": L.AMAX_FP8_SCALE, "nvfp4": L.AMAX_NVFP4_SCALE, "raw": L.AMAX_RAW}[kind]
+    a = amax.reshape(-1)[:1].contiguous().float()
+    out = torch.empty((), dtype=torch.float32, device=amax.device)
+    with torch.cuda.device(amax.device):
+        L.check(lib.qcc_scale_from_amax(_p(a), mode, _fmt(fmt), _p(out), _stream(amax)), "scale_from_amax")
+    L.launch_count += 1
+    return out
+
+
+def float8_tensorwise_scale_cuda(x, fmt="e4m3"):
+    """gold float8_tensorwise_scale (G:1179-1183): 0-dim fp32 scale = max(amax, bf16(1e-12)) / fp8_max."""
+    return _amax(x, L.AMAX_FP8_SCALE, _fmt(fmt))
+
+
+def nvfp4_gs_scale_cuda(x):
+    """gold nvfp4_gs_scale (G:1243-1246): 0-dim fp32 outer scale = amax / (448 * 6)."""
+    return _amax(x, L.AMAX_NVFP4_SCALE)
+
+
+# --------------------------------------------------------------------------------------------
+# fp8
+# --------------------------------------------------------------------------------------------
+def float8_tensorwise_cuda(x, scale, fmt="e4m3", **kwargs):
+    """gold float8_tensorwise_f (G:1186-1191): (qdata,) = fp8(x * (1 / scale))."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.qcc_fp8_tensorwise(_p(x), x.numel(), _p(scale), f, _p(q), _stream(x)), "fp8_tensorwise")
+    L.launch_count += 1
+    return (q.view(_FP8_DTYPE[f]),)
+
+
+def rowwise_fp8_cuda(x, fmt="e4m3", **kwargs):
+    """gold rowwise_fp8_f (G:301-307): (qdata (M, N), scale (M, 1) fp32)."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    M, N = x.shape
+    q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, f, _p(q), _p(s), _stream(x)), "fp8_rowwise")
+    L.launch_count += 1
+    return q.view(_FP8_DTYPE[f]), s
+
+
+def rowwise_precalc_scale_cuda(x, fmt="e4m3"):
+    """gold rowwise_precalc_scale (G:389-393): (M, 1) fp32 per-row scale."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, _fmt(fmt), None, _p(s), _stream(x)), "fp8_rowwise_scale")
+    L.launch_count += 1
+    return s
+
+
+def rowwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
+    """gold rowwise_precalc_f (G:396-399): (qdata,) = fp8(x / scale) with a given (M, 1) scale."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    M, N = x.shape
+    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == M and scale.is_contiguous()
+    q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.qcc_fp8_rowwise_precalc(_p(x), M, N, _p(scale), f, _p(q), _stream(x)), "fp8_rowwise_precalc")
+    L.launch_count += 1
+    return (q.view(_FP8_DTYPE[f]),)
+
+
+# --------------------------------------------------------------------------------------------
+# mxfp8
+# --------------------------------------------------------------------------------------------
+def _mxfp8(x, flags):
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 32 == 0, f"mxfp8 needs N % 32 == 0, got N={N}"
+    if flags & L.COLWISE:
+        assert M % 32 == 0, f"mxfp8 dim-m needs M % 32 == 0, got M={M}"
+    swz = bool(flags & L.SWIZZLE)
+    dev = x.device
+    qk = sk = qm = sm = None
+    if flags & L.ROWWISE:
+        qk = torch.empty((M, N), dtype=torch.uint8, device=dev)
+        sk = torch.empty(blocked_shape(M, N // 32) if swz else (M, N // 32), dtype=torch.uint8, device=dev)
+    if flags & L.COLWISE:
+        qm = torch.empty((N, M), dtype=torch.uint8, device=dev)
+        sm = torch.empty(blocked_shape(N, M // 32) if swz else (N, M // 32), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        L.check(lib.qcc_mxfp8(_p(x), M, N, flags, _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "mxfp8")
+    L.launch_count += 1
+    outs = []
+    if flags & L.ROWWISE:
+        outs += [qk.view(torch.float8_e4m3fn), sk.view(torch.float8_e8m0fnu)]
+    if flags & L.COLWISE:
+        outs += [qm.view(torch.float8_e4m3fn), sm.view(torch.float8_e8m0fnu)]
+    return tuple(outs)
+
+
+def mxfp8_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_f (G:561-568): (qdata (M, N) e4m3, scale (M, N/32) e8m0)."""
+    return _mxfp8(x, L.ROWWISE | _mode(mode))
+
+
+def mxfp8_swizzle_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_swizzle_f (G:1051-1053): scale as the (ceil(M/128), ceil(N/128), 32, 16) blocked grid."""
+    return _mxfp8(x, L.ROWWISE | L.SWIZZLE | _mode(mode))
+
+
+def mxfp8_dim_m_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_dim_m_f (G:656-671): (qdata (N, M), scale (N, M/32)), 32x1 blocks, transposed."""
+    return _mxfp8(x, L.COLWISE | _mode(mode))
+
+
+def mxfp8_dim_m_swizzle_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_dim_m_swizzle_f (G:1092-1094)."""
+    return _mxfp8(x, L.COLWISE | L.SWIZZLE | _mode(mode))
+
+
+def mxfp8_dim_km_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_dim_km_f (G:701-719): (qk, sk, qm, sm) from one read of x."""
+    return _mxfp8(x, L.ROWWISE | L.COLWISE | _mode(mode))
+
+
+def mxfp8_dim_km_swizzle_cuda(x, mode="rceil", **kwargs):
+    """gold mxfp8_dim_km_swizzle_f (G:1134-1139)."""
+    return _mxfp8(x, L.ROWWISE | L.COLWISE | L.SWIZZLE | _mode(mode))
+
+
+# --------------------------------------------------------------------------------------------
+# nvfp4
+# --------------------------------------------------------------------------------------------
+def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    dev = x.device
+    assert outer_scale.is_cuda and outer_scale.dtype == torch.float32, "outer_scale must be a CUDA fp32 tensor"
+    per_row = int(outer_scale.ndim == 2)
+    o = outer_scale.contiguous()
+    if per_row:
+        assert o.numel() == M and not transposed, "per-token outer scale must be (M, 1)"
+    else:
+        assert o.numel() == 1
+    if flags & L.SR:
+        assert key is not None and key.is_cuda and key.numel() >= 2 and key.element_size() == 8, (
+            "stochastic rounding needs a uint64 [seed, offset] key on the device (see philox_key)")
+    swz = bool(flags & L.SWIZZLE)
+    with torch.cuda.device(dev):
+        if transposed:
+            assert M % 32 == 0 and N % 8 == 0, f"transposed nvfp4 needs M % 32 == 0 and N % 8 == 0, got {M}x{N}"
+            q = torch.empty((N, M // 2), dtype=torch.uint8, device=dev)
+            s = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=torch.uint8, device=dev)
+            L.check(lib.qcc_nvfp4_transposed(_p(x), M, N, _p(o), flags, _p(key), _p(q), _p(s), _stream(x)), "nvfp4_t")
+        else:
+            assert N % 16 == 0, f"nvfp4 needs N % 16 == 0, got N={N}"
+            q = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
+            s = torch.empty(blocked_shape(M, N // 16) if swz else (M, N // 16), dtype=torch.uint8, device=dev)
+            L.check(lib.qcc_nvfp4(_p(x), M, N, _p(o), per_row, flags, _p(key), _p(q), _p(s), _stream(x)), "nvfp4")
+    L.launch_count += 1
+    return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
+
+
+def nvfp4_gs_cuda(x, outer_scale, **kwargs):
+    """gold nvfp4_gs_f (G:1494-1517): (qdata (M, N/2) packed fp4, inner (M, N/16) e4m3); outer_scale a
+    0-dim / (1,) per-tensor value or an (M, 1) per-token column."""
+    return _nvfp4(x, outer_scale, 0)
+
+
+def nvfp4_gs_swizzle_cuda(x, outer_scale, **kwargs):
+    """gold nvfp4_gs_swizzle_f (G:1249-1266): inner scale as the blocked (.., .., 32, 16) grid."""
+    return _nvfp4(x, outer_scale, L.SWIZZLE)
+
+
+def nvfp4_gs_swizzle_sr_cuda(x, outer_scale, key, **kwargs):
+    """gold nvfp4_gs_swizzle_sr_f (G:1409-1426) with the dither drawn from Philox4x32-10 keyed by
+    `key` = uint64 [seed, offset] (extension: the gold draws from torch.func._random.uniform)."""
+    return _nvfp4(x, outer_scale, L.SWIZZLE | L.SR, key=key)
+
+
+def nvfp4_gs_t_cuda(x, outer_scale, **kwargs):
+    """Extension: nvfp4_gs_f(x.t().contiguous(), outer_scale) without materialising the transpose."""
+    return _nvfp4(x, outer_scale, 0, transposed=True)
+
+
+def nvfp4_gs_swizzle_t_cuda(x, outer_scale, **kwargs):
+    """Extension: nvfp4_gs_swizzle_f(x.t().contiguous(), outer_scale), the transposed operand of
+    test/test_quant_cast_gold.py:104, without materialising the transpose."""
+    return _nvfp4(x, outer_scale, L.SWIZZLE, transposed=True)
+
+
+def nvfp4_gs_swizzle_t_sr_cuda(x, outer_scale, key, **kwargs):
+    """Extension: stochastic-rounding variant of nvfp4_gs_swizzle_t_cuda (stream indexed in the
+    transposed frame)."""
+    return _nvfp4(x, outer_scale, L.SWIZZLE | L.SR, key=key, transposed=True)
+
+
+# --------------------------------------------------------------------------------------------
+# recipe records
+# --------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class QuantCastCudaRecipe:
+    """A gold recipe plus its CUDA implementation (`cuda_fn`, same `(inputs) -> outputs` signature as
+    `pt_ref_fn`).  Same fields as QuantCastSingleKernelGold (quant_cast_gold/recipes.py:63-88) plus
+    `cuda_fn`, built with `from_gold` like the other backends' recipe classes.  When the reference
+    package is not importable the gold fields are None and only `cuda_fn` / `example_input_fn` are set."""
+
+    pt_ref_fn: Optional[Callable]
+    correctness_fn: Optional[Callable]
+    example_input_fn: Optional[Callable]
+    perf_description: str
+    cuda_fn: Optional[Callable] = None
+
+    @classmethod
+    def from_gold(cls, gold, cuda_fn: Callable) -> "QuantCastCudaRecipe":
+        return cls(
+            pt_ref_fn=gold.pt_ref_fn,
+            correctness_fn=gold.correctness_fn,
+            example_input_fn=gold.example_input_fn,
+            perf_description=gold.perf_description,
+            cuda_fn=cuda_fn,
+        )
+
+
+def _x(M, K):
+    return torch.randn(M, K, dtype=torch.bfloat16, device="cuda")
+
+
+def _inputs_x(M, K):
+    return (_x(M, K),)
+
+
+def _inputs_tensorwise(M, K):
+    x = _x(M, K)
+    return (x, float8_tensorwise_scale_cuda(x))
+
+
+def _inputs_rowwise_precalc(M, K):
+    x = _x(M, K)
+    return (x, rowwise_precalc_scale_cuda(x))
+
+
+def _inputs_nvfp4(M, K):
+    x = _x(M, K)
+    return (x, nvfp4_gs_scale_cuda(x))
+
+
+# (gold recipe name, gold attribute in quant_cast_gold.recipes, cuda fn, input builder, description)
+_TABLE = [
+    ("fp8_tensorwise_precalc_scale", "Float8TensorwiseGold", float8_tensorwise_cuda, _inputs_tensorwise, "elementwise"),
+    ("fp8_rowwise_precalc_scale", "RowwisePrecalcGold", rowwise_precalc_cuda, _inputs_rowwise_precalc, "elementwise"),
+    ("mxfp8", "Mxfp8Gold", mxfp8_cuda, _inputs_x, "(1,32) block"),
+    ("mxfp8_swizzle", "Mxfp8SwizzleGold", mxfp8_swizzle_cuda, _inputs_x, "(1,32) block, swizzle"),
+    ("mxfp8_dim_m", "Mxfp8DimMGold", mxfp8_dim_m_cuda, _inputs_x, "(32,1) block, t-contig"),
+    ("mxfp8_dim_m_swizzle", "Mxfp8DimMSwizzleGold", mxfp8_dim_m_swizzle_cuda, _inputs_x, "(32,1) block, t-contig, swizzle"),
+    ("mxfp8_dim_km", "Mxfp8DimKmGold", mxfp8_dim_km_cuda, _inputs_x, "(1,32) dim-k + (32,1) dim-m, one pass, t-contig"),
+    ("mxfp8_dim_km_swizzle", "Mxfp8DimKmSwizzleGold", mxfp8_dim_km_swizzle_cuda, _inputs_x,
+     "(1,32) dim-k + (32,1) dim-m, one pass, t-contig, swizzle"),
+    ("fp8_rowwise", "RowwiseFp8Gold", rowwise_fp8_cuda, _inputs_x, "(1,-1) block"),
+    ("nvfp4", "Nvfp4GsGold", nvfp4_gs_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, no swizzle"),
+    ("nvfp4_swizzle", "Nvfp4GsSwizzleGold", nvfp4_gs_swizzle_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, swizzle"),
+]
+
+
+def _build_recipes():
+    try:  # the reference package, when this backend is dropped in beside it
+        from quant_cast_bench.quant_cast_gold import recipes as gold
+    except Exception:
+        gold = None
+    out = []
+    for name, gold_attr, fn, inputs, desc in _TABLE:
+        g = getattr(gold, gold_attr, None) if gold is not None else None
+        if g is not None:
+            out.append((name, QuantCastCudaRecipe.from_gold(g, fn)))
+        else:
+            out.append((name, QuantCastCudaRecipe(None, None, inputs, desc, fn)))
+    return out
+
+
+# Order follows quant_cast_gold.ALL_RECIPES (G:1929-1973), restricted to the recipes this backend implements.
+ALL_RECIPES = _build_recipes()
+
+__all__ = [n for n in dir() if n.endswith("_cuda")] + ["ALL_RECIPES", "QuantCastCudaRecipe", "blocked_shape", "philox_key"]

@@ -1,0 +1,330 @@
+"""Parity of the CUDA casts with the CPU oracle and with golden vectors of the reference's gold
+recipes, bit for bit.  Same skeleton as the reference's backend tests
+(test/test_quant_cast_triton.py:59-107 of vkuzo/quant_cast_bench: same output count, shapes, dtypes,
+then raw equality, at an aligned shape and at ragged shapes that force blocked-layout padding) --
+but without the tolerance fallback: every non-stochastic output must match exactly, and the
+stochastic one must too because checker and kernel share the Philox stream definition.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from helpers import assert_same_bits, golden_cases, golden_n_outputs, golden_out, golden_x, same_outputs
+from oracle import gold_port as O
+from quant_cast_bench_b200 import quant_cast_cuda as Q
+from quant_cast_bench_b200.quant_cast_cuda import _lib as L
+from quant_cast_bench_b200.workloads import make_input
+
+pytestmark = pytest.mark.gpu
+
+# aligned shape + the reference's two ragged shapes + shapes crossing tile / atom boundaries
+SHAPES = [(512, 512), (96, 160), (128, 160), (32, 32), (160, 416), (384, 96), (1024, 2048), (2080, 1056)]
+ONE_INPUT = ["rowwise_fp8", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m", "mxfp8_dim_m_swizzle", "mxfp8_dim_km",
+             "mxfp8_dim_km_swizzle"]
+
+
+def cuda_fn(name):
+    return getattr(Q, name + "_cuda")
+
+
+def oracle_fn(name):
+    return getattr(O, name + "_f")
+
+
+@pytest.fixture(autouse=True)
+def _no_device_error():
+    yield
+    err = ctypes.c_uint(0)
+    assert L.load().qcc_device_error(ctypes.byref(err)) == 0
+    assert err.value == 0, f"a kernel gave up a bounded wait (code {err.value})"
+
+
+def _x(M, N, seed=0, **kw):
+    return make_input(M, N, seed, **kw)
+
+
+# ---------------------------------------------------------------------------- golden vectors
+@pytest.mark.parametrize("tag", golden_cases())
+@pytest.mark.parametrize("fn", ONE_INPUT)
+def test_golden_single_input(tag, fn):
+    x = golden_x(tag).cuda()
+    outs = cuda_fn(fn)(x)
+    gname = fn + "_f"
+    assert len(outs) == golden_n_outputs(tag, gname)
+    for i, o in enumerate(outs):
+        assert_same_bits(o, golden_out(tag, gname, i), f"{fn}[{i}] {tag}")
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+def test_golden_fp8_tensorwise_and_precalc(tag):
+    x = golden_x(tag).cuda()
+    s = Q.float8_tensorwise_scale_cuda(x)
+    assert s.shape == () and s.dtype == torch.float32
+    assert_same_bits(s.reshape(1), golden_out(tag, "float8_tensorwise_scale", 0), "scale")
+    (q,) = Q.float8_tensorwise_cuda(x, s)
+    assert q.dtype == torch.float8_e4m3fn
+    assert_same_bits(q, golden_out(tag, "float8_tensorwise_f", 0), "q")
+    ps = Q.rowwise_precalc_scale_cuda(x)
+    assert_same_bits(ps, golden_out(tag, "rowwise_precalc_scale", 0), "row scale")
+    assert_same_bits(Q.rowwise_precalc_cuda(x, ps)[0], golden_out(tag, "rowwise_precalc_f", 0), "precalc q")
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+def test_golden_nvfp4(tag):
+    x = golden_x(tag).cuda()
+    gs = Q.nvfp4_gs_scale_cuda(x)
+    assert_same_bits(gs.reshape(1), golden_out(tag, "nvfp4_gs_scale", 0), "outer")
+    for fn in ("nvfp4_gs", "nvfp4_gs_swizzle", "nvfp4_gs_swizzle_t", "nvfp4_gs_t"):
+        outs = cuda_fn(fn)(x, gs)
+        assert outs[0].dtype == torch.float4_e2m1fn_x2 and outs[1].dtype == torch.float8_e4m3fn
+        for i, o in enumerate(outs):
+            assert_same_bits(o, golden_out(tag, fn + "_f", i), f"{fn}[{i}] {tag}")
+    pt = golden_out(tag, "nvfp4_per_token_scale", 0).view(torch.float32).cuda()
+    for i, o in enumerate(Q.nvfp4_gs_cuda(x, pt)):
+        assert_same_bits(o, golden_out(tag, "nvfp4_gs_f_per_token", i), f"per-token[{i}] {tag}")
+
+
+# ---------------------------------------------------------------------------- oracle, many shapes
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("fn", ONE_INPUT)
+def test_matches_oracle(fn, shape):
+    x = _x(*shape, seed=shape[0] + shape[1])
+    kw = {"global_row": 0, "global_col": 0, "num_col": shape[1]}  # tile kwargs are accepted and ignored
+    same_outputs(cuda_fn(fn)(x.cuda(), **kw), oracle_fn(fn)(x), f"{fn} {shape}")
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("fn", [f for f in ONE_INPUT if f.startswith("mxfp8")])
+def test_mxfp8_floor_mode(fn, shape):
+    x = _x(*shape, seed=7)
+    same_outputs(cuda_fn(fn)(x.cuda(), mode="floor"), oracle_fn(fn)(x, mode="floor"), f"{fn} floor {shape}")
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("shape", SHAPES + [(17, 100), (3, 7), (5, 20000), (64, 16384)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_fp8_family(fmt, shape):
+    x = _x(*shape, seed=11, spread=8.0)
+    xc = x.cuda()
+    s = Q.float8_tensorwise_scale_cuda(xc, fmt)
+    so = O.float8_tensorwise_scale(x, fmt)
+    assert_same_bits(s, so, "tensorwise scale")
+    same_outputs(Q.float8_tensorwise_cuda(xc, s, fmt), O.float8_tensorwise_f(x, so, fmt), f"tensorwise {fmt}")
+    same_outputs(Q.rowwise_fp8_cuda(xc, fmt), O.rowwise_fp8_f(x, fmt), f"rowwise {fmt}")
+    ps = Q.rowwise_precalc_scale_cuda(xc, fmt)
+    assert_same_bits(ps, O.rowwise_precalc_scale(x, fmt), "row scale")
+    same_outputs(Q.rowwise_precalc_cuda(xc, ps, fmt), O.rowwise_precalc_f(x, ps.cpu(), fmt), f"precalc {fmt}")
+
+
+def test_fp8_all_zero_and_tiny():
+    x = torch.zeros(64, 256, dtype=torch.bfloat16)
+    x[3, 5] = 1e-30
+    xc = x.cuda()
+    s = Q.float8_tensorwise_scale_cuda(xc)
+    assert_same_bits(s, O.float8_tensorwise_scale(x), "scale of ~zero tensor (bf16 clamp at 1e-12)")
+    same_outputs(Q.rowwise_fp8_cuda(xc), O.rowwise_fp8_f(x), "rowwise zero rows")
+    for fn in ONE_INPUT[1:]:
+        same_outputs(cuda_fn(fn)(xc), oracle_fn(fn)(x), f"{fn} zeros")
+
+
+@pytest.mark.parametrize("shape", [(512, 512), (128, 192), (96, 160), (128, 160), (160, 416), (1024, 2048), (2080, 1056)],
+                         ids=lambda s: f"{s[0]}x{s[1]}")
+def test_nvfp4_matches_oracle(shape):
+    x = _x(*shape, seed=5)
+    xc = x.cuda()
+    gs = Q.nvfp4_gs_scale_cuda(xc)
+    gso = O.nvfp4_gs_scale(x)
+    assert_same_bits(gs, gso, "outer scale")
+    for fn in ("nvfp4_gs", "nvfp4_gs_swizzle", "nvfp4_gs_t", "nvfp4_gs_swizzle_t"):
+        same_outputs(cuda_fn(fn)(xc, gs), oracle_fn(fn)(x, gso), f"{fn} {shape}")
+    # per-token outer scale (M, 1)
+    amax_rows = x.float().abs().amax(dim=1, keepdim=True).clamp(min=2.0 ** -100)
+    pt = amax_rows / 2688.0
+    same_outputs(Q.nvfp4_gs_cuda(xc, pt.cuda()), O.nvfp4_gs_f(x, pt), f"per-token {shape}")
+
+
+def test_all_bf16_values_through_every_conversion():
+    """Every finite bf16 bit pattern goes through the fp8, e8m0 and fp4 paths (ties, subnormals,
+    signed zeros, saturation), with several scales."""
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32)
+    finite = (bits & 0x7F80) != 0x7F80
+    v = bits[finite].to(torch.int16).view(torch.bfloat16)           # 65024 values
+    n = (v.numel() // 512) * 512
+    x = v[:n].reshape(-1, 512).contiguous()
+    g = torch.Generator().manual_seed(3)
+    xs = x.flatten()[torch.randperm(n, generator=g)].reshape(-1, 512).contiguous()  # mixed magnitudes per block
+    for t in (x, xs):
+        tc = t.cuda()
+        for fmt in ("e4m3", "e5m2"):
+            for scale in (1.0, 0.37, 3.1e-5, 2.0 ** 40, 1.7e30):
+                s = torch.tensor(scale, dtype=torch.float32)
+                # the checker saturates like the kernel, so overflowing products are compared too
+                same_outputs(Q.float8_tensorwise_cuda(tc, s.cuda(), fmt), O.float8_tensorwise_f(t, s, fmt), f"{fmt} {scale}")
+        for fn in ONE_INPUT:
+            same_outputs(cuda_fn(fn)(tc), oracle_fn(fn)(t), fn)
+            if fn.startswith("mxfp8"):
+                same_outputs(cuda_fn(fn)(tc, mode="floor"), oracle_fn(fn)(t, mode="floor"), fn + " floor")
+        for outer in (1.0, 2.0 ** -20, 3.3e3, 7.7e-12, 1.1e25):
+            o = torch.tensor(outer, dtype=torch.float32)
+            for fn in ("nvfp4_gs", "nvfp4_gs_swizzle", "nvfp4_gs_t", "nvfp4_gs_swizzle_t"):
+                same_outputs(cuda_fn(fn)(tc, o.cuda()), oracle_fn(fn)(t, o), f"{fn} outer={outer}")
+
+
+def test_fp4_ties_round_to_even():
+    """Scaled values exactly on e2m1 midpoints: outer = 1/6 and a block amax of 6 make recip == 1."""
+    vals = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -2.5, -5.0, 6.0, 0.0, -0.0, 0.5, 1.0]
+    x = torch.tensor(vals, dtype=torch.bfloat16).repeat(32, 4).contiguous()   # (32, 64)
+    outer = torch.tensor(1.0 / 6.0, dtype=torch.float32)
+    q, s = Q.nvfp4_gs_cuda(x.cuda(), outer.cuda())
+    qo, so = O.nvfp4_gs_f(x, outer)
+    assert_same_bits(q, qo, "fp4 ties")
+    assert_same_bits(s, so, "inner")
+    nib = q.view(torch.uint8).cpu()[0, :8]
+    lo = (nib & 15).tolist()
+    hi = (nib >> 4).tolist()
+    got = [c for pair in zip(lo, hi) for c in pair]
+    # 0.25->0, 0.75->1.0, 1.25->1.0, 1.75->2, 2.5->2, 3.5->4, 5->4, negatives mirror, -0.25 -> -0
+    assert got == [0, 2, 2, 4, 4, 6, 6, 8, 10, 12, 14, 7, 0, 8, 1, 2]
+
+
+# ---------------------------------------------------------------------------- stochastic rounding
+@pytest.mark.parametrize("shape", [(128, 256), (96, 160), (1024, 2048)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_sr_bit_exact_against_oracle_stream(shape):
+    x = _x(*shape, seed=9, spread=0.0, outlier_p=1e-3, outlier_mul=50.0, zero_row_p=0.0)
+    xc = x.cuda()
+    gs = Q.nvfp4_gs_scale_cuda(xc)
+    for seed, off in ((0, 0), (12345, 0), (2 ** 40 + 17, 2 ** 33 + 5)):
+        key = Q.philox_key(seed, off)
+        same_outputs(Q.nvfp4_gs_swizzle_sr_cuda(xc, gs, key), O.nvfp4_gs_swizzle_sr_f(x, gs.cpu(), (seed, off)), f"sr {seed}")
+        if shape[0] % 32 == 0:
+            same_outputs(Q.nvfp4_gs_swizzle_t_sr_cuda(xc, gs, key), O.nvfp4_gs_swizzle_t_sr_f(x, gs.cpu(), (seed, off)),
+                         f"sr transposed {seed}")
+    # scales and layout do not depend on the rounding mode
+    q_sr, s_sr = Q.nvfp4_gs_swizzle_sr_cuda(xc, gs, Q.philox_key(1))
+    q_rn, s_rn = Q.nvfp4_gs_swizzle_cuda(xc, gs)
+    assert_same_bits(s_sr, s_rn, "sr scales == rne scales")
+    assert q_sr.shape == q_rn.shape and q_sr.dtype == q_rn.dtype
+
+
+def _fp4_decode(q):
+    lut = torch.tensor([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6], device=q.device)
+    b = q.view(torch.uint8).long()
+    return torch.stack([lut[b & 15], lut[b >> 4]], dim=-1).flatten(-2)
+
+
+def test_sr_unbiased_over_seeds():
+    """Mean of the dequantised values over 16 seeds approaches x (relative error of the mean <= 1e-3),
+    every draw lands on one of the two fp4 neighbours, and the draw frequency matches the distance
+    (the property test of the reference: quant_cast_gold/recipes.py:1854-1869 and
+    experiments/stochastic_rounding_api/test_vs_gold.py:116-176)."""
+    M, N = 1024, 2048
+    x = _x(M, N, seed=21, spread=0.0, outlier_p=1e-3, outlier_mul=50.0, zero_row_p=0.0).cuda()
+    gs = Q.nvfp4_gs_scale_cuda(x)
+    q_rn, s = Q.nvfp4_gs_swizzle_cuda(x, gs)
+    qp, sp = Q.nvfp4_gs_cuda(x, gs)   # plain-layout scales to dequantise with
+    inner = sp.float().repeat_interleave(16, dim=1)
+    recip_scale = inner * gs
+    acc = torch.zeros(M, N, device="cuda", dtype=torch.float64)
+    n_seeds = 16
+    for seed in range(n_seeds):
+        q, s_sr = Q.nvfp4_gs_swizzle_sr_cuda(x, gs, Q.philox_key(seed))
+        assert_same_bits(s_sr, s, "scales")
+        acc += (_fp4_decode(q) * recip_scale).double()
+    mean = acc / n_seeds
+    xf = x.double()
+    # aggregate relative error of the mean
+    rel = (mean - xf).abs().sum() / xf.abs().sum()
+    rne = ((_fp4_decode(q_rn) * recip_scale).double() - xf).abs().sum() / xf.abs().sum()
+    assert rel < rne, f"SR mean error {rel:.4g} should beat RNE error {rne:.4g}"
+    signed = ((mean - xf).sum() / xf.abs().sum()).abs()
+    assert signed <= 1e-3, f"relative bias of the SR mean {signed:.3g} > 1e-3"
+    # P(round up) on a constant probe: value 1.25 between fp4 neighbours 1.0 and 1.5 -> 50 %; 1.125 -> 25 %
+    for v, p_up, lo, hi in ((1.25, 0.5, 1.0, 1.5), (1.125, 0.25, 1.0, 1.5), (2.25, 0.25, 2.0, 3.0), (0.625, 0.25, 0.5, 1.0)):
+        probe = torch.full((256, 1024), v, dtype=torch.bfloat16, device="cuda")
+        probe[:, ::16] = 6.0   # block amax 6 with outer 1/6 -> recip == 1
+        outer = torch.tensor(1.0 / 6.0, device="cuda")
+        q, _ = Q.nvfp4_gs_swizzle_sr_cuda(probe, outer, Q.philox_key(99))
+        d = _fp4_decode(q)
+        body = d[:, torch.arange(1024, device="cuda") % 16 != 0]
+        assert set(body.unique().tolist()) <= {lo, hi}
+        frac = (body == hi).double().mean().item()
+        assert abs(frac - p_up) < 0.01, f"P(up) for {v}: {frac:.4f} vs {p_up}"
+
+
+# ---------------------------------------------------------------------------- unwritten bytes / padding
+@pytest.mark.parametrize("fill", [0x00, 0xFF])
+def test_outputs_fully_written_with_guard_bytes(fill):
+    """Call the C ABI on pre-filled buffers (ragged shape -> blocked-layout padding): every output byte
+    must equal the oracle's whatever the buffer held before, and the guard bytes after each buffer
+    stay untouched."""
+    lib = L.load()
+    M, N = 160, 416
+    x = _x(M, N, seed=2)
+    xc = x.cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    GUARD = 256
+
+    def buf(nbytes):
+        t = torch.full((nbytes + GUARD,), fill, dtype=torch.uint8, device="cuda")
+        t[nbytes:] = 0xA5
+        return t
+
+    def check(t, want, what):
+        n = want.numel() * want.element_size()
+        assert_same_bits(t[:n].cpu(), want.contiguous().view(torch.uint8).flatten(), what)
+        assert bool((t[n:] == 0xA5).all()), f"{what}: guard bytes overwritten"
+
+    for flags, ofn in ((L.ROWWISE | L.COLWISE | L.SWIZZLE, O.mxfp8_dim_km_swizzle_f), (L.ROWWISE | L.COLWISE, O.mxfp8_dim_km_f)):
+        want = ofn(x)
+        bufs = [buf(w.numel()) for w in want]
+        rc = lib.qcc_mxfp8(xc.data_ptr(), M, N, flags, *[b.data_ptr() for b in bufs], stream)
+        assert rc == 0
+        for b, w, n in zip(bufs, want, ("qk", "sk", "qm", "sm")):
+            check(b, w, f"mxfp8 flags={flags} {n}")
+    gs = O.nvfp4_gs_scale(x)
+    gsc = gs.cuda()
+    for tr, flags, ofn in ((False, L.SWIZZLE, O.nvfp4_gs_swizzle_f), (True, L.SWIZZLE, O.nvfp4_gs_swizzle_t_f),
+                           (False, 0, O.nvfp4_gs_f), (True, 0, O.nvfp4_gs_t_f)):
+        want = ofn(x, gs)
+        bufs = [buf(w.numel()) for w in want]
+        if tr:
+            rc = lib.qcc_nvfp4_transposed(xc.data_ptr(), M, N, gsc.data_ptr(), flags, None, bufs[0].data_ptr(), bufs[1].data_ptr(), stream)
+        else:
+            rc = lib.qcc_nvfp4(xc.data_ptr(), M, N, gsc.data_ptr(), 0, flags, None, bufs[0].data_ptr(), bufs[1].data_ptr(), stream)
+        assert rc == 0
+        for b, w, n in zip(bufs, want, ("q", "s")):
+            check(b, w, f"nvfp4 transposed={tr} flags={flags} {n}")
+
+
+# ---------------------------------------------------------------------------- errors
+def test_rejected_arguments():
+    x = torch.randn(64, 48, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(AssertionError):
+        Q.mxfp8_cuda(x)                       # N % 32 != 0
+    with pytest.raises(AssertionError):
+        Q.mxfp8_dim_m_cuda(torch.randn(48, 64, dtype=torch.bfloat16, device="cuda"))  # M % 32 != 0
+    with pytest.raises(AssertionError):
+        Q.mxfp8_cuda(x.t())                   # not contiguous
+    with pytest.raises(ValueError):
+        Q.mxfp8_cuda(x.cpu())                 # no CPU path
+    with pytest.raises(ValueError):
+        Q.float8_tensorwise_cuda(x, torch.ones((), device="cuda"), fmt="e3m4")
+    lib = L.load()
+    assert lib.qcc_mxfp8(x.data_ptr(), 64, 48, L.ROWWISE, x.data_ptr(), x.data_ptr(), None, None, None) == -1
+    assert lib.qcc_mxfp8(x.data_ptr() + 2, 64, 64, L.ROWWISE, x.data_ptr(), x.data_ptr(), None, None, None) == -2
+    assert lib.qcc_mxfp8(None, 64, 64, L.ROWWISE, x.data_ptr(), x.data_ptr(), None, None, None) == -3
+    assert lib.qcc_amax_bf16(x.data_ptr(), 10, 0, 0, x.data_ptr(), x.data_ptr(), 16, None) == -4
+    # empty input is a no-op
+    e = torch.empty(0, 64, dtype=torch.bfloat16, device="cuda")
+    q, s = Q.mxfp8_cuda(e)
+    assert q.shape == (0, 64) and s.shape == (0, 2)
+
+
+def test_recipe_index_mirrors_reference_backends():
+    names = [n for n, _ in Q.ALL_RECIPES]
+    assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
+                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "nvfp4", "nvfp4_swizzle"]
+    for name, r in Q.ALL_RECIPES:
+        inputs = r.example_input_fn(256, 256)
+        outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
+        assert isinstance(outs, tuple) and all(o.is_cuda for o in outs)
