@@ -336,10 +336,10 @@ int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *
 
 int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream)
 {
+    if (n == 0) return 0;
     if (!x || !scale || !q || n < 0) return QCC_ERR_ARG;
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
-    if (n == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t per_cta = (int64_t)TW_THREADS * TW_UNROLL * 16;
     int64_t grid = (n + per_cta - 1) / per_cta;
@@ -353,6 +353,7 @@ int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, vo
 
 int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *stream)
 {
+    if (M == 0 || N == 0) return 0;
     if (!x || !scale || M < 0 || N < 0) return QCC_ERR_ARG;
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (N % 8 == 0 && (!aligned16(x) || (q && !aligned16(q)))) return QCC_ERR_ALIGN;
@@ -364,6 +365,7 @@ int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
 
 int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
 {
+    if (M == 0 || N == 0) return 0;
     if (!x || !scale || !q || M < 0 || N < 0) return QCC_ERR_ARG;
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (N % 8 == 0 && (!aligned16(x) || !aligned16(q))) return QCC_ERR_ALIGN;

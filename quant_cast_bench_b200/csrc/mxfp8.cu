@@ -267,6 +267,7 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
                          void *stream)
 {
     const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
+    if (M == 0 || N == 0) return 0;
     if (!x || (!row && !col) || (flags & ~(QCC_ROWWISE | QCC_COLWISE | QCC_SWIZZLE | QCC_FLOOR))) return QCC_ERR_ARG;
     if ((row && (!qk || !sk)) || (col && (!qm || !sm))) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;

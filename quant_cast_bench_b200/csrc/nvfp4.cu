@@ -270,6 +270,7 @@ extern "C" int qcc_nvfp4_device_error(unsigned int *out) { return read_clear_dev
 extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
                          const uint64_t *philox_key, void *q, void *s, void *stream)
 {
+    if (M == 0 || N == 0) return 0;
     if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || N % 16 != 0) return QCC_ERR_SHAPE;
@@ -324,6 +325,7 @@ static int launch_nvt(const CUtensorMap &tx, const CUtensorMap &tq, const float 
 extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
                                     const uint64_t *philox_key, void *q, void *s, void *stream)
 {
+    if (M == 0 || N == 0) return 0;
     if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
