@@ -320,8 +320,8 @@ def cpu_baseline():
 
 
 def bench_other_casts(Q, x, dev, peak):
-    """Per-cast GB/s of the other casts (same run, CUDA events per launch, inputs larger than L2 or an
-    L2 flush write in between)."""
+    """Per-cast GB/s of the other casts (same run, CUDA events per launch, a 256 MB L2-flush write
+    before every timed launch)."""
     import torch
     out = {}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
@@ -332,8 +332,9 @@ def bench_other_casts(Q, x, dev, peak):
         torch.cuda.synchronize()
         ts = []
         for _ in range(iters):
-            if flush_l2:
-                flush.zero_()
+            # the 256 MB write both evicts L2 and keeps the GPU busy while the host enqueues the
+            # launch, so the start event sits directly in front of the kernel
+            flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()

@@ -33,7 +33,8 @@ def _deps():
 
 def _compile(src, verbose):
     obj = os.path.join(LIB_DIR, os.path.basename(src)[:-3] + ".o")
-    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    extra = os.environ.get("QCC_NVCC_EXTRA", "").split()  # e.g. -DQCC_MX_GROUP_M=8 when tuning
+    cmd = [NVCC] + FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")

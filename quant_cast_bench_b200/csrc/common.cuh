@@ -32,6 +32,14 @@ __device__ __forceinline__ uint32_t absmax2(uint32_t acc, uint32_t w)
     __nv_bfloat162 r = __hmax2(__habs2(a), __habs2(b));
     return *reinterpret_cast<uint32_t *>(&r);
 }
+// same, for an accumulator that is already non-negative
+__device__ __forceinline__ uint32_t absmax2_acc(uint32_t acc, uint32_t w)
+{
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&acc);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&w);
+    __nv_bfloat162 r = __hmax2(a, __habs2(b));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
 // max of the two halves of a non-negative bf16x2, widened to fp32 (exact)
 __device__ __forceinline__ float hmax_halves_f32(uint32_t acc)
 {
@@ -208,6 +216,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
 {

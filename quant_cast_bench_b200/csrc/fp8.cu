@@ -23,7 +23,7 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v)
 }
 
 // partial[blockIdx.x] = max |x| over this CTA's grid-stride share, as fp32 bits
-__global__ void __launch_bounds__(AMAX_THREADS) amax_partial_kernel(const uint16_t *__restrict__ x, int64_t n,
+__global__ void __launch_bounds__(AMAX_THREADS, 8) amax_partial_kernel(const uint16_t *__restrict__ x, int64_t n,
                                                                    uint32_t *__restrict__ partial)
 {
     const int64_t nvec = n >> 3;  // 16-byte chunks
@@ -34,14 +34,14 @@ __global__ void __launch_bounds__(AMAX_THREADS) amax_partial_kernel(const uint16
     for (; i + 3 * stride < nvec; i += 4 * stride) {
         uint4 a = ld_nc_v4(xv + i), b = ld_nc_v4(xv + i + stride), c = ld_nc_v4(xv + i + 2 * stride),
               d = ld_nc_v4(xv + i + 3 * stride);
-        acc0 = absmax2(absmax2(acc0, a.x), a.y); acc1 = absmax2(absmax2(acc1, a.z), a.w);
-        acc2 = absmax2(absmax2(acc2, b.x), b.y); acc3 = absmax2(absmax2(acc3, b.z), b.w);
-        acc0 = absmax2(absmax2(acc0, c.x), c.y); acc1 = absmax2(absmax2(acc1, c.z), c.w);
-        acc2 = absmax2(absmax2(acc2, d.x), d.y); acc3 = absmax2(absmax2(acc3, d.z), d.w);
+        acc0 = absmax2_acc(absmax2_acc(acc0, a.x), a.y); acc1 = absmax2_acc(absmax2_acc(acc1, a.z), a.w);
+        acc2 = absmax2_acc(absmax2_acc(acc2, b.x), b.y); acc3 = absmax2_acc(absmax2_acc(acc3, b.z), b.w);
+        acc0 = absmax2_acc(absmax2_acc(acc0, c.x), c.y); acc1 = absmax2_acc(absmax2_acc(acc1, c.z), c.w);
+        acc2 = absmax2_acc(absmax2_acc(acc2, d.x), d.y); acc3 = absmax2_acc(absmax2_acc(acc3, d.z), d.w);
     }
     for (; i < nvec; i += stride) {
         uint4 a = ld_nc_v4(xv + i);
-        acc0 = absmax2(absmax2(acc0, a.x), a.y); acc1 = absmax2(absmax2(acc1, a.z), a.w);
+        acc0 = absmax2_acc(absmax2_acc(acc0, a.x), a.y); acc1 = absmax2_acc(absmax2_acc(acc1, a.z), a.w);
     }
     uint32_t acc = absmax2(absmax2(acc0, acc1), absmax2(acc2, acc3));
     uint32_t m = f2u(hmax_halves_f32(acc));

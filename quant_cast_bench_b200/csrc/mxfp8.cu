@@ -1,17 +1,25 @@
-// mxfp8 (1x32 / 32x1 blocks, e8m0 scales, e4m3 elements) for sm_100a: one tiled kernel for the
-// rowwise, the colwise (transposed) and the fused two-direction cast.
+// mxfp8 (1x32 / 32x1 blocks, e8m0 scales, e4m3 elements) for sm_100a.
 //
-// Data movement is all TMA: a CTA owns a tile of 128 rows x (128 * G) columns of x.  The tile is
-// fetched as 64-column x 32-row boxes (cp.async.bulk.tensor, 128-byte swizzle) that complete on one
-// mbarrier per 32-row slab, so warps start as soon as their slab has landed.  Four "row" warps per
-// 128-column group quantise along the row (lane = row, four 1x32 blocks each) and four "column"
-// warps quantise down the rows (lane = four adjacent columns, one 32x1 block each).  Both write
-// their bytes into 128-byte-swizzled staging tiles in shared memory -- every shared access of a
-// quarter warp lands in eight distinct 16-byte bank groups -- and the staged tiles leave through
-// TMA stores: (32 rows x 128 B) boxes for the rowwise output and, for the transposed output, a
-// rank-3 view (m, column % 4, column / 4) of the (N, M) matrix so that one box is the 32 columns
-// {4 l + k} a warp produced with all their 128 consecutive m.  Out-of-range parts of edge tiles are
-// zero-filled on load and clipped on store by the TMA unit.
+// Two kernels:
+//
+//  * rowwise only: a flat stream.  A thread owns one 1x32 block (four 16-byte loads, two 16-byte
+//    stores, one scale byte); x, q and the plain scales are addressed by the flat block index.
+//
+//  * colwise (transposed) and the fused two-direction cast: a one-shot tile kernel, one CTA of
+//    four warps per 64-row x 128-column tile of x and five to six CTAs resident per SM, so that
+//    loads, conversion and stores of different tiles overlap the way they do in a plain streaming
+//    kernel.  The tile arrives by TMA (two 64-column x 64-row boxes, 128-byte swizzle, one
+//    mbarrier).  Two "row" warps quantise along the row (lane = row of a 32-row slab, four 1x32
+//    blocks each) and two "column" warps quantise down the rows (lane = four adjacent columns of a
+//    slab, one 32x1 block each, held in registers).  Both write their bytes into swizzled staging
+//    tiles in shared memory -- every shared access of a quarter warp lands in eight distinct
+//    16-byte bank groups -- and the staged tiles leave as coalesced 16-byte global stores, a
+//    quarter warp per 128-byte row segment of the rowwise output and four lanes per 64-byte row
+//    segment of the transposed output.  (Measured on B200: TMA stores top out near 6.0 TB/s where
+//    plain stores reach 7.2 TB/s, and a persistent one-CTA-per-SM pipeline of the same work was
+//    20 % slower than this one-shot grid.)  Out-of-range parts of edge tiles are zero-filled by
+//    the TMA load and masked on store.  The wait on the mbarrier is bounded and records an error
+//    code instead of hanging.
 //
 // Numerics: G = quant_cast_bench/quant_cast_gold/recipes.py of vkuzo/quant_cast_bench.
 // mxfp8_f G:561-568, mxfp8_dim_m_f G:656-671, mxfp8_dim_km_f G:701-719, the blocked scale layout
@@ -20,24 +28,6 @@
 #include "host_util.h"
 
 namespace qcc {
-
-constexpr int MX_THREADS = 256;
-constexpr int MX_TILE_M = 128;
-constexpr int MX_GROUP_N = 128;          // columns per warp group
-constexpr int MX_PANEL_BYTES = 128 * 128; // one 64-column panel of the tile: 128 rows x 128 B
-constexpr int MX_SLAB_BYTES = 32 * 128;   // 32 rows of a panel / of a staging tile
-
-template <int RG, int CG>
-struct MxSmem {
-    static constexpr int G = RG > CG ? RG : CG;
-    static constexpr int X_OFF = 0;
-    static constexpr int QK_OFF = X_OFF + G * 2 * MX_PANEL_BYTES;
-    static constexpr int QM_OFF = QK_OFF + RG * MX_PANEL_BYTES;
-    static constexpr int SM_OFF = QM_OFF + CG * MX_PANEL_BYTES;
-    static constexpr int BAR_OFF = SM_OFF + CG * 512;
-    static constexpr int BYTES = BAR_OFF + G * 4 * 8;
-    static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
-};
 
 // 32 fp32-scaled values of one row block -> 32 e4m3 bytes, given the four 16-byte chunks
 __device__ __forceinline__ void quant_row_block(const uint4 c[4], float rcp, uint4 &o0, uint4 &o1)
@@ -52,75 +42,180 @@ __device__ __forceinline__ void quant_row_block(const uint4 c[4], float rcp, uin
     o1.w = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].z) * rcp, bf16hi(c[3].z) * rcp, bf16lo(c[3].w) * rcp, bf16hi(c[3].w) * rcp);
 }
 
-template <int RG, int CG, bool SWZ, bool FLOOR>
-__global__ void __launch_bounds__(MX_THREADS)
-mxfp8_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_qk,
-                  const __grid_constant__ CUtensorMap tm_qm, uint8_t *__restrict__ sk, uint8_t *__restrict__ sm, int M,
-                  int N)
+__device__ __forceinline__ float amax_of_block(const uint4 c[4])
 {
-    using L = MxSmem<RG, CG>;
-    constexpr int G = L::G;
+    uint32_t a0 = absmax2(c[0].x, c[0].y), a1 = absmax2(c[0].z, c[0].w);
+#pragma unroll
+    for (int i = 1; i < 4; i++) {
+        a0 = absmax2_acc(absmax2_acc(a0, c[i].x), c[i].y);
+        a1 = absmax2_acc(absmax2_acc(a1, c[i].z), c[i].w);
+    }
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162 *>(&a0), y = *reinterpret_cast<__nv_bfloat162 *>(&a1);
+    __nv_bfloat162 m = __hmax2(x, y);
+    return hmax_halves_f32(*reinterpret_cast<uint32_t *>(&m));
+}
+
+// ---------------------------------------------------------------------------------------------
+// rowwise stream
+// ---------------------------------------------------------------------------------------------
+constexpr int RS_THREADS = 256;
+constexpr int RS_UNROLL = 2;
+
+struct FastDiv32 {
+    uint32_t mul, shift;
+    void init(uint32_t div)
+    {
+        shift = 0;
+        while ((1ull << shift) < div) shift++;
+        mul = (uint32_t)(((1ull << 32) * ((1ull << shift) - div)) / div + 1);
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return (uint32_t)(((uint64_t)__umulhi(n, mul) + n) >> shift); }
+};
+
+template <bool SWZ, bool FLOOR>
+__global__ void __launch_bounds__(RS_THREADS)
+mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
+                            uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+{
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint4 *qv = reinterpret_cast<uint4 *>(q);
+    const uint32_t base = blockIdx.x * (RS_THREADS * RS_UNROLL) + threadIdx.x;
+    uint4 c[RS_UNROLL][4];
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; u++) {
+        const uint32_t bi = base + u * RS_THREADS;
+        if (bi < nblocks) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) c[u][i] = ld_nc_v4(xv + 4 * (size_t)bi + i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) c[u][i] = make_uint4(0, 0, 0, 0);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; u++) {
+        const uint32_t bi = base + u * RS_THREADS;
+        const bool ok = bi < nblocks;
+        const uint32_t e = e8m0_from_amax<FLOOR>(amax_of_block(c[u]));
+        const float rcp = e8m0_recip<FLOOR>(e);
+        uint4 o0, o1;
+        quant_row_block(c[u], rcp, o0, o1);
+        if (ok) {
+            __stcs(qv + 2 * (size_t)bi, o0);
+            __stcs(qv + 2 * (size_t)bi + 1, o1);
+        }
+        if (!SWZ) {
+            if (ok) s[bi] = (uint8_t)e;
+        } else if ((nb & 3) == 0) {
+            // four consecutive lanes hold the four scale columns of one (row, column block): one 4-byte store
+            uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 1) << 8);
+            v |= __shfl_down_sync(0xFFFFFFFFu, v, 2) << 16;
+            if (ok && (threadIdx.x & 3) == 0) {
+                const uint32_t row = div_nb.div(bi), cb = bi - row * nb;
+                *reinterpret_cast<uint32_t *>(s + blocked_offset(row, cb, nb >> 2)) = v;
+            }
+        } else if (ok) {
+            const uint32_t row = div_nb.div(bi), cb = bi - row * nb;
+            s[blocked_offset(row, cb, (nb + 3) >> 2)] = (uint8_t)e;
+        }
+    }
+}
+
+// Zero the padding of a blocked scale grid that a stream over the real blocks does not visit: rows
+// H..ceil128(H) and scale columns W..ceil4(W).
+__global__ void blocked_zero_pad_kernel(uint8_t *__restrict__ s, uint32_t H, uint32_t W)
+{
+    const uint32_t Hp = ((H + 127) >> 7) << 7, Wp = ((W + 3) >> 2) << 2, ncb = Wp >> 2;
+    const uint64_t total = (uint64_t)Hp * Wp;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / Wp), c = (uint32_t)(i % Wp);
+        if (r >= H || c >= W) s[blocked_offset(r, c, ncb)] = 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// one-shot tile kernel: one CTA per 64-row x 128-column tile, many CTAs resident per SM
+// ---------------------------------------------------------------------------------------------
+// Tile order.  CTAs are dispatched in tile-number order and those resident at any moment work on
+// consecutive numbers, so the numbering decides which cache lines are touched together.  Tiles are
+// numbered down groups of QCC_MX_GROUP_M tile rows, column by column; with the default of 1 the
+// sweep is row-major, which measured best on B200 (the 128-byte segments of x rows and of the
+// rowwise output written at the same time are neighbours; taller groups favour the transposed
+// output instead).
+#ifndef QCC_MX_GROUP_M
+#define QCC_MX_GROUP_M 1
+#endif
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tile_m, int &tile_n)
+{
+    constexpr int GM = QCC_MX_GROUP_M;
+    const int per_group = GM * tiles_n;
+    const int g = t / per_group;
+    const int r = t - g * per_group;
+    const int h = min(GM, tiles_m - g * GM);
+    tile_n = r / h;
+    tile_m = g * GM + (r - tile_n * h);
+}
+
+constexpr int T64_ROWS = 64;
+constexpr int T64_PANEL = T64_ROWS * 128;          // one 64-column panel: 64 rows x 128 B
+
+template <bool DO_K, bool DO_M>
+struct T64 {
+    static constexpr int THREADS = 32 * ((DO_K ? 2 : 0) + (DO_M ? 2 : 0));
+    static constexpr int X_OFF = 0;
+    static constexpr int QK_OFF = 2 * T64_PANEL;                              // 64 rows x 128 B
+    static constexpr int QM_OFF = QK_OFF + (DO_K ? T64_ROWS * 128 : 0);       // 4 sub-tiles x 32 rows x 64 B
+    static constexpr int SM_OFF = QM_OFF + (DO_M ? 4 * 32 * 64 : 0);          // 128 columns x 2 scale bytes
+    static constexpr int BAR_OFF = SM_OFF + 256;
+    static constexpr int BYTES = BAR_OFF + 16;
+    static constexpr int ALLOC = BYTES + 1024;
+};
+
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
+__global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS)
+mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
+                    uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n)
+{
+    using L = T64<DO_K, DO_M>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (base - smem_u32(smem_raw)) + L::BAR_OFF);
-
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + L::BAR_OFF);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int tile_m, tile_n;
+    tile_coords((int)blockIdx.x, tiles_m, tiles_n, tile_m, tile_n);
 
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int i = 0; i < G * 4; i++) mbar_init(&bars[i], 1);
+        mbar_init(bar, 1);
         fence_barrier_init();
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-#pragma unroll
-            for (int g = 0; g < G; g++) {
-                const int col0 = (tile_n * G + g) * MX_GROUP_N;
-                if (col0 >= N) continue;
-                uint64_t *bar = &bars[g * 4 + b];
-                mbar_expect_tx(bar, 2 * MX_SLAB_BYTES);
-                uint8_t *dst = smem_raw + (base - smem_u32(smem_raw)) + L::X_OFF + g * 2 * MX_PANEL_BYTES + b * MX_SLAB_BYTES;
-                tma_load_2d(dst, &tm_x, bar, col0, tile_m * MX_TILE_M + b * 32);
-                tma_load_2d(dst + MX_PANEL_BYTES, &tm_x, bar, col0 + 64, tile_m * MX_TILE_M + b * 32);
-            }
-        }
+        mbar_expect_tx(bar, 2 * T64_PANEL);
+        tma_load_2d(sbase + L::X_OFF, &tm_x, bar, tile_n * 128, tile_m * T64_ROWS);
+        tma_load_2d(sbase + L::X_OFF + T64_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * T64_ROWS);
     }
-
-    const bool is_row = warp < 4 * RG;
-    const int role = is_row ? warp : warp - 4 * RG;
-    const int g = role >> 2, b = role & 3;
-    const int grp = tile_n * G + g;               // 128-column group index in the whole matrix
-    if (grp * MX_GROUP_N >= N) return;            // this group lies entirely right of the matrix
-    const uint32_t xs = base + L::X_OFF + g * 2 * MX_PANEL_BYTES;
-    const int nb = N >> 5, mb = M >> 5;           // scale columns of the two frames
-
-    mbar_wait(&bars[g * 4 + b], 0, 1u);
+    const bool is_row = DO_K && warp < 2;
+    const int b = warp & 1;                        // 32-row slab of this warp
+    const int nb = N >> 5, mb = M >> 5;
+    const uint32_t xs = base + L::X_OFF;
+    mbar_wait(bar, 0, 4u);
 
     if (is_row) {
         // ------------------------------------------------------------------ along the row
-        const int row_t = b * 32 + lane;          // row inside the tile
+        const int row_t = b * 32 + lane;
         const uint32_t key = lane & 7;
         const uint32_t xrow = xs + row_t * 128;
-        const uint32_t qrow = base + L::QK_OFF + g * MX_PANEL_BYTES + row_t * 128;
+        const uint32_t qrow = base + L::QK_OFF + row_t * 128;
         uint32_t sbytes = 0;
 #pragma unroll
         for (int kb = 0; kb < 4; kb++) {
-            const uint32_t prow = xrow + (kb >> 1) * MX_PANEL_BYTES;
+            const uint32_t prow = xrow + (kb >> 1) * T64_PANEL;
             const uint32_t j0 = (kb & 1) * 4;
             uint4 c[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) c[i] = lds_v4(prow + (((j0 + i) ^ key) << 4));
-            uint32_t a0 = 0, a1 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                a0 = absmax2(absmax2(a0, c[i].x), c[i].y);
-                a1 = absmax2(absmax2(a1, c[i].z), c[i].w);
-            }
-            const float amax = hmax_halves_f32(absmax2(a0, a1));
-            const uint32_t e = e8m0_from_amax<FLOOR>(amax);
+            const uint32_t e = e8m0_from_amax<FLOOR>(amax_of_block(c));
             const float rcp = e8m0_recip<FLOOR>(e);
             sbytes |= e << (8 * kb);
             uint4 o0, o1;
@@ -128,13 +223,26 @@ mxfp8_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             sts_v4(qrow + (((2 * kb) ^ key) << 4), o0);
             sts_v4(qrow + (((2 * kb + 1) ^ key) << 4), o1);
         }
-        // scales: four consecutive bytes (row, 4 * grp .. 4 * grp + 3) in either layout
-        const int R = tile_m * MX_TILE_M + row_t;
-        const int C = grp * 4;
+        __syncwarp();
+        {
+            const int j = lane & 7;
+            const int col = tile_n * 128 + j * 16;
+            const uint32_t slab = base + L::QK_OFF + b * 32 * 128;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int r = i * 4 + (lane >> 3);
+                const int R = tile_m * T64_ROWS + b * 32 + r;
+                const uint4 v = lds_v4(slab + r * 128 + ((j ^ (r & 7)) << 4));
+                if (R < M && col < N) *reinterpret_cast<uint4 *>(qk + (size_t)R * N + col) = v;
+            }
+        }
+        const int R = tile_m * T64_ROWS + row_t;
+        const int C = tile_n * 4;
         if (SWZ) {
             const uint32_t ncb = (nb + 3) >> 2;
-            const size_t off = ((size_t)tile_m * ncb + grp) * 512u + lane * 16u + b * 4u;
-            *reinterpret_cast<uint32_t *>(sk + off) = sbytes;
+            const uint32_t rr = (uint32_t)R & 127u;
+            const size_t off = ((size_t)(R >> 7) * ncb + tile_n) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u;
+            *reinterpret_cast<uint32_t *>(sk + off) = sbytes;      // padding rows carry zeros (zero-filled x)
         } else if (R < M) {
             uint8_t *dst = sk + (size_t)R * nb + C;
             if ((nb & 3) == 0) {
@@ -145,115 +253,110 @@ mxfp8_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (C + kb < nb) dst[kb] = (uint8_t)(sbytes >> (8 * kb));
             }
         }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0 && tile_m * MX_TILE_M + b * 32 < M) {
-            tma_store_2d(&tm_qk, reinterpret_cast<const void *>(smem_raw + (base - smem_u32(smem_raw)) + L::QK_OFF +
-                                                               g * MX_PANEL_BYTES + b * MX_SLAB_BYTES),
-                         grp * MX_GROUP_N, tile_m * MX_TILE_M + b * 32);
-            tma_commit();
-            tma_wait_read_all();
-        }
     } else {
         // ------------------------------------------------------------------ down the rows
-        const uint32_t pbase = xs + (lane >> 4) * MX_PANEL_BYTES + (b * 32) * 128 + (lane & 1) * 8;
+        const uint32_t pbase = xs + (lane >> 4) * T64_PANEL + (b * 32) * 128 + (lane & 1) * 8;
         const uint32_t j = (lane & 15) >> 1;
+        uint2 w[32];
         uint32_t a0 = 0, a1 = 0;
 #pragma unroll
         for (int r = 0; r < 32; r++) {
-            uint2 w = lds_v2(pbase + r * 128 + ((j ^ (r & 7)) << 4));
-            a0 = absmax2(a0, w.x);
-            a1 = absmax2(a1, w.y);
+            w[r] = lds_v2(pbase + r * 128 + ((j ^ (r & 7)) << 4));
+            a0 = absmax2_acc(a0, w[r].x);
+            a1 = absmax2_acc(a1, w[r].y);
         }
         float rcp[4];
         uint32_t e[4];
         {
             const float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                e[k] = e8m0_from_amax<FLOOR>(am[k]);
-                rcp[k] = e8m0_recip<FLOOR>(e[k]);
+            for (int kk = 0; kk < 4; kk++) {
+                e[kk] = e8m0_from_amax<FLOOR>(am[kk]);
+                rcp[kk] = e8m0_recip<FLOOR>(e[kk]);
             }
         }
-        uint32_t out[4][8];
+        // staging: sub-tile kk holds columns {4 l + kk}, one 64-byte row (the tile's 64 m) per column;
+        // 16-byte chunk c of row l sits at position c ^ ((l >> 1) & 3)
+        const uint32_t qms = base + L::QM_OFF;
+        const uint32_t key = (lane >> 1) & 3;
 #pragma unroll
-        for (int w = 0; w < 8; w++) {
-            uint2 r0 = lds_v2(pbase + (4 * w + 0) * 128 + ((j ^ ((4 * w + 0) & 7)) << 4));
-            uint2 r1 = lds_v2(pbase + (4 * w + 1) * 128 + ((j ^ ((4 * w + 1) & 7)) << 4));
-            uint2 r2 = lds_v2(pbase + (4 * w + 2) * 128 + ((j ^ ((4 * w + 2) & 7)) << 4));
-            uint2 r3 = lds_v2(pbase + (4 * w + 3) * 128 + ((j ^ ((4 * w + 3) & 7)) << 4));
-            out[0][w] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.x) * rcp[0], bf16lo(r1.x) * rcp[0], bf16lo(r2.x) * rcp[0], bf16lo(r3.x) * rcp[0]);
-            out[1][w] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.x) * rcp[1], bf16hi(r1.x) * rcp[1], bf16hi(r2.x) * rcp[1], bf16hi(r3.x) * rcp[1]);
-            out[2][w] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.y) * rcp[2], bf16lo(r1.y) * rcp[2], bf16lo(r2.y) * rcp[2], bf16lo(r3.y) * rcp[2]);
-            out[3][w] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.y) * rcp[3], bf16hi(r1.y) * rcp[3], bf16hi(r2.y) * rcp[3], bf16hi(r3.y) * rcp[3]);
-        }
-        // staging: sub-tile k holds columns {4 l + k}, one 128-byte row per column, swizzled on l
-        const uint32_t qms = base + L::QM_OFF + g * MX_PANEL_BYTES;
-        const uint32_t key = lane & 7;
+        for (int kk = 0; kk < 4; kk++) {
+            uint32_t o[8];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t rowp = qms + k * MX_SLAB_BYTES + lane * 128;
-            sts_v4(rowp + (((2 * b) ^ key) << 4), make_uint4(out[k][0], out[k][1], out[k][2], out[k][3]));
-            sts_v4(rowp + (((2 * b + 1) ^ key) << 4), make_uint4(out[k][4], out[k][5], out[k][6], out[k][7]));
+            for (int q4 = 0; q4 < 8; q4++) {
+                const uint2 r0 = w[4 * q4], r1 = w[4 * q4 + 1], r2 = w[4 * q4 + 2], r3 = w[4 * q4 + 3];
+                const float sc = rcp[kk];
+                if (kk == 0)
+                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.x) * sc, bf16lo(r1.x) * sc, bf16lo(r2.x) * sc, bf16lo(r3.x) * sc);
+                else if (kk == 1)
+                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.x) * sc, bf16hi(r1.x) * sc, bf16hi(r2.x) * sc, bf16hi(r3.x) * sc);
+                else if (kk == 2)
+                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.y) * sc, bf16lo(r1.y) * sc, bf16lo(r2.y) * sc, bf16lo(r3.y) * sc);
+                else
+                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.y) * sc, bf16hi(r1.y) * sc, bf16hi(r2.y) * sc, bf16hi(r3.y) * sc);
+            }
+            const uint32_t rowp = qms + kk * 2048 + lane * 64;
+            sts_v4(rowp + (((2 * b) ^ key) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+            sts_v4(rowp + (((2 * b + 1) ^ key) << 4), make_uint4(o[4], o[5], o[6], o[7]));
         }
-        // scale bytes of this slab into the staging block (layout = the one written to memory)
-        uint8_t *sms = smem_raw + (base - smem_u32(smem_raw)) + L::SM_OFF + g * 512;
+        uint8_t *sms = sbase + L::SM_OFF;
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int c = 4 * lane + k;
-            const int off = SWZ ? ((c & 31) * 16 + (c >> 5) * 4 + b) : (c * 4 + b);
-            sms[off] = (uint8_t)e[k];
+        for (int kk = 0; kk < 4; kk++) sms[(4 * lane + kk) * 2 + b] = (uint8_t)e[kk];
+        named_barrier(1, 64);
+        // write-out: col warp b takes sub-tiles 2b and 2b+1; four lanes move one 64-byte row segment
+        {
+            const int jj = lane & 3;
+            const int mcol = tile_m * T64_ROWS + jj * 16;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int kk = 2 * b + (i >> 2);
+                const int l = (i & 3) * 8 + (lane >> 2);
+                const int Cn = tile_n * 128 + 4 * l + kk;
+                const uint4 v = lds_v4(qms + kk * 2048 + l * 64 + ((jj ^ ((l >> 1) & 3)) << 4));
+                if (Cn < N && mcol < M) *reinterpret_cast<uint4 *>(qm + (size_t)Cn * M + mcol) = v;
+            }
         }
-        fence_proxy_async();
-        named_barrier(1 + g, 128);
-        if (lane == 0) {
-            tma_store_3d(&tm_qm, reinterpret_cast<const void *>(smem_raw + (base - smem_u32(smem_raw)) + L::QM_OFF +
-                                                               g * MX_PANEL_BYTES + b * MX_SLAB_BYTES),
-                         tile_m * MX_TILE_M, b, grp * 32);
-            tma_commit();
-        }
-        if (SWZ) {
-            // one 512-byte atom: rows = columns of x in this group, 4 scale columns = the 4 slabs
-            if (b == 0) {
+        // scales: thread (b, lane) writes the two bytes (m-blocks 2 tile_m, 2 tile_m + 1) of columns 2t, 2t+1
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int c = (b * 32 + lane) * 2 + h;
+            const int Cn = tile_n * 128 + c;
+            const uint16_t v = *reinterpret_cast<const uint16_t *>(sms + c * 2);
+            if (SWZ) {
                 const uint32_t ncb = (mb + 3) >> 2;
-                const size_t off = ((size_t)grp * ncb + tile_m) * 512u + lane * 16u;
-                *reinterpret_cast<uint4 *>(sm + off) = *reinterpret_cast<const uint4 *>(sms + lane * 16);
-            }
-        } else {
-            const int c = b * 32 + lane;            // column inside the group
-            const int Cn = grp * MX_GROUP_N + c;
-            if (Cn < N) {
-                const uint32_t v = *reinterpret_cast<const uint32_t *>(sms + c * 4);
-                uint8_t *dst = sm + (size_t)Cn * mb + tile_m * 4;
-                if ((mb & 3) == 0) {
-                    *reinterpret_cast<uint32_t *>(dst) = v;
-                } else {
-#pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
-                        if (tile_m * 4 + kk < mb) dst[kk] = (uint8_t)(v >> (8 * kk));
-                }
+                const size_t off = ((size_t)tile_n * ncb + (tile_m >> 1)) * 512u + (c & 31) * 16u + (c >> 5) * 4u + (tile_m & 1) * 2u;
+                *reinterpret_cast<uint16_t *>(sm + off) = v;       // padding columns carry zeros (zero-filled x)
+            } else if (Cn < N) {
+                uint8_t *dst = sm + (size_t)Cn * mb + tile_m * 2;
+                if (tile_m * 2 < mb) dst[0] = (uint8_t)v;
+                if (tile_m * 2 + 1 < mb) dst[1] = (uint8_t)(v >> 8);
             }
         }
-        if (lane == 0) tma_wait_read_all();
     }
 }
 
-template <int RG, int CG, bool SWZ, bool FLOOR>
-static int launch_mx(const CUtensorMap &tx, const CUtensorMap &tqk, const CUtensorMap &tqm, uint8_t *sk, uint8_t *sm,
-                     int M, int N, cudaStream_t st)
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
+static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st)
 {
-    using L = MxSmem<RG, CG>;
-    auto kern = mxfp8_tile_kernel<RG, CG, SWZ, FLOOR>;
+    using L = T64<DO_K, DO_M>;
+    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
         if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((N + L::G * MX_GROUP_N - 1) / (L::G * MX_GROUP_N)), (unsigned)((M + MX_TILE_M - 1) / MX_TILE_M));
-    kern<<<grid, MX_THREADS, L::ALLOC, st>>>(tx, tqk, tqm, sk, sm, M, N);
+    // With blocked scales the tiles must cover whole 128-row atoms so that the padding gets its zeros:
+    // a tile that lies entirely below the matrix loads zero-filled data and stores nothing but scales.
+    const int tiles_n = (N + 127) / 128;
+    const int tiles_m = SWZ ? 2 * ((M + 127) / 128) : (M + T64_ROWS - 1) / T64_ROWS;
+    const long long num_tiles = (long long)tiles_n * tiles_m;
+    if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    kern<<<(unsigned)num_tiles, L::THREADS, L::ALLOC, st>>>(tx, qk, sk, qm, sm, M, N, tiles_m, tiles_n);
     return (int)cudaGetLastError();
 }
 
@@ -274,44 +377,49 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
     if (N % 32 != 0 || (col && M % 32 != 0)) return QCC_ERR_SHAPE;
     if (!aligned16(x) || (row && !aligned16(qk)) || (col && !aligned16(qm))) return QCC_ERR_ALIGN;
     if ((row && !aligned16(sk)) || (col && !aligned16(sm))) return QCC_ERR_ALIGN;
-    if (M == 0 || N == 0) return 0;
-    if ((M + 127) / 128 > 65535) return QCC_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
-
-    CUtensorMap tx, tqk, tqm;
-    {
-        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
-        uint64_t strides[1] = {(uint64_t)N * 2};
-        uint32_t box[2] = {64, 32};
-        int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (e) return e;
-    }
-    tqk = tx;
-    tqm = tx;
-    if (row) {
-        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
-        uint64_t strides[1] = {(uint64_t)N};
-        uint32_t box[2] = {128, 32};
-        int e = make_tensor_map(&tqk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, qk, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (e) return e;
-    }
-    if (col) {
-        // (N, M) bytes seen as (column / 4, column % 4, m): a box is 32 columns of equal residue
-        uint64_t dims[3] = {(uint64_t)M, 4, (uint64_t)N / 4};
-        uint64_t strides[2] = {(uint64_t)M, (uint64_t)M * 4};
-        uint32_t box[3] = {128, 1, 32};
-        int e = make_tensor_map(&tqm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, qm, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (e) return e;
-    }
     const bool swz = flags & QCC_SWIZZLE, fl = flags & QCC_FLOOR;
     uint8_t *skp = (uint8_t *)sk, *smp = (uint8_t *)sm;
-#define QCC_MX(RG, CG)                                                                                         \
-    (swz ? (fl ? launch_mx<RG, CG, true, true>(tx, tqk, tqm, skp, smp, (int)M, (int)N, st)                     \
-               : launch_mx<RG, CG, true, false>(tx, tqk, tqm, skp, smp, (int)M, (int)N, st))                   \
-         : (fl ? launch_mx<RG, CG, false, true>(tx, tqk, tqm, skp, smp, (int)M, (int)N, st)                    \
-               : launch_mx<RG, CG, false, false>(tx, tqk, tqm, skp, smp, (int)M, (int)N, st)))
-    if (row && col) return QCC_MX(1, 1);
-    if (row) return QCC_MX(2, 0);
-    return QCC_MX(0, 2);
-#undef QCC_MX
+
+    if (!col) {
+        const int64_t nb = N / 32;
+        if (M * nb >= (1ll << 32) - 2 * RS_THREADS * RS_UNROLL) return QCC_ERR_SHAPE;
+        const uint32_t nblocks = (uint32_t)(M * nb);
+        FastDiv32 dv;
+        dv.init((uint32_t)nb);
+        if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
+            blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(skp, (uint32_t)M, (uint32_t)nb);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return (int)e;
+        }
+        const unsigned grid = (nblocks + RS_THREADS * RS_UNROLL - 1) / (RS_THREADS * RS_UNROLL);
+        const uint16_t *xp = (const uint16_t *)x;
+        uint8_t *qp = (uint8_t *)qk;
+        if (swz) {
+            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+        } else {
+            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+        }
+        return (int)cudaGetLastError();
+    }
+
+    uint8_t *qkp = (uint8_t *)qk, *qmp = (uint8_t *)qm;
+    {
+        CUtensorMap t64;
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        uint64_t strides[1] = {(uint64_t)N * 2};
+        uint32_t box[2] = {64, 64};
+        int e = make_tensor_map(&t64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (e) return e;
+#define QCC_T64(DO_K)                                                                                        \
+    (swz ? (fl ? launch_t64<DO_K, true, true, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)             \
+               : launch_t64<DO_K, true, true, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st))           \
+         : (fl ? launch_t64<DO_K, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)            \
+               : launch_t64<DO_K, true, false, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)))
+        if (row) return QCC_T64(true);
+        return QCC_T64(false);
+#undef QCC_T64
+    }
 }
