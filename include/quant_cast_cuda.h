@@ -51,6 +51,7 @@ extern "C" {
 #define QCC_ERR_ARG -3       /* NULL pointer, unknown format or flag combination     */
 #define QCC_ERR_WORKSPACE -4 /* scratch buffer too small                             */
 #define QCC_ERR_DRIVER -5    /* the CUDA driver entry point for tensor maps is missing */
+#define QCC_ERR_TOO_LARGE -6 /* the input exceeds what a fixed-size built-in buffer supports */
 
 /* Library version (major * 100 + minor). */
 int qcc_version(void);
@@ -77,6 +78,32 @@ size_t qcc_amax_workspace_bytes(void);
  */
 int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace,
                   size_t workspace_bytes, void *stream);
+
+/*
+ * Same result as qcc_amax_bf16, for callers that cannot hand over scratch memory.
+ * (No counterpart in the reference; an addition of this library.)
+ *
+ * Some hosts of these kernels are not allowed to allocate device memory at the point where they
+ * need the amax: code running inside a region that forbids cudaMalloc (a pre-sized memory pool that
+ * is already exhausted or frozen, a real-time or interrupt-like path, a plugin that only receives
+ * its input and output buffers from the framework that calls it).  For them the per-CTA partial
+ * maxima go into an 8 KB buffer that is part of the library image, so the call needs nothing but
+ * x and out.  Nothing here calls cudaMalloc, cudaFree or any allocating routine.
+ *
+ * Limits and rules:
+ *  - n may be at most QCC_AMAX_NOALLOC_MAX_ELEMS (2^32 bf16 values, 8 GiB); larger inputs are
+ *    rejected with QCC_ERR_TOO_LARGE and nothing is launched.
+ *  - Every GPU that loads the library holds the 8 KB until the process exits.
+ *  - The first call on each device looks the buffer's device address up (cudaGetSymbolAddress with
+ *    that device current); make that first call outside of any stream capture.
+ *  - All calls on one device share the buffer.  Two calls whose kernels may run at the same time
+ *    (different streams, or different host threads on different streams) race on it and can return
+ *    a wrong amax; serialise them on one stream or use qcc_amax_bf16 with separate workspaces.
+ *    The buffer keeps the last call's partial maxima; each call overwrites every slot it reads, so
+ *    no clearing is needed between calls.
+ */
+#define QCC_AMAX_NOALLOC_MAX_ELEMS (1ll << 32)
+int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *out, void *stream);
 
 /* out[0] = f(amax[0]) for an amax that is already reduced (e.g. after an all-reduce over shards);
  * same `mode` / `fmt` as above.  One tiny launch. */

@@ -59,6 +59,10 @@ __global__ void __launch_bounds__(AMAX_THREADS, 8) amax_partial_kernel(const uin
     }
 }
 
+// Built-in scratch of qcc_amax_bf16_noalloc: the per-CTA partial maxima of one call.  It lives in
+// the library image, so every GPU that loads the library keeps these 8 KB until the process exits.
+static __device__ __align__(256) uint32_t g_amax_noalloc_scratch[AMAX_MAX_CTAS];
+
 __device__ __forceinline__ float amax_finish(float amax, int mode, int fmt)
 {
     if (mode == QCC_AMAX_FP8_SCALE)
@@ -322,6 +326,39 @@ int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>((const uint32_t *)workspace, grid, mode, fmt, out);
+    return (int)cudaGetLastError();
+}
+
+int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *out, void *stream)
+{
+    if (!x || !out || n < 0) return QCC_ERR_ARG;
+    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
+        return QCC_ERR_ARG;
+    if (!aligned16(x)) return QCC_ERR_ALIGN;
+    if (n > QCC_AMAX_NOALLOC_MAX_ELEMS) return QCC_ERR_TOO_LARGE;
+    // In host code the array's name is only a handle: the device address has to be asked for, once per
+    // device, with that device current.  The first call on a device does it here.
+    static uint32_t *scratch[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return QCC_ERR_ARG;
+    if (!scratch[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_amax_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        scratch[dev] = static_cast<uint32_t *>(p);
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int64_t want = ((n >> 3) + AMAX_THREADS * 4 - 1) / (AMAX_THREADS * 4);
+    int64_t cap = (int64_t)sm_count() * 8;
+    if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
+    int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    // every slot the finish reads is written by this launch, so nothing has to be cleared
+    amax_partial_kernel<<<grid, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, scratch[dev]);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>(scratch[dev], grid, mode, fmt, out);
     return (int)cudaGetLastError();
 }
 

@@ -19,6 +19,7 @@ ERRORS = {
     -3: "argument: missing tensor, unknown format or flag combination",
     -4: "workspace too small",
     -5: "the CUDA driver does not provide cuTensorMapEncodeTiled",
+    -6: "input too large for the library's built-in fixed-size buffer",
 }
 
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -28,6 +29,7 @@ SIGNATURES = {
     "qcc_sm_count": (_int, []),
     "qcc_amax_workspace_bytes": (_sz, []),
     "qcc_amax_bf16": (_int, [_vp, _i64, _int, _int, _vp, _vp, _sz, _vp]),
+    "qcc_amax_bf16_noalloc": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
     "qcc_scale_from_amax": (_int, [_vp, _int, _int, _vp, _vp]),
     "qcc_fp8_tensorwise": (_int, [_vp, _i64, _vp, _int, _vp, _vp]),
     "qcc_fp8_rowwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
