@@ -287,6 +287,14 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void *p)
                  : "l"(p));
     return r;
 }
+// 16-byte load that allocates in L1: for threads that read several neighbouring 16-byte pieces of the
+// same sectors with separate instructions (measured +9 % on the 64-bytes-per-thread streams)
+__device__ __forceinline__ uint4 ld_v4(const void *p)
+{
+    uint4 r;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr)
 {
     uint4 r;

@@ -86,7 +86,7 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
         const uint32_t bi = base + u * RS_THREADS;
         if (bi < nblocks) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) c[u][i] = ld_nc_v4(xv + 4 * (size_t)bi + i);
+            for (int i = 0; i < 4; i++) c[u][i] = ld_v4(xv + 4 * (size_t)bi + i);
         } else {
 #pragma unroll
             for (int i = 0; i < 4; i++) c[u][i] = make_uint4(0, 0, 0, 0);
@@ -162,6 +162,7 @@ constexpr int T64_PANEL = T64_ROWS * 128;          // one 64-column panel: 64 ro
 template <bool DO_K, bool DO_M>
 struct T64 {
     static constexpr int THREADS = 32 * ((DO_K ? 2 : 0) + (DO_M ? 2 : 0));
+    static constexpr int MIN_CTAS = DO_K ? 6 : 8;                             // register cap: measured best on B200
     static constexpr int X_OFF = 0;
     static constexpr int QK_OFF = 2 * T64_PANEL;                              // 64 rows x 128 B
     static constexpr int QM_OFF = QK_OFF + (DO_K ? T64_ROWS * 128 : 0);       // 4 sub-tiles x 32 rows x 64 B
@@ -172,7 +173,7 @@ struct T64 {
 };
 
 template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
-__global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS)
+__global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS, T64<DO_K, DO_M>::MIN_CTAS)
 mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
                     uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n)
 {

@@ -85,20 +85,37 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
 #pragma unroll
     for (int u = 0; u < NV_UNROLL; u++) {
         const uint32_t bi = base + u * NV_THREADS;
-        if (bi < nblocks) { a[u] = ld_nc_v4(xv + 2 * (size_t)bi); b[u] = ld_nc_v4(xv + 2 * (size_t)bi + 1); }
+        if (bi < nblocks) {
+            a[u] = ld_v4(xv + 2 * (size_t)bi);
+            b[u] = ld_v4(xv + 2 * (size_t)bi + 1);
+        } else {
+            a[u] = b[u] = make_uint4(0, 0, 0, 0);
+        }
     }
+    // every lane runs the whole body (the shuffles below need the full warp); stores are predicated
 #pragma unroll
     for (int u = 0; u < NV_UNROLL; u++) {
         const uint32_t bi = base + u * NV_THREADS;
-        if (bi >= nblocks) continue;
+        const bool ok = bi < nblocks;
         uint32_t row = 0, cb = 0;
-        if (SWZ || PER_ROW) { row = div_nb.div(bi); cb = bi - row * nb; }
+        if (SWZ || PER_ROW) { row = div_nb.div(ok ? bi : 0u); cb = (ok ? bi : 0u) - row * nb; }
         float o = o_all, inv = inv_all;
         if (PER_ROW) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
         uint2 packed;
         const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, (uint64_t)bi * 16u, seed, offset, packed);
-        __stcs(qv + bi, packed);
-        s[SWZ ? blocked_offset(row, cb, (nb + 3) >> 2) : (size_t)bi] = (uint8_t)byte;
+        if (ok) __stcs(qv + bi, packed);
+        if (SWZ) {
+            // four consecutive lanes hold the four scale columns of one (row, column block)
+            uint32_t v = byte | (__shfl_down_sync(0xFFFFFFFFu, byte, 1) << 8);
+            v |= __shfl_down_sync(0xFFFFFFFFu, v, 2) << 16;
+            if ((nb & 3) == 0) {
+                if (ok && (threadIdx.x & 3) == 0) *reinterpret_cast<uint32_t *>(s + blocked_offset(row, cb, nb >> 2)) = v;
+            } else if (ok) {
+                s[blocked_offset(row, cb, (nb + 3) >> 2)] = (uint8_t)byte;
+            }
+        } else if (ok) {
+            s[bi] = (uint8_t)byte;
+        }
     }
 }
 
