@@ -7,6 +7,10 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#ifndef QCC_AMAX_LD
+#define QCC_AMAX_LD ld_nc_v4
+#endif
+
 namespace qcc {
 
 // ---------------------------------------------------------------------------------------------
@@ -22,25 +26,36 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v)
     return v;
 }
 
+#ifndef QCC_AMAX_U
+#define QCC_AMAX_U 8
+#endif
+#ifndef QCC_AMAX_CTAS
+#define QCC_AMAX_CTAS 6
+#endif
+constexpr int AMAX_U = QCC_AMAX_U;            // 16-byte loads in flight per thread
+constexpr int AMAX_CTAS_PER_SM = QCC_AMAX_CTAS;
+
 // partial[blockIdx.x] = max |x| over this CTA's grid-stride share, as fp32 bits
-__global__ void __launch_bounds__(AMAX_THREADS, 8) amax_partial_kernel(const uint16_t *__restrict__ x, int64_t n,
-                                                                   uint32_t *__restrict__ partial)
+__global__ void __launch_bounds__(AMAX_THREADS, AMAX_CTAS_PER_SM) amax_partial_kernel(const uint16_t *__restrict__ x, int64_t n,
+                                                                                   uint32_t *__restrict__ partial)
 {
     const int64_t nvec = n >> 3;  // 16-byte chunks
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint32_t acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
     const int64_t stride = (int64_t)gridDim.x * AMAX_THREADS;
     int64_t i = (int64_t)blockIdx.x * AMAX_THREADS + threadIdx.x;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        uint4 a = ld_nc_v4(xv + i), b = ld_nc_v4(xv + i + stride), c = ld_nc_v4(xv + i + 2 * stride),
-              d = ld_nc_v4(xv + i + 3 * stride);
-        acc0 = absmax2_acc(absmax2_acc(acc0, a.x), a.y); acc1 = absmax2_acc(absmax2_acc(acc1, a.z), a.w);
-        acc2 = absmax2_acc(absmax2_acc(acc2, b.x), b.y); acc3 = absmax2_acc(absmax2_acc(acc3, b.z), b.w);
-        acc0 = absmax2_acc(absmax2_acc(acc0, c.x), c.y); acc1 = absmax2_acc(absmax2_acc(acc1, c.z), c.w);
-        acc2 = absmax2_acc(absmax2_acc(acc2, d.x), d.y); acc3 = absmax2_acc(absmax2_acc(acc3, d.z), d.w);
+    for (; i + (AMAX_U - 1) * stride < nvec; i += AMAX_U * stride) {
+        uint4 v[AMAX_U];
+#pragma unroll
+        for (int u = 0; u < AMAX_U; u++) v[u] = QCC_AMAX_LD(xv + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < AMAX_U; u += 2) {
+            acc0 = absmax2_acc(absmax2_acc(acc0, v[u].x), v[u].y); acc1 = absmax2_acc(absmax2_acc(acc1, v[u].z), v[u].w);
+            acc2 = absmax2_acc(absmax2_acc(acc2, v[u + 1].x), v[u + 1].y); acc3 = absmax2_acc(absmax2_acc(acc3, v[u + 1].z), v[u + 1].w);
+        }
     }
     for (; i < nvec; i += stride) {
-        uint4 a = ld_nc_v4(xv + i);
+        uint4 a = QCC_AMAX_LD(xv + i);
         acc0 = absmax2_acc(absmax2_acc(acc0, a.x), a.y); acc1 = absmax2_acc(absmax2_acc(acc1, a.z), a.w);
     }
     uint32_t acc = absmax2(absmax2(acc0, acc1), absmax2(acc2, acc3));
@@ -318,8 +333,8 @@ int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void 
     if (!aligned16(x)) return QCC_ERR_ALIGN;
     if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
-    int64_t want = ((n >> 3) + AMAX_THREADS * 4 - 1) / (AMAX_THREADS * 4);
-    int64_t cap = (int64_t)sm_count() * 8;
+    int64_t want = ((n >> 3) + AMAX_THREADS * AMAX_U - 1) / (AMAX_THREADS * AMAX_U);
+    int64_t cap = (int64_t)sm_count() * AMAX_CTAS_PER_SM;
     if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
     int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
     amax_partial_kernel<<<grid, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, (uint32_t *)workspace);
@@ -350,8 +365,8 @@ int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *ou
         scratch[dev] = static_cast<uint32_t *>(p);
     }
     cudaStream_t st = (cudaStream_t)stream;
-    int64_t want = ((n >> 3) + AMAX_THREADS * 4 - 1) / (AMAX_THREADS * 4);
-    int64_t cap = (int64_t)sm_count() * 8;
+    int64_t want = ((n >> 3) + AMAX_THREADS * AMAX_U - 1) / (AMAX_THREADS * AMAX_U);
+    int64_t cap = (int64_t)sm_count() * AMAX_CTAS_PER_SM;
     if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
     int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
     // every slot the finish reads is written by this launch, so nothing has to be cleared

@@ -4,11 +4,12 @@
 //  * rowwise: a flat stream -- a thread owns one 16-element block (two 16-byte loads, one 8-byte
 //    store of packed nibbles, one scale byte); x, q and the plain scales are addressed by the flat
 //    block index, only the blocked scale layout and per-row outer scales need (row, column).
-//  * transposed: a TMA tile kernel.  A CTA owns 256 rows x 128 columns of x, fetched as 64-column x
-//    32-row boxes with 128-byte swizzle, one mbarrier per 32-row slab.  Warp b quantises slab b down
-//    the rows (lane = four adjacent columns, two 16x1 blocks each) and writes 16 packed bytes per
-//    column into a swizzled staging tile whose rows are output rows; the tile leaves through rank-3
-//    TMA stores over the (column / 4, column % 4, m / 2) view of the (N, M/2) output.
+//  * transposed: a one-shot tile kernel like the mxfp8 one.  A CTA of four warps owns 128 rows x 128
+//    columns of x, fetched by TMA (two 64-column x 128-row boxes, 128-byte swizzle, one mbarrier with
+//    a bounded wait); five CTAs are resident per SM.  Warp b quantises the 32-row slab b down the rows
+//    (lane = four adjacent columns, two 16x1 blocks each) and writes 16 packed bytes per column into
+//    a swizzled staging tile whose rows are output rows; the tile leaves as coalesced 16-byte stores,
+//    four lanes per 64-byte row segment, and the block scales as whole 512-byte atoms.
 //
 // Numerics: G = quant_cast_bench/quant_cast_gold/recipes.py, GU = quant_cast_gold/utils.py of
 // vkuzo/quant_cast_bench.  nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266,
@@ -132,53 +133,49 @@ __global__ void nvfp4_zero_pad_kernel(uint8_t *__restrict__ s, uint32_t M, uint3
 }
 
 // ---------------------------------------------------------------------------------------------
-// transposed cast: TMA tile kernel
+// transposed cast: one-shot tile kernel
 // ---------------------------------------------------------------------------------------------
-constexpr int NVT_TILE_M = 256;
-constexpr int NVT_PANEL_BYTES = NVT_TILE_M * 128;  // one 64-column panel: 256 rows x 128 B
-constexpr int NVT_SLAB_BYTES = 32 * 128;
+constexpr int NVT_TILE_M = 128;
+constexpr int NVT_PANEL_BYTES = NVT_TILE_M * 128;  // one 64-column panel: 128 rows x 128 B
 constexpr int NVT_X_OFF = 0;
-constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 rows x 128 B
-constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * NVT_SLAB_BYTES;  // 128 columns x 16 block scales
-constexpr int NVT_BAR_OFF = NVT_S_OFF + 2048;
-constexpr int NVT_BYTES = NVT_BAR_OFF + 8 * 8;
+constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 rows x 64 B
+constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * 32 * 64; // 128 columns x 8 block scales
+constexpr int NVT_BAR_OFF = NVT_S_OFF + 1024;
+constexpr int NVT_BYTES = NVT_BAR_OFF + 16;
 constexpr int NVT_ALLOC = NVT_BYTES + 1024;
 
+// row-major tile order (column tiles fastest), as in the mxfp8 tile kernel
 template <bool SWZ, bool SR>
-__global__ void __launch_bounds__(256)
-nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_q,
-                        const float *__restrict__ outer_p, const uint64_t *__restrict__ key, uint8_t *__restrict__ s, int M,
-                        int N)
+__global__ void __launch_bounds__(128, 5)
+nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *__restrict__ outer_p,
+                        const uint64_t *__restrict__ key, uint8_t *__restrict__ q, uint8_t *__restrict__ s, int M, int N,
+                        int tiles_n)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sbase + NVT_BAR_OFF);
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
-    const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + NVT_BAR_OFF);
+    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
+    const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;   // warp b owns the 32-row slab b
 
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+        mbar_init(bar, 1);
         fence_barrier_init();
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            mbar_expect_tx(&bars[i], 2 * NVT_SLAB_BYTES);
-            uint8_t *dst = sbase + NVT_X_OFF + i * NVT_SLAB_BYTES;
-            tma_load_2d(dst, &tm_x, &bars[i], tile_n * 128, tile_m * NVT_TILE_M + i * 32);
-            tma_load_2d(dst + NVT_PANEL_BYTES, &tm_x, &bars[i], tile_n * 128 + 64, tile_m * NVT_TILE_M + i * 32);
-        }
+        mbar_expect_tx(bar, 2 * NVT_PANEL_BYTES);
+        tma_load_2d(sbase + NVT_X_OFF, &tm_x, bar, tile_n * 128, tile_m * NVT_TILE_M);
+        tma_load_2d(sbase + NVT_X_OFF + NVT_PANEL_BYTES, &tm_x, bar, tile_n * 128 + 64, tile_m * NVT_TILE_M);
     }
     const float outer = __ldg(outer_p);
     const float inv_outer = __fdiv_rn(1.0f, outer);
     uint64_t seed = 0, offset = 0;
     if (SR) { seed = key[0]; offset = key[1]; }
-    const int mb16 = M >> 4;  // scale columns of the transposed frame
+    const int mb16 = M >> 4;   // scale columns of the transposed frame
+    const int halfM = M >> 1;  // bytes per output row
 
-    mbar_wait(&bars[b], 0, 2u);
+    mbar_wait(bar, 0, 2u);
 
     const uint32_t pbase = base + NVT_X_OFF + (lane >> 4) * NVT_PANEL_BYTES + (b * 32) * 128 + (lane & 1) * 8;
     const uint32_t j = (lane & 15) >> 1;
@@ -192,8 +189,8 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
         for (int r = 0; r < 16; r++) {
             const int rr = 16 * h + r;
             w[r] = lds_v2(pbase + rr * 128 + ((j ^ (rr & 7)) << 4));
-            a0 = absmax2(a0, w[r].x);
-            a1 = absmax2(a1, w[r].y);
+            a0 = absmax2_acc(a0, w[r].x);
+            a1 = absmax2_acc(a1, w[r].y);
         }
         const float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
 #pragma unroll
@@ -226,10 +223,12 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             if (h == 0) { outw[k].x = p0; outw[k].y = p1; } else { outw[k].z = p0; outw[k].w = p1; }
         }
     }
-    const uint32_t key7 = lane & 7;
+    // staging: sub-tile k holds columns {4 l + k}, one 64-byte row (the tile's 128 m, two per byte) per
+    // column; 16-byte chunk c of row l sits at position c ^ ((l >> 1) & 3).  Slab b is chunk b.
+    const uint32_t qs = base + NVT_Q_OFF;
+    const uint32_t key4 = (lane >> 1) & 3;
 #pragma unroll
-    for (int k = 0; k < 4; k++)
-        sts_v4(base + NVT_Q_OFF + k * NVT_SLAB_BYTES + lane * 128 + ((b ^ key7) << 4), outw[k]);
+    for (int k = 0; k < 4; k++) sts_v4(qs + k * 2048 + lane * 64 + ((b ^ key4) << 4), outw[k]);
     // block scales of this slab -> staging, zero outside the matrix
     uint8_t *ss = sbase + NVT_S_OFF;
 #pragma unroll
@@ -238,44 +237,50 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
         const bool col_ok = tile_n * 128 + c < N;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int blk = 2 * b + h;                       // 0..15 inside the tile
-            const bool ok = col_ok && (tile_m * 16 + blk < mb16);
-            const int off = SWZ ? ((blk >> 2) * 512 + (c & 31) * 16 + (c >> 5) * 4 + (blk & 3)) : (c * 16 + blk);
+            const int blk = 2 * b + h;                       // 0..7 inside the tile
+            const bool ok = col_ok && (tile_m * 8 + blk < mb16);
+            const int off = SWZ ? ((blk >> 2) * 512 + (c & 31) * 16 + (c >> 5) * 4 + (blk & 3)) : (c * 8 + blk);
             ss[off] = ok ? (uint8_t)sc[k][h] : (uint8_t)0;
         }
     }
-    fence_proxy_async();
     __syncthreads();
-    if (b < 4 && lane == 0) {
-        tma_store_3d(&tm_q, sbase + NVT_Q_OFF + b * NVT_SLAB_BYTES, tile_m * (NVT_TILE_M / 2), b, tile_n * 32);
-        tma_commit();
+    // write-out: warp b takes sub-tile b; four lanes move one 64-byte row segment
+    {
+        const int jj = lane & 3;
+        const int mbyte = tile_m * (NVT_TILE_M / 2) + jj * 16;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int l = i * 8 + (lane >> 2);
+            const int Cn = tile_n * 128 + 4 * l + b;
+            const uint4 v = lds_v4(qs + b * 2048 + l * 64 + ((jj ^ ((l >> 1) & 3)) << 4));
+            if (Cn < N && mbyte < halfM) *reinterpret_cast<uint4 *>(q + (size_t)Cn * halfM + mbyte) = v;
+        }
     }
-    if (threadIdx.x < 128) {
-        const int t = threadIdx.x;
-        const uint4 v = *reinterpret_cast<const uint4 *>(ss + t * 16);
-        if (SWZ) {
-            // four consecutive 512-byte atoms (row block = tile_n, column blocks 4 tile_m .. 4 tile_m + 3)
+    if (SWZ) {
+        // two consecutive 512-byte atoms (row block = tile_n, column blocks 2 tile_m and 2 tile_m + 1)
+        if (threadIdx.x < 64) {
+            const int t = threadIdx.x;
             const uint32_t ncb = (mb16 + 3) >> 2;
             const uint32_t atom = t >> 5;
-            if ((uint32_t)tile_m * 4 + atom < ncb) {
-                const size_t off = ((size_t)tile_n * ncb + tile_m * 4 + atom) * 512u + (t & 31) * 16u;
-                *reinterpret_cast<uint4 *>(s + off) = v;
+            if ((uint32_t)tile_m * 2 + atom < ncb) {
+                const size_t off = ((size_t)tile_n * ncb + tile_m * 2 + atom) * 512u + (t & 31) * 16u;
+                *reinterpret_cast<uint4 *>(s + off) = *reinterpret_cast<const uint4 *>(ss + t * 16);
             }
-        } else {
-            const int Cn = tile_n * 128 + t;
-            if (Cn < N) {
-                uint8_t *dst = s + (size_t)Cn * mb16 + tile_m * 16;
-                if ((mb16 & 15) == 0) {
-                    *reinterpret_cast<uint4 *>(dst) = v;
-                } else {
-                    const uint8_t *src = ss + t * 16;
-                    for (int kk = 0; kk < 16; kk++)
-                        if (tile_m * 16 + kk < mb16) dst[kk] = src[kk];
-                }
+        }
+    } else {
+        const int t = threadIdx.x;
+        const int Cn = tile_n * 128 + t;
+        if (Cn < N) {
+            uint8_t *dst = s + (size_t)Cn * mb16 + tile_m * 8;
+            if ((mb16 & 7) == 0) {
+                *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(ss + t * 8);
+            } else {
+                const uint8_t *src = ss + t * 8;
+                for (int kk = 0; kk < 8; kk++)
+                    if (tile_m * 8 + kk < mb16) dst[kk] = src[kk];
             }
         }
     }
-    if (b < 4 && lane == 0) tma_wait_read_all();
 }
 
 }  // namespace qcc
@@ -322,8 +327,8 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
 }
 
 template <bool SWZ, bool SR>
-static int launch_nvt(const CUtensorMap &tx, const CUtensorMap &tq, const float *outer, const uint64_t *key, uint8_t *s,
-                      int M, int N, cudaStream_t st)
+static int launch_nvt(const CUtensorMap &tx, const float *outer, const uint64_t *key, uint8_t *q, uint8_t *s, int M, int N,
+                      cudaStream_t st)
 {
     auto kern = nvfp4_transposed_kernel<SWZ, SR>;
     static bool configured[64] = {false};
@@ -332,10 +337,14 @@ static int launch_nvt(const CUtensorMap &tx, const CUtensorMap &tq, const float 
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, NVT_ALLOC);
         if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + NVT_TILE_M - 1) / NVT_TILE_M));
-    kern<<<grid, 256, NVT_ALLOC, st>>>(tx, tq, outer, key, s, M, N);
+    const int tiles_n = (N + 127) / 128, tiles_m = (M + NVT_TILE_M - 1) / NVT_TILE_M;
+    const long long num_tiles = (long long)tiles_n * tiles_m;
+    if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    kern<<<(unsigned)num_tiles, 128, NVT_ALLOC, st>>>(tx, outer, key, q, s, M, N, tiles_n);
     return (int)cudaGetLastError();
 }
 
@@ -346,34 +355,22 @@ extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const f
     if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
-    // M / 2 bytes per output row must be a multiple of 16 for the TMA store: M % 32 == 0
+    // output rows of M / 2 bytes are written in 16-byte pieces: M % 32 == 0; the TMA load needs N % 8 == 0
     if (M % 32 != 0 || N % 8 != 0) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
-    if (M == 0 || N == 0) return 0;
-    if ((M + NVT_TILE_M - 1) / NVT_TILE_M > 65535) return QCC_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
-    CUtensorMap tx, tq;
+    CUtensorMap tx;
     {
         uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
         uint64_t strides[1] = {(uint64_t)N * 2};
-        uint32_t box[2] = {64, 32};
+        uint32_t box[2] = {64, 128};
         int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (e) return e;
     }
-    {
-        // (N, M/2) bytes seen as (column / 4, column % 4, byte): a box is 32 columns of equal residue
-        uint64_t dims[3] = {(uint64_t)M / 2, 4, ((uint64_t)N + 3) / 4};
-        uint64_t strides[2] = {(uint64_t)M / 2, (uint64_t)M * 2};
-        uint32_t box[3] = {128, 1, 32};
-        if (N % 4 != 0) return QCC_ERR_SHAPE;
-        dims[2] = (uint64_t)N / 4;
-        int e = make_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (e) return e;
-    }
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR;
-    uint8_t *sp = (uint8_t *)s;
-    if (swz) return sr ? launch_nvt<true, true>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st)
-                       : launch_nvt<true, false>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st);
-    return sr ? launch_nvt<false, true>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st)
-              : launch_nvt<false, false>(tx, tq, outer, philox_key, sp, (int)M, (int)N, st);
+    uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
+    if (swz) return sr ? launch_nvt<true, true>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st)
+                       : launch_nvt<true, false>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st);
+    return sr ? launch_nvt<false, true>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st)
+              : launch_nvt<false, false>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st);
 }
