@@ -150,6 +150,7 @@ def run_reference(args):
     import torch
     from oracle import gold_port as O
     from quant_cast_bench_b200.workloads import make_input
+    O.set_num_threads(os.cpu_count() or 1)
     rows = 4096  # bounded sample: a quarter of the 16384-row workload per step
     x = make_input(rows, N_STEP, seed=0)
     nbytes = algorithmic_bytes(rows, N_STEP, "mxfp8_dim_km")
@@ -202,6 +203,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     from quant_cast_bench_b200 import quant_cast_cuda as Q
@@ -289,7 +292,7 @@ def run_ours(args):
                    "l2": "inputs (512 MiB) and outputs (528 MiB) exceed the 126 MB L2; no flush between iterations",
                    "vs_baseline_ref": "reference CuTe kernel on B200, 4987.5 GB/s (benchmarks/bench_results.csv:34)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "mxfp8_tile_kernel<1,1,swizzle,rceil>",
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "mxfp8_tile64_kernel<dim_k+dim_m,swizzle,rceil>",
                      "launch_ms_avg": k_avg, "launch_ms_min": k_min, "frac_of_8TBps": achieved / 8000.0},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -306,6 +309,7 @@ def cpu_baseline():
     import torch
     from oracle import gold_port as O
     from quant_cast_bench_b200.workloads import make_input
+    O.set_num_threads(os.cpu_count() or 1)
     rows = 4096
     x = make_input(rows, N_STEP, seed=0)
     cpu_reference_step(x)

@@ -63,6 +63,13 @@ int qcc_device_error(unsigned int *out);
 /* Number of SMs of the current device (cached per device). */
 int qcc_sm_count(void);
 
+/* Strided copy between (pinned) host memory and the device on `stream`: `rows` rows of `width_bytes`
+ * bytes, row starts `dst_pitch` / `src_pitch` bytes apart; to_host != 0 copies device -> host, else
+ * host -> device.  Used by the host-buffer casters to place the transposed outputs of a row chunk into
+ * the columns of the full host matrix (no counterpart in the reference, which keeps data on the GPU). */
+int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
+                     size_t rows, int to_host, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * amax and per-tensor scales
  * ------------------------------------------------------------------------------------------- */

@@ -43,6 +43,10 @@ def num_threads() -> int:
     return lib().qco_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    lib().qco_set_num_threads(int(n))
+
+
 def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 

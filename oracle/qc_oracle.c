@@ -549,6 +549,16 @@ int qco_nvfp4_t(const uint16_t *x, int64_t M, int64_t N, const float *outer, int
     return 0;
 }
 
+/* torchrun exports OMP_NUM_THREADS=1; the CPU baseline asks for all host threads explicitly */
+void qco_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int qco_num_threads(void)
 {
     int n = 1;

@@ -322,6 +322,15 @@ int qcc_device_error(unsigned int *out)
 
 int qcc_sm_count(void) { return sm_count(); }
 
+int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                     int to_host, void *stream)
+{
+    if (!dst || !src) return QCC_ERR_ARG;
+    if (width_bytes == 0 || rows == 0) return 0;
+    return (int)cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                  to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice, (cudaStream_t)stream);
+}
+
 size_t qcc_amax_workspace_bytes(void) { return (size_t)AMAX_MAX_CTAS * sizeof(uint32_t); }
 
 int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace, size_t workspace_bytes,

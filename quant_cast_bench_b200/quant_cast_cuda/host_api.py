@@ -1,8 +1,12 @@
 """Host-buffer entry to the mxfp8 two-direction cast: pinned host bf16 in, pinned host outputs back.
 
-This is the call a user with data in host memory makes; it owns the device staging buffers and the
-pinned output buffers, so repeated casts allocate nothing.  Each cast copies x to the device,
-launches the CUDA cast and copies the four outputs back; it returns after the outputs are complete.
+This is the call a user with data in host memory makes.  The caster owns device staging buffers and the
+pinned output buffers, so repeated casts allocate nothing.  A cast is pipelined over row chunks on three
+streams: while chunk i is being cast, chunk i+1 travels host -> device and the outputs of chunk i-1 travel
+device -> host (PCIe is full duplex), so the call takes about max(H2D, D2H) instead of their sum.  Row
+chunks are multiples of 128 rows, so every block and every 128x4 scale atom lies inside one chunk and the
+chunked result is bit-identical to the one-shot cast: rowwise outputs of a chunk are row slabs of the
+host outputs; transposed outputs are column slabs, placed with strided copies.
 """
 import torch
 
@@ -13,31 +17,81 @@ from .recipes import blocked_shape
 class HostMxfp8Caster:
     """mxfp8_dim_km(_swizzle) for an (M, N) bf16 matrix that lives in (pinned) host memory."""
 
-    def __init__(self, M, N, device, swizzle=True, mode="rceil"):
-        assert M % 32 == 0 and N % 32 == 0
+    def __init__(self, M, N, device, swizzle=True, mode="rceil", chunk_rows=2048):
+        assert M % 128 == 0 and N % 32 == 0, "host caster wants M % 128 == 0 and N % 32 == 0"
         self.M, self.N, self.device = M, N, torch.device(device)
+        self.swizzle = swizzle
         self.flags = L.ROWWISE | L.COLWISE | (L.SWIZZLE if swizzle else 0) | (L.FLOOR if mode == "floor" else 0)
+        rc = min(chunk_rows, M)
+        while M % rc or rc % 128:
+            rc -= 128
+        self.rc = rc
+        dev = self.device
+        sk_c = blocked_shape(rc, N // 32) if swizzle else (rc, N // 32)
+        sm_c = blocked_shape(N, rc // 32) if swizzle else (N, rc // 32)
+        self.x_dev = [torch.empty((rc, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.out_dev = [[torch.empty(s, dtype=torch.uint8, device=dev) for s in ((rc, N), sk_c, (N, rc), sm_c)]
+                        for _ in range(2)]
         sk_shape = blocked_shape(M, N // 32) if swizzle else (M, N // 32)
         sm_shape = blocked_shape(N, M // 32) if swizzle else (N, M // 32)
-        shapes = [(M, N), sk_shape, (N, M), sm_shape]
-        self.x_dev = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-        self.dev = [torch.empty(s, dtype=torch.uint8, device=self.device) for s in shapes]
-        self.host = [torch.empty(s, dtype=torch.uint8, pin_memory=True) for s in shapes]
+        self.host = [torch.empty(s, dtype=torch.uint8, pin_memory=True) for s in ((M, N), sk_shape, (N, M), sm_shape)]
         self.dtypes = [torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float8_e4m3fn, torch.float8_e8m0fnu]
+        with torch.cuda.device(dev):
+            self.s_h2d, self.s_cmp, self.s_d2h = (torch.cuda.Stream() for _ in range(3))
+        self.bytes_in = M * N * 2
+        self.bytes_out = sum(h.numel() for h in self.host)
 
     def cast(self, x_host):
-        """x_host: contiguous (M, N) bf16 host tensor (pinned for full copy speed).  Returns
-        (qk, sk, qm, sm) as views of this object's pinned host buffers (overwritten by the next cast)."""
+        """x_host: contiguous (M, N) bf16 host tensor (pinned for full copy speed).  Returns (qk, sk, qm, sm)
+        as views of this object's pinned host buffers (overwritten by the next cast); complete on return."""
         lib = L.load()
-        assert x_host.shape == (self.M, self.N) and x_host.dtype == torch.bfloat16 and x_host.is_contiguous()
+        M, N, rc = self.M, self.N, self.rc
+        assert x_host.shape == (M, N) and x_host.dtype == torch.bfloat16 and x_host.is_contiguous()
+        qk_h, sk_h, qm_h, sm_h = self.host
+        n_chunks = M // rc
         with torch.cuda.device(self.device):
-            stream = torch.cuda.current_stream(self.device)
-            self.x_dev.copy_(x_host, non_blocking=True)
-            L.check(lib.qcc_mxfp8(self.x_dev.data_ptr(), self.M, self.N, self.flags, self.dev[0].data_ptr(),
-                                  self.dev[1].data_ptr(), self.dev[2].data_ptr(), self.dev[3].data_ptr(),
-                                  stream.cuda_stream), "mxfp8")
-            L.launch_count += 1
-            for h, d in zip(self.host, self.dev):
-                h.copy_(d, non_blocking=True)
-            stream.synchronize()
+            cur = torch.cuda.current_stream()
+            for s in (self.s_h2d, self.s_cmp, self.s_d2h):
+                s.wait_stream(cur)
+            x_free = [None, None]     # event: the cast that read x_dev[b] is done
+            out_free = [None, None]   # event: the copies out of out_dev[b] are done
+            for i in range(n_chunks):
+                b = i & 1
+                r0 = i * rc
+                with torch.cuda.stream(self.s_h2d):
+                    if x_free[b] is not None:
+                        self.s_h2d.wait_event(x_free[b])
+                    self.x_dev[b].copy_(x_host[r0:r0 + rc], non_blocking=True)
+                    x_ready = torch.cuda.Event()
+                    x_ready.record(self.s_h2d)
+                qk_d, sk_d, qm_d, sm_d = self.out_dev[b]
+                with torch.cuda.stream(self.s_cmp):
+                    self.s_cmp.wait_event(x_ready)
+                    if out_free[b] is not None:
+                        self.s_cmp.wait_event(out_free[b])
+                    L.check(lib.qcc_mxfp8(self.x_dev[b].data_ptr(), rc, N, self.flags, qk_d.data_ptr(), sk_d.data_ptr(),
+                                          qm_d.data_ptr(), sm_d.data_ptr(), self.s_cmp.cuda_stream), "mxfp8")
+                    L.launch_count += 1
+                    done = torch.cuda.Event()
+                    done.record(self.s_cmp)
+                    x_free[b] = done
+                with torch.cuda.stream(self.s_d2h):
+                    self.s_d2h.wait_event(done)
+                    st = self.s_d2h.cuda_stream
+                    qk_h[r0:r0 + rc].copy_(qk_d, non_blocking=True)                       # row slab
+                    if self.swizzle:
+                        sk_h[r0 // 128:(r0 + rc) // 128].copy_(sk_d, non_blocking=True)   # first-axis slab
+                        w = (rc // 128) * 512                                             # second-axis slab
+                        L.check(lib.qcc_copy2d_async(sm_h.data_ptr() + (r0 // 128) * 512, (M // 128) * 512, sm_d.data_ptr(),
+                                                     w, w, sm_d.shape[0], 1, st), "copy2d sm")
+                    else:
+                        sk_h[r0:r0 + rc].copy_(sk_d, non_blocking=True)
+                        w = rc // 32
+                        L.check(lib.qcc_copy2d_async(sm_h.data_ptr() + r0 // 32, M // 32, sm_d.data_ptr(), w, w, N, 1, st),
+                                "copy2d sm")
+                    L.check(lib.qcc_copy2d_async(qm_h.data_ptr() + r0, M, qm_d.data_ptr(), rc, rc, N, 1, st), "copy2d qm")
+                    ev = torch.cuda.Event()
+                    ev.record(self.s_d2h)
+                    out_free[b] = ev
+            self.s_d2h.synchronize()
         return tuple(h.view(dt) for h, dt in zip(self.host, self.dtypes))

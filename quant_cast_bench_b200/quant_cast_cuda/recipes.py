@@ -49,6 +49,23 @@ def _stream(x):
     return torch.cuda.current_stream(x.device).cuda_stream
 
 
+class _on_device:
+    """`with torch.cuda.device(...)` only when the tensor's device is not already current (the context
+    manager costs more host time than a whole launch)."""
+
+    def __init__(self, dev):
+        self.ctx = None if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
+
+
 def _cdiv(a, b):
     return (a + b - 1) // b
 
@@ -73,7 +90,7 @@ def _amax(x, mode, fmt=L.FMT_E4M3):
     out = torch.empty((), dtype=torch.float32, device=x.device)
     ws_bytes = lib.qcc_amax_workspace_bytes()
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
     L.launch_count += 2
     return out
@@ -91,7 +108,7 @@ def scale_from_amax_cuda(amax, kind, fmt="e4m3"):
     mode = {"fp8": L.AMAX_FP8_SCALE, "nvfp4": L.AMAX_NVFP4_SCALE, "raw": L.AMAX_RAW}[kind]
     a = amax.reshape(-1)[:1].contiguous().float()
     out = torch.empty((), dtype=torch.float32, device=amax.device)
-    with torch.cuda.device(amax.device):
+    with _on_device(amax.device):
         L.check(lib.qcc_scale_from_amax(_p(a), mode, _fmt(fmt), _p(out), _stream(amax)), "scale_from_amax")
     L.launch_count += 1
     return out
@@ -117,7 +134,7 @@ def float8_tensorwise_cuda(x, scale, fmt="e4m3", **kwargs):
     f = _fmt(fmt)
     assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         L.check(lib.qcc_fp8_tensorwise(_p(x), x.numel(), _p(scale), f, _p(q), _stream(x)), "fp8_tensorwise")
     L.launch_count += 1
     return (q.view(_FP8_DTYPE[f]),)
@@ -131,7 +148,7 @@ def rowwise_fp8_cuda(x, fmt="e4m3", **kwargs):
     M, N = x.shape
     q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
     s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         L.check(lib.qcc_fp8_rowwise(_p(x), M, N, f, _p(q), _p(s), _stream(x)), "fp8_rowwise")
     L.launch_count += 1
     return q.view(_FP8_DTYPE[f]), s
@@ -143,7 +160,7 @@ def rowwise_precalc_scale_cuda(x, fmt="e4m3"):
     _check_x(x)
     M, N = x.shape
     s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         L.check(lib.qcc_fp8_rowwise(_p(x), M, N, _fmt(fmt), None, _p(s), _stream(x)), "fp8_rowwise_scale")
     L.launch_count += 1
     return s
@@ -157,7 +174,7 @@ def rowwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
     M, N = x.shape
     assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == M and scale.is_contiguous()
     q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         L.check(lib.qcc_fp8_rowwise_precalc(_p(x), M, N, _p(scale), f, _p(q), _stream(x)), "fp8_rowwise_precalc")
     L.launch_count += 1
     return (q.view(_FP8_DTYPE[f]),)
@@ -182,7 +199,7 @@ def _mxfp8(x, flags):
     if flags & L.COLWISE:
         qm = torch.empty((N, M), dtype=torch.uint8, device=dev)
         sm = torch.empty(blocked_shape(N, M // 32) if swz else (N, M // 32), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         L.check(lib.qcc_mxfp8(_p(x), M, N, flags, _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "mxfp8")
     L.launch_count += 1
     outs = []
@@ -242,7 +259,7 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
         assert key is not None and key.is_cuda and key.numel() >= 2 and key.element_size() == 8, (
             "stochastic rounding needs a uint64 [seed, offset] key on the device (see philox_key)")
     swz = bool(flags & L.SWIZZLE)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if transposed:
             assert M % 32 == 0 and N % 8 == 0, f"transposed nvfp4 needs M % 32 == 0 and N % 8 == 0, got {M}x{N}"
             q = torch.empty((N, M // 2), dtype=torch.uint8, device=dev)
