@@ -154,6 +154,23 @@ __device__ __forceinline__ uint32_t nvfp4_inner(float amax, float outer, float i
     return byte;
 }
 
+// Same with the second division read from a 128-entry table in shared memory: for a per-tensor outer
+// scale the multiplier (1 / outer) / fp32(inner) depends on the inner byte only, so a CTA divides once
+// per possible byte (nvfp4_fill_recip_lut) instead of once per block.  Entry i is the IEEE quotient for
+// byte i, hence bit-identical to nvfp4_inner.
+__device__ __forceinline__ void nvfp4_fill_recip_lut(float *lut, float inv_outer)
+{
+    if (threadIdx.x < 128) lut[threadIdx.x] = __fdiv_rn(inv_outer, e4m3_to_f32(threadIdx.x));
+}
+__device__ __forceinline__ uint32_t nvfp4_inner_lut(float amax, float outer, const float *lut, float &recip)
+{
+    float f = __fdiv_rn(__fdiv_rn(amax, 6.0f), outer);
+    f = fminf(fmaxf(f, 0.015625f), 448.0f);
+    uint32_t byte = cvt_fp8x2<QCC_FMT_E4M3>(f, 0.0f) & 0xFFu;
+    recip = lut[byte & 127u];
+    return byte;
+}
+
 // Offset of block scale (r, c) in the 32x4x4 blocked layout with `ncb` column blocks (G:1000-1037)
 __device__ __forceinline__ size_t blocked_offset(uint32_t r, uint32_t c, uint32_t ncb)
 {

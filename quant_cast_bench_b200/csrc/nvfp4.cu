@@ -36,13 +36,14 @@ struct FastDiv {
 
 // One block: 16 bf16 in two uint4 -> 8 packed bytes and the inner scale byte.
 template <bool SR>
-__device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer, float inv_outer, uint64_t flat0,
-                                                 uint64_t seed, uint64_t offset, uint2 &packed)
+__device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer, float inv_outer, const float *lut,
+                                                 uint64_t flat0, uint64_t seed, uint64_t offset, uint2 &packed)
 {
     uint32_t acc = absmax2(absmax2(absmax2(absmax2(0u, a.x), a.y), absmax2(a.z, a.w)),
                            absmax2(absmax2(b.x, b.y), absmax2(b.z, b.w)));
     float recip;
-    const uint32_t byte = nvfp4_inner(hmax_halves_f32(acc), outer, inv_outer, recip);
+    const uint32_t byte = lut ? nvfp4_inner_lut(hmax_halves_f32(acc), outer, lut, recip)
+                              : nvfp4_inner(hmax_halves_f32(acc), outer, inv_outer, recip);
     float v[16] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w),
                    bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
 #pragma unroll
@@ -80,7 +81,13 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
     uint64_t seed = 0, offset = 0;
     if (SR) { seed = key[0]; offset = key[1]; }
     float o_all = 0.f, inv_all = 0.f;
-    if (!PER_ROW) { o_all = __ldg(outer); inv_all = __fdiv_rn(1.0f, o_all); }
+    // (a shared-memory table of the second division, as the transposed kernel uses, measured slower here:
+    // its loads compete with the scale shuffles for the same issue queue)
+    const float *lut = nullptr;
+    if (!PER_ROW) {
+        o_all = __ldg(outer);
+        inv_all = __fdiv_rn(1.0f, o_all);
+    }
     const uint32_t base = blockIdx.x * (NV_THREADS * NV_UNROLL) + threadIdx.x;
     uint4 a[NV_UNROLL], b[NV_UNROLL];
 #pragma unroll
@@ -103,7 +110,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         float o = o_all, inv = inv_all;
         if (PER_ROW) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
         uint2 packed;
-        const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, (uint64_t)bi * 16u, seed, offset, packed);
+        const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, lut, (uint64_t)bi * 16u, seed, offset, packed);
         if (ok) __stcs(qv + bi, packed);
         if (SWZ) {
             // four consecutive lanes hold the four scale columns of one (row, column block)
@@ -140,7 +147,8 @@ constexpr int NVT_PANEL_BYTES = NVT_TILE_M * 128;  // one 64-column panel: 128 r
 constexpr int NVT_X_OFF = 0;
 constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 rows x 64 B
 constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * 32 * 64; // 128 columns x 8 block scales
-constexpr int NVT_BAR_OFF = NVT_S_OFF + 1024;
+constexpr int NVT_LUT_OFF = NVT_S_OFF + 1024;      // 128 multipliers, one per inner-scale byte
+constexpr int NVT_BAR_OFF = NVT_LUT_OFF + 512;
 constexpr int NVT_BYTES = NVT_BAR_OFF + 16;
 constexpr int NVT_ALLOC = NVT_BYTES + 1024;
 
@@ -170,6 +178,9 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
     }
     const float outer = __ldg(outer_p);
     const float inv_outer = __fdiv_rn(1.0f, outer);
+    float *lut = reinterpret_cast<float *>(sbase + NVT_LUT_OFF);
+    nvfp4_fill_recip_lut(lut, inv_outer);
+    __syncthreads();
     uint64_t seed = 0, offset = 0;
     if (SR) { seed = key[0]; offset = key[1]; }
     const int mb16 = M >> 4;   // scale columns of the transposed frame
@@ -196,7 +207,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             float recip;
-            sc[k][h] = nvfp4_inner(am[k], outer, inv_outer, recip);
+            sc[k][h] = nvfp4_inner_lut(am[k], outer, lut, recip);
             float v[16];
 #pragma unroll
             for (int r = 0; r < 16; r++) {
