@@ -272,6 +272,9 @@ def run_ours(args):
     h2d = x_host.numel() * 2
     d2h = sum(o.numel() * o.element_size() for o in outs_host)
 
+    del caster, x_host, outs_host
+    torch.cuda.empty_cache()
+    c4 = bench_c4_sharded(dev, world, rank, peak)
     casts = {}
     cpu = None
     if rank == 0:
@@ -299,6 +302,7 @@ def run_ours(args):
                 "steps": e2e_steps},
         "gpu_launches": launches,
         "clocks": clocks,
+        "c4_sharded": c4,
         "casts": casts,
     }
     print(json.dumps(line))
@@ -321,6 +325,63 @@ def cpu_baseline():
     return {"value": algorithmic_bytes(rows, N_STEP, "mxfp8_dim_km") / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(),
             "kind": "port", "sample": f"{rows} of {M_STEP} rows x {N_STEP} cols, mean of {reps} after 1 warm-up",
             "host_cpus": os.cpu_count()}
+
+
+def chunk_seeded_input(rows, N, row_offset, seed, device, spread, chunk=2048):
+    """Rows [row_offset, row_offset + rows) of a matrix whose every 2048-row chunk has its own seed, so a row
+    shard holds the same values whatever the number of shards."""
+    import torch
+    assert rows % chunk == 0 and row_offset % chunk == 0
+    x = torch.empty((rows, N), dtype=torch.bfloat16, device=device)
+    g = torch.Generator(device=device)
+    for r0 in range(0, rows, chunk):
+        g.manual_seed(seed * 1000003 + (row_offset + r0) // chunk)
+        t = torch.randn(chunk, N, generator=g, device=device)
+        t *= torch.exp2((torch.rand(chunk, 1, generator=g, device=device) * 2 - 1) * spread)
+        x[r0:r0 + chunk] = t.to(torch.bfloat16)
+    return x
+
+
+def bench_c4_sharded(dev, world, rank, peak, iters=10):
+    """Config 4: MoE activation bf16 [131072, 7168], N(0,1)*2^U(-6,6) per token, row-sharded over the ranks.
+    Each iteration: local amax -> all-reduce(MAX) of one fp32 (NCCL) overlapped with the mxfp8 cast -> nvfp4
+    cast with the global scale.  Reports whole-job GB/s and a checksum of all output bytes, which must not
+    depend on the number of ranks (sharded outputs are bit-identical to the single-GPU ones)."""
+    import torch
+    import torch.distributed as dist
+    from quant_cast_bench_b200.quant_cast_cuda.sharded import ShardedCaster, shard_rows
+    M, N = 131072, 7168
+    r0, r1 = shard_rows(M, world, rank, multiple=2048)
+    x = chunk_seeded_input(r1 - r0, N, r0, seed=4, device=dev, spread=6.0)
+    caster = ShardedCaster()
+    for _ in range(3):
+        mx, nv = caster.mxfp8_then_nvfp4(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        mx, nv = caster.mxfp8_then_nvfp4(x)
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device=dev, dtype=torch.float64)
+    chk = torch.zeros(1, device=dev, dtype=torch.int64)
+    for o in (mx[0], mx[1], nv[0], nv[1]):
+        chk += o.view(torch.uint8).reshape(-1).view(torch.int32).sum(dtype=torch.int64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(chk, op=dist.ReduceOp.SUM)
+    e = M * N
+    nbytes = (2 * e + e + e // 32) + (2 * e + 4) + (2 * e + 4 + e // 2 + e // 16)   # mxfp8_swizzle + amax + nvfp4_swizzle
+    ms = float(t.item())
+    outer = float(nv[2].item())
+    del x, mx, nv
+    torch.cuda.empty_cache()
+    return {"workload": "bf16[131072,7168] row-sharded: mxfp8_swizzle + nvfp4 amax (all-reduce MAX) + nvfp4_swizzle",
+            "ms_per_iter": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "bytes": nbytes, "n_gpus": world,
+            "frac_measured_peak_per_gpu": nbytes / (ms * 1e-3) / 1e9 / world / peak,
+            "output_checksum": int(chk.item()), "outer_scale": outer}
 
 
 def bench_other_casts(Q, x, dev, peak):
