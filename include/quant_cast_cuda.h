@@ -176,6 +176,15 @@ int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer
 int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
                          const uint64_t *philox_key, void *q, void *s, void *stream);
 
+/*
+ * Both orientations from one read of x: (qk, sk) are the outputs of qcc_nvfp4 (one per-tensor outer
+ * scale, round to nearest), (qm, sm) those of qcc_nvfp4_transposed -- the pair of casts an nvfp4 linear
+ * layer makes of one operand (test/test_quant_cast_gold.py:103-104).  flags: QCC_SWIZZLE or 0.
+ * Needs M % 32 == 0 and N % 32 == 0.
+ */
+int qcc_nvfp4_both(const void *x, int64_t M, int64_t N, const float *outer, int flags, void *qk, void *sk,
+                   void *qm, void *sm, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,31 @@ __device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi)
         asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// (a * s, b * s) with one packed fp32x2 multiply (sm_100), each lane rounded to nearest like a scalar multiply
+__device__ __forceinline__ void mul2(float a, float b, float s, float &oa, float &ob)
+{
+#ifdef QCC_NO_F32X2
+    oa = a * s;
+    ob = b * s;
+#else
+    asm("{\n.reg .b64 x, y, z;\n"
+        "mov.b64 x, {%2, %3};\n"
+        "mov.b64 y, {%4, %4};\n"
+        "mul.rn.f32x2 z, x, y;\n"
+        "mov.b64 {%0, %1}, z;\n}\n"
+        : "=f"(oa), "=f"(ob)
+        : "f"(a), "f"(b), "f"(s));
+#endif
+}
+// four fp32, all scaled by s -> four fp8 bytes in one word, element 0 in the lowest byte
+template <int FMT>
+__device__ __forceinline__ uint32_t scale_cvt_fp8x4(float a, float b, float c, float d, float s)
+{
+    float sa, sb, sc, sd;
+    mul2(a, b, s, sa, sb);
+    mul2(c, d, s, sc, sd);
+    return cvt_fp8x2<FMT>(sa, sb) | (cvt_fp8x2<FMT>(sc, sd) << 16);
+}
 // four fp32 -> four fp8 bytes in one word, element 0 in the lowest byte
 template <int FMT>
 __device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d)

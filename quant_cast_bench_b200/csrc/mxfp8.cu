@@ -32,14 +32,14 @@ namespace qcc {
 // 32 fp32-scaled values of one row block -> 32 e4m3 bytes, given the four 16-byte chunks
 __device__ __forceinline__ void quant_row_block(const uint4 c[4], float rcp, uint4 &o0, uint4 &o1)
 {
-    o0.x = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].x) * rcp, bf16hi(c[0].x) * rcp, bf16lo(c[0].y) * rcp, bf16hi(c[0].y) * rcp);
-    o0.y = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].z) * rcp, bf16hi(c[0].z) * rcp, bf16lo(c[0].w) * rcp, bf16hi(c[0].w) * rcp);
-    o0.z = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].x) * rcp, bf16hi(c[1].x) * rcp, bf16lo(c[1].y) * rcp, bf16hi(c[1].y) * rcp);
-    o0.w = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].z) * rcp, bf16hi(c[1].z) * rcp, bf16lo(c[1].w) * rcp, bf16hi(c[1].w) * rcp);
-    o1.x = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].x) * rcp, bf16hi(c[2].x) * rcp, bf16lo(c[2].y) * rcp, bf16hi(c[2].y) * rcp);
-    o1.y = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].z) * rcp, bf16hi(c[2].z) * rcp, bf16lo(c[2].w) * rcp, bf16hi(c[2].w) * rcp);
-    o1.z = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].x) * rcp, bf16hi(c[3].x) * rcp, bf16lo(c[3].y) * rcp, bf16hi(c[3].y) * rcp);
-    o1.w = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].z) * rcp, bf16hi(c[3].z) * rcp, bf16lo(c[3].w) * rcp, bf16hi(c[3].w) * rcp);
+    o0.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].x), bf16hi(c[0].x), bf16lo(c[0].y), bf16hi(c[0].y), rcp);
+    o0.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].z), bf16hi(c[0].z), bf16lo(c[0].w), bf16hi(c[0].w), rcp);
+    o0.z = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].x), bf16hi(c[1].x), bf16lo(c[1].y), bf16hi(c[1].y), rcp);
+    o0.w = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].z), bf16hi(c[1].z), bf16lo(c[1].w), bf16hi(c[1].w), rcp);
+    o1.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].x), bf16hi(c[2].x), bf16lo(c[2].y), bf16hi(c[2].y), rcp);
+    o1.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].z), bf16hi(c[2].z), bf16lo(c[2].w), bf16hi(c[2].w), rcp);
+    o1.z = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].x), bf16hi(c[3].x), bf16lo(c[3].y), bf16hi(c[3].y), rcp);
+    o1.w = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].z), bf16hi(c[3].z), bf16lo(c[3].w), bf16hi(c[3].w), rcp);
 }
 
 __device__ __forceinline__ float amax_of_block(const uint4 c[4])
@@ -288,13 +288,13 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
                 const uint2 r0 = w[4 * q4], r1 = w[4 * q4 + 1], r2 = w[4 * q4 + 2], r3 = w[4 * q4 + 3];
                 const float sc = rcp[kk];
                 if (kk == 0)
-                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.x) * sc, bf16lo(r1.x) * sc, bf16lo(r2.x) * sc, bf16lo(r3.x) * sc);
+                    o[q4] = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.x), bf16lo(r1.x), bf16lo(r2.x), bf16lo(r3.x), sc);
                 else if (kk == 1)
-                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.x) * sc, bf16hi(r1.x) * sc, bf16hi(r2.x) * sc, bf16hi(r3.x) * sc);
+                    o[q4] = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.x), bf16hi(r1.x), bf16hi(r2.x), bf16hi(r3.x), sc);
                 else if (kk == 2)
-                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.y) * sc, bf16lo(r1.y) * sc, bf16lo(r2.y) * sc, bf16lo(r3.y) * sc);
+                    o[q4] = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(r0.y), bf16lo(r1.y), bf16lo(r2.y), bf16lo(r3.y), sc);
                 else
-                    o[q4] = cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.y) * sc, bf16hi(r1.y) * sc, bf16hi(r2.y) * sc, bf16hi(r3.y) * sc);
+                    o[q4] = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16hi(r0.y), bf16hi(r1.y), bf16hi(r2.y), bf16hi(r3.y), sc);
             }
             const uint32_t rowp = qms + kk * 2048 + lane * 64;
             sts_v4(rowp + (((2 * b) ^ key) << 4), make_uint4(o[0], o[1], o[2], o[3]));

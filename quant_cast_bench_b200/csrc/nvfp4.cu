@@ -149,15 +149,17 @@ constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 
 constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * 32 * 64; // 128 columns x 8 block scales
 constexpr int NVT_LUT_OFF = NVT_S_OFF + 1024;      // 128 multipliers, one per inner-scale byte
 constexpr int NVT_BAR_OFF = NVT_LUT_OFF + 512;
-constexpr int NVT_BYTES = NVT_BAR_OFF + 16;
-constexpr int NVT_ALLOC = NVT_BYTES + 1024;
+constexpr int NVT_QK_OFF = NVT_BAR_OFF + 512;      // rowwise staging (fused form only): 128 rows x 64 B
+constexpr int nvt_alloc(bool do_k) { return NVT_QK_OFF + (do_k ? 128 * 64 : 0) + 1024; }
 
-// row-major tile order (column tiles fastest), as in the mxfp8 tile kernel
-template <bool SWZ, bool SR>
-__global__ void __launch_bounds__(128, 5)
+// Row-major tile order (column tiles fastest), as in the mxfp8 tile kernel.  Warps 0-3 quantise down the
+// rows (transposed outputs q, s); with DO_K warps 4-7 also quantise along the rows (outputs qk, sk), so both
+// orientations come from one read of x.
+template <bool DO_K, bool SWZ, bool SR>
+__global__ void __launch_bounds__(DO_K ? 256 : 128, DO_K ? 3 : 5)
 nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *__restrict__ outer_p,
-                        const uint64_t *__restrict__ key, uint8_t *__restrict__ q, uint8_t *__restrict__ s, int M, int N,
-                        int tiles_n)
+                        const uint64_t *__restrict__ key, uint8_t *__restrict__ q, uint8_t *__restrict__ s,
+                        uint8_t *__restrict__ qk, uint8_t *__restrict__ sk, int M, int N, int tiles_n)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -187,6 +189,63 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
     const int halfM = M >> 1;  // bytes per output row
 
     mbar_wait(bar, 0, 2u);
+
+    if (DO_K && b >= 4) {
+        // ------------------------------------------------------------------ along the row (fused form)
+        const int rw = b - 4;
+        const int row_t = rw * 32 + lane;
+        const int R = tile_m * NVT_TILE_M + row_t;
+        const int nb16 = N >> 4, halfN = N >> 1;
+        const uint32_t xrow = base + NVT_X_OFF + row_t * 128;
+        const uint32_t key7 = lane & 7;
+        const uint32_t key2 = ((row_t >> 1) & 3) << 1;       // staging swizzle on 8-byte units, pairs kept together
+        const uint32_t qrow = base + NVT_QK_OFF + row_t * 64;
+        uint32_t sb[2] = {0u, 0u};
+#pragma unroll
+        for (int kb = 0; kb < 8; kb++) {
+            const uint32_t prow = xrow + (kb >> 2) * NVT_PANEL_BYTES;
+            const uint32_t j0 = (kb & 3) * 2;
+            const uint4 a4 = lds_v4(prow + (((j0) ^ key7) << 4));
+            const uint4 b4 = lds_v4(prow + (((j0 + 1) ^ key7) << 4));
+            uint2 packed;
+            uint32_t byte = nvfp4_quant16<false>(a4, b4, outer, inv_outer, lut, 0, 0, 0, packed);
+            const bool ok = R < M && (tile_n * 8 + kb) < nb16;
+            sb[kb >> 2] |= (ok ? byte : 0u) << (8 * (kb & 3));
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(qrow + ((kb ^ key2) << 3)), "r"(packed.x), "r"(packed.y) : "memory");
+        }
+        __syncwarp();
+        {
+            const int jj = lane & 3;
+            const int cbyte = tile_n * 64 + jj * 16;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int r = i * 8 + (lane >> 2);
+                const int rt = rw * 32 + r;
+                const int Rr = tile_m * NVT_TILE_M + rt;
+                const uint4 v = lds_v4(base + NVT_QK_OFF + rt * 64 + ((jj ^ ((rt >> 1) & 3)) << 4));
+                if (Rr < M && cbyte < halfN) *reinterpret_cast<uint4 *>(qk + (size_t)Rr * halfN + cbyte) = v;
+            }
+        }
+        if (SWZ) {
+            const uint32_t ncb = (nb16 + 3) >> 2;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t bc = tile_n * 2 + h;
+                if (bc < ncb)
+                    *reinterpret_cast<uint32_t *>(sk + ((size_t)tile_m * ncb + bc) * 512u + lane * 16u + rw * 4u) = sb[h];
+            }
+        } else if (R < M) {
+            uint8_t *dst = sk + (size_t)R * nb16 + tile_n * 8;
+            if ((nb16 & 7) == 0) {
+                *reinterpret_cast<uint2 *>(dst) = make_uint2(sb[0], sb[1]);
+            } else {
+#pragma unroll
+                for (int kb = 0; kb < 8; kb++)
+                    if (tile_n * 8 + kb < nb16) dst[kb] = (uint8_t)(sb[kb >> 2] >> (8 * (kb & 3)));
+            }
+        }
+        return;
+    }
 
     const uint32_t pbase = base + NVT_X_OFF + (lane >> 4) * NVT_PANEL_BYTES + (b * 32) * 128 + (lane & 1) * 8;
     const uint32_t j = (lane & 15) >> 1;
@@ -254,7 +313,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             ss[off] = ok ? (uint8_t)sc[k][h] : (uint8_t)0;
         }
     }
-    __syncthreads();
+    named_barrier(1, 128);   // the four column warps
     // write-out: warp b takes sub-tile b; four lanes move one 64-byte row segment
     {
         const int jj = lane & 3;
@@ -337,16 +396,17 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
     return (int)cudaGetLastError();
 }
 
-template <bool SWZ, bool SR>
-static int launch_nvt(const CUtensorMap &tx, const float *outer, const uint64_t *key, uint8_t *q, uint8_t *s, int M, int N,
-                      cudaStream_t st)
+template <bool DO_K, bool SWZ, bool SR>
+static int launch_nvt(const CUtensorMap &tx, const float *outer, const uint64_t *key, uint8_t *q, uint8_t *s, uint8_t *qk,
+                      uint8_t *sk, int M, int N, cudaStream_t st)
 {
-    auto kern = nvfp4_transposed_kernel<SWZ, SR>;
+    auto kern = nvfp4_transposed_kernel<DO_K, SWZ, SR>;
+    constexpr int ALLOC = nvt_alloc(DO_K);
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, NVT_ALLOC);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ALLOC);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
@@ -355,20 +415,20 @@ static int launch_nvt(const CUtensorMap &tx, const float *outer, const uint64_t 
     const int tiles_n = (N + 127) / 128, tiles_m = (M + NVT_TILE_M - 1) / NVT_TILE_M;
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, 128, NVT_ALLOC, st>>>(tx, outer, key, q, s, M, N, tiles_n);
+    kern<<<(unsigned)num_tiles, DO_K ? 256 : 128, ALLOC, st>>>(tx, outer, key, q, s, qk, sk, M, N, tiles_n);
     return (int)cudaGetLastError();
 }
 
-extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
-                                    const uint64_t *philox_key, void *q, void *s, void *stream)
+static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const float *outer, int flags, const uint64_t *philox_key,
+                            void *qk, void *sk, void *q, void *s, bool both, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
-    if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
+    if (!x || !outer || !q || !s || (both && (!qk || !sk)) || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if ((flags & QCC_SR) && (!philox_key || both)) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     // output rows of M / 2 bytes are written in 16-byte pieces: M % 32 == 0; the TMA load needs N % 8 == 0
-    if (M % 32 != 0 || N % 8 != 0) return QCC_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
+    if (M % 32 != 0 || N % 8 != 0 || (both && N % 32 != 0)) return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(s) || (both && (!aligned16(qk) || !aligned16(sk)))) return QCC_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tx;
     {
@@ -379,9 +439,24 @@ extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const f
         if (e) return e;
     }
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR;
-    uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
-    if (swz) return sr ? launch_nvt<true, true>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st)
-                       : launch_nvt<true, false>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st);
-    return sr ? launch_nvt<false, true>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st)
-              : launch_nvt<false, false>(tx, outer, philox_key, qp, sp, (int)M, (int)N, st);
+    uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s, *qkp = (uint8_t *)qk, *skp = (uint8_t *)sk;
+    if (both)
+        return swz ? launch_nvt<true, true, false>(tx, outer, philox_key, qp, sp, qkp, skp, (int)M, (int)N, st)
+                   : launch_nvt<true, false, false>(tx, outer, philox_key, qp, sp, qkp, skp, (int)M, (int)N, st);
+    if (swz) return sr ? launch_nvt<false, true, true>(tx, outer, philox_key, qp, sp, nullptr, nullptr, (int)M, (int)N, st)
+                       : launch_nvt<false, true, false>(tx, outer, philox_key, qp, sp, nullptr, nullptr, (int)M, (int)N, st);
+    return sr ? launch_nvt<false, false, true>(tx, outer, philox_key, qp, sp, nullptr, nullptr, (int)M, (int)N, st)
+              : launch_nvt<false, false, false>(tx, outer, philox_key, qp, sp, nullptr, nullptr, (int)M, (int)N, st);
+}
+
+extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
+                                    const uint64_t *philox_key, void *q, void *s, void *stream)
+{
+    return nvfp4_tile_entry(x, M, N, outer, flags, philox_key, nullptr, nullptr, q, s, false, stream);
+}
+
+extern "C" int qcc_nvfp4_both(const void *x, int64_t M, int64_t N, const float *outer, int flags, void *qk, void *sk,
+                              void *qm, void *sm, void *stream)
+{
+    return nvfp4_tile_entry(x, M, N, outer, flags, nullptr, qk, sk, qm, sm, true, stream);
 }

@@ -38,6 +38,7 @@ SIGNATURES = {
     "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
+    "qcc_nvfp4_both": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp, _vp]),
 }
 
 _lib = None

@@ -308,6 +308,38 @@ def nvfp4_gs_swizzle_t_sr_cuda(x, outer_scale, key, **kwargs):
     return _nvfp4(x, outer_scale, L.SWIZZLE | L.SR, key=key, transposed=True)
 
 
+def _nvfp4_both(x, outer_scale, flags):
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    dev = x.device
+    assert outer_scale.is_cuda and outer_scale.dtype == torch.float32 and outer_scale.numel() == 1
+    assert M % 32 == 0 and N % 32 == 0, f"fused nvfp4 needs M % 32 == 0 and N % 32 == 0, got {M}x{N}"
+    swz = bool(flags & L.SWIZZLE)
+    qk = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
+    sk = torch.empty(blocked_shape(M, N // 16) if swz else (M, N // 16), dtype=torch.uint8, device=dev)
+    qm = torch.empty((N, M // 2), dtype=torch.uint8, device=dev)
+    sm = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=torch.uint8, device=dev)
+    with _on_device(dev):
+        L.check(lib.qcc_nvfp4_both(_p(x), M, N, _p(outer_scale.contiguous()), flags, _p(qk), _p(sk), _p(qm), _p(sm),
+                                   _stream(x)), "nvfp4_both")
+    L.launch_count += 1
+    f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+    return qk.view(f4), sk.view(e4), qm.view(f4), sm.view(e4)
+
+
+def nvfp4_gs_both_cuda(x, outer_scale, **kwargs):
+    """Extension: nvfp4_gs_f(x, s) and nvfp4_gs_f(x.t().contiguous(), s) from one read of x:
+    (qk (M, N/2), sk (M, N/16), qm (N, M/2), sm (N, M/16))."""
+    return _nvfp4_both(x, outer_scale, 0)
+
+
+def nvfp4_gs_swizzle_both_cuda(x, outer_scale, **kwargs):
+    """Extension: the two casts an nvfp4 linear layer makes of one operand
+    (test/test_quant_cast_gold.py:103-104: nvfp4_gs_swizzle_f of x and of x.t().contiguous()) from one read."""
+    return _nvfp4_both(x, outer_scale, L.SWIZZLE)
+
+
 # --------------------------------------------------------------------------------------------
 # recipe records
 # --------------------------------------------------------------------------------------------

@@ -137,6 +137,10 @@ def test_nvfp4_matches_oracle(shape):
     assert_same_bits(gs, gso, "outer scale")
     for fn in ("nvfp4_gs", "nvfp4_gs_swizzle", "nvfp4_gs_t", "nvfp4_gs_swizzle_t"):
         same_outputs(cuda_fn(fn)(xc, gs), oracle_fn(fn)(x, gso), f"{fn} {shape}")
+    if shape[0] % 32 == 0 and shape[1] % 32 == 0:   # both orientations from one read
+        same_outputs(Q.nvfp4_gs_swizzle_both_cuda(xc, gs), O.nvfp4_gs_swizzle_f(x, gso) + O.nvfp4_gs_swizzle_t_f(x, gso),
+                     f"fused swizzle {shape}")
+        same_outputs(Q.nvfp4_gs_both_cuda(xc, gs), O.nvfp4_gs_f(x, gso) + O.nvfp4_gs_t_f(x, gso), f"fused plain {shape}")
     # per-token outer scale (M, 1)
     amax_rows = x.float().abs().amax(dim=1, keepdim=True).clamp(min=2.0 ** -100)
     pt = amax_rows / 2688.0
@@ -169,6 +173,8 @@ def test_all_bf16_values_through_every_conversion():
             o = torch.tensor(outer, dtype=torch.float32)
             for fn in ("nvfp4_gs", "nvfp4_gs_swizzle", "nvfp4_gs_t", "nvfp4_gs_swizzle_t"):
                 same_outputs(cuda_fn(fn)(tc, o.cuda()), oracle_fn(fn)(t, o), f"{fn} outer={outer}")
+            same_outputs(Q.nvfp4_gs_swizzle_both_cuda(tc, o.cuda()), O.nvfp4_gs_swizzle_f(t, o) + O.nvfp4_gs_swizzle_t_f(t, o),
+                         f"fused outer={outer}")
 
 
 def test_fp4_ties_round_to_even():
