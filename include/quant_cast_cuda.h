@@ -133,6 +133,17 @@ int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
 int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q,
                             void *stream);
 
+/* One scale per column (amax over all rows), outputs transposed: q (N, M), scale[c] for column c.
+ * colwise_fp8_f, G:339-349.  workspace: N * 4 bytes of scratch (column maxima; cleared by the call).
+ * Needs N % 8 == 0 and M % 16 == 0. */
+int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *workspace,
+                    size_t workspace_bytes, void *stream);
+
+/* q (N, M) = fp8(float(x) / scale[c]) with a caller-supplied per-column scale; a true division.
+ * colwise_precalc_f, G:445-449. */
+int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q,
+                            void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * mxfp8: 32-element blocks, e8m0 scales, e4m3 elements
  * ------------------------------------------------------------------------------------------- */

@@ -7,6 +7,7 @@ may import it; the product package must never do so.
 Reference functions mirrored (quant_cast_bench/quant_cast_gold/recipes.py = "G"):
   float8_tensorwise_scale G:1179-1183, float8_tensorwise_f G:1186-1191, rowwise_fp8_f G:301-307,
   rowwise_precalc_scale G:389-393, rowwise_precalc_f G:396-399, colwise_fp8_f G:339-349,
+  colwise_precalc_scale G:438-442, colwise_precalc_f G:445-449,
   mxfp8_f G:561-568, mxfp8_swizzle_f G:1051-1053, mxfp8_dim_m_f G:656-671,
   mxfp8_dim_m_swizzle_f G:1092-1094, mxfp8_dim_km_f G:701-719, mxfp8_dim_km_swizzle_f G:1134-1139,
   nvfp4_gs_scale G:1243-1246, nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266,
@@ -219,6 +220,26 @@ def colwise_fp8_f(x, fmt="e4m3", **kwargs):
     s = torch.empty((N, 1), dtype=torch.float32)
     lib().qco_fp8_colwise(_p(x), _i64(M), _i64(N), FMT[fmt], _p(q), _p(s))
     return q.view(FP8_DTYPE[fmt]), s
+
+
+def colwise_precalc_scale(x, fmt="e4m3"):
+    """G:438-442: (1, N) fp32 per-column scale."""
+    _check_x(x)
+    M, N = x.shape
+    s = torch.empty((1, N), dtype=torch.float32)
+    lib().qco_fp8_colwise_scale(_p(x), _i64(M), _i64(N), FMT[fmt], _p(s))
+    return s
+
+
+def colwise_precalc_f(x, scale, fmt="e4m3", **kwargs):
+    """G:445-449: (qdata (N, M),) = fp8(x / scale) with a given (1, N) scale."""
+    _check_x(x)
+    M, N = x.shape
+    s = scale.float().contiguous()
+    assert s.numel() == N
+    q = torch.empty((N, M), dtype=torch.uint8)
+    lib().qco_fp8_colwise_precalc(_p(x), _i64(M), _i64(N), _p(s), FMT[fmt], _p(q))
+    return (q.view(FP8_DTYPE[fmt]),)
 
 
 # ------------------------------------------------------------------ mxfp8

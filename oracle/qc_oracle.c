@@ -385,6 +385,29 @@ void qco_fp8_colwise(const uint16_t *x, int64_t M, int64_t N, int fmt, uint8_t *
     free(best);
 }
 
+/* per-column scale only, as a row of N values.  G:438-442 (colwise_precalc_scale). */
+void qco_fp8_colwise_scale(const uint16_t *x, int64_t M, int64_t N, int fmt, float *scale)
+{
+    uint16_t *best = (uint16_t *)calloc((size_t)N, 2);
+    for (int64_t r = 0; r < M; r++)
+        for (int64_t c = 0; c < N; c++) {
+            uint16_t a = bf16_abs(x[r * N + c]);
+            if (a > best[c]) best[c] = a;
+        }
+    for (int64_t c = 0; c < N; c++) qco_fp8_scale_from_amax(bf16_to_f32(best[c]), fmt, &scale[c]);
+    free(best);
+}
+
+/* q (N, M) = fp8(x_f32 / scale[col]) -- a true division, transposed output.  G:445-449. */
+void qco_fp8_colwise_precalc(const uint16_t *x, int64_t M, int64_t N, const float *scale, int fmt,
+                             uint8_t *q)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < N; c++)
+        for (int64_t r = 0; r < M; r++)
+            q[c * M + r] = f32_to_fp8_fmt(bf16_to_f32(x[r * N + c]) / scale[c], fmt);
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* mxfp8                                                                                      */
 /* ------------------------------------------------------------------------------------------ */

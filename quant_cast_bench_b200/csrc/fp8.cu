@@ -297,6 +297,172 @@ static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scal
     return (int)cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// colwise cast: one scale per column, transposed outputs q (N, M), scale (N, 1).
+// colwise_fp8_f G:339-349, colwise_precalc_f G:445-449.  Two passes over x: column maxima into a
+// caller-supplied scratch of N words (atomic max on the bit patterns: exact and order independent), then
+// a tile kernel that casts and transposes; for matrices that fit in L2 the second pass never reaches HBM.
+// ---------------------------------------------------------------------------------------------
+constexpr int CW_AMAX_ROWS = 64;
+
+__global__ void __launch_bounds__(256) fp8_colwise_amax_kernel(const uint16_t *__restrict__ x, int M, int N,
+                                                              uint32_t *__restrict__ amax_bits)
+{
+    const int chunk = blockIdx.x * 256 + threadIdx.x;       // 8 adjacent columns
+    if (chunk * 8 >= N) return;
+    const int r0 = blockIdx.y * CW_AMAX_ROWS;
+    const int r1 = min(M, r0 + CW_AMAX_ROWS);
+    const uint4 *p = reinterpret_cast<const uint4 *>(x + (size_t)r0 * N) + chunk;
+    const size_t stride = (size_t)N >> 3;
+    uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+    int r = r0;
+    for (; r + 8 <= r1; r += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = ld_nc_v4(p + (size_t)(r - r0 + u) * stride);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            a0 = absmax2_acc(a0, v[u].x); a1 = absmax2_acc(a1, v[u].y);
+            a2 = absmax2_acc(a2, v[u].z); a3 = absmax2_acc(a3, v[u].w);
+        }
+    }
+    for (; r < r1; r++) {
+        const uint4 v = ld_nc_v4(p + (size_t)(r - r0) * stride);
+        a0 = absmax2_acc(a0, v.x); a1 = absmax2_acc(a1, v.y); a2 = absmax2_acc(a2, v.z); a3 = absmax2_acc(a3, v.w);
+    }
+    uint32_t *dst = amax_bits + chunk * 8;
+    const uint32_t acc[4] = {a0, a1, a2, a3};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        atomicMax(dst + 2 * i, acc[i] << 16);
+        atomicMax(dst + 2 * i + 1, acc[i] & 0xFFFF0000u);
+    }
+}
+
+constexpr int CW_PANEL = 64 * 128;                // one 64-column panel of a 64-row tile
+constexpr int CW_Q_OFF = 2 * CW_PANEL;            // staging: 4 sub-tiles x 32 rows x 64 B
+constexpr int CW_BAR_OFF = CW_Q_OFF + 4 * 32 * 64;
+constexpr int CW_ALLOC = CW_BAR_OFF + 16 + 1024;
+
+// One CTA (two warps) per 64-row x 128-column tile; warp b owns the 32-row slab b, lane = four adjacent columns.
+// PRECALC: per-column scale given, true division (G:448); otherwise scale = f(column amax), multiply by 1/scale.
+template <int FMT, bool PRECALC>
+__global__ void __launch_bounds__(64, 8)
+fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t *__restrict__ amax_bits,
+                        const float *__restrict__ scale_in, uint8_t *__restrict__ q, float *__restrict__ scale_out, int M,
+                        int N, int tiles_n)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + CW_BAR_OFF);
+    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
+    const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(bar, 2 * CW_PANEL);
+        tma_load_2d(sbase, &tm_x, bar, tile_n * 128, tile_m * 64);
+        tma_load_2d(sbase + CW_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * 64);
+    }
+    float sc[4];   // multiplier (or divisor when PRECALC) of the four columns
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int Cn = tile_n * 128 + 4 * lane + k;
+        float s = 1.0f;
+        if (Cn < N) {
+            if (PRECALC) {
+                s = __ldg(scale_in + Cn);
+            } else {
+                s = fp8_scale_from_amax<FMT>(u2f(__ldg(amax_bits + Cn)));
+                if (tile_m == 0 && b == 0) scale_out[Cn] = s;
+            }
+        }
+        sc[k] = PRECALC ? s : __fdiv_rn(1.0f, s);
+    }
+    mbar_wait(bar, 0, 5u);
+    const uint32_t pbase = base + (lane >> 4) * CW_PANEL + (b * 32) * 128 + (lane & 1) * 8;
+    const uint32_t j = (lane & 15) >> 1;
+    const uint32_t qs = base + CW_Q_OFF;
+    const uint32_t key = (lane >> 1) & 3;
+    uint32_t o[4][8];
+#pragma unroll
+    for (int q4 = 0; q4 < 8; q4++) {
+        uint2 w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = lds_v2(pbase + (4 * q4 + i) * 128 + ((j ^ ((4 * q4 + i) & 7)) << 4));
+        if (PRECALC) {
+            o[0][q4] = cvt_fp8x4<FMT>(__fdiv_rn(bf16lo(w[0].x), sc[0]), __fdiv_rn(bf16lo(w[1].x), sc[0]), __fdiv_rn(bf16lo(w[2].x), sc[0]), __fdiv_rn(bf16lo(w[3].x), sc[0]));
+            o[1][q4] = cvt_fp8x4<FMT>(__fdiv_rn(bf16hi(w[0].x), sc[1]), __fdiv_rn(bf16hi(w[1].x), sc[1]), __fdiv_rn(bf16hi(w[2].x), sc[1]), __fdiv_rn(bf16hi(w[3].x), sc[1]));
+            o[2][q4] = cvt_fp8x4<FMT>(__fdiv_rn(bf16lo(w[0].y), sc[2]), __fdiv_rn(bf16lo(w[1].y), sc[2]), __fdiv_rn(bf16lo(w[2].y), sc[2]), __fdiv_rn(bf16lo(w[3].y), sc[2]));
+            o[3][q4] = cvt_fp8x4<FMT>(__fdiv_rn(bf16hi(w[0].y), sc[3]), __fdiv_rn(bf16hi(w[1].y), sc[3]), __fdiv_rn(bf16hi(w[2].y), sc[3]), __fdiv_rn(bf16hi(w[3].y), sc[3]));
+        } else {
+            o[0][q4] = scale_cvt_fp8x4<FMT>(bf16lo(w[0].x), bf16lo(w[1].x), bf16lo(w[2].x), bf16lo(w[3].x), sc[0]);
+            o[1][q4] = scale_cvt_fp8x4<FMT>(bf16hi(w[0].x), bf16hi(w[1].x), bf16hi(w[2].x), bf16hi(w[3].x), sc[1]);
+            o[2][q4] = scale_cvt_fp8x4<FMT>(bf16lo(w[0].y), bf16lo(w[1].y), bf16lo(w[2].y), bf16lo(w[3].y), sc[2]);
+            o[3][q4] = scale_cvt_fp8x4<FMT>(bf16hi(w[0].y), bf16hi(w[1].y), bf16hi(w[2].y), bf16hi(w[3].y), sc[3]);
+        }
+    }
+    // staging as in the mxfp8 tile kernel: sub-tile k = columns {4 l + k}, 64-byte rows, chunk c at c ^ ((l >> 1) & 3)
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const uint32_t rowp = qs + k * 2048 + lane * 64;
+        sts_v4(rowp + (((2 * b) ^ key) << 4), make_uint4(o[k][0], o[k][1], o[k][2], o[k][3]));
+        sts_v4(rowp + (((2 * b + 1) ^ key) << 4), make_uint4(o[k][4], o[k][5], o[k][6], o[k][7]));
+    }
+    __syncthreads();
+    const int jj = lane & 3;
+    const int mcol = tile_m * 64 + jj * 16;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int kk = 2 * b + (i >> 2);
+        const int l = (i & 3) * 8 + (lane >> 2);
+        const int Cn = tile_n * 128 + 4 * l + kk;
+        const uint4 v = lds_v4(qs + kk * 2048 + l * 64 + ((jj ^ ((l >> 1) & 3)) << 4));
+        if (Cn < N && mcol < M) *reinterpret_cast<uint4 *>(q + (size_t)Cn * M + mcol) = v;
+    }
+}
+
+template <int FMT, bool PRECALC>
+static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scale_in, void *q, float *scale_out,
+                          uint32_t *amax_bits, cudaStream_t st)
+{
+    CUtensorMap tx;
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)N * 2};
+    uint32_t box[2] = {64, 64};
+    int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (e) return e;
+    if (!PRECALC) {
+        cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)N * 4, st);
+        if (ce != cudaSuccess) return (int)ce;
+        dim3 grid((unsigned)((N / 8 + 255) / 256), (unsigned)((M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS));
+        fp8_colwise_amax_kernel<<<grid, 256, 0, st>>>((const uint16_t *)x, (int)M, (int)N, amax_bits);
+        ce = cudaGetLastError();
+        if (ce != cudaSuccess) return (int)ce;
+    }
+    auto kern = fp8_colwise_cast_kernel<FMT, PRECALC>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CW_ALLOC);
+        if (ce != cudaSuccess) return (int)ce;
+        ce = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (ce != cudaSuccess) return (int)ce;
+        configured[dev] = true;
+    }
+    const int tiles_n = (int)((N + 127) / 128), tiles_m = (int)((M + 63) / 64);
+    const long long num_tiles = (long long)tiles_n * tiles_m;
+    if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    kern<<<(unsigned)num_tiles, 64, CW_ALLOC, st>>>(tx, amax_bits, scale_in, (uint8_t *)q, scale_out, (int)M, (int)N, tiles_n);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace qcc
 
 using namespace qcc;
@@ -434,6 +600,33 @@ int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
     cudaStream_t st = (cudaStream_t)stream;
     return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, st)
                                : launch_rowwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, st);
+}
+
+int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *workspace,
+                    size_t workspace_bytes, void *stream)
+{
+    if (M == 0 || N == 0) return 0;
+    if (!x || !q || !scale || !workspace || M < 0 || N < 0) return QCC_ERR_ARG;
+    if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00 || (M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS > 65535)
+        return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(workspace)) return QCC_ERR_ALIGN;
+    if (workspace_bytes < (size_t)N * 4) return QCC_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st)
+                               : launch_colwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st);
+}
+
+int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
+{
+    if (M == 0 || N == 0) return 0;
+    if (!x || !q || !scale || M < 0 || N < 0) return QCC_ERR_ARG;
+    if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, nullptr, st)
+                               : launch_colwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, nullptr, st);
 }
 
 }  // extern "C"

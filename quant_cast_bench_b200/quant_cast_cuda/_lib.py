@@ -35,6 +35,8 @@ SIGNATURES = {
     "qcc_fp8_tensorwise": (_int, [_vp, _i64, _vp, _int, _vp, _vp]),
     "qcc_fp8_rowwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_fp8_rowwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
+    "qcc_fp8_colwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
+    "qcc_fp8_colwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
     "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),

@@ -180,6 +180,42 @@ def rowwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
     return (q.view(_FP8_DTYPE[f]),)
 
 
+def colwise_fp8_cuda(x, fmt="e4m3", **kwargs):
+    """gold colwise_fp8_f (G:339-349): (qdata (N, M), scale (N, 1) fp32), one scale per column, transposed."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    M, N = x.shape
+    assert N % 8 == 0 and M % 16 == 0, f"colwise fp8 needs N % 8 == 0 and M % 16 == 0, got {M}x{N}"
+    q = torch.empty((N, M), dtype=torch.uint8, device=x.device)
+    s = torch.empty((N, 1), dtype=torch.float32, device=x.device)
+    ws = torch.empty(N, dtype=torch.int32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_fp8_colwise(_p(x), M, N, f, _p(q), _p(s), _p(ws), N * 4, _stream(x)), "fp8_colwise")
+    L.launch_count += 3
+    return q.view(_FP8_DTYPE[f]), s
+
+
+def colwise_precalc_scale_cuda(x, fmt="e4m3"):
+    """gold colwise_precalc_scale (G:438-442): (1, N) fp32 per-column scale."""
+    return colwise_fp8_cuda(x, fmt)[1].reshape(1, -1)
+
+
+def colwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
+    """gold colwise_precalc_f (G:445-449): (qdata (N, M),) = fp8(x / scale) with a given (1, N) scale."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    M, N = x.shape
+    assert N % 8 == 0 and M % 16 == 0, f"colwise fp8 needs N % 8 == 0 and M % 16 == 0, got {M}x{N}"
+    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == N and scale.is_contiguous()
+    q = torch.empty((N, M), dtype=torch.uint8, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_fp8_colwise_precalc(_p(x), M, N, _p(scale), f, _p(q), _stream(x)), "fp8_colwise_precalc")
+    L.launch_count += 1
+    return (q.view(_FP8_DTYPE[f]),)
+
+
 # --------------------------------------------------------------------------------------------
 # mxfp8
 # --------------------------------------------------------------------------------------------
@@ -385,6 +421,11 @@ def _inputs_rowwise_precalc(M, K):
     return (x, rowwise_precalc_scale_cuda(x))
 
 
+def _inputs_colwise_precalc(M, K):
+    x = _x(M, K)
+    return (x, colwise_precalc_scale_cuda(x))
+
+
 def _inputs_nvfp4(M, K):
     x = _x(M, K)
     return (x, nvfp4_gs_scale_cuda(x))
@@ -394,6 +435,7 @@ def _inputs_nvfp4(M, K):
 _TABLE = [
     ("fp8_tensorwise_precalc_scale", "Float8TensorwiseGold", float8_tensorwise_cuda, _inputs_tensorwise, "elementwise"),
     ("fp8_rowwise_precalc_scale", "RowwisePrecalcGold", rowwise_precalc_cuda, _inputs_rowwise_precalc, "elementwise"),
+    ("fp8_colwise_precalc_scale", "ColwisePrecalcGold", colwise_precalc_cuda, _inputs_colwise_precalc, "elementwise"),
     ("mxfp8", "Mxfp8Gold", mxfp8_cuda, _inputs_x, "(1,32) block"),
     ("mxfp8_swizzle", "Mxfp8SwizzleGold", mxfp8_swizzle_cuda, _inputs_x, "(1,32) block, swizzle"),
     ("mxfp8_dim_m", "Mxfp8DimMGold", mxfp8_dim_m_cuda, _inputs_x, "(32,1) block, t-contig"),
@@ -402,6 +444,7 @@ _TABLE = [
     ("mxfp8_dim_km_swizzle", "Mxfp8DimKmSwizzleGold", mxfp8_dim_km_swizzle_cuda, _inputs_x,
      "(1,32) dim-k + (32,1) dim-m, one pass, t-contig, swizzle"),
     ("fp8_rowwise", "RowwiseFp8Gold", rowwise_fp8_cuda, _inputs_x, "(1,-1) block"),
+    ("fp8_colwise", "ColwiseFp8Gold", colwise_fp8_cuda, _inputs_x, "(-1,1) block, t-contig"),
     ("nvfp4", "Nvfp4GsGold", nvfp4_gs_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, no swizzle"),
     ("nvfp4_swizzle", "Nvfp4GsSwizzleGold", nvfp4_gs_swizzle_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, swizzle"),
 ]

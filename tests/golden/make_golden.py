@@ -75,6 +75,9 @@ def main():
         ps = G.rowwise_precalc_scale(x)
         out[f"{tag}/rowwise_precalc_scale/0"] = raw(ps)
         out[f"{tag}/rowwise_precalc_f/0"] = raw(G.rowwise_precalc_f(x, ps)[0])
+        cs = G.colwise_precalc_scale(x)
+        out[f"{tag}/colwise_precalc_scale/0"] = raw(cs)
+        out[f"{tag}/colwise_precalc_f/0"] = raw(G.colwise_precalc_f(x, cs)[0])
         for fn in ("rowwise_fp8_f", "colwise_fp8_f", "mxfp8_f", "mxfp8_swizzle_f", "mxfp8_dim_m_f",
                    "mxfp8_dim_m_swizzle_f", "mxfp8_dim_km_f", "mxfp8_dim_km_swizzle_f"):
             for i, o in enumerate(getattr(G, fn)(x)):

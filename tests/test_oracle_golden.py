@@ -39,6 +39,14 @@ def test_fp8_rowwise_precalc(tag):
 
 
 @pytest.mark.parametrize("tag", golden_cases())
+def test_fp8_colwise_precalc(tag):
+    x = golden_x(tag)
+    cs = O.colwise_precalc_scale(x)
+    assert_same_bits(cs, golden_out(tag, "colwise_precalc_scale", 0), "scale")
+    assert_same_bits(O.colwise_precalc_f(x, cs)[0], golden_out(tag, "colwise_precalc_f", 0), "q")
+
+
+@pytest.mark.parametrize("tag", golden_cases())
 def test_nvfp4(tag):
     x = golden_x(tag)
     gs = O.nvfp4_gs_scale(x)

@@ -116,6 +116,27 @@ def test_fp8_family(fmt, shape):
     same_outputs(Q.rowwise_precalc_cuda(xc, ps, fmt), O.rowwise_precalc_f(x, ps.cpu(), fmt), f"precalc {fmt}")
 
 
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("shape", [(512, 512), (96, 160), (128, 160), (16, 8), (2080, 1056), (4096, 264)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_fp8_colwise(fmt, shape):
+    x = _x(*shape, seed=13, spread=8.0)
+    xc = x.cuda()
+    same_outputs(Q.colwise_fp8_cuda(xc, fmt), O.colwise_fp8_f(x, fmt), f"colwise {fmt} {shape}")
+    cs = Q.colwise_precalc_scale_cuda(xc, fmt)
+    assert_same_bits(cs, O.colwise_precalc_scale(x, fmt), "column scale")
+    same_outputs(Q.colwise_precalc_cuda(xc, cs, fmt), O.colwise_precalc_f(x, cs.cpu(), fmt), f"colwise precalc {fmt} {shape}")
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+def test_golden_fp8_colwise(tag):
+    x = golden_x(tag).cuda()
+    q, s = Q.colwise_fp8_cuda(x)
+    assert_same_bits(q, golden_out(tag, "colwise_fp8_f", 0), "colwise q")
+    assert_same_bits(s, golden_out(tag, "colwise_fp8_f", 1), "colwise scale")
+    cs = golden_out(tag, "colwise_precalc_scale", 0).view(torch.float32).cuda()
+    assert_same_bits(Q.colwise_precalc_cuda(x, cs)[0], golden_out(tag, "colwise_precalc_f", 0), "colwise precalc q")
+
+
 def test_fp8_all_zero_and_tiny():
     x = torch.zeros(64, 256, dtype=torch.bfloat16)
     x[3, 5] = 1e-30
@@ -346,8 +367,8 @@ def test_host_buffer_caster_matches_oracle(swizzle):
 
 def test_recipe_index_mirrors_reference_backends():
     names = [n for n, _ in Q.ALL_RECIPES]
-    assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
-                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "nvfp4", "nvfp4_swizzle"]
+    assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "fp8_colwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
+                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
         outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
