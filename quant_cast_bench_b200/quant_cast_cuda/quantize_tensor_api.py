@@ -1,0 +1,185 @@
+"""`quantize_tensor` / `quantize_tensor_bidirectional` over the CUDA casts.
+
+Same keyword surface, enums, return values and error behaviour as the proposed user-facing API of
+vkuzo/quant_cast_bench (experiments/quantize_tensor_api/api.py:76-298), which dispatches
+`(scaling_type, orientation, swizzle_type)` to that project's Triton recipes; here every supported
+combination lands on a kernel of this package.  On top of the reference's table this backend also takes:
+the transposed and the bidirectional nvfp4 casts, stochastic rounding for nvfp4 (`random_key` = uint64
+[seed, offset], see `philox_key`), and `InnerScaleCalc.E8M0_FLOOR`.
+
+3-D `(E, M, K)` inputs are quantised per expert (scaling never crosses the E dimension, blocked scales
+are per expert and returned flattened as `(E, flat_len)`), one launch per expert into slices of the
+stacked outputs.  The 32x32 block recipes of the reference are not part of this backend.
+"""
+from enum import IntEnum
+
+import torch
+from torch import Tensor
+
+try:  # core enum (NO_SWIZZLE = 0, SWIZZLE_32_4_4 = 1) where this torch has it
+    from torch.nn.functional import SwizzleType
+except ImportError:  # pragma: no cover
+    class SwizzleType(IntEnum):
+        NO_SWIZZLE = 0
+        SWIZZLE_32_4_4 = 1
+
+try:
+    from enum import StrEnum
+except ImportError:  # pragma: no cover
+    from enum import Enum
+
+    class StrEnum(str, Enum):
+        pass
+
+from . import _lib as L
+from . import recipes as R
+
+
+class ScalingType(IntEnum):
+    """Mirrors torch.nn.functional.ScalingType values (api.py:36-48)."""
+    TensorWise = 0
+    RowWise = 1
+    BlockWise1x16 = 2
+    BlockWise1x32 = 3
+    BlockWise1x128 = 4
+    BlockWise128x128 = 5
+    BlockWise32x32 = 6
+
+
+class QuantOrientation(StrEnum):
+    NATURAL = "natural"          # block maps to (M, K) as given
+    TRANSPOSED = "transposed"    # block maps to the (K, M) view; outputs written transposed-contiguous
+
+
+class RoundingMode(StrEnum):
+    RTNE = "rtne"
+    STOCHASTIC = "stochastic"
+
+
+class InnerScaleCalc(StrEnum):
+    E8M0_RCEIL = "e8m0_rceil"
+    E8M0_FLOOR = "e8m0_floor"    # addition of this backend (OCP MX FLOOR mode)
+    E4M3_NVFP4 = "e4m3_nvfp4"
+
+
+def _is_swz(swizzle_type):
+    if swizzle_type == SwizzleType.SWIZZLE_32_4_4:
+        return True
+    if swizzle_type == SwizzleType.NO_SWIZZLE:
+        return False
+    raise ValueError(f"unsupported swizzle_type={swizzle_type!r}; supported: NO_SWIZZLE, SWIZZLE_32_4_4")
+
+
+def _mx_flags(inner_scale_calc, swz):
+    return (L.SWIZZLE if swz else 0) | (L.FLOOR if inner_scale_calc == InnerScaleCalc.E8M0_FLOOR else 0)
+
+
+def _per_expert(x, flags):
+    """mxfp8 of every (M, K) slice of a contiguous (E, M, K) tensor into stacked outputs."""
+    E, M, K = x.shape
+    dev, u8 = x.device, torch.uint8
+    swz = bool(flags & L.SWIZZLE)
+    row, col = bool(flags & L.ROWWISE), bool(flags & L.COLWISE)
+    qk = torch.empty((E, M, K), dtype=u8, device=dev) if row else None
+    qm = torch.empty((E, K, M), dtype=u8, device=dev) if col else None
+    nk = R.blocked_shape(M, K // 32) if swz else (M, K // 32)
+    nm = R.blocked_shape(K, M // 32) if swz else (K, M // 32)
+    sk = torch.empty((E,) + tuple(nk), dtype=u8, device=dev) if row else None
+    sm = torch.empty((E,) + tuple(nm), dtype=u8, device=dev) if col else None
+    for e in range(E):
+        R._mxfp8(x[e], flags, out=(qk[e] if row else None, sk[e] if row else None, qm[e] if col else None,
+                                   sm[e] if col else None))
+    f8, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    outs = []
+    if row:
+        outs += [qk.view(f8), (sk.reshape(E, -1) if swz else sk).view(e8)]
+    if col:
+        outs += [qm.view(f8), (sm.reshape(E, -1) if swz else sm).view(e8)]
+    return tuple(outs)
+
+
+def quantize_tensor(input: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4m3fn,
+                    inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL,
+                    scaling_type: ScalingType = ScalingType.BlockWise1x32,
+                    orientation: QuantOrientation = QuantOrientation.NATURAL,
+                    swizzle_type=SwizzleType.SWIZZLE_32_4_4, rounding_mode: RoundingMode = RoundingMode.RTNE,
+                    random_key: Tensor | None = None, outer_scale: Tensor | None = None) -> tuple[Tensor, Tensor]:
+    """One-orientation block-scaled cast: returns (qdata, scale).  See the module docstring for the table."""
+    assert input.dim() in (2, 3), f"only 2D or 3D input supported, got {input.dim()}D"
+    swz = _is_swz(swizzle_type)
+    sr = rounding_mode == RoundingMode.STOCHASTIC
+    if sr != (random_key is not None):
+        raise ValueError("rounding_mode=STOCHASTIC needs random_key, and random_key is only used by it")
+
+    if qdata_dtype == torch.float4_e2m1fn_x2:
+        assert input.dim() == 2, "fp4 quantization is only supported for 2D input"
+        assert input.is_contiguous(), "input must be contiguous"
+        if inner_scale_calc != InnerScaleCalc.E4M3_NVFP4:
+            raise ValueError(f"float4_e2m1fn_x2 qdata requires inner_scale_calc=E4M3_NVFP4 here, got {inner_scale_calc!r} "
+                             "(mxfp4 is not part of this backend)")
+        assert outer_scale is not None, "nvfp4 quantization requires a precomputed outer_scale"
+        if scaling_type != ScalingType.BlockWise1x16:
+            raise ValueError(f"unsupported scaling_type={scaling_type!r} for nvfp4; supported: BlockWise1x16")
+        flags = (L.SWIZZLE if swz else 0) | (L.SR if sr else 0)
+        if outer_scale.ndim == 2:
+            assert outer_scale.shape == (input.shape[0], 1), (
+                f"per-token nvfp4 outer_scale must be (M, 1)=({input.shape[0]}, 1), got {tuple(outer_scale.shape)}")
+            if orientation != QuantOrientation.NATURAL:
+                raise ValueError("per-token nvfp4 supports orientation=NATURAL only")
+        return R._nvfp4(input, outer_scale, flags, key=random_key, transposed=orientation == QuantOrientation.TRANSPOSED)
+
+    assert qdata_dtype == torch.float8_e4m3fn, f"only float8_e4m3fn or float4_e2m1fn_x2 qdata supported, got {qdata_dtype}"
+    if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
+        raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
+    assert outer_scale is None, "outer_scale is only used by nvfp4 (float4_e2m1fn_x2) quantization"
+    if sr:
+        raise NotImplementedError("stochastic rounding is implemented for nvfp4 only")
+    if scaling_type != ScalingType.BlockWise1x32:
+        raise ValueError(f"unsupported scaling_type={scaling_type!r} for mxfp8; supported: BlockWise1x32")
+    if orientation == QuantOrientation.NATURAL:
+        direction = L.ROWWISE
+    elif orientation == QuantOrientation.TRANSPOSED:
+        direction = L.COLWISE
+    else:
+        raise ValueError(f"orientation={orientation!r} is not supported; supported: NATURAL, TRANSPOSED")
+    flags = direction | _mx_flags(inner_scale_calc, swz)
+    if input.dim() == 3:
+        if not swz:
+            raise ValueError("quantize_tensor with 3D (E, N, K) input supports only SWIZZLE_32_4_4")
+        return _per_expert(input.contiguous(), flags)
+    assert input.is_contiguous(), "input must be contiguous"
+    return R._mxfp8(input, flags)
+
+
+def quantize_tensor_bidirectional(input: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4m3fn,
+                                  inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL,
+                                  scaling_type: ScalingType = ScalingType.BlockWise1x32,
+                                  swizzle_type=SwizzleType.SWIZZLE_32_4_4, skip_transposed_qdata: bool = False,
+                                  rounding_mode: RoundingMode = RoundingMode.RTNE, random_key: Tensor | None = None,
+                                  outer_scale: Tensor | None = None):
+    """Both orientations from one read of `input`: returns (qk, sk, qm, sm)."""
+    assert input.dim() in (2, 3), f"only 2D or 3D input supported, got {input.dim()}D"
+    if rounding_mode == RoundingMode.STOCHASTIC or random_key is not None:
+        raise NotImplementedError("stochastic rounding is not implemented for the bidirectional casts")
+    if skip_transposed_qdata:
+        raise NotImplementedError("skip_transposed_qdata belongs to the 32x32 block recipes, which this backend lacks")
+    swz = _is_swz(swizzle_type)
+    if qdata_dtype == torch.float4_e2m1fn_x2:
+        assert input.dim() == 2 and input.is_contiguous(), "nvfp4 bidirectional takes a contiguous 2D input"
+        if inner_scale_calc != InnerScaleCalc.E4M3_NVFP4 or scaling_type != ScalingType.BlockWise1x16:
+            raise ValueError("nvfp4 bidirectional takes inner_scale_calc=E4M3_NVFP4 and scaling_type=BlockWise1x16")
+        assert outer_scale is not None and outer_scale.numel() == 1, "nvfp4 bidirectional needs a per-tensor outer_scale"
+        return R._nvfp4_both(input, outer_scale, L.SWIZZLE if swz else 0)
+    assert qdata_dtype == torch.float8_e4m3fn, f"only float8_e4m3fn or float4_e2m1fn_x2 qdata supported, got {qdata_dtype}"
+    if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
+        raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
+    assert outer_scale is None, "outer_scale is only used by nvfp4 (float4_e2m1fn_x2) quantization"
+    if scaling_type != ScalingType.BlockWise1x32:
+        raise ValueError(f"unsupported scaling_type={scaling_type!r}; supported: BlockWise1x32")
+    flags = L.ROWWISE | L.COLWISE | _mx_flags(inner_scale_calc, swz)
+    if input.dim() == 3:
+        if not swz:
+            raise ValueError("quantize_tensor_bidirectional with 3D (E, N, K) input supports only SWIZZLE_32_4_4")
+        return _per_expert(input.contiguous(), flags)
+    assert input.is_contiguous(), "input must be contiguous"
+    return R._mxfp8(input, flags)

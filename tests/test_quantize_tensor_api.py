@@ -1,0 +1,77 @@
+"""The `quantize_tensor` dispatch against the CPU oracle: every supported (scaling, orientation, swizzle)
+combination of the reference's table (experiments/quantize_tensor_api/api.py:76-298, tested there by
+test_dense.py) plus the additions of this backend, and the errors for unsupported ones."""
+import pytest
+import torch
+
+from helpers import same_outputs, assert_same_bits
+from oracle import gold_port as O
+from quant_cast_bench_b200 import quant_cast_cuda as Q
+from quant_cast_bench_b200.quant_cast_cuda import quantize_tensor_api as A
+from quant_cast_bench_b200.workloads import make_input
+
+pytestmark = pytest.mark.gpu
+SW, NOSW = A.SwizzleType.SWIZZLE_32_4_4, A.SwizzleType.NO_SWIZZLE
+NAT, TR = A.QuantOrientation.NATURAL, A.QuantOrientation.TRANSPOSED
+
+
+def test_mxfp8_table():
+    x = make_input(256, 384, seed=3)
+    xc = x.cuda()
+    for orient, swz, ofn in ((NAT, NOSW, O.mxfp8_f), (NAT, SW, O.mxfp8_swizzle_f), (TR, NOSW, O.mxfp8_dim_m_f), (TR, SW, O.mxfp8_dim_m_swizzle_f)):
+        same_outputs(A.quantize_tensor(xc, orientation=orient, swizzle_type=swz), ofn(x), f"{orient} {swz}")
+        same_outputs(A.quantize_tensor(xc, orientation=orient, swizzle_type=swz, inner_scale_calc=A.InnerScaleCalc.E8M0_FLOOR),
+                     ofn(x, mode="floor"), f"floor {orient} {swz}")
+    same_outputs(A.quantize_tensor_bidirectional(xc, swizzle_type=SW), O.mxfp8_dim_km_swizzle_f(x), "bidirectional swizzle")
+    same_outputs(A.quantize_tensor_bidirectional(xc, swizzle_type=NOSW), O.mxfp8_dim_km_f(x), "bidirectional plain")
+
+
+def test_nvfp4_table():
+    x = make_input(256, 384, seed=4)
+    xc = x.cuda()
+    gs = Q.nvfp4_gs_scale_cuda(xc)
+    kw = dict(qdata_dtype=torch.float4_e2m1fn_x2, inner_scale_calc=A.InnerScaleCalc.E4M3_NVFP4, scaling_type=A.ScalingType.BlockWise1x16)
+    same_outputs(A.quantize_tensor(xc, outer_scale=gs, swizzle_type=SW, **kw), O.nvfp4_gs_swizzle_f(x, gs.cpu()), "nvfp4 swizzle")
+    same_outputs(A.quantize_tensor(xc, outer_scale=gs, swizzle_type=NOSW, **kw), O.nvfp4_gs_f(x, gs.cpu()), "nvfp4 plain")
+    same_outputs(A.quantize_tensor(xc, outer_scale=gs, swizzle_type=SW, orientation=TR, **kw), O.nvfp4_gs_swizzle_t_f(x, gs.cpu()), "nvfp4 transposed")
+    pt = (x.float().abs().amax(dim=1, keepdim=True).clamp(min=2.0 ** -100) / 2688.0)
+    same_outputs(A.quantize_tensor(xc, outer_scale=pt.cuda(), swizzle_type=NOSW, **kw), O.nvfp4_gs_f(x, pt), "nvfp4 per-token")
+    key = Q.philox_key(7)
+    same_outputs(A.quantize_tensor(xc, outer_scale=gs, swizzle_type=SW, rounding_mode=A.RoundingMode.STOCHASTIC, random_key=key, **kw),
+                 O.nvfp4_gs_swizzle_sr_f(x, gs.cpu(), (7, 0)), "nvfp4 stochastic")
+    same_outputs(A.quantize_tensor_bidirectional(xc, outer_scale=gs, swizzle_type=SW, **kw),
+                 O.nvfp4_gs_swizzle_f(x, gs.cpu()) + O.nvfp4_gs_swizzle_t_f(x, gs.cpu()), "nvfp4 bidirectional")
+
+
+def test_per_expert_3d():
+    E, M, K = 3, 160, 256
+    x = make_input(E * M, K, seed=5).reshape(E, M, K)
+    xc = x.cuda()
+    q, s = A.quantize_tensor(xc)
+    assert q.shape == (E, M, K) and s.shape[0] == E and s.dim() == 2
+    qt, st = A.quantize_tensor(xc, orientation=TR)
+    qk, sk, qm, sm = A.quantize_tensor_bidirectional(xc)
+    for e in range(E):
+        wq, ws = O.mxfp8_swizzle_f(x[e].contiguous())
+        assert_same_bits(q[e], wq, f"expert {e} q")
+        assert_same_bits(s[e], ws.reshape(-1), f"expert {e} scale")
+        wqt, wst = O.mxfp8_dim_m_swizzle_f(x[e].contiguous())
+        assert_same_bits(qt[e], wqt, f"expert {e} transposed q")
+        assert_same_bits(st[e], wst.reshape(-1), f"expert {e} transposed scale")
+        assert_same_bits(qk[e], wq, "bidir qk"); assert_same_bits(sk[e], ws.reshape(-1), "bidir sk")
+        assert_same_bits(qm[e], wqt, "bidir qm"); assert_same_bits(sm[e], wst.reshape(-1), "bidir sm")
+
+
+def test_unsupported_combinations_raise():
+    x = torch.randn(64, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        A.quantize_tensor(x, scaling_type=A.ScalingType.BlockWise32x32)
+    with pytest.raises(ValueError):
+        A.quantize_tensor(x, rounding_mode=A.RoundingMode.STOCHASTIC)
+    with pytest.raises(AssertionError):
+        A.quantize_tensor(x, qdata_dtype=torch.float4_e2m1fn_x2, inner_scale_calc=A.InnerScaleCalc.E4M3_NVFP4,
+                          scaling_type=A.ScalingType.BlockWise1x16)            # no outer_scale
+    with pytest.raises(NotImplementedError):
+        A.quantize_tensor_bidirectional(x, skip_transposed_qdata=True)
+    with pytest.raises(ValueError):
+        A.quantize_tensor(x.reshape(1, 64, 64), swizzle_type=NOSW)
