@@ -391,6 +391,14 @@ def bench_other_casts(Q, x, dev, peak):
     out = {}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
+    flush_graph = torch.cuda.CUDAGraph()
+    _side = torch.cuda.Stream()
+    flush.zero_()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(flush_graph, stream=_side):
+        for _ in range(10):
+            flush.zero_()
+
     def timed(fn, nbytes, flush_l2=False, iters=10):
         """Launches are replayed from CUDA graphs so that host-side launch cost never sits between the
         events.  `ms`: one launch right after a 256 MB L2-flush write (the reference's method);
@@ -416,6 +424,25 @@ def bench_other_casts(Q, x, dev, peak):
             torch.cuda.synchronize()
             ts.append(a.elapsed_time(b))
         ms = statistics.median(ts)
+        if flush_l2:
+            # data fit in L2: kernel time with a cold L2 but without launch latency = (10 x [flush, cast]) - (10 x flush),
+            # both replayed from graphs
+            gfk = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gfk, stream=side):
+                for _ in range(10):
+                    flush.zero_()
+                    fn()
+            def replay_ms(g):
+                g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b)
+            ms_cold = (min(replay_ms(gfk) for _ in range(3)) - min(replay_ms(flush_graph) for _ in range(3))) / 10
+            del gfk
         g10.replay()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -429,6 +456,9 @@ def bench_other_casts(Q, x, dev, peak):
         if not flush_l2:
             res["ms_sustained"] = ms_sus
             res["GBps_sustained"] = nbytes / (ms_sus * 1e-3) / 1e9
+        else:
+            res["ms_cold_in_graph"] = ms_cold
+            res["GBps_cold_in_graph"] = nbytes / (ms_cold * 1e-3) / 1e9
         del g1, g10
         return res
 
@@ -450,6 +480,8 @@ def bench_other_casts(Q, x, dev, peak):
     out["nvfp4_16384"] = timed(lambda: Q.nvfp4_gs_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
     out["nvfp4_swizzle_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
     out["nvfp4_swizzle_t_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_t_cuda(x, gs), algorithmic_bytes(M, N, "nvfp4"))
+    out["nvfp4_swizzle_both_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_both_cuda(x, gs), 2 * M * N + 4 + 2 * (M * N // 2 + M * N // 16))
+    out["fp8_colwise_16384"] = timed(lambda: Q.colwise_fp8_cuda(x), algorithmic_bytes(M, N, "fp8_rowwise"))
     key = Q.philox_key(0, device=dev)
     out["nvfp4_swizzle_sr_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key), algorithmic_bytes(M, N, "nvfp4") + 16)
     x1 = x[:4096, :4096].contiguous()          # config 1 shape (fits L2: flush between iterations)

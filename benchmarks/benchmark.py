@@ -58,6 +58,7 @@ def _extensions(x):
         ("mxfp8_swizzle_floor", (x,), lambda: Q.mxfp8_swizzle_cuda(x, mode="floor")),
         ("mxfp8_dim_m_swizzle_floor", (x,), lambda: Q.mxfp8_dim_m_swizzle_cuda(x, mode="floor")),
         ("mxfp8_dim_km_swizzle_floor", (x,), lambda: Q.mxfp8_dim_km_swizzle_cuda(x, mode="floor")),
+        ("nvfp4_swizzle_both", (x, gs), lambda: Q.nvfp4_gs_swizzle_both_cuda(x, gs)),
         ("nvfp4_t", (x, gs), lambda: Q.nvfp4_gs_t_cuda(x, gs)),
         ("nvfp4_swizzle_t", (x, gs), lambda: Q.nvfp4_gs_swizzle_t_cuda(x, gs)),
         ("nvfp4_swizzle_sr", (x, gs, key), lambda: Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key)),
