@@ -61,17 +61,6 @@ __device__ __forceinline__ float amax_of_block(const uint4 c[4])
 constexpr int RS_THREADS = 256;
 constexpr int RS_UNROLL = 2;
 
-struct FastDiv32 {
-    uint32_t mul, shift;
-    void init(uint32_t div)
-    {
-        shift = 0;
-        while ((1ull << shift) < div) shift++;
-        mul = (uint32_t)(((1ull << 32) * ((1ull << shift) - div)) / div + 1);
-    }
-    __device__ __forceinline__ uint32_t div(uint32_t n) const { return (uint32_t)(((uint64_t)__umulhi(n, mul) + n) >> shift); }
-};
-
 template <bool SWZ, bool FLOOR>
 __global__ void __launch_bounds__(RS_THREADS)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
@@ -118,18 +107,6 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             const uint32_t row = div_nb.div(bi), cb = bi - row * nb;
             s[blocked_offset(row, cb, (nb + 3) >> 2)] = (uint8_t)e;
         }
-    }
-}
-
-// Zero the padding of a blocked scale grid that a stream over the real blocks does not visit: rows
-// H..ceil128(H) and scale columns W..ceil4(W).
-__global__ void blocked_zero_pad_kernel(uint8_t *__restrict__ s, uint32_t H, uint32_t W)
-{
-    const uint32_t Hp = ((H + 127) >> 7) << 7, Wp = ((W + 3) >> 2) << 2, ncb = Wp >> 2;
-    const uint64_t total = (uint64_t)Hp * Wp;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t r = (uint32_t)(i / Wp), c = (uint32_t)(i % Wp);
-        if (r >= H || c >= W) s[blocked_offset(r, c, ncb)] = 0;
     }
 }
 

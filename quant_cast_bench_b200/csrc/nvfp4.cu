@@ -21,19 +21,6 @@
 
 namespace qcc {
 
-// n / d for n < 2^32 by multiply-shift (d >= 1)
-struct FastDiv {
-    uint32_t d, mul, shift;
-    __host__ void init(uint32_t div)
-    {
-        d = div;
-        shift = 0;
-        while ((1ull << shift) < div) shift++;
-        mul = (uint32_t)(((1ull << 32) * ((1ull << shift) - div)) / div + 1);
-    }
-    __device__ __forceinline__ uint32_t div(uint32_t n) const { return (uint32_t)(((uint64_t)__umulhi(n, mul) + n) >> shift); }
-};
-
 // One block: 16 bf16 in two uint4 -> 8 packed bytes and the inner scale byte.
 template <bool SR>
 __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer, float inv_outer, const float *lut,
@@ -72,7 +59,7 @@ constexpr int NV_UNROLL = 2;
 
 template <bool SWZ, bool SR, bool PER_ROW>
 __global__ void __launch_bounds__(NV_THREADS)
-nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv div_nb,
+nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                      const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
                      uint8_t *__restrict__ s)
 {
@@ -124,18 +111,6 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         } else if (ok) {
             s[bi] = (uint8_t)byte;
         }
-    }
-}
-
-// Zero the padding of a blocked scale grid that the rowwise stream does not visit: rows M..ceil128(M)
-// and scale columns nb..ceil4(nb).
-__global__ void nvfp4_zero_pad_kernel(uint8_t *__restrict__ s, uint32_t M, uint32_t nb)
-{
-    const uint32_t Hp = ((M + 127) >> 7) << 7, Wp = ((nb + 3) >> 2) << 2, ncb = Wp >> 2;
-    const uint64_t total = (uint64_t)Hp * Wp;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t r = (uint32_t)(i / Wp), c = (uint32_t)(i % Wp);
-        if (r >= M || c >= nb) s[blocked_offset(r, c, ncb)] = 0;
     }
 }
 
@@ -372,14 +347,14 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
     if (M * nb >= (1ll << 32) - 2 * NV_THREADS * NV_UNROLL || nb > 0x7FFFFFFF || M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
     const uint32_t nblocks = (uint32_t)(M * nb);
-    FastDiv dv;
+    FastDiv32 dv;
     dv.init((uint32_t)nb);
     const unsigned grid = (nblocks + NV_THREADS * NV_UNROLL - 1) / (NV_THREADS * NV_UNROLL);
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row != 0;
     const uint16_t *xp = (const uint16_t *)x;
     uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
     if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
-        nvfp4_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(sp, (uint32_t)M, (uint32_t)nb);
+        blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(sp, (uint32_t)M, (uint32_t)nb);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
