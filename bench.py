@@ -31,6 +31,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 M_STEP, N_STEP = 16384, 16384
+# dram__bytes_read.sum + dram__bytes_write.sum of the timed kernel from one ncu capture of an 8192 x 16384 case
+# (profiles/mxfp8_tile64_dim_km_swizzle_8192x16384.txt: 268.5 MB read + 232.2 MB written), scaled by two to the
+# 16384 x 16384 launch; traffic grows in proportion to the tiles processed.  It is below the algorithmic bytes
+# because the last ~90 MB a launch writes are still in L2 when it ends.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (268_485_376 + 232_167_168)
 WORKLOAD = "mxfp8_dim_km_swizzle bf16[16384,16384] (config 2: N(0,1)*2^U(-10,10) per row, 0.1% outliers x100, 1% zero rows)"
 
 
@@ -295,7 +300,7 @@ def run_ours(args):
                    "l2": "inputs (512 MiB) and outputs (528 MiB) exceed the 126 MB L2; no flush between iterations",
                    "vs_baseline_ref": "reference CuTe kernel on B200, 4987.5 GB/s (benchmarks/bench_results.csv:34)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "mxfp8_tile64_kernel<dim_k+dim_m,swizzle,rceil>",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "mxfp8_tile64_kernel<dim_k+dim_m,swizzle,rceil>",
                      "launch_ms_avg": k_avg, "launch_ms_min": k_min, "frac_of_8TBps": achieved / 8000.0},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
