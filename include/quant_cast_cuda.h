@@ -56,8 +56,10 @@ extern "C" {
 /* Library version (major * 100 + minor). */
 int qcc_version(void);
 
-/* Reads and clears the device-side error word of the current device (non-zero means a kernel gave
- * up a bounded wait on a TMA barrier).  Synchronises the device; meant for tests. */
+/* Reads and clears the device-side error word of the current device.  Non-zero: a kernel gave up a
+ * bounded wait on a TMA barrier (codes 1..15), or qcc_mxfp8_grouped was given group offsets that are
+ * not ascending multiples of 32 ending at M (code 16; the scale buffers then hold zeros only).
+ * Synchronises the device. */
 int qcc_device_error(unsigned int *out);
 
 /* Number of SMs of the current device (cached per device). */
@@ -160,6 +162,24 @@ int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
  */
 int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
               void *stream);
+
+/*
+ * mxfp8 of token groups (MoE activations): x is (M, N) with G groups of consecutive rows, offs[g] = end row
+ * of group g (device int32, ascending, every group a multiple of 32 rows).  Element bytes are those of
+ * qcc_mxfp8; the blocked scales are laid out per group, as the grouped block-scaled GEMM reads them
+ * (experiments/quantize_tensor_api/api.py:301-411, moe_utils.py:62-128 of the reference):
+ *   sk: (M + G * 128, N / 32) bytes -- each group's (rows, N/32) scales blocked on their own, padded to 128
+ *       rows, stacked in group order (_to_blocked_2d_m_groups);
+ *   sm: ceil128(N) * (M / 32 + G * 4) bytes -- each group's (N, rows/32) transposed scales blocked on their
+ *       own, columns padded to 4, stored group after group (_to_blocked_2d_k_groups).
+ * flags must contain QCC_SWIZZLE; QCC_ROWWISE needs N % 128 == 0 (as the reference's reshape does).  workspace: qcc_mxfp8_grouped_workspace_bytes(M) bytes of scratch.  At most
+ * 4096 groups.  Both scale buffers are cleared by the call.  offs lives on the device, so it is checked
+ * there: offsets that are not ascending multiples of 32 ending at M leave the scale buffers zero and
+ * set code 16 in the word qcc_device_error reads (the data outputs do not depend on the groups).
+ */
+size_t qcc_mxfp8_grouped_workspace_bytes(int64_t M);
+int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G, void *qk,
+                      void *sk, void *qm, void *sm, void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * nvfp4: 16-element blocks, e4m3 block scales relative to an fp32 outer scale, e2m1 elements

@@ -338,3 +338,58 @@ def nvfp4_gs_swizzle_t_f(x, outer_scale, **kwargs):
 
 def nvfp4_gs_swizzle_t_sr_f(x, outer_scale, key, **kwargs):
     return _nvfp4(x, outer_scale, SWIZZLE | SR, key=key, transposed=True)
+
+
+# ------------------------------------------------------------------ token groups (MoE activations)
+def to_blocked_2d_m_groups(scales, offs):
+    """Blocked layout of (M, W) scales whose rows form token groups ending at `offs`: each group is blocked on
+    its own, padded to 128 rows, and the groups are stacked; result (M + G * 128, W).
+    Follows experiments/quantize_tensor_api/moe_utils.py:62-81 (_to_blocked_2d_m_groups)."""
+    s = scales.contiguous().view(torch.uint8)
+    M, W = s.shape
+    assert W % 4 == 0
+    ends = [int(v) for v in offs.tolist()]
+    out = torch.zeros((M + len(ends) * 128) * W, dtype=torch.uint8)
+    ncb = W // 4
+    start, prow = 0, 0
+    cols = torch.arange(W)
+    for end in ends:
+        size = end - start
+        if size == 0:
+            continue
+        r = torch.arange(size).view(-1, 1) + prow
+        off = ((r // 128) * ncb + cols // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + cols % 4
+        out[off.reshape(-1)] = s[start:end].reshape(-1)
+        prow += _cdiv(size, 128) * 128
+        start = end
+    return out.view(M + len(ends) * 128, W).view(scales.dtype)
+
+
+def to_blocked_2d_k_groups(scales, offs):
+    """Blocked layout of (H, W) scales whose COLUMNS form groups ending at `offs` (in scale columns): each group
+    (H, w_g) is blocked on its own, columns padded to 4, and stored group after group; result
+    (ceil128(H), W + G * 4).  Follows moe_utils.py:93-128 (_to_blocked_2d_k_groups)."""
+    s = scales.contiguous().view(torch.uint8)
+    H, W = s.shape
+    Hp = _cdiv(H, 128) * 128
+    ends = [int(v) for v in offs.tolist()]
+    out = torch.zeros(Hp * (W + len(ends) * 4), dtype=torch.uint8)
+    start, pcol = 0, 0
+    r = torch.arange(H).view(-1, 1)
+    for end in ends:
+        size = end - start
+        if size == 0:
+            continue
+        ncb = _cdiv(size, 4)
+        c = torch.arange(size)
+        off = pcol * Hp + ((r // 128) * ncb + c // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + c % 4
+        out[off.reshape(-1)] = s[:, start:end].reshape(-1)
+        pcol += ncb * 4
+        start = end
+    return out.view(Hp, W + len(ends) * 4).view(scales.dtype)
+
+
+def quantize_grouped(x, offs, mode="rceil"):
+    """(q (M, C), sk grouped, q_t (C, M), sm grouped): api.py:301-411 (quantize_tensor_grouped_bidirectional)."""
+    qk, sk, qm, sm = _mxfp8(x, ROWWISE | COLWISE | _mode(mode))
+    return qk, to_blocked_2d_m_groups(sk, offs), qm, to_blocked_2d_k_groups(sm, offs // 32)

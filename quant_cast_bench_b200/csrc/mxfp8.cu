@@ -64,7 +64,7 @@ constexpr int RS_UNROLL = 2;
 template <bool SWZ, bool FLOOR>
 __global__ void __launch_bounds__(RS_THREADS)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
-                            uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+                            uint8_t *__restrict__ q, uint8_t *__restrict__ s, const int32_t *__restrict__ row_map)
 {
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint4 *qv = reinterpret_cast<uint4 *>(q);
@@ -100,12 +100,18 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 1) << 8);
             v |= __shfl_down_sync(0xFFFFFFFFu, v, 2) << 16;
             if (ok && (threadIdx.x & 3) == 0) {
-                const uint32_t row = div_nb.div(bi), cb = bi - row * nb;
-                *reinterpret_cast<uint32_t *>(s + blocked_offset(row, cb, nb >> 2)) = v;
+                uint32_t row = div_nb.div(bi);
+                const uint32_t cb = bi - row * nb;
+                int32_t dst = (int32_t)row;
+                if (row_map) dst = __ldg(row_map + row);      // token groups: row inside the padded, stacked groups
+                if (dst >= 0) *reinterpret_cast<uint32_t *>(s + blocked_offset((uint32_t)dst, cb, nb >> 2)) = v;
             }
         } else if (ok) {
-            const uint32_t row = div_nb.div(bi), cb = bi - row * nb;
-            s[blocked_offset(row, cb, (nb + 3) >> 2)] = (uint8_t)e;
+            uint32_t row = div_nb.div(bi);
+            const uint32_t cb = bi - row * nb;
+            int32_t dst = (int32_t)row;
+            if (row_map) dst = __ldg(row_map + row);
+            if (dst >= 0) s[blocked_offset((uint32_t)dst, cb, (nb + 3) >> 2)] = (uint8_t)e;
         }
     }
 }
@@ -119,6 +125,17 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
 // sweep is row-major, which measured best on B200 (the 128-byte segments of x rows and of the
 // rowwise output written at the same time are neighbours; taller groups favour the transposed
 // output instead).
+// Scale placement tables of the token-group casts (all null for the plain casts).
+//   row_map[r]  row of x -> row inside the 128-padded, stacked groups (-1: not in any group)
+//   mb_a[b]     32-row block b of x -> byte offset of its scale column inside its group's blocked matrix
+//               (group base + (column / 4) * 512 + column % 4), 0xFFFFFFFF: not in any group
+//   mb_b[b]     bytes between consecutive 128-row blocks of that group's blocked matrix
+struct GroupTables {
+    const int32_t *row_map;
+    const uint32_t *mb_a;
+    const uint32_t *mb_b;
+};
+
 #ifndef QCC_MX_GROUP_M
 #define QCC_MX_GROUP_M 1
 #endif
@@ -152,7 +169,7 @@ struct T64 {
 template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
 __global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS, T64<DO_K, DO_M>::MIN_CTAS)
 mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
-                    uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n)
+                    uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n, GroupTables g)
 {
     using L = T64<DO_K, DO_M>;
     extern __shared__ uint8_t smem_raw[];
@@ -218,9 +235,13 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
         const int C = tile_n * 4;
         if (SWZ) {
             const uint32_t ncb = (nb + 3) >> 2;
-            const uint32_t rr = (uint32_t)R & 127u;
-            const size_t off = ((size_t)(R >> 7) * ncb + tile_n) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u;
-            *reinterpret_cast<uint32_t *>(sk + off) = sbytes;      // padding rows carry zeros (zero-filled x)
+            int32_t Rd = R;
+            if (g.row_map) Rd = R < M ? __ldg(g.row_map + R) : -1;   // token groups: row inside the stacked groups
+            if (Rd >= 0) {
+                const uint32_t rr = (uint32_t)Rd & 127u;
+                const size_t off = ((size_t)(Rd >> 7) * ncb + tile_n) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u;
+                *reinterpret_cast<uint32_t *>(sk + off) = sbytes;  // padding rows carry zeros (zero-filled x)
+            }
         } else if (R < M) {
             uint8_t *dst = sk + (size_t)R * nb + C;
             if ((nb & 3) == 0) {
@@ -300,7 +321,18 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
             const int c = (b * 32 + lane) * 2 + h;
             const int Cn = tile_n * 128 + c;
             const uint16_t v = *reinterpret_cast<const uint16_t *>(sms + c * 2);
-            if (SWZ) {
+            if (SWZ && g.mb_a) {
+                // token groups: every 32-row block of x has its own place (group base, column inside the group)
+#pragma unroll
+                for (int hb = 0; hb < 2; hb++) {
+                    const int mblk = tile_m * 2 + hb;
+                    if (Cn < N && mblk < mb) {
+                        const uint32_t a = __ldg(g.mb_a + mblk);
+                        if (a != 0xFFFFFFFFu)
+                            sm[(size_t)a + (size_t)tile_n * __ldg(g.mb_b + mblk) + (c & 31) * 16u + (c >> 5) * 4u] = (uint8_t)(v >> (8 * hb));
+                    }
+                }
+            } else if (SWZ) {
                 const uint32_t ncb = (mb + 3) >> 2;
                 const size_t off = ((size_t)tile_n * ncb + (tile_m >> 1)) * 512u + (c & 31) * 16u + (c >> 5) * 4u + (tile_m & 1) * 2u;
                 *reinterpret_cast<uint16_t *>(sm + off) = v;       // padding columns carry zeros (zero-filled x)
@@ -314,7 +346,8 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
 }
 
 template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
-static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st)
+static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st,
+                      GroupTables g)
 {
     using L = T64<DO_K, DO_M>;
     auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR>;
@@ -331,10 +364,11 @@ static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *
     // With blocked scales the tiles must cover whole 128-row atoms so that the padding gets its zeros:
     // a tile that lies entirely below the matrix loads zero-filled data and stores nothing but scales.
     const int tiles_n = (N + 127) / 128;
-    const int tiles_m = SWZ ? 2 * ((M + 127) / 128) : (M + T64_ROWS - 1) / T64_ROWS;
+    // (the token-group casts clear their scale buffers up front instead)
+    const int tiles_m = (SWZ && !g.row_map) ? 2 * ((M + 127) / 128) : (M + T64_ROWS - 1) / T64_ROWS;
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, L::THREADS, L::ALLOC, st>>>(tx, qk, sk, qm, sm, M, N, tiles_m, tiles_n);
+    kern<<<(unsigned)num_tiles, L::THREADS, L::ALLOC, st>>>(tx, qk, sk, qm, sm, M, N, tiles_m, tiles_n, g);
     return (int)cudaGetLastError();
 }
 
@@ -344,8 +378,8 @@ using namespace qcc;
 
 extern "C" int qcc_mxfp8_device_error(unsigned int *out) { return read_clear_device_error(out); }
 
-extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
-                         void *stream)
+static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
+                       void *stream, GroupTables g)
 {
     const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
     if (M == 0 || N == 0) return 0;
@@ -365,7 +399,7 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
         const uint32_t nblocks = (uint32_t)(M * nb);
         FastDiv32 dv;
         dv.init((uint32_t)nb);
-        if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
+        if (swz && !g.row_map && ((M & 127) != 0 || (nb & 3) != 0)) {
             blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(skp, (uint32_t)M, (uint32_t)nb);
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return (int)e;
@@ -374,11 +408,11 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
         if (swz) {
-            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
-            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
+            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
         } else {
-            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
-            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
+            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
+            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
         }
         return (int)cudaGetLastError();
     }
@@ -392,12 +426,112 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
         int e = make_tensor_map(&t64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (e) return e;
 #define QCC_T64(DO_K)                                                                                        \
-    (swz ? (fl ? launch_t64<DO_K, true, true, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)             \
-               : launch_t64<DO_K, true, true, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st))           \
-         : (fl ? launch_t64<DO_K, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)            \
-               : launch_t64<DO_K, true, false, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st)))
+    (swz ? (fl ? launch_t64<DO_K, true, true, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)             \
+               : launch_t64<DO_K, true, true, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g))           \
+         : (fl ? launch_t64<DO_K, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)            \
+               : launch_t64<DO_K, true, false, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)))
         if (row) return QCC_T64(true);
         return QCC_T64(false);
 #undef QCC_T64
     }
+}
+
+extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
+                         void *stream)
+{
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr});
+}
+
+// ---------------------------------------------------------------------------------------------
+// token groups (MoE activations): blocked scales per group
+// ---------------------------------------------------------------------------------------------
+namespace qcc {
+
+constexpr int GROUPS_MAX = 4096;
+constexpr unsigned int QCC_DEVERR_GROUPS = 16u;   // reported by qcc_device_error
+
+// offs[g] = end row of group g (ascending, multiples of 32).  Fills the three tables of GroupTables.
+// Every CTA recomputes the (short) prefix sums over the groups, then fills its share of the tables.
+__global__ void __launch_bounds__(256) group_tables_kernel(const int32_t *__restrict__ offs, int G, int M, int padded_c,
+                                                          int32_t *__restrict__ row_map, uint32_t *__restrict__ mb_a,
+                                                          uint32_t *__restrict__ mb_b)
+{
+    __shared__ int32_t s_end[GROUPS_MAX];
+    __shared__ int32_t s_prow[GROUPS_MAX];     // first row of the group inside the stacked, 128-padded groups
+    __shared__ uint32_t s_pcol[GROUPS_MAX];    // first scale column of the group after padding each group to 4
+    for (int i = threadIdx.x; i < G; i += blockDim.x) s_end[i] = offs[i];
+    __syncthreads();
+    int bad = 0;
+    if (threadIdx.x == 0) {
+        int32_t prow = 0, start = 0;
+        uint32_t pcol = 0;
+        for (int i = 0; i < G; i++) {
+            const int32_t size = s_end[i] - start;
+            bad |= (size < 0) | (s_end[i] & 31) | (s_end[i] > M);
+            s_prow[i] = prow;
+            s_pcol[i] = pcol;
+            if (size > 0) {
+                prow += ((size + 127) >> 7) << 7;
+                pcol += (uint32_t)((((size >> 5) + 3) >> 2) << 2);
+                start = s_end[i];
+            }
+        }
+        bad |= (start != M);
+        if (bad && blockIdx.x == 0) atomicMax(&g_qcc_error, QCC_DEVERR_GROUPS);
+    }
+    // offsets that are not ascending multiples of 32 ending at M: no scale is written at all
+    const int total = __syncthreads_or(bad) ? 0 : s_end[G - 1];
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
+        int32_t dst = -1;
+        uint32_t a = 0xFFFFFFFFu, bstride = 0;
+        if (r < total) {
+            int lo = 0, hi = G - 1;                 // first group whose end is above r
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (s_end[mid] > r) hi = mid; else lo = mid + 1;
+            }
+            const int start = lo > 0 ? s_end[lo - 1] : 0;
+            const int size = s_end[lo] - start;
+            dst = s_prow[lo] + (r - start);
+            const uint32_t cg = (uint32_t)(r - start) >> 5;
+            const uint32_t ncb = (uint32_t)(((size >> 5) + 3) >> 2);
+            a = s_pcol[lo] * (uint32_t)padded_c + (cg >> 2) * 512u + (cg & 3u);
+            bstride = ncb * 512u;
+        }
+        row_map[r] = dst;
+        if ((r & 31) == 0) { mb_a[r >> 5] = a; mb_b[r >> 5] = bstride; }
+    }
+}
+
+}  // namespace qcc
+
+extern "C" size_t qcc_mxfp8_grouped_workspace_bytes(int64_t M)
+{
+    return (size_t)(M * 4 + 2 * ((M + 31) / 32) * 4 + 64);
+}
+
+extern "C" int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G, void *qk,
+                                 void *sk, void *qm, void *sm, void *workspace, size_t workspace_bytes, void *stream)
+{
+    const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
+    if (M == 0 || N == 0) return 0;
+    if (!offs || !workspace || G <= 0 || !(flags & QCC_SWIZZLE)) return QCC_ERR_ARG;
+    if (G > GROUPS_MAX || M % 32 != 0 || M > 0x7FFFFF00) return QCC_ERR_SHAPE;
+    if (row && N % 128 != 0) return QCC_ERR_SHAPE;   // (M + G * 128, N / 32) holds whole 4-column atoms only
+    if (workspace_bytes < qcc_mxfp8_grouped_workspace_bytes(M)) return QCC_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return QCC_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t nb = N / 32, mb = M / 32, padded_c = ((N + 127) / 128) * 128;
+    if ((uint64_t)padded_c * (uint64_t)(mb + G * 4) >= (1ull << 32)) return QCC_ERR_SHAPE;
+    int32_t *row_map = (int32_t *)workspace;
+    uint32_t *mb_a = (uint32_t *)(row_map + M);
+    uint32_t *mb_b = mb_a + mb;
+    cudaError_t e;
+    if (row && sk && (e = cudaMemsetAsync(sk, 0, (size_t)(M + G * 128) * nb, st)) != cudaSuccess) return (int)e;
+    if (col && sm && (e = cudaMemsetAsync(sm, 0, (size_t)padded_c * (mb + G * 4), st)) != cudaSuccess) return (int)e;
+    int grid = (int)((M + 255) / 256);
+    if (grid > sm_count()) grid = sm_count();
+    group_tables_kernel<<<grid, 256, 0, st>>>(offs, (int)G, (int)M, (int)padded_c, row_map, mb_a, mb_b);
+    if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b});
 }

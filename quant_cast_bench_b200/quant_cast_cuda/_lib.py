@@ -38,6 +38,8 @@ SIGNATURES = {
     "qcc_fp8_colwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "qcc_fp8_colwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
     "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "qcc_mxfp8_grouped_workspace_bytes": (_sz, [_i64]),
+    "qcc_mxfp8_grouped": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "qcc_nvfp4": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_both": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp, _vp]),
@@ -71,3 +73,12 @@ def check(rc, what):
     if rc < 0:
         raise ValueError(f"{what}: {ERRORS.get(rc, rc)}")
     raise RuntimeError(f"{what}: CUDA error {rc}")
+
+
+def device_error():
+    """Reads and clears the device-side error word of the current CUDA device (synchronises): 0 when no kernel
+    reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets."""
+    v = ctypes.c_uint(0)
+    check(load().qcc_device_error(ctypes.byref(v)), "device_error")
+    return int(v.value)
+

@@ -10,6 +10,11 @@ the transposed and the bidirectional nvfp4 casts, stochastic rounding for nvfp4 
 3-D `(E, M, K)` inputs are quantised per expert (scaling never crosses the E dimension, blocked scales
 are per expert and returned flattened as `(E, flat_len)`), one launch per expert into slices of the
 stacked outputs.  The 32x32 block recipes of the reference are not part of this backend.
+
+`quantize_tensor_grouped` / `quantize_tensor_grouped_bidirectional` (api.py:301-411) cast a `(total_M, C)`
+activation whose rows form token groups ending at `offs`: the data is cast as one matrix, the blocked
+scales are laid out per group (moe_utils.py:62-128).  One kernel writes data and grouped scales; the
+reference re-lays the scales out afterwards.
 """
 from enum import IntEnum
 
@@ -183,3 +188,82 @@ def quantize_tensor_bidirectional(input: Tensor, *, qdata_dtype: torch.dtype = t
         return _per_expert(input.contiguous(), flags)
     assert input.is_contiguous(), "input must be contiguous"
     return R._mxfp8(input, flags)
+
+
+def _grouped(x, offs, flags):
+    lib = L.load()
+    assert x.dim() == 2, f"grouped casts take a 2D (total_M, C) input, got {x.dim()}D"
+    x = x.contiguous()
+    R._check_x(x)
+    M, C = x.shape
+    assert C % 32 == 0 and M % 32 == 0, f"grouped mxfp8 needs total_M % 32 == 0 and C % 32 == 0, got {(M, C)}"
+    assert offs.dim() == 1 and offs.device == x.device, "offs: 1-D tensor of group ends on the input's device"
+    offs = offs.to(torch.int32).contiguous()
+    G = offs.numel()
+    dev, u8 = x.device, torch.uint8
+    row, col = bool(flags & L.ROWWISE), bool(flags & L.COLWISE)
+    assert not row or C % 128 == 0, f"the natural orientation of a grouped cast needs C % 128 == 0, got C={C}"
+    qk = torch.empty((M, C), dtype=u8, device=dev) if row else None
+    sk = torch.empty((M + G * 128, C // 32), dtype=u8, device=dev) if row else None
+    qm = torch.empty((C, M), dtype=u8, device=dev) if col else None
+    sm = torch.empty((-(-C // 128) * 128, M // 32 + G * 4), dtype=u8, device=dev) if col else None
+    nws = lib.qcc_mxfp8_grouped_workspace_bytes(M)
+    ws = torch.empty(max(nws, 16), dtype=u8, device=dev)
+    with R._on_device(dev):
+        L.check(lib.qcc_mxfp8_grouped(R._p(x), M, C, flags, R._p(offs), G, R._p(qk), R._p(sk), R._p(qm), R._p(sm),
+                                      R._p(ws), nws, R._stream(x)), "mxfp8_grouped")
+    L.launch_count += 1
+    f8, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    outs = []
+    if row:
+        outs += [qk.view(f8), sk.view(e8)]
+    if col:
+        outs += [qm.view(f8), sm.view(e8)]
+    return tuple(outs)
+
+
+def _check_grouped(qdata_dtype, inner_scale_calc, scaling_type, swizzle_type, rounding_mode, random_key, outer_scale, who):
+    assert qdata_dtype == torch.float8_e4m3fn, f"only float8_e4m3fn qdata supported, got {qdata_dtype}"
+    if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
+        raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
+    assert outer_scale is None, f"outer_scale is not supported by {who}"
+    if rounding_mode == RoundingMode.STOCHASTIC or random_key is not None:
+        raise NotImplementedError("stochastic rounding is not implemented for the grouped casts")
+    if scaling_type != ScalingType.BlockWise1x32 or not _is_swz(swizzle_type):
+        raise ValueError(f"unsupported (scaling_type, swizzle_type)=({scaling_type!r}, {swizzle_type!r}); "
+                         f"{who} supports only (BlockWise1x32, SWIZZLE_32_4_4)")
+
+
+def quantize_tensor_grouped(input: Tensor, offs: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4m3fn,
+                            inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL,
+                            scaling_type: ScalingType = ScalingType.BlockWise1x32,
+                            orientation: QuantOrientation = QuantOrientation.NATURAL,
+                            swizzle_type=SwizzleType.SWIZZLE_32_4_4, rounding_mode: RoundingMode = RoundingMode.RTNE,
+                            random_key: Tensor | None = None, outer_scale: Tensor | None = None) -> tuple[Tensor, Tensor]:
+    """One-orientation cast of token groups (api.py:301-359).  `offs[g]` is the row where group g ends; every
+    group size must be a multiple of 32 (the caller pads).  NATURAL: (q (M, C), scales (M + G*128, C/32));
+    TRANSPOSED: (q (C, M), scales (ceil128(C), M/32 + G*4))."""
+    _check_grouped(qdata_dtype, inner_scale_calc, scaling_type, swizzle_type, rounding_mode, random_key, outer_scale,
+                   "quantize_tensor_grouped")
+    if orientation == QuantOrientation.NATURAL:
+        direction = L.ROWWISE
+    elif orientation == QuantOrientation.TRANSPOSED:
+        direction = L.COLWISE
+    else:
+        raise ValueError(f"orientation={orientation!r} is not supported; supported: NATURAL, TRANSPOSED")
+    return _grouped(input, offs, direction | _mx_flags(inner_scale_calc, True))
+
+
+def quantize_tensor_grouped_bidirectional(input: Tensor, offs: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4m3fn,
+                                          inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL,
+                                          scaling_type: ScalingType = ScalingType.BlockWise1x32,
+                                          swizzle_type=SwizzleType.SWIZZLE_32_4_4, skip_transposed_qdata: bool = False,
+                                          rounding_mode: RoundingMode = RoundingMode.RTNE,
+                                          random_key: Tensor | None = None, outer_scale: Tensor | None = None):
+    """Both orientations of the grouped cast from one read of `input` (api.py:362-411):
+    (q_nat, sb_nat, q_t, sb_t)."""
+    _check_grouped(qdata_dtype, inner_scale_calc, scaling_type, swizzle_type, rounding_mode, random_key, outer_scale,
+                   "quantize_tensor_grouped_bidirectional")
+    if skip_transposed_qdata:
+        raise NotImplementedError("skip_transposed_qdata is not supported by quantize_tensor_grouped_bidirectional")
+    return _grouped(input, offs, L.ROWWISE | L.COLWISE | _mx_flags(inner_scale_calc, True))

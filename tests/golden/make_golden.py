@@ -138,6 +138,17 @@ def main():
         sc = torch.randint(0, 256, (H, W), generator=g, dtype=torch.uint8)
         out[f"kat/blocked_{H}x{W}_in"] = raw(sc)
         out[f"kat/blocked_{H}x{W}_out"] = raw(G._to_blocked_4d(sc))
+    # token-group blocked layouts (experiments/quantize_tensor_api/moe_utils.py)
+    from experiments.quantize_tensor_api import moe_utils as MU
+    for name, M, W, offs in (("a", 160, 8, [32, 32, 96, 160]), ("b", 384, 12, [128, 160, 384]), ("c", 64, 4, [64])):
+        sc = torch.randint(1, 256, (M, W), generator=g, dtype=torch.uint8)
+        o = torch.tensor(offs, dtype=torch.int32)
+        out[f"kat/mgroups_{name}_in"] = raw(sc)
+        out[f"kat/mgroups_{name}_offs"] = o.numpy()
+        out[f"kat/mgroups_{name}_out"] = raw(MU._to_blocked_2d_m_groups(sc, o))
+        sct = torch.randint(1, 256, (W * 16, M // 32), generator=g, dtype=torch.uint8)   # (C, M/32) transposed scales
+        out[f"kat/kgroups_{name}_in"] = raw(sct)
+        out[f"kat/kgroups_{name}_out"] = raw(MU._to_blocked_2d_k_groups(sct, o // 32))
     out["kat/bf16_clamp_min"] = raw(torch.zeros(1, dtype=torch.bfloat16).clamp(min=1e-12))
 
     np.savez_compressed(args.out, **out)

@@ -94,6 +94,16 @@ def test_e4m3_decode_e8m0_and_blocked_layout():
     assert g["kat/bf16_clamp_min"].view("uint16")[0] == 0x2B8D
 
 
+def test_token_group_layouts():
+    g = golden()
+    for name in ("a", "b", "c"):
+        offs = torch.from_numpy(g[f"kat/mgroups_{name}_offs"].copy())
+        sc = torch.from_numpy(g[f"kat/mgroups_{name}_in"].copy())
+        assert_same_bits(O.to_blocked_2d_m_groups(sc, offs), torch.from_numpy(g[f"kat/mgroups_{name}_out"].copy()), f"m groups {name}")
+        sct = torch.from_numpy(g[f"kat/kgroups_{name}_in"].copy())
+        assert_same_bits(O.to_blocked_2d_k_groups(sct, offs // 32), torch.from_numpy(g[f"kat/kgroups_{name}_out"].copy()), f"k groups {name}")
+
+
 def test_philox_known_answers():
     """Random123 known-answer vectors for Philox4x32-10."""
     kat = [

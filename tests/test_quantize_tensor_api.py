@@ -8,6 +8,7 @@ from helpers import same_outputs, assert_same_bits
 from oracle import gold_port as O
 from quant_cast_bench_b200 import quant_cast_cuda as Q
 from quant_cast_bench_b200.quant_cast_cuda import quantize_tensor_api as A
+from quant_cast_bench_b200.quant_cast_cuda import _lib as L
 from quant_cast_bench_b200.workloads import make_input
 
 pytestmark = pytest.mark.gpu
@@ -75,3 +76,51 @@ def test_unsupported_combinations_raise():
         A.quantize_tensor_bidirectional(x, skip_transposed_qdata=True)
     with pytest.raises(ValueError):
         A.quantize_tensor(x.reshape(1, 64, 64), swizzle_type=NOSW)
+
+
+@pytest.mark.parametrize("M,C,ends", [
+    (512, 256, [128, 256, 512]),              # groups on 128-row boundaries
+    (384, 384, [32, 32, 160, 384]),           # ragged groups and an empty one
+    (256, 160, [64, 256]),                    # C not a multiple of 128: transposed orientation only
+    (1024, 512, [0, 96, 96, 608, 1024]),      # empty first group, groups that straddle 128-row atoms
+])
+def test_token_groups(M, C, ends):
+    """quantize_tensor_grouped{,_bidirectional} (experiments/quantize_tensor_api/api.py:301-411): data as the
+    ungrouped cast, scales blocked per group (moe_utils.py:62-128; the layout functions are pinned against the
+    reference's in the CPU suite)."""
+    x = make_input(M, C, seed=M + C)
+    xc = x.cuda()
+    offs = torch.tensor(ends, dtype=torch.int32)
+    for mode, calc in (("rceil", A.InnerScaleCalc.E8M0_RCEIL), ("floor", A.InnerScaleCalc.E8M0_FLOOR)):
+        if C % 128:
+            wq, ws = O.mxfp8_dim_m_f(x, mode=mode)
+            same_outputs(A.quantize_tensor_grouped(xc, offs.cuda(), orientation=TR, inner_scale_calc=calc),
+                         (wq, O.to_blocked_2d_k_groups(ws, offs // 32)), f"grouped transposed {mode}")
+            with pytest.raises(AssertionError):
+                A.quantize_tensor_grouped(xc, offs.cuda(), inner_scale_calc=calc)
+            continue
+        want = O.quantize_grouped(x, offs, mode)
+        got = A.quantize_tensor_grouped_bidirectional(xc, offs.cuda(), inner_scale_calc=calc)
+        same_outputs(got, want, f"grouped bidirectional {mode}")
+        same_outputs(A.quantize_tensor_grouped(xc, offs.cuda(), inner_scale_calc=calc), want[:2], f"grouped natural {mode}")
+        same_outputs(A.quantize_tensor_grouped(xc, offs.cuda(), orientation=TR, inner_scale_calc=calc), want[2:],
+                     f"grouped transposed {mode}")
+
+
+def test_token_groups_errors():
+    xc = make_input(128, 128, seed=1).cuda()
+    offs = torch.tensor([128], dtype=torch.int32).cuda()
+    with pytest.raises(ValueError):
+        A.quantize_tensor_grouped(xc, offs, swizzle_type=NOSW)
+    with pytest.raises(NotImplementedError):
+        A.quantize_tensor_grouped_bidirectional(xc, offs, skip_transposed_qdata=True)
+    # offsets live on the device and are checked there: bad ones (a group that is not a multiple of 32 rows,
+    # a last end other than total_M, descending ends) write no scale and raise the device error word
+    want_q = O.mxfp8_f(make_input(128, 128, seed=1))[0]
+    for ends in ([48, 128], [64], [96, 64, 128], [128, 160]):
+        assert L.device_error() == 0
+        q, s = A.quantize_tensor_grouped(xc, torch.tensor(ends, dtype=torch.int32).cuda())
+        assert L.device_error() == 16, ends
+        assert_same_bits(q, want_q, f"data with bad offsets {ends}")
+        assert int(s.view(torch.uint8).max()) == 0
+    assert L.device_error() == 0
