@@ -58,8 +58,9 @@ int qcc_version(void);
 
 /* Reads and clears the device-side error word of the current device.  Non-zero: a kernel gave up a
  * bounded wait on a TMA barrier (codes 1..15), or qcc_mxfp8_grouped was given group offsets that are
- * not ascending multiples of 32 ending at M (code 16; the scale buffers then hold zeros only).
- * Synchronises the device. */
+ * not ascending multiples of 32 ending at M (code 16; the scale buffers then hold zeros only), or a
+ * transform matrix that is not diag(+-1) @ H16 / 4 was passed to one of the qcc_*rht* calls (code 17;
+ * the outputs then follow the signs of its first column).  Synchronises the device. */
 int qcc_device_error(unsigned int *out);
 
 /* Number of SMs of the current device (cached per device). */
@@ -201,8 +202,8 @@ int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer
  * Transposed: the outputs that the rowwise cast gives on x.t().contiguous() (the call of
  * test/test_quant_cast_gold.py:104), without materialising the transpose: q (N, M/2), s over the
  * (N, M/16) frame.  The stochastic-rounding stream is indexed in the transposed frame.
- * Needs M % 32 == 0 (output rows of M/2 bytes must be 16-byte multiples for the TMA store) and
- * N % 8 == 0; outer is a single value.
+ * Needs M % 32 == 0 (output rows of M/2 bytes are written in 16-byte pieces) and N % 8 == 0; outer
+ * is a single value.
  */
 int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
                          const uint64_t *philox_key, void *q, void *s, void *stream);
@@ -215,6 +216,43 @@ int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer
  */
 int qcc_nvfp4_both(const void *x, int64_t M, int64_t N, const float *outer, int flags, void *qk, void *sk,
                    void *qm, void *sm, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * 16-point randomised Hadamard transform (RHT) and the nvfp4 casts built on it
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * rht: device, 16x16 bf16, row-major, = diag(sign) @ H / 4 with H the Sylvester-Walsh matrix
+ * (hadamard_rht_matrix G:1778-1781); only such matrices are supported (checked on the device, code 17 of
+ * qcc_device_error).  y[16 b + j] = bf16(sum_i x[16 b + i] * rht[i][j]) with fp32 accumulation in a fixed
+ * order: butterfly over strides 1, 2, 4, 8, then the exact scaling by 1/4 and one rounding.  The reference
+ * evaluates the same sum as a bf16 matmul whose accumulation order is its GEMM library's; the results agree
+ * bit for bit whenever the 16-term sums are exact in fp32 (block values within a 2^12 magnitude range).
+ */
+
+/* y (M, N) bf16 = the transform of x along the rows (hadamard_rht_f G:1784-1789).  N % 16 == 0. */
+int qcc_hadamard_rht(const void *x, int64_t M, int64_t N, const void *rht, void *y, void *stream);
+
+/*
+ * out[0] = max |RHT(x.t())| (transform down the rows of x, 16-row blocks), as QCC_AMAX_RAW, or divided by
+ * 2688 as QCC_AMAX_NVFP4_SCALE: the dim-m outer scale of G:1364-1365 without materialising the transposed,
+ * transformed tensor.  M % 16 == 0, N % 4 == 0.
+ */
+int qcc_nvfp4_rht_amax(const void *x, int64_t M, int64_t N, const void *rht, int mode, float *out, void *stream);
+
+/*
+ * nvfp4 in both orientations from one read of x, the dim-m half through the transform
+ * (nvfp4_gs_swizzle_dim_k_dim_m_rht_f G:1324-1333; with QCC_SR nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_f
+ * G:1429-1438):
+ *   (qk, sk) = qcc_nvfp4(x, outer_k)                       -- no transform
+ *   (qm, sm) = nvfp4 along M of RHT(x.t()) under outer_m   -- q (N, M/2), scales over the (N, M/16) frame
+ * qk == sk == NULL gives the dim-m half alone.  flags: QCC_SWIZZLE, QCC_SR (key_k / key_m: device uint64[2]
+ * each, the stream of a half indexed by the row-major position in that half's own frame).
+ * Needs M % 32 == 0, N % 8 == 0, and N % 32 == 0 when the dim-k half is requested.
+ */
+int qcc_nvfp4_rht(const void *x, int64_t M, int64_t N, const float *outer_k, const float *outer_m, const void *rht,
+                  int flags, const uint64_t *key_k, const uint64_t *key_m, void *qk, void *sk, void *qm, void *sm,
+                  void *stream);
 
 #ifdef __cplusplus
 }

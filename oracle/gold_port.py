@@ -37,6 +37,8 @@ def lib():
         _lib.qco_nvfp4.restype = ctypes.c_int
         _lib.qco_nvfp4_t.restype = ctypes.c_int
         _lib.qco_num_threads.restype = ctypes.c_int
+        _lib.qco_hadamard_rht.restype = ctypes.c_int
+        _lib.qco_hadamard_rht_t.restype = ctypes.c_int
     return _lib
 
 
@@ -338,6 +340,58 @@ def nvfp4_gs_swizzle_t_f(x, outer_scale, **kwargs):
 
 def nvfp4_gs_swizzle_t_sr_f(x, outer_scale, key, **kwargs):
     return _nvfp4(x, outer_scale, SWIZZLE | SR, key=key, transposed=True)
+
+
+# ------------------------------------------------------------------ randomised Hadamard transform
+def hadamard_rht_matrix(sign_vector, dtype=torch.bfloat16):
+    """diag(sign) @ H / 4 with H[i][j] = (-1)^popcount(i & j) (G:1753-1781)."""
+    i = torch.arange(16)
+    par = (i.view(-1, 1) & i.view(1, -1))
+    par = (par ^ (par >> 1) ^ (par >> 2) ^ (par >> 3)) & 1
+    h = (1.0 - 2.0 * par.float()) / 4.0
+    return (sign_vector.float().view(-1, 1) * h).to(dtype)
+
+
+def rht_sign_mask(rht):
+    """Bit i set where row i of `rht` carries sign -1; asserts that rht is diag(sign) @ H / 4."""
+    sign = torch.where(rht[:, 0].float() < 0, -1.0, 1.0)
+    assert torch.equal(hadamard_rht_matrix(sign, rht.dtype), rht.cpu()), "rht must be diag(+-1) @ H16 / 4"
+    return int(sum(1 << i for i in range(16) if sign[i] < 0))
+
+
+def hadamard_rht_f(x, rht, **kwargs):
+    """gold hadamard_rht_f (G:1784-1789): RHT along the last dim, bf16 out (1-tuple)."""
+    _check_x(x)
+    y = torch.empty_like(x)
+    rc = lib().qco_hadamard_rht(_p(x), _i64(x.shape[0]), _i64(x.shape[1]), ctypes.c_uint32(rht_sign_mask(rht)), _p(y))
+    assert rc == 0, "hadamard_rht: last dim must be a multiple of 16"
+    return (y,)
+
+
+def hadamard_rht_t(x, rht):
+    """RHT(x.t().contiguous()) along M: the (N, M) tensor the dim-m half of G:1324-1333 quantises."""
+    _check_x(x)
+    M, N = x.shape
+    y = torch.empty((N, M), dtype=x.dtype)
+    rc = lib().qco_hadamard_rht_t(_p(x), _i64(M), _i64(N), ctypes.c_uint32(rht_sign_mask(rht)), _p(y))
+    assert rc == 0, "hadamard_rht_t: M must be a multiple of 16"
+    return y
+
+
+def nvfp4_rht_outer_scale_m(x, rht):
+    """The dim-m outer scale of _nvfp4_gs_swizzle_dim_k_dim_m_rht_inputs (G:1364-1365)."""
+    return hadamard_rht_t(x, rht).abs().to(torch.float32).amax() / (448.0 * 6.0)
+
+
+def nvfp4_gs_swizzle_dim_k_dim_m_rht_f(x, outer_scale_k, outer_scale_m, rht, **kwargs):
+    """G:1324-1333: (qk, sk) plain nvfp4 of x; (qm, sm) nvfp4 of RHT(x.t()) along M."""
+    return nvfp4_gs_swizzle_f(x, outer_scale_k) + nvfp4_gs_swizzle_f(hadamard_rht_t(x, rht), outer_scale_m)
+
+
+def nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_f(x, outer_scale_k, outer_scale_m, rht, key_k, key_m, **kwargs):
+    """G:1429-1438: the same with stochastic rounding of both fp4 casts, one Philox key per direction."""
+    return (nvfp4_gs_swizzle_sr_f(x, outer_scale_k, key_k)
+            + nvfp4_gs_swizzle_sr_f(hadamard_rht_t(x, rht), outer_scale_m, key_m))
 
 
 # ------------------------------------------------------------------ token groups (MoE activations)

@@ -572,6 +572,60 @@ int qco_nvfp4_t(const uint16_t *x, int64_t M, int64_t N, const float *outer, int
     return 0;
 }
 
+/*
+ * 16x16 randomised Hadamard transform along the last dim (hadamard_rht_f G:1784-1789 with
+ * rht = diag(sign) @ H / 4, hadamard_rht_matrix G:1778-1781; H the Sylvester-Walsh matrix
+ * H[i][j] = (-1)^popcount(i & j), G:1753-1775):
+ *     y[16 b + j] = bf16( sum_i x[16 b + i] * sign[i] * H[i][j] / 4 ),   fp32 accumulation.
+ * The reference evaluates this as a bf16 matmul, whose fp32 accumulation order belongs to the GEMM
+ * library that runs it.  This restatement fixes the order: the four-stage in-place butterfly
+ * (strides 1, 2, 4, 8; (a, b) -> (a + b, a - b)), then the exact scaling by 1/4 and ONE rounding to
+ * bf16 (nearest even).  Whenever the 16-term sums are exact in fp32 -- inputs of one block within a
+ * 2^12 magnitude range, in practice all activations -- every order gives the same bits; the golden
+ * vectors from the reference's CPU run confirm it for those inputs.
+ * sign_mask: bit i set -> sign[i] = -1.
+ */
+static inline uint16_t f32_to_bf16_rne(float f)
+{
+    uint32_t u = f2u(f);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40u);
+    return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+
+static void rht16(const uint16_t *x, int64_t stride, uint32_t sign_mask, uint16_t *y)
+{
+    float t[16];
+    for (int i = 0; i < 16; i++) t[i] = bf16_to_f32((uint16_t)(x[i * stride] ^ (((sign_mask >> i) & 1u) << 15)));
+    for (int s = 1; s < 16; s <<= 1)
+        for (int i = 0; i < 16; i++)
+            if (!(i & s)) {
+                float a = t[i], b = t[i | s];
+                t[i] = a + b;
+                t[i | s] = a - b;
+            }
+    for (int j = 0; j < 16; j++) y[j] = f32_to_bf16_rne(t[j] * 0.25f);
+}
+
+int qco_hadamard_rht(const uint16_t *x, int64_t rows, int64_t cols, uint32_t sign_mask, uint16_t *y)
+{
+    if (cols % 16) return -1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t b = 0; b < cols / 16; b++) rht16(x + r * cols + b * 16, 1, sign_mask, y + r * cols + b * 16);
+    return 0;
+}
+
+/* y (N, M) = RHT along M of x.t(): the tensor the dim-m half of G:1324-1333 quantises, without the
+ * transposed copy of x. */
+int qco_hadamard_rht_t(const uint16_t *x, int64_t M, int64_t N, uint32_t sign_mask, uint16_t *y)
+{
+    if (M % 16) return -1;
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < N; c++)
+        for (int64_t b = 0; b < M / 16; b++) rht16(x + (b * 16) * N + c, N, sign_mask, y + c * M + b * 16);
+    return 0;
+}
+
 /* torchrun exports OMP_NUM_THREADS=1; the CPU baseline asks for all host threads explicitly */
 void qco_set_num_threads(int n)
 {

@@ -196,6 +196,104 @@ __device__ __forceinline__ uint32_t nvfp4_inner_lut(float amax, float outer, con
     return byte;
 }
 
+// ---------------------------------------------------------------------------------------------
+// 16-point randomised Hadamard transform (hadamard_rht_f G:1784-1789 with rht = diag(sign) @ H / 4)
+// ---------------------------------------------------------------------------------------------
+// y[j] = bf16( (1/4) sum_i sign[i] x[i] (-1)^popcount(i & j) ): in-place fp32 butterfly over strides 1, 2, 4, 8
+// ((a, b) -> (a + b, a - b)), exact scaling by 1/4, one rounding to bf16.  The reference's bf16 matmul leaves
+// the fp32 accumulation order to its GEMM library; this order is the one the CPU oracle restates.
+constexpr unsigned int QCC_DEVERR_RHT = 17u;   // rht is not diag(+-1) @ H16 / 4
+
+// packed fp32 pairs (sm_100 f32x2 arithmetic): two independent lanes, each rounded like the scalar operation
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// (lo / 4, hi / 4) rounded to bf16, lo in the low half
+__device__ __forceinline__ uint32_t quarter_to_bf16x2(uint64_t v)
+{
+    uint32_t r;
+    asm("{\n.reg .b64 q, z;\n.reg .f32 lo, hi;\n"
+        "mov.b64 q, {0f3E800000, 0f3E800000};\n"
+        "mul.rn.f32x2 z, %1, q;\n"
+        "mov.b64 {lo, hi}, z;\n"
+        "cvt.rn.bf16x2.f32 %0, hi, lo;\n}\n"
+        : "=r"(r)
+        : "l"(v));
+    return r;
+}
+
+// Sign mask of the transform from its matrix: bit i set where row i is negated (column 0 of H is all ones).
+// Call with all 32 lanes of the warp.
+__device__ __forceinline__ uint32_t rht_sign_mask(const uint16_t *__restrict__ rht)
+{
+    const uint32_t e = __ldg(rht + (threadIdx.x & 15) * 16);
+    return __ballot_sync(0xFFFFFFFFu, (e >> 15) & 1u) & 0xFFFFu;
+}
+
+// Transform of two independent 16-vectors held as the low and high halves of w[0..15] (bf16x2 words), in place.
+__device__ __forceinline__ void rht16_bf16x2(uint32_t (&w)[16], uint32_t sgn)
+{
+    uint64_t t[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t word = w[i] ^ (((sgn >> i) & 1u) * 0x80008000u);
+        t[i] = pack2(bf16lo(word), bf16hi(word));
+    }
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (!(i & s)) {
+                const uint64_t a = t[i], b = t[i | s];
+                t[i] = add2(a, b);
+                t[i | s] = sub2(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; j++) w[j] = quarter_to_bf16x2(t[j]);
+}
+
+// Transform of one 16-vector of consecutive elements (eight bf16x2 words), in place.
+__device__ __forceinline__ void rht16_bf16_row(uint32_t (&w)[8], uint32_t sgn)
+{
+    float t[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t word = w[i] ^ (((sgn >> (2 * i)) & 1u) << 15) ^ (((sgn >> (2 * i + 1)) & 1u) << 31);
+        t[2 * i] = bf16lo(word);
+        t[2 * i + 1] = bf16hi(word);
+    }
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (!(i & s)) {
+                const float a = t[i], b = t[i | s];
+                t[i] = __fadd_rn(a, b);
+                t[i | s] = __fsub_rn(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) w[j] = quarter_to_bf16x2(pack2(t[2 * j], t[2 * j + 1]));
+}
+
 // Offset of block scale (r, c) in the 32x4x4 blocked layout with `ncb` column blocks (G:1000-1037)
 __device__ __forceinline__ size_t blocked_offset(uint32_t r, uint32_t c, uint32_t ncb)
 {

@@ -60,4 +60,8 @@ inline int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, c
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// Launches the one-CTA check that `rht` (device, 16x16 bf16) is diag(+-1) @ H16 / 4; a matrix of another form
+// sets code 17 in the device error word (defined with the nvfp4 kernels).
+int launch_rht_check(const void *rht, cudaStream_t st);
+
 }  // namespace qcc

@@ -43,6 +43,9 @@ SIGNATURES = {
     "qcc_nvfp4": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_both": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp, _vp]),
+    "qcc_hadamard_rht": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "qcc_nvfp4_rht_amax": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
+    "qcc_nvfp4_rht": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
 }
 
 _lib = None
@@ -77,7 +80,7 @@ def check(rc, what):
 
 def device_error():
     """Reads and clears the device-side error word of the current CUDA device (synchronises): 0 when no kernel
-    reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets."""
+    reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets, 17 an unsupported transform matrix."""
     v = ctypes.c_uint(0)
     check(load().qcc_device_error(ctypes.byref(v)), "device_error")
     return int(v.value)

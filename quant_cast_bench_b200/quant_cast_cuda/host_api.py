@@ -17,7 +17,7 @@ from .recipes import blocked_shape
 class HostMxfp8Caster:
     """mxfp8_dim_km(_swizzle) for an (M, N) bf16 matrix that lives in (pinned) host memory."""
 
-    def __init__(self, M, N, device, swizzle=True, mode="rceil", chunk_rows=2048):
+    def __init__(self, M, N, device, swizzle=True, mode="rceil", chunk_rows=1024):
         assert M % 128 == 0 and N % 32 == 0, "host caster wants M % 128 == 0 and N % 32 == 0"
         self.M, self.N, self.device = M, N, torch.device(device)
         self.swizzle = swizzle

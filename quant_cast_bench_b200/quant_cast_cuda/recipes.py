@@ -381,6 +381,98 @@ def nvfp4_gs_swizzle_both_cuda(x, outer_scale, **kwargs):
 
 
 # --------------------------------------------------------------------------------------------
+# randomised Hadamard transform and the nvfp4 casts on it
+# --------------------------------------------------------------------------------------------
+def hadamard_rht_matrix_cuda(sign_vector, device="cuda", dtype=torch.bfloat16):
+    """gold hadamard_rht_matrix (G:1778-1781): diag(sign) @ H / 4, H[i][j] = (-1)^popcount(i & j)."""
+    i = torch.arange(16, device=device)
+    par = i.view(-1, 1) & i.view(1, -1)
+    par = (par ^ (par >> 1) ^ (par >> 2) ^ (par >> 3)) & 1
+    h = (1.0 - 2.0 * par.float()) / 4.0
+    return (sign_vector.to(device=device, dtype=torch.float32).view(-1, 1) * h).to(dtype)
+
+
+def _check_rht(rht, x):
+    assert rht.is_cuda and rht.device == x.device and rht.dtype == torch.bfloat16 and rht.shape == (16, 16), (
+        "rht: a (16, 16) bf16 tensor on x's device, built with hadamard_rht_matrix")
+    return rht.contiguous()
+
+
+def hadamard_rht_cuda(x, rht, **kwargs):
+    """gold hadamard_rht_f (G:1784-1789): the transform along the last dim, bf16 out (1-tuple).  Only matrices
+    of the form diag(+-1) @ H16 / 4 are supported; the fp32 accumulation order is the butterfly's."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 16 == 0, f"hadamard_rht needs N % 16 == 0, got N={N}"
+    rht = _check_rht(rht, x)
+    y = torch.empty_like(x)
+    with _on_device(x.device):
+        L.check(lib.qcc_hadamard_rht(_p(x), M, N, _p(rht), _p(y), _stream(x)), "hadamard_rht")
+    L.launch_count += 2
+    return (y,)
+
+
+def nvfp4_rht_outer_scale_m_cuda(x, rht):
+    """The dim-m outer scale of G:1364-1365: max |RHT(x.t())| / 2688, from one read of x (0-dim fp32)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert M % 16 == 0 and N % 4 == 0, f"needs M % 16 == 0 and N % 4 == 0, got {M}x{N}"
+    rht = _check_rht(rht, x)
+    out = torch.empty((), dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_nvfp4_rht_amax(_p(x), M, N, _p(rht), L.AMAX_NVFP4_SCALE, _p(out), _stream(x)), "nvfp4_rht_amax")
+    L.launch_count += 3
+    return out
+
+
+def _nvfp4_rht(x, outer_scale_k, outer_scale_m, rht, flags, key_k=None, key_m=None, both=True):
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    dev = x.device
+    for o in (outer_scale_k, outer_scale_m) if both else (outer_scale_m,):
+        assert o.is_cuda and o.dtype == torch.float32 and o.numel() == 1, "outer scales: one fp32 value each, on the device"
+    assert M % 32 == 0 and N % (32 if both else 8) == 0, f"nvfp4 with RHT needs M % 32 == 0 and N % 32 == 0, got {M}x{N}"
+    rht = _check_rht(rht, x)
+    if flags & L.SR:
+        for k in (key_k, key_m) if both else (key_m,):
+            assert k is not None and k.is_cuda and k.dtype == torch.uint64 and k.numel() == 2, "keys: philox_key(...) on the device"
+    swz = bool(flags & L.SWIZZLE)
+    u8 = torch.uint8
+    qk = torch.empty((M, N // 2), dtype=u8, device=dev) if both else None
+    sk = torch.empty(blocked_shape(M, N // 16) if swz else (M, N // 16), dtype=u8, device=dev) if both else None
+    qm = torch.empty((N, M // 2), dtype=u8, device=dev)
+    sm = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=u8, device=dev)
+    with _on_device(dev):
+        L.check(lib.qcc_nvfp4_rht(_p(x), M, N, _p(outer_scale_k.contiguous()) if both else None, _p(outer_scale_m.contiguous()),
+                                  _p(rht), flags, _p(key_k), _p(key_m), _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "nvfp4_rht")
+    L.launch_count += 2
+    f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+    if both:
+        return qk.view(f4), sk.view(e4), qm.view(f4), sm.view(e4)
+    return qm.view(f4), sm.view(e4)
+
+
+def nvfp4_gs_swizzle_dim_k_dim_m_rht_cuda(x, outer_scale_k, outer_scale_m, rht, **kwargs):
+    """gold nvfp4_gs_swizzle_dim_k_dim_m_rht_f (G:1324-1333): (qk, sk) plain nvfp4 of x, (qm, sm) nvfp4 along M of
+    RHT(x.t()), both with blocked scales, from one read of x."""
+    return _nvfp4_rht(x, outer_scale_k, outer_scale_m, rht, L.SWIZZLE)
+
+
+def nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_cuda(x, outer_scale_k, outer_scale_m, rht, key_k, key_m, **kwargs):
+    """gold nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_f (G:1429-1438): the same with stochastic rounding of both fp4 casts
+    (keys: philox_key(seed); the reference's torch.func._random keys are not available to this backend)."""
+    return _nvfp4_rht(x, outer_scale_k, outer_scale_m, rht, L.SWIZZLE | L.SR, key_k, key_m)
+
+
+def nvfp4_gs_swizzle_dim_m_rht_cuda(x, outer_scale_m, rht, **kwargs):
+    """Extension: the dim-m half alone, nvfp4_gs_swizzle_f(RHT(x.t().contiguous()), outer_scale_m)."""
+    return _nvfp4_rht(x, None, outer_scale_m, rht, L.SWIZZLE, both=False)
+
+
+# --------------------------------------------------------------------------------------------
 # recipe records
 # --------------------------------------------------------------------------------------------
 @dataclass(frozen=True)
@@ -435,6 +527,25 @@ def _inputs_nvfp4(M, K):
     return (x, nvfp4_gs_scale_cuda(x))
 
 
+def _rht_matrix(x):
+    return hadamard_rht_matrix_cuda(torch.tensor([1, -1] * 8), x.device, x.dtype)
+
+
+def _inputs_rht(M, K):
+    x = _x(M, K)
+    return (x, _rht_matrix(x))
+
+
+def _inputs_nvfp4_rht(M, K):
+    x = _x(M, K)
+    rht = _rht_matrix(x)
+    return (x, nvfp4_gs_scale_cuda(x), nvfp4_rht_outer_scale_m_cuda(x, rht), rht)
+
+
+def _inputs_nvfp4_rht_sr(M, K):
+    return _inputs_nvfp4_rht(M, K) + (philox_key(0, device="cuda"), philox_key(1, device="cuda"))
+
+
 # (gold recipe name, gold attribute in quant_cast_gold.recipes, cuda fn, input builder, description)
 _TABLE = [
     ("fp8_tensorwise_precalc_scale", "Float8TensorwiseGold", float8_tensorwise_cuda, _inputs_tensorwise, "elementwise"),
@@ -451,6 +562,11 @@ _TABLE = [
     ("fp8_colwise", "ColwiseFp8Gold", colwise_fp8_cuda, _inputs_x, "(-1,1) block, t-contig"),
     ("nvfp4", "Nvfp4GsGold", nvfp4_gs_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, no swizzle"),
     ("nvfp4_swizzle", "Nvfp4GsSwizzleGold", nvfp4_gs_swizzle_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, swizzle"),
+    ("nvfp4_swizzle_dim_k_dim_m_rht", "Nvfp4GsSwizzle_DimK_DimMRHT_Gold", nvfp4_gs_swizzle_dim_k_dim_m_rht_cuda, _inputs_nvfp4_rht,
+     "(1,16) block, fp4 qdata, swizzle; dim-k (no RHT) + dim-m (RHT), two outer scales"),
+    ("nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "Nvfp4GsSwizzle_DimKSR_DimMRHTSR_Gold", nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_cuda,
+     _inputs_nvfp4_rht_sr, "(1,16) block, fp4 qdata (stochastic rounding), swizzle; dim-k (no RHT) + dim-m (RHT), two outer scales"),
+    ("bf16_rht", "HadamardRht", hadamard_rht_cuda, _inputs_rht, "elementwise RHT"),
 ]
 
 

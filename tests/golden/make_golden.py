@@ -92,6 +92,17 @@ def main():
             out[f"{tag}/nvfp4_gs_swizzle_t_f/{i}"] = raw(o)
         for i, o in enumerate(G.nvfp4_gs_f(x.t().contiguous(), gs)):
             out[f"{tag}/nvfp4_gs_t_f/{i}"] = raw(o)
+        # randomised Hadamard transform and the two-orientation nvfp4 cast built on it (G:1324-1372, G:1778-1810)
+        sign = torch.tensor([1, -1] * 8 if seed % 2 == 0 else [1, 1, -1, 1, -1, -1, -1, 1, 1, -1, 1, 1, -1, 1, -1, -1],
+                            dtype=torch.bfloat16)
+        rht = G.hadamard_rht_matrix(sign, "cpu", torch.bfloat16)
+        out[f"{tag}/rht"] = raw(rht)
+        out[f"{tag}/hadamard_rht_f/0"] = raw(G.hadamard_rht_f(x, rht)[0])
+        (x_t_rht,) = G.hadamard_rht_f(x.t().contiguous(), rht)
+        gs_m = x_t_rht.abs().to(torch.float32).amax() / (G.F8E4M3_MAX * G.F4_E2M1_MAX)
+        out[f"{tag}/nvfp4_rht_outer_scale_m/0"] = raw(gs_m.reshape(1))
+        for i, o in enumerate(G.nvfp4_gs_swizzle_dim_k_dim_m_rht_f(x, gs, gs_m, rht)):
+            out[f"{tag}/nvfp4_gs_swizzle_dim_k_dim_m_rht_f/{i}"] = raw(o)
         pt = G.nvfp4_gs_per_token_scale(x).clamp(min=2.0 ** -100)
         out[f"{tag}/nvfp4_per_token_scale/0"] = raw(pt)
         for i, o in enumerate(G.nvfp4_gs_f(x, pt)):

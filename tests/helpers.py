@@ -23,6 +23,11 @@ def golden_x(tag):
     return torch.from_numpy(golden()[f"{tag}/x"].copy()).view(torch.bfloat16)
 
 
+def golden_rht(tag):
+    """The 16x16 bf16 transform matrix of a golden case."""
+    return torch.from_numpy(golden()[f"{tag}/rht"].copy()).view(torch.bfloat16)
+
+
 def golden_out(tag, fn, i):
     return torch.from_numpy(golden()[f"{tag}/{fn}/{i}"].copy())
 

@@ -5,7 +5,7 @@ import os
 import pytest
 import torch
 
-from helpers import assert_same_bits, golden, golden_cases, golden_n_outputs, golden_out, golden_x
+from helpers import assert_same_bits, golden, golden_cases, golden_n_outputs, golden_out, golden_rht, golden_x
 from oracle import gold_port as O
 
 ONE_INPUT = ["rowwise_fp8_f", "colwise_fp8_f", "mxfp8_f", "mxfp8_swizzle_f", "mxfp8_dim_m_f",
@@ -92,6 +92,21 @@ def test_e4m3_decode_e8m0_and_blocked_layout():
         sc = torch.from_numpy(g[f"kat/blocked_{H}x{W}_in"].copy())
         assert_same_bits(O.to_blocked_4d(sc), torch.from_numpy(g[f"kat/blocked_{H}x{W}_out"].copy()), "blocked")
     assert g["kat/bf16_clamp_min"].view("uint16")[0] == 0x2B8D
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+def test_hadamard_rht(tag):
+    """The transform and the two-orientation nvfp4 cast on it (gold G:1324-1333, G:1784-1789).  The gold matmul's
+    accumulation order is the GEMM library's; the restatement's fixed butterfly order gives the same bits here."""
+    x, rht = golden_x(tag), golden_rht(tag)
+    assert_same_bits(O.hadamard_rht_matrix(torch.where(rht[:, 0].float() < 0, -1.0, 1.0)), rht, "rht matrix")
+    assert_same_bits(O.hadamard_rht_f(x, rht)[0], golden_out(tag, "hadamard_rht_f", 0), f"rht {tag}")
+    gs = O.nvfp4_gs_scale(x)
+    gs_m = O.nvfp4_rht_outer_scale_m(x, rht)
+    assert_same_bits(gs_m.reshape(1), golden_out(tag, "nvfp4_rht_outer_scale_m", 0), "outer m")
+    fn = "nvfp4_gs_swizzle_dim_k_dim_m_rht_f"
+    for i, o in enumerate(O.nvfp4_gs_swizzle_dim_k_dim_m_rht_f(x, gs, gs_m, rht)):
+        assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
 
 
 def test_token_group_layouts():

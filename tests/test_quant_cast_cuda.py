@@ -368,7 +368,8 @@ def test_host_buffer_caster_matches_oracle(swizzle):
 def test_recipe_index_mirrors_reference_backends():
     names = [n for n, _ in Q.ALL_RECIPES]
     assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "fp8_colwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
-                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle"]
+                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
+                     "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "bf16_rht"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
         outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
