@@ -489,6 +489,17 @@ def bench_other_casts(Q, x, dev, peak):
     out["fp8_colwise_16384"] = timed(lambda: Q.colwise_fp8_cuda(x), algorithmic_bytes(M, N, "fp8_rowwise"))
     key = Q.philox_key(0, device=dev)
     out["nvfp4_swizzle_sr_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key), algorithmic_bytes(M, N, "nvfp4") + 16)
+    # randomised Hadamard transform rows (gold recipes bf16_rht, nvfp4_swizzle_dim_k_dim_m_rht and its stochastic form)
+    rht = Q.hadamard_rht_matrix_cuda(torch.tensor([1, -1] * 8), dev)
+    gs_m = Q.nvfp4_rht_outer_scale_m_cuda(x, rht)
+    key_m = Q.philox_key(1, device=dev)
+    both_bytes = 2 * M * N + 8 + 512 + 2 * (M * N // 2 + M * N // 16)
+    out["bf16_rht_16384"] = timed(lambda: Q.hadamard_rht_cuda(x, rht), 4 * M * N + 512)
+    out["nvfp4_rht_amax_16384"] = timed(lambda: Q.nvfp4_rht_outer_scale_m_cuda(x, rht), 2 * M * N + 4 + 512)
+    out["nvfp4_swizzle_dim_k_dim_m_rht_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_dim_k_dim_m_rht_cuda(x, gs, gs_m, rht), both_bytes)
+    out["nvfp4_swizzle_dim_m_rht_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_dim_m_rht_cuda(x, gs_m, rht), algorithmic_bytes(M, N, "nvfp4") + 512)
+    out["nvfp4_swizzle_dim_k_sr_dim_m_rht_sr_16384"] = timed(
+        lambda: Q.nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_cuda(x, gs, gs_m, rht, key, key_m), both_bytes + 32)
     x1 = x[:4096, :4096].contiguous()          # config 1 shape (fits L2: flush between iterations)
     s1 = Q.float8_tensorwise_scale_cuda(x1)
     out["c1_fp8_tensorwise_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)

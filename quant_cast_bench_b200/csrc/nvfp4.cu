@@ -123,26 +123,24 @@ constexpr int NVT_X_OFF = 0;
 constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 rows x 64 B
 constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * 32 * 64; // 128 columns x 8 block scales
 constexpr int NVT_LUT_OFF = NVT_S_OFF + 1024;      // 128 multipliers, one per inner-scale byte
-constexpr int NVT_LUTK_OFF = NVT_LUT_OFF + 512;    // the same for the rowwise half when its outer scale differs
-constexpr int NVT_BAR_OFF = NVT_LUTK_OFF + 512;
+constexpr int NVT_BAR_OFF = NVT_LUT_OFF + 512;
 constexpr int NVT_QK_OFF = NVT_BAR_OFF + 512;      // rowwise staging (fused form only): 128 rows x 64 B
 constexpr int nvt_alloc(bool do_k) { return NVT_QK_OFF + (do_k ? 128 * 64 : 0) + 1024; }
 
 // Row-major tile order (column tiles fastest), as in the mxfp8 tile kernel.  Warps 0-3 quantise down the
 // rows (transposed outputs q, s); with DO_K warps 4-7 also quantise along the rows (outputs qk, sk), so both
 // orientations come from one read of x.
-// RHT: the 16-row blocks going down the rows pass through the 16-point randomised Hadamard transform before
-// they are quantised (the dim-m half of nvfp4_gs_swizzle_dim_k_dim_m_rht_f, G:1324-1333 and its stochastic form
-// G:1429-1438); the two halves then have their own outer scales (outer_p: down the rows, outer_k_p: along
-// the rows) and Philox keys.
+// RHT (transposed outputs only): the 16-row blocks going down the rows pass through the 16-point randomised
+// Hadamard transform before they are quantised -- the dim-m half of nvfp4_gs_swizzle_dim_k_dim_m_rht_f
+// (G:1324-1333) and of its stochastic form (G:1429-1438).
 template <bool DO_K, bool SWZ, bool SR, bool RHT>
-__global__ void __launch_bounds__(DO_K ? 256 : 128, DO_K ? (RHT ? 2 : 3) : (RHT ? 4 : 5))
+__global__ void __launch_bounds__(DO_K ? 256 : 128, DO_K ? 3 : ((RHT && SR) ? 4 : 5))
 nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *__restrict__ outer_p,
-                        const float *__restrict__ outer_k_p, const uint64_t *__restrict__ key,
-                        const uint64_t *__restrict__ key_k, const uint16_t *__restrict__ rht, uint8_t *__restrict__ q,
+                        const uint64_t *__restrict__ key, const uint16_t *__restrict__ rht, uint8_t *__restrict__ q,
                         uint8_t *__restrict__ s, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk, int M, int N,
                         int tiles_n)
 {
+    static_assert(!(DO_K && (RHT || SR)), "the fused rowwise half is round-to-nearest without transform");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
@@ -164,14 +162,6 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
     const float inv_outer = __fdiv_rn(1.0f, outer);
     float *lut = reinterpret_cast<float *>(sbase + NVT_LUT_OFF);
     nvfp4_fill_recip_lut(lut, inv_outer);
-    float outer_k = outer, inv_outer_k = inv_outer;
-    float *lut_k = lut;
-    if (DO_K && RHT) {
-        outer_k = __ldg(outer_k_p);
-        inv_outer_k = __fdiv_rn(1.0f, outer_k);
-        lut_k = reinterpret_cast<float *>(sbase + NVT_LUTK_OFF);
-        if (threadIdx.x >= 128) lut_k[threadIdx.x - 128] = __fdiv_rn(inv_outer_k, e4m3_to_f32(threadIdx.x - 128));
-    }
     const uint32_t sgn = RHT ? rht_sign_mask(rht) : 0u;
     __syncthreads();
     uint64_t seed = 0, offset = 0;
@@ -192,8 +182,6 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
         const uint32_t key2 = ((row_t >> 1) & 3) << 1;       // staging swizzle on 8-byte units, pairs kept together
         const uint32_t qrow = base + NVT_QK_OFF + row_t * 64;
         uint32_t sb[2] = {0u, 0u};
-        uint64_t seed_k = 0, offset_k = 0;
-        if (SR) { seed_k = key_k[0]; offset_k = key_k[1]; }
 #pragma unroll
         for (int kb = 0; kb < 8; kb++) {
             const uint32_t prow = xrow + (kb >> 2) * NVT_PANEL_BYTES;
@@ -201,8 +189,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             const uint4 a4 = lds_v4(prow + (((j0) ^ key7) << 4));
             const uint4 b4 = lds_v4(prow + (((j0 + 1) ^ key7) << 4));
             uint2 packed;
-            const uint64_t flat0 = (uint64_t)R * (uint64_t)N + (uint64_t)(tile_n * 128 + kb * 16);
-            uint32_t byte = nvfp4_quant16<SR>(a4, b4, outer_k, inv_outer_k, lut_k, flat0, seed_k, offset_k, packed);
+            uint32_t byte = nvfp4_quant16<false>(a4, b4, outer, inv_outer, lut, 0, 0, 0, packed);
             const bool ok = R < M && (tile_n * 8 + kb) < nb16;
             sb[kb >> 2] |= (ok ? byte : 0u) << (8 * (kb & 3));
             asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(qrow + ((kb ^ key2) << 3)), "r"(packed.x), "r"(packed.y) : "memory");
@@ -425,9 +412,9 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
 }
 
 struct NvtArgs {
-    const float *outer, *outer_k;          // down the rows / along the rows (fused forms)
-    const uint64_t *key, *key_k;
-    const uint16_t *rht;
+    const float *outer;
+    const uint64_t *key;
+    const uint16_t *rht;     // non-null: transform down the rows (transposed outputs only)
     uint8_t *q, *s, *qk, *sk;
 };
 
@@ -449,29 +436,23 @@ static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cud
     const int tiles_n = (N + 127) / 128, tiles_m = (M + NVT_TILE_M - 1) / NVT_TILE_M;
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, DO_K ? 256 : 128, ALLOC, st>>>(tx, a.outer, a.outer_k, a.key, a.key_k, a.rht, a.q, a.s, a.qk,
-                                                              a.sk, M, N, tiles_n);
+    kern<<<(unsigned)num_tiles, DO_K ? 256 : 128, ALLOC, st>>>(tx, a.outer, a.key, a.rht, a.q, a.s, a.qk, a.sk, M, N, tiles_n);
     return (int)cudaGetLastError();
 }
 
-template <bool DO_K, bool RHT>
-static int launch_nvt_flags(const CUtensorMap &tx, const NvtArgs &a, bool swz, bool sr, int M, int N, cudaStream_t st)
+template <bool RHT>
+static int launch_nvt_t(const CUtensorMap &tx, const NvtArgs &a, bool swz, bool sr, int M, int N, cudaStream_t st)
 {
-    // stochastic rounding of the fused rowwise half exists for the transform form only
-    constexpr bool SR_OK = !DO_K || RHT;
-    if (sr && !SR_OK) return QCC_ERR_ARG;
-    if (swz) return (sr && SR_OK) ? launch_nvt<DO_K, true, SR_OK, RHT>(tx, a, M, N, st) : launch_nvt<DO_K, true, false, RHT>(tx, a, M, N, st);
-    return (sr && SR_OK) ? launch_nvt<DO_K, false, SR_OK, RHT>(tx, a, M, N, st) : launch_nvt<DO_K, false, false, RHT>(tx, a, M, N, st);
+    if (swz) return sr ? launch_nvt<false, true, true, RHT>(tx, a, M, N, st) : launch_nvt<false, true, false, RHT>(tx, a, M, N, st);
+    return sr ? launch_nvt<false, false, true, RHT>(tx, a, M, N, st) : launch_nvt<false, false, false, RHT>(tx, a, M, N, st);
 }
 
-static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &a, int flags, bool both, bool with_rht,
-                            void *stream)
+static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &a, int flags, bool both, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || !a.outer_k)) || (flags & ~(QCC_SWIZZLE | QCC_SR)))
+    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || a.rht)) || (flags & ~(QCC_SWIZZLE | QCC_SR)))
         return QCC_ERR_ARG;
-    if ((flags & QCC_SR) && (!a.key || (both && !with_rht) || (both && !a.key_k))) return QCC_ERR_ARG;
-    if (with_rht && !a.rht) return QCC_ERR_ARG;
+    if ((flags & QCC_SR) && (!a.key || both)) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     // output rows of M / 2 bytes are written in 16-byte pieces: M % 32 == 0; the TMA load needs N % 8 == 0
     if (M % 32 != 0 || N % 8 != 0 || (both && N % 32 != 0)) return QCC_ERR_SHAPE;
@@ -486,35 +467,46 @@ static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &
         if (e) return e;
     }
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR;
-    if (with_rht) {
+    if (both)
+        return swz ? launch_nvt<true, true, false, false>(tx, a, (int)M, (int)N, st)
+                   : launch_nvt<true, false, false, false>(tx, a, (int)M, (int)N, st);
+    if (a.rht) {
         int e = launch_rht_check(a.rht, st);
         if (e) return e;
-        return both ? launch_nvt_flags<true, true>(tx, a, swz, sr, (int)M, (int)N, st)
-                    : launch_nvt_flags<false, true>(tx, a, swz, sr, (int)M, (int)N, st);
+        return launch_nvt_t<true>(tx, a, swz, sr, (int)M, (int)N, st);
     }
-    return both ? launch_nvt_flags<true, false>(tx, a, swz, sr, (int)M, (int)N, st)
-                : launch_nvt_flags<false, false>(tx, a, swz, sr, (int)M, (int)N, st);
+    return launch_nvt_t<false>(tx, a, swz, sr, (int)M, (int)N, st);
 }
 
 extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
                                     const uint64_t *philox_key, void *q, void *s, void *stream)
 {
-    NvtArgs a = {outer, nullptr, philox_key, nullptr, nullptr, (uint8_t *)q, (uint8_t *)s, nullptr, nullptr};
-    return nvfp4_tile_entry(x, M, N, a, flags, false, false, stream);
+    NvtArgs a = {outer, philox_key, nullptr, (uint8_t *)q, (uint8_t *)s, nullptr, nullptr};
+    return nvfp4_tile_entry(x, M, N, a, flags, false, stream);
 }
 
 extern "C" int qcc_nvfp4_both(const void *x, int64_t M, int64_t N, const float *outer, int flags, void *qk, void *sk,
                               void *qm, void *sm, void *stream)
 {
-    NvtArgs a = {outer, outer, nullptr, nullptr, nullptr, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
-    return nvfp4_tile_entry(x, M, N, a, flags, true, false, stream);
+    NvtArgs a = {outer, nullptr, nullptr, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
+    return nvfp4_tile_entry(x, M, N, a, flags, true, stream);
 }
 
+// Two launches when both halves are asked for: the rowwise stream cast, then the tile kernel with the transform
+// for the dim-m half.  (A single kernel doing both from one read exists for the transform-free pair,
+// qcc_nvfp4_both; with the transform in the column warps it ran slower than these two.)
 extern "C" int qcc_nvfp4_rht(const void *x, int64_t M, int64_t N, const float *outer_k, const float *outer_m,
                              const void *rht, int flags, const uint64_t *key_k, const uint64_t *key_m, void *qk, void *sk,
                              void *qm, void *sm, void *stream)
 {
+    if (M == 0 || N == 0) return 0;
+    if (!rht || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
     const bool both = qk != nullptr || sk != nullptr;
-    NvtArgs a = {outer_m, outer_k, key_m, key_k, (const uint16_t *)rht, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
-    return nvfp4_tile_entry(x, M, N, a, flags, both, true, stream);
+    if (M % 32 != 0 || N % 8 != 0 || (both && N % 32 != 0)) return QCC_ERR_SHAPE;
+    if (both) {
+        int e = qcc_nvfp4(x, M, N, outer_k, 0, flags, key_k, qk, sk, stream);
+        if (e) return e;
+    }
+    NvtArgs a = {outer_m, key_m, (const uint16_t *)rht, (uint8_t *)qm, (uint8_t *)sm, nullptr, nullptr};
+    return nvfp4_tile_entry(x, M, N, a, flags, false, stream);
 }
