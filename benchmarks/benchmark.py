@@ -49,6 +49,8 @@ def _extensions(x):
     s5 = Q.float8_tensorwise_scale_cuda(x, "e5m2")
     gs = Q.nvfp4_gs_scale_cuda(x)
     key = Q.philox_key(0, device=x.device)
+    rht = Q.hadamard_rht_matrix_cuda(torch.tensor([1, -1] * 8), x.device)
+    gs_m = Q.nvfp4_rht_outer_scale_m_cuda(x, rht)
     return [
         ("amax_fp8_scale", (x,), lambda: (Q.float8_tensorwise_scale_cuda(x),)),
         ("amax_nvfp4_scale", (x,), lambda: (Q.nvfp4_gs_scale_cuda(x),)),
@@ -62,6 +64,8 @@ def _extensions(x):
         ("nvfp4_t", (x, gs), lambda: Q.nvfp4_gs_t_cuda(x, gs)),
         ("nvfp4_swizzle_t", (x, gs), lambda: Q.nvfp4_gs_swizzle_t_cuda(x, gs)),
         ("nvfp4_swizzle_sr", (x, gs, key), lambda: Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key)),
+        ("nvfp4_rht_outer_scale_m", (x, rht), lambda: (Q.nvfp4_rht_outer_scale_m_cuda(x, rht),)),
+        ("nvfp4_swizzle_dim_m_rht", (x, gs_m, rht), lambda: Q.nvfp4_gs_swizzle_dim_m_rht_cuda(x, gs_m, rht)),
     ]
 
 

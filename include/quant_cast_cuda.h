@@ -39,6 +39,7 @@ extern "C" {
 #define QCC_SWIZZLE 4  /* block scales in the blocked 32x4x4 layout instead of plain row-major      */
 #define QCC_FLOOR 8    /* mxfp8: FLOOR scale mode (OCP MX v1.0) instead of RCEIL                     */
 #define QCC_SR 16      /* nvfp4: stochastic rounding of the fp4 values, Philox4x32-10 keyed          */
+#define QCC_BLOCK32 32 /* mxfp8: one scale per 32x32 block instead of per 1x32 / 32x1 block        */
 
 /* what qcc_amax_finalize writes */
 #define QCC_AMAX_RAW 0        /* the amax itself, fp32                                   */
@@ -160,6 +161,15 @@ int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
  * flags & QCC_FLOOR:   FLOOR scale mode (extension, not in the reference)
  * Needs N % 32 == 0, and M % 32 == 0 when QCC_COLWISE is set.  Outputs of a direction that is not
  * requested may be NULL.
+ *
+ * flags & QCC_BLOCK32: one RCEIL scale per 32x32 block of x, shared by both orientations (needs M % 32 == 0):
+ *   QCC_ROWWISE alone, no QCC_SWIZZLE: qk (M, N) and sk the plain (M/32, N/32) grid   mxfp8_32x32_f         G:753-773
+ *   QCC_ROWWISE | QCC_SWIZZLE: sk = the block scales repeated over their 32 rows, i.e. the (M, N/32) frame
+ *                              of the 1x32 cast, blocked                              mxfp8_32x32_swizzle_f G:809-815
+ *   QCC_COLWISE | QCC_SWIZZLE: qm (N, M) and sm over the (N, M/32) frame, blocked     mxfp8_32x32_dim_m_swizzle_f G:856-862
+ *   both | QCC_SWIZZLE: all four                                                      mxfp8_32x32_dim_km_swizzle_f G:900-910
+ *   both | QCC_SWIZZLE with qm == NULL: qk, sk and sm only      mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f G:946-959
+ * QCC_FLOOR is not available with QCC_BLOCK32.
  */
 int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
               void *stream);

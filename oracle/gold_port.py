@@ -38,6 +38,7 @@ def lib():
         _lib.qco_nvfp4_t.restype = ctypes.c_int
         _lib.qco_num_threads.restype = ctypes.c_int
         _lib.qco_hadamard_rht.restype = ctypes.c_int
+        _lib.qco_mxfp8_32x32.restype = ctypes.c_int
         _lib.qco_hadamard_rht_t.restype = ctypes.c_int
     return _lib
 
@@ -295,6 +296,50 @@ def mxfp8_dim_km_swizzle_f(x, mode="rceil", **kwargs):
 
 
 # ------------------------------------------------------------------ nvfp4
+# ------------------------------------------------------------------ mxfp8, 32x32 blocks
+def mxfp8_32x32_f(x, **kwargs):
+    """gold mxfp8_32x32_f (G:753-773): (qdata (M, N) e4m3, scale (M/32, N/32) e8m0)."""
+    _check_x(x)
+    M, N = x.shape
+    q = torch.empty((M, N), dtype=torch.uint8)
+    s = torch.empty((M // 32, N // 32), dtype=torch.uint8)
+    rc = lib().qco_mxfp8_32x32(_p(x), _i64(M), _i64(N), _p(q), _p(s))
+    assert rc == 0, "mxfp8_32x32 needs M % 32 == 0 and N % 32 == 0"
+    return q.view(torch.float8_e4m3fn), s.view(torch.float8_e8m0fnu)
+
+
+def _expand_k(s):   # (M/32, N/32) -> blocked (M, N/32): every block scale repeated over its 32 rows
+    return to_blocked_4d(s.view(torch.uint8).repeat_interleave(32, dim=0)).view(torch.float8_e8m0fnu)
+
+
+def _expand_m(s):   # (M/32, N/32) -> blocked (N, M/32): repeated over its 32 columns, transposed
+    return to_blocked_4d(s.view(torch.uint8).repeat_interleave(32, dim=1).t().contiguous()).view(torch.float8_e8m0fnu)
+
+
+def mxfp8_32x32_swizzle_f(x, **kwargs):
+    """G:809-815"""
+    q, s = mxfp8_32x32_f(x)
+    return q, _expand_k(s)
+
+
+def mxfp8_32x32_dim_m_swizzle_f(x, **kwargs):
+    """G:856-862"""
+    q, s = mxfp8_32x32_f(x)
+    return q.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn), _expand_m(s)
+
+
+def mxfp8_32x32_dim_km_swizzle_f(x, **kwargs):
+    """G:900-910"""
+    q, s = mxfp8_32x32_f(x)
+    return q, _expand_k(s), q.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn), _expand_m(s)
+
+
+def mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f(x, **kwargs):
+    """G:946-959"""
+    q, s = mxfp8_32x32_f(x)
+    return q, _expand_k(s), _expand_m(s)
+
+
 def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     _check_x(x)
     M, N = x.shape

@@ -474,6 +474,37 @@ int qco_mxfp8(const uint16_t *x, int64_t M, int64_t N, int flags, uint8_t *qk, u
     return 0;
 }
 
+/*
+ * mxfp8 with one RCEIL e8m0 scale per 32x32 block (mxfp8_32x32_f G:753-773): q (M, N) in the
+ * layout of x, s the plain (M/32, N/32) grid.  The expanded / blocked / transposed forms of the
+ * other 32x32 recipes (G:809-815, G:856-862, G:900-910, G:946-959) are index permutations of these
+ * two outputs, done by the caller.
+ */
+int qco_mxfp8_32x32(const uint16_t *x, int64_t M, int64_t N, uint8_t *q, uint8_t *s)
+{
+    if (M % 32 || N % 32) return -1;
+    int64_t mb = M / 32, nb = N / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t bi = 0; bi < mb * nb; bi++) {
+        int64_t br = bi / nb, bc = bi % nb;
+        uint16_t best = 0;
+        for (int r = 0; r < 32; r++)
+            for (int c = 0; c < 32; c++) {
+                uint16_t a = bf16_abs(x[(br * 32 + r) * N + bc * 32 + c]);
+                if (a > best) best = a;
+            }
+        uint8_t e = amax_to_e8m0_rceil(bf16_to_f32(best));
+        float rcp = e8m0_to_recip(e, 0);
+        s[bi] = e;
+        for (int r = 0; r < 32; r++)
+            for (int c = 0; c < 32; c++) {
+                int64_t i = (br * 32 + r) * N + bc * 32 + c;
+                q[i] = f32_to_fp8(bf16_to_f32(x[i]) * rcp, 3, 7, 0x7E);
+            }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* nvfp4                                                                                      */
 /* ------------------------------------------------------------------------------------------ */

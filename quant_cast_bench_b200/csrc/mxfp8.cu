@@ -156,7 +156,7 @@ constexpr int T64_PANEL = T64_ROWS * 128;          // one 64-column panel: 64 ro
 template <bool DO_K, bool DO_M>
 struct T64 {
     static constexpr int THREADS = 32 * ((DO_K ? 2 : 0) + (DO_M ? 2 : 0));
-    static constexpr int MIN_CTAS = DO_K ? 6 : 8;                             // register cap: measured best on B200
+    static constexpr int MIN_CTAS = DO_K ? (DO_M ? 6 : 10) : 8;               // register cap: measured best on B200
     static constexpr int X_OFF = 0;
     static constexpr int QK_OFF = 2 * T64_PANEL;                              // 64 rows x 128 B
     static constexpr int QM_OFF = QK_OFF + (DO_K ? T64_ROWS * 128 : 0);       // 4 sub-tiles x 32 rows x 64 B
@@ -166,7 +166,11 @@ struct T64 {
     static constexpr int ALLOC = BYTES + 1024;
 };
 
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
+// B32: one scale per 32x32 block (gold mxfp8_32x32_f and its layouts, G:753-984): the block maximum is the
+// maximum over the 32 lanes of a row warp, or over the eight lanes (32 columns) of a column warp; both give the
+// same byte, which is then stored once per row / per column in the expanded 1x32 and 32x1 scale frames.  The
+// rowwise form (DO_M false) can also write the transposed frame's scales (sm non-null) without the transposed data.
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32>
 __global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS, T64<DO_K, DO_M>::MIN_CTAS)
 mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
                     uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n, GroupTables g)
@@ -210,7 +214,9 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
             uint4 c[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) c[i] = lds_v4(prow + (((j0 + i) ^ key) << 4));
-            const uint32_t e = e8m0_from_amax<FLOOR>(amax_of_block(c));
+            float am = amax_of_block(c);
+            if (B32) am = u2f(__reduce_max_sync(0xFFFFFFFFu, f2u(am)));   // non-negative floats order like integers
+            const uint32_t e = e8m0_from_amax<FLOOR>(am);
             const float rcp = e8m0_recip<FLOOR>(e);
             sbytes |= e << (8 * kb);
             uint4 o0, o1;
@@ -242,6 +248,14 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
                 const size_t off = ((size_t)(Rd >> 7) * ncb + tile_n) * 512u + (rr & 31u) * 16u + (rr >> 5) * 4u;
                 *reinterpret_cast<uint32_t *>(sk + off) = sbytes;  // padding rows carry zeros (zero-filled x)
             }
+        } else if (B32) {
+            // plain (M / 32, N / 32) grid: one writer per 32-row slab
+            if (lane == 0 && R < M) {
+                uint8_t *dst = sk + (size_t)(R >> 5) * nb + C;
+#pragma unroll
+                for (int kb = 0; kb < 4; kb++)
+                    if (C + kb < nb) dst[kb] = (uint8_t)(sbytes >> (8 * kb));
+            }
         } else if (R < M) {
             uint8_t *dst = sk + (size_t)R * nb + C;
             if ((nb & 3) == 0) {
@@ -252,7 +266,19 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
                     if (C + kb < nb) dst[kb] = (uint8_t)(sbytes >> (8 * kb));
             }
         }
-    } else {
+        if (B32 && SWZ && !DO_M && sm != nullptr) {
+            // scales of the transposed frame (N, M / 32), expanded over the 32 columns of each block
+            const uint32_t ncb_m = (uint32_t)(mb + 3) >> 2;
+            const uint32_t mblk = (uint32_t)tile_m * 2 + b;
+            const uint32_t byte = (sbytes >> (8 * (lane >> 3))) & 0xFFu;
+            const size_t atom = ((size_t)tile_n * ncb_m + (mblk >> 2)) * 512u + (mblk & 3u);
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const uint32_t c = 4 * lane + cc;
+                sm[atom + (c & 31u) * 16u + (c >> 5) * 4u] = (uint8_t)byte;
+            }
+        }
+    } else if constexpr (DO_M) {
         // ------------------------------------------------------------------ down the rows
         const uint32_t pbase = xs + (lane >> 4) * T64_PANEL + (b * 32) * 128 + (lane & 1) * 8;
         const uint32_t j = (lane & 15) >> 1;
@@ -267,7 +293,15 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
         float rcp[4];
         uint32_t e[4];
         {
-            const float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
+            float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
+            if (B32) {
+                // 32 columns = this lane's four and those of the seven other lanes of its group of eight
+                uint32_t m = max(max(f2u(am[0]), f2u(am[1])), max(f2u(am[2]), f2u(am[3])));
+                m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+                m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+                m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+                am[0] = am[1] = am[2] = am[3] = u2f(m);
+            }
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
                 e[kk] = e8m0_from_amax<FLOOR>(am[kk]);
@@ -345,12 +379,12 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
     }
 }
 
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR>
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32 = false>
 static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st,
                       GroupTables g)
 {
     using L = T64<DO_K, DO_M>;
-    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR>;
+    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -383,15 +417,35 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
 {
     const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
     if (M == 0 || N == 0) return 0;
-    if (!x || (!row && !col) || (flags & ~(QCC_ROWWISE | QCC_COLWISE | QCC_SWIZZLE | QCC_FLOOR))) return QCC_ERR_ARG;
-    if ((row && (!qk || !sk)) || (col && (!qm || !sm))) return QCC_ERR_ARG;
+    if (!x || (!row && !col) || (flags & ~(QCC_ROWWISE | QCC_COLWISE | QCC_SWIZZLE | QCC_FLOOR | QCC_BLOCK32))) return QCC_ERR_ARG;
+    const bool b32 = flags & QCC_BLOCK32;
+    // 32x32 blocks: the transposed data may be left out when only its scales are wanted (with the rowwise outputs)
+    if ((row && (!qk || !sk)) || (col && (!sm || (!qm && !(b32 && row))))) return QCC_ERR_ARG;
+    if (b32 && ((flags & QCC_FLOOR) || g.row_map || (col && !(flags & QCC_SWIZZLE)))) return QCC_ERR_ARG;
+    if (b32 && M % 32 != 0) return QCC_ERR_SHAPE;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     if (N % 32 != 0 || (col && M % 32 != 0)) return QCC_ERR_SHAPE;
-    if (!aligned16(x) || (row && !aligned16(qk)) || (col && !aligned16(qm))) return QCC_ERR_ALIGN;
+    if (!aligned16(x) || (row && !aligned16(qk)) || (col && qm && !aligned16(qm))) return QCC_ERR_ALIGN;
     if ((row && !aligned16(sk)) || (col && !aligned16(sm))) return QCC_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     const bool swz = flags & QCC_SWIZZLE, fl = flags & QCC_FLOOR;
     uint8_t *skp = (uint8_t *)sk, *smp = (uint8_t *)sm;
+
+    if (b32) {
+        CUtensorMap t64;
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        uint64_t strides[1] = {(uint64_t)N * 2};
+        uint32_t box[2] = {64, 64};
+        int e = make_tensor_map(&t64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (e) return e;
+        uint8_t *qkp = (uint8_t *)qk, *qmp = (uint8_t *)qm;
+        if (!col)
+            return swz ? launch_t64<true, false, true, false, true>(t64, qkp, skp, nullptr, nullptr, (int)M, (int)N, st, g)
+                       : launch_t64<true, false, false, false, true>(t64, qkp, skp, nullptr, nullptr, (int)M, (int)N, st, g);
+        if (!row) return launch_t64<false, true, true, false, true>(t64, nullptr, nullptr, qmp, smp, (int)M, (int)N, st, g);
+        if (!qm) return launch_t64<true, false, true, false, true>(t64, qkp, skp, nullptr, smp, (int)M, (int)N, st, g);
+        return launch_t64<true, true, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
+    }
 
     if (!col) {
         const int64_t nb = N / 32;

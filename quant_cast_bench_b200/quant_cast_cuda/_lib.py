@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libquant_cast_cuda.so")
 
 # constants of include/quant_cast_cuda.h
 FMT_E4M3, FMT_E5M2 = 0, 1
-ROWWISE, COLWISE, SWIZZLE, FLOOR, SR = 1, 2, 4, 8, 16
+ROWWISE, COLWISE, SWIZZLE, FLOOR, SR, BLOCK32 = 1, 2, 4, 8, 16, 32
 AMAX_RAW, AMAX_FP8_SCALE, AMAX_NVFP4_SCALE = 0, 1, 2
 ERRORS = {
     -1: "shape: a dimension violates the divisibility this cast needs",

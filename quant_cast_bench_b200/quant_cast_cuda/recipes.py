@@ -250,6 +250,55 @@ def _mxfp8(x, flags, out=None):
     return tuple(outs)
 
 
+def _mxfp8_32x32(x, row, col, swz, transposed_data=True):
+    """32x32 blocks: one e8m0 scale per block, shared by both orientations (QCC_BLOCK32)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert M % 32 == 0 and N % 32 == 0, f"mxfp8 32x32 needs M % 32 == 0 and N % 32 == 0, got {M}x{N}"
+    dev, u8 = x.device, torch.uint8
+    qk = torch.empty((M, N), dtype=u8, device=dev) if row else None
+    sk = torch.empty(blocked_shape(M, N // 32) if swz else (M // 32, N // 32), dtype=u8, device=dev) if row else None
+    qm = torch.empty((N, M), dtype=u8, device=dev) if col and transposed_data else None
+    sm = torch.empty(blocked_shape(N, M // 32), dtype=u8, device=dev) if col else None
+    flags = L.BLOCK32 | (L.ROWWISE if row else 0) | (L.COLWISE if col else 0) | (L.SWIZZLE if swz else 0)
+    with _on_device(dev):
+        L.check(lib.qcc_mxfp8(_p(x), M, N, flags, _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "mxfp8 32x32")
+    L.launch_count += 1
+    f8, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    outs = []
+    if row:
+        outs += [qk.view(f8), sk.view(e8)]
+    if col:
+        outs += ([qm.view(f8)] if transposed_data else []) + [sm.view(e8)]
+    return tuple(outs)
+
+
+def mxfp8_32x32_cuda(x, **kwargs):
+    """gold mxfp8_32x32_f (G:753-773): (qdata (M, N), scale (M/32, N/32))."""
+    return _mxfp8_32x32(x, True, False, False)
+
+
+def mxfp8_32x32_swizzle_cuda(x, **kwargs):
+    """gold mxfp8_32x32_swizzle_f (G:809-815): scale repeated over the 32 rows of its block, blocked (M, N/32) frame."""
+    return _mxfp8_32x32(x, True, False, True)
+
+
+def mxfp8_32x32_dim_m_swizzle_cuda(x, **kwargs):
+    """gold mxfp8_32x32_dim_m_swizzle_f (G:856-862): (qdata (N, M), blocked scale over the (N, M/32) frame)."""
+    return _mxfp8_32x32(x, False, True, True)
+
+
+def mxfp8_32x32_dim_km_swizzle_cuda(x, **kwargs):
+    """gold mxfp8_32x32_dim_km_swizzle_f (G:900-910): (qk, sk, qm, sm) from one read."""
+    return _mxfp8_32x32(x, True, True, True)
+
+
+def mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda(x, **kwargs):
+    """gold mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f (G:946-959): (qk, sk, sm), no transposed data."""
+    return _mxfp8_32x32(x, True, True, True, transposed_data=False)
+
+
 def mxfp8_cuda(x, mode="rceil", **kwargs):
     """gold mxfp8_f (G:561-568): (qdata (M, N) e4m3, scale (M, N/32) e8m0)."""
     return _mxfp8(x, L.ROWWISE | _mode(mode))
@@ -558,6 +607,14 @@ _TABLE = [
     ("mxfp8_dim_km", "Mxfp8DimKmGold", mxfp8_dim_km_cuda, _inputs_x, "(1,32) dim-k + (32,1) dim-m, one pass, t-contig"),
     ("mxfp8_dim_km_swizzle", "Mxfp8DimKmSwizzleGold", mxfp8_dim_km_swizzle_cuda, _inputs_x,
      "(1,32) dim-k + (32,1) dim-m, one pass, t-contig, swizzle"),
+    ("mxfp8_32x32", "Mxfp832x32Gold", mxfp8_32x32_cuda, _inputs_x, "(32,32) block"),
+    ("mxfp8_32x32_swizzle", "Mxfp832x32SwizzleGold", mxfp8_32x32_swizzle_cuda, _inputs_x, "(32,32) block, swizzle"),
+    ("mxfp8_32x32_dim_m_swizzle", "Mxfp832x32DimMSwizzleGold", mxfp8_32x32_dim_m_swizzle_cuda, _inputs_x,
+     "(32,32) block, t-contig, swizzle"),
+    ("mxfp8_32x32_dim_km_swizzle", "Mxfp832x32DimKMSwizzleGold", mxfp8_32x32_dim_km_swizzle_cuda, _inputs_x,
+     "(32,32) block, one pass, t-contig, swizzle"),
+    ("mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle", "Mxfp832x32QdataDimKScaleDimKMSwizzleGold",
+     mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda, _inputs_x, "(32,32) block, one pass, dim-k qdata + km scales, swizzle"),
     ("fp8_rowwise", "RowwiseFp8Gold", rowwise_fp8_cuda, _inputs_x, "(1,-1) block"),
     ("fp8_colwise", "ColwiseFp8Gold", colwise_fp8_cuda, _inputs_x, "(-1,1) block, t-contig"),
     ("nvfp4", "Nvfp4GsGold", nvfp4_gs_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, no swizzle"),

@@ -82,6 +82,11 @@ def main():
                    "mxfp8_dim_m_swizzle_f", "mxfp8_dim_km_f", "mxfp8_dim_km_swizzle_f"):
             for i, o in enumerate(getattr(G, fn)(x)):
                 out[f"{tag}/{fn}/{i}"] = raw(o)
+        if M % 32 == 0:   # 32x32 blocks (G:753-959)
+            for fn in ("mxfp8_32x32_f", "mxfp8_32x32_swizzle_f", "mxfp8_32x32_dim_m_swizzle_f", "mxfp8_32x32_dim_km_swizzle_f",
+                       "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"):
+                for i, o in enumerate(getattr(G, fn)(x)):
+                    out[f"{tag}/{fn}/{i}"] = raw(o)
         gs = G.nvfp4_gs_scale(x)
         out[f"{tag}/nvfp4_gs_scale/0"] = raw(gs.reshape(1))
         for fn in ("nvfp4_gs_f", "nvfp4_gs_swizzle_f"):

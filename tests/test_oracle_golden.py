@@ -22,6 +22,20 @@ def test_single_input_recipes(tag, fn):
         assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
 
 
+B32 = ["mxfp8_32x32_f", "mxfp8_32x32_swizzle_f", "mxfp8_32x32_dim_m_swizzle_f", "mxfp8_32x32_dim_km_swizzle_f",
+       "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"]
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+@pytest.mark.parametrize("fn", B32)
+def test_mxfp8_32x32_recipes(tag, fn):
+    x = golden_x(tag)
+    outs = getattr(O, fn)(x)
+    assert len(outs) == golden_n_outputs(tag, fn) > 0
+    for i, o in enumerate(outs):
+        assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
+
+
 @pytest.mark.parametrize("tag", golden_cases())
 def test_fp8_tensorwise(tag):
     x = golden_x(tag)

@@ -44,6 +44,38 @@ def _x(M, N, seed=0, **kw):
     return make_input(M, N, seed, **kw)
 
 
+B32 = ["mxfp8_32x32", "mxfp8_32x32_swizzle", "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle",
+       "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle"]
+
+
+@pytest.mark.parametrize("tag", golden_cases())
+@pytest.mark.parametrize("fn", B32)
+def test_golden_32x32(tag, fn):
+    x = golden_x(tag).cuda()
+    outs = cuda_fn(fn)(x)
+    assert len(outs) == golden_n_outputs(tag, fn + "_f") > 0
+    for i, o in enumerate(outs):
+        assert_same_bits(o, golden_out(tag, fn + "_f", i), f"{fn}[{i}] {tag}")
+
+
+@pytest.mark.parametrize("shape", [(512, 512), (96, 160), (128, 160), (32, 32), (160, 416), (384, 96), (1024, 2048), (2080, 1056)])
+@pytest.mark.parametrize("fn", B32)
+def test_32x32_matches_oracle(fn, shape):
+    x = _x(*shape, seed=shape[0] + 7)
+    same_outputs(cuda_fn(fn)(x.cuda()), oracle_fn(fn)(x), f"{fn} {shape}")
+
+
+def test_32x32_outputs_fully_written():
+    """Blocked scale padding is zero whatever the buffers held before (ragged shape: 160 rows, 13 column blocks)."""
+    x = _x(160, 416, seed=3)
+    xc = x.cuda()
+    for fill in (0x00, 0xFF):
+        junk = [torch.full((1 << 22,), fill, dtype=torch.uint8, device="cuda") for _ in range(4)]
+        del junk
+        same_outputs(Q.mxfp8_32x32_dim_km_swizzle_cuda(xc), O.mxfp8_32x32_dim_km_swizzle_f(x), f"fill {fill}")
+        same_outputs(Q.mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda(xc), O.mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f(x), f"fill {fill}")
+
+
 # ---------------------------------------------------------------------------- golden vectors
 @pytest.mark.parametrize("tag", golden_cases())
 @pytest.mark.parametrize("fn", ONE_INPUT)
@@ -368,7 +400,9 @@ def test_host_buffer_caster_matches_oracle(swizzle):
 def test_recipe_index_mirrors_reference_backends():
     names = [n for n, _ in Q.ALL_RECIPES]
     assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "fp8_colwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
-                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
+                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "mxfp8_32x32", "mxfp8_32x32_swizzle",
+                     "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle", "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle",
+                     "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
                      "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "bf16_rht"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
