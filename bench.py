@@ -476,6 +476,13 @@ def bench_other_casts(Q, x, dev, peak):
         out["mxfp8_dim_m_swizzle" + sfx] = timed(lambda: Q.mxfp8_dim_m_swizzle_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_m"))
         out["mxfp8_dim_km" + sfx] = timed(lambda: Q.mxfp8_dim_km_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_km"))
         out["mxfp8_dim_km_swizzle" + sfx] = timed(lambda: Q.mxfp8_dim_km_swizzle_cuda(x, mode=mode), algorithmic_bytes(M, N, "mxfp8_dim_km"))
+    e_ = M * N
+    out["mxfp8_32x32"] = timed(lambda: Q.mxfp8_32x32_cuda(x), 3 * e_ + e_ // 1024)
+    out["mxfp8_32x32_swizzle"] = timed(lambda: Q.mxfp8_32x32_swizzle_cuda(x), 3 * e_ + e_ // 32)
+    out["mxfp8_32x32_dim_m_swizzle"] = timed(lambda: Q.mxfp8_32x32_dim_m_swizzle_cuda(x), 3 * e_ + e_ // 32)
+    out["mxfp8_32x32_dim_km_swizzle"] = timed(lambda: Q.mxfp8_32x32_dim_km_swizzle_cuda(x), 4 * e_ + e_ // 16)
+    out["mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle"] = timed(
+        lambda: Q.mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda(x), 3 * e_ + e_ // 16)
     # reference shape for the fp8 / nvfp4 rows as well (16384^2), then the smaller configurations
     s = Q.float8_tensorwise_scale_cuda(x)
     gs = Q.nvfp4_gs_scale_cuda(x)

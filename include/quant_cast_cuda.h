@@ -148,6 +148,22 @@ int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
 int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q,
                             void *stream);
 
+/*
+ * fp8 e4m3 with one fp32 scale per 128-element block: scale = clamp(amax, 1e-12) / 448, q = e4m3(x * (1 / scale)).
+ *   QCC_ROWWISE: qk (M, N), sk (M, N/128) fp32 -- 1x128 blocks along the rows   deepseek_1x128_f        G:103-110
+ *   QCC_COLWISE: qm (N, M), sm (N, M/128) fp32 -- 128x1 blocks down the rows,
+ *                outputs transposed                                             deepseek_1x128_dim_m_f  G:194-214
+ *   both:        one read of x, four outputs                                    deepseek_1x128_dim_km_f G:251-277
+ * The amax is clamped in bf16 (bf16(1e-12)) for a single direction and in fp32 for the fused form, as in the
+ * reference; the two differ only in the scale of an all-zero block.
+ * QCC_ROWWISE needs N % 128 == 0; QCC_COLWISE needs M % 128 == 0 and N % 8 == 0.
+ */
+int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, void *qk, float *sk, void *qm, float *sm,
+                     void *stream);
+
+/* 128x128 blocks: q (M, N), scale (M/128, N/128) fp32 (deepseek_128x128_f G:141-161).  M % 128 == 0, N % 128 == 0. */
+int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, void *q, float *scale, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * mxfp8: 32-element blocks, e8m0 scales, e4m3 elements
  * ------------------------------------------------------------------------------------------- */

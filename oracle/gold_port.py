@@ -39,6 +39,7 @@ def lib():
         _lib.qco_num_threads.restype = ctypes.c_int
         _lib.qco_hadamard_rht.restype = ctypes.c_int
         _lib.qco_mxfp8_32x32.restype = ctypes.c_int
+        _lib.qco_fp8_blockwise.restype = ctypes.c_int
         _lib.qco_hadamard_rht_t.restype = ctypes.c_int
     return _lib
 
@@ -296,6 +297,38 @@ def mxfp8_dim_km_swizzle_f(x, mode="rceil", **kwargs):
 
 
 # ------------------------------------------------------------------ nvfp4
+# ------------------------------------------------------------------ fp8 with 1x128 / 128x128 blocks
+def _fp8_blockwise(x, bm, bn, clamp_f32=False, transposed=False):
+    _check_x(x)
+    M, N = x.shape
+    q = torch.empty((N, M) if transposed else (M, N), dtype=torch.uint8)
+    sshape = (N // bn, M // bm) if transposed else (M // bm, N // bn)
+    s = torch.empty(sshape, dtype=torch.float32)
+    rc = lib().qco_fp8_blockwise(_p(x), _i64(M), _i64(N), _i64(bm), _i64(bn), int(clamp_f32), int(transposed), _p(q), _p(s))
+    assert rc == 0, f"blocks of {bm}x{bn} must tile the {M}x{N} input"
+    return q.view(torch.float8_e4m3fn), s
+
+
+def deepseek_1x128_f(x, **kwargs):
+    """G:103-110"""
+    return _fp8_blockwise(x, 1, 128)
+
+
+def deepseek_128x128_f(x, **kwargs):
+    """G:141-161"""
+    return _fp8_blockwise(x, 128, 128)
+
+
+def deepseek_1x128_dim_m_f(x, **kwargs):
+    """G:194-214"""
+    return _fp8_blockwise(x, 128, 1, transposed=True)
+
+
+def deepseek_1x128_dim_km_f(x, **kwargs):
+    """G:251-277 (amax clamped in fp32 there)"""
+    return _fp8_blockwise(x, 1, 128, clamp_f32=True) + _fp8_blockwise(x, 128, 1, clamp_f32=True, transposed=True)
+
+
 # ------------------------------------------------------------------ mxfp8, 32x32 blocks
 def mxfp8_32x32_f(x, **kwargs):
     """gold mxfp8_32x32_f (G:753-773): (qdata (M, N) e4m3, scale (M/32, N/32) e8m0)."""

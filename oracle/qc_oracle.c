@@ -408,6 +408,43 @@ void qco_fp8_colwise_precalc(const uint16_t *x, int64_t M, int64_t N, const floa
             q[c * M + r] = f32_to_fp8_fmt(bf16_to_f32(x[r * N + c]) / scale[c], fmt);
 }
 
+/*
+ * fp8 e4m3 with one fp32 scale per bm x bn block ("deepseek" recipes): scale = clamp(amax) / 448,
+ * q = e4m3(x * (1 / scale)).
+ *   bm = 1,   bn = 128: deepseek_1x128_f        G:103-110   q (M, N),  scale (M, N/128)
+ *   bm = 128, bn = 128: deepseek_128x128_f      G:141-161   q (M, N),  scale (M/128, N/128)
+ *   bm = 128, bn = 1, transposed != 0: deepseek_1x128_dim_m_f  G:194-214   q (N, M), scale (N, M/128)
+ * deepseek_1x128_dim_km_f (G:251-277) is the first and the third on one fp32 view of x; there the
+ * amax is clamped in fp32 (clamp_f32 != 0: 1e-12 as fp32), elsewhere in bf16 (bf16(1e-12)).
+ */
+int qco_fp8_blockwise(const uint16_t *x, int64_t M, int64_t N, int64_t bm, int64_t bn, int clamp_f32,
+                      int transposed, uint8_t *q, float *scale)
+{
+    if (bm <= 0 || bn <= 0 || M % bm || N % bn) return -1;
+    int64_t nbr = M / bm, nbc = N / bn;
+    const float tiny = clamp_f32 ? 1e-12f : u2f(0x2B8D0000u);
+#pragma omp parallel for schedule(static)
+    for (int64_t bi = 0; bi < nbr * nbc; bi++) {
+        int64_t br = bi / nbc, bc = bi % nbc;
+        uint16_t best = 0;
+        for (int64_t r = 0; r < bm; r++)
+            for (int64_t c = 0; c < bn; c++) {
+                uint16_t a = bf16_abs(x[(br * bm + r) * N + bc * bn + c]);
+                if (a > best) best = a;
+            }
+        float amax = bf16_to_f32(best);
+        float s = (amax < tiny ? tiny : amax) / 448.0f;
+        float inv = 1.0f / s;
+        scale[transposed ? bc * nbr + br : br * nbc + bc] = s;
+        for (int64_t r = 0; r < bm; r++)
+            for (int64_t c = 0; c < bn; c++) {
+                int64_t R = br * bm + r, C = bc * bn + c;
+                q[transposed ? C * M + R : R * N + C] = f32_to_fp8(bf16_to_f32(x[R * N + C]) * inv, 3, 7, 0x7E);
+            }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* mxfp8                                                                                      */
 /* ------------------------------------------------------------------------------------------ */

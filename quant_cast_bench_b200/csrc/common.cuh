@@ -92,6 +92,32 @@ __device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d
 {
     return cvt_fp8x2<FMT>(a, b) | (cvt_fp8x2<FMT>(c, d) << 16);
 }
+// 32 fp32-scaled values of one row block -> 32 e4m3 bytes, given the four 16-byte chunks
+__device__ __forceinline__ void quant_row_block(const uint4 c[4], float rcp, uint4 &o0, uint4 &o1)
+{
+    o0.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].x), bf16hi(c[0].x), bf16lo(c[0].y), bf16hi(c[0].y), rcp);
+    o0.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[0].z), bf16hi(c[0].z), bf16lo(c[0].w), bf16hi(c[0].w), rcp);
+    o0.z = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].x), bf16hi(c[1].x), bf16lo(c[1].y), bf16hi(c[1].y), rcp);
+    o0.w = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[1].z), bf16hi(c[1].z), bf16lo(c[1].w), bf16hi(c[1].w), rcp);
+    o1.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].x), bf16hi(c[2].x), bf16lo(c[2].y), bf16hi(c[2].y), rcp);
+    o1.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[2].z), bf16hi(c[2].z), bf16lo(c[2].w), bf16hi(c[2].w), rcp);
+    o1.z = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].x), bf16hi(c[3].x), bf16lo(c[3].y), bf16hi(c[3].y), rcp);
+    o1.w = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[3].z), bf16hi(c[3].z), bf16lo(c[3].w), bf16hi(c[3].w), rcp);
+}
+
+__device__ __forceinline__ float amax_of_block(const uint4 c[4])
+{
+    uint32_t a0 = absmax2(c[0].x, c[0].y), a1 = absmax2(c[0].z, c[0].w);
+#pragma unroll
+    for (int i = 1; i < 4; i++) {
+        a0 = absmax2_acc(absmax2_acc(a0, c[i].x), c[i].y);
+        a1 = absmax2_acc(absmax2_acc(a1, c[i].z), c[i].w);
+    }
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162 *>(&a0), y = *reinterpret_cast<__nv_bfloat162 *>(&a1);
+    __nv_bfloat162 m = __hmax2(x, y);
+    return hmax_halves_f32(*reinterpret_cast<uint32_t *>(&m));
+}
+
 // e4m3 byte -> fp32 (exact)
 __device__ __forceinline__ float e4m3_to_f32(uint32_t byte)
 {

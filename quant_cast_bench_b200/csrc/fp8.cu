@@ -470,6 +470,7 @@ using namespace qcc;
 // per-translation-unit error words of the tiled kernels
 extern "C" int qcc_mxfp8_device_error(unsigned int *out);
 extern "C" int qcc_nvfp4_device_error(unsigned int *out);
+extern "C" int qcc_block128_device_error(unsigned int *out);
 
 extern "C" {
 
@@ -482,6 +483,9 @@ int qcc_device_error(unsigned int *out)
     if (e) return e;
     if ((e = qcc_mxfp8_device_error(&b)) != 0) return e;
     if ((e = qcc_nvfp4_device_error(&c)) != 0) return e;
+    unsigned int d = 0;
+    if ((e = qcc_block128_device_error(&d)) != 0) return e;
+    c = c > d ? c : d;
     if (out) *out = a > b ? (a > c ? a : c) : (b > c ? b : c);
     return 0;
 }

@@ -250,6 +250,60 @@ def _mxfp8(x, flags, out=None):
     return tuple(outs)
 
 
+def _fp8_block128(x, row, col):
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    if row:
+        assert N % 128 == 0, f"1x128 blocks need N % 128 == 0, got N={N}"
+    if col:
+        assert M % 128 == 0 and N % 8 == 0, f"128x1 blocks need M % 128 == 0 and N % 8 == 0, got {M}x{N}"
+    dev = x.device
+    qk = torch.empty((M, N), dtype=torch.uint8, device=dev) if row else None
+    sk = torch.empty((M, N // 128), dtype=torch.float32, device=dev) if row else None
+    qm = torch.empty((N, M), dtype=torch.uint8, device=dev) if col else None
+    sm = torch.empty((N, M // 128), dtype=torch.float32, device=dev) if col else None
+    flags = (L.ROWWISE if row else 0) | (L.COLWISE if col else 0)
+    with _on_device(dev):
+        L.check(lib.qcc_fp8_block128(_p(x), M, N, flags, _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "fp8_block128")
+    L.launch_count += 1
+    outs = []
+    if row:
+        outs += [qk.view(torch.float8_e4m3fn), sk]
+    if col:
+        outs += [qm.view(torch.float8_e4m3fn), sm]
+    return tuple(outs)
+
+
+def deepseek_1x128_cuda(x, **kwargs):
+    """gold deepseek_1x128_f (G:103-110): (qdata (M, N) e4m3, scale (M, N/128) fp32)."""
+    return _fp8_block128(x, True, False)
+
+
+def deepseek_1x128_dim_m_cuda(x, **kwargs):
+    """gold deepseek_1x128_dim_m_f (G:194-214): 128x1 blocks, (qdata (N, M), scale (N, M/128))."""
+    return _fp8_block128(x, False, True)
+
+
+def deepseek_1x128_dim_km_cuda(x, **kwargs):
+    """gold deepseek_1x128_dim_km_f (G:251-277): both from one read (the amax clamp is in fp32 there)."""
+    return _fp8_block128(x, True, True)
+
+
+def deepseek_128x128_cuda(x, **kwargs):
+    """gold deepseek_128x128_f (G:141-161): (qdata (M, N), scale (M/128, N/128) fp32)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert M % 128 == 0 and N % 128 == 0, f"128x128 blocks need M % 128 == 0 and N % 128 == 0, got {M}x{N}"
+    q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M // 128, N // 128), dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_fp8_block128x128(_p(x), M, N, _p(q), _p(s), _stream(x)), "fp8_block128x128")
+    L.launch_count += 1
+    return q.view(torch.float8_e4m3fn), s
+
+
 def _mxfp8_32x32(x, row, col, swz, transposed_data=True):
     """32x32 blocks: one e8m0 scale per block, shared by both orientations (QCC_BLOCK32)."""
     lib = L.load()
@@ -602,11 +656,15 @@ _TABLE = [
     ("fp8_colwise_precalc_scale", "ColwisePrecalcGold", colwise_precalc_cuda, _inputs_colwise_precalc, "elementwise"),
     ("mxfp8", "Mxfp8Gold", mxfp8_cuda, _inputs_x, "(1,32) block"),
     ("mxfp8_swizzle", "Mxfp8SwizzleGold", mxfp8_swizzle_cuda, _inputs_x, "(1,32) block, swizzle"),
+    ("fp8_deepseek_1x128", "Deepseek1x128Gold", deepseek_1x128_cuda, _inputs_x, "(1,128) block"),
     ("mxfp8_dim_m", "Mxfp8DimMGold", mxfp8_dim_m_cuda, _inputs_x, "(32,1) block, t-contig"),
     ("mxfp8_dim_m_swizzle", "Mxfp8DimMSwizzleGold", mxfp8_dim_m_swizzle_cuda, _inputs_x, "(32,1) block, t-contig, swizzle"),
+    ("fp8_deepseek_1x128_dim_m", "Deepseek1x128DimMGold", deepseek_1x128_dim_m_cuda, _inputs_x, "(128,1) block, t-contig"),
     ("mxfp8_dim_km", "Mxfp8DimKmGold", mxfp8_dim_km_cuda, _inputs_x, "(1,32) dim-k + (32,1) dim-m, one pass, t-contig"),
     ("mxfp8_dim_km_swizzle", "Mxfp8DimKmSwizzleGold", mxfp8_dim_km_swizzle_cuda, _inputs_x,
      "(1,32) dim-k + (32,1) dim-m, one pass, t-contig, swizzle"),
+    ("fp8_deepseek_1x128_dim_km", "Deepseek1x128DimKmGold", deepseek_1x128_dim_km_cuda, _inputs_x,
+     "(1,128) dim-k + (128,1) dim-m, one pass, t-contig"),
     ("mxfp8_32x32", "Mxfp832x32Gold", mxfp8_32x32_cuda, _inputs_x, "(32,32) block"),
     ("mxfp8_32x32_swizzle", "Mxfp832x32SwizzleGold", mxfp8_32x32_swizzle_cuda, _inputs_x, "(32,32) block, swizzle"),
     ("mxfp8_32x32_dim_m_swizzle", "Mxfp832x32DimMSwizzleGold", mxfp8_32x32_dim_m_swizzle_cuda, _inputs_x,
@@ -615,6 +673,7 @@ _TABLE = [
      "(32,32) block, one pass, t-contig, swizzle"),
     ("mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle", "Mxfp832x32QdataDimKScaleDimKMSwizzleGold",
      mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda, _inputs_x, "(32,32) block, one pass, dim-k qdata + km scales, swizzle"),
+    ("fp8_deepseek_128x128", "Deepseek128x128Gold", deepseek_128x128_cuda, _inputs_x, "(128,128) block"),
     ("fp8_rowwise", "RowwiseFp8Gold", rowwise_fp8_cuda, _inputs_x, "(1,-1) block"),
     ("fp8_colwise", "ColwiseFp8Gold", colwise_fp8_cuda, _inputs_x, "(-1,1) block, t-contig"),
     ("nvfp4", "Nvfp4GsGold", nvfp4_gs_cuda, _inputs_nvfp4, "(1,16) block, fp4 qdata, no swizzle"),

@@ -62,7 +62,7 @@ def main():
     G, GU = import_gold(args.reference)
     out = {}
 
-    cases = [(128, 128, 0), (96, 160, 1), (128, 160, 2), (160, 320, 4)]
+    cases = [(128, 128, 0), (96, 160, 1), (128, 160, 2), (160, 320, 4), (256, 256, 5)]
     names = []
     for M, N, seed in cases:
         x = make_input(M, N, seed)
@@ -82,6 +82,10 @@ def main():
                    "mxfp8_dim_m_swizzle_f", "mxfp8_dim_km_f", "mxfp8_dim_km_swizzle_f"):
             for i, o in enumerate(getattr(G, fn)(x)):
                 out[f"{tag}/{fn}/{i}"] = raw(o)
+        if M % 128 == 0 and N % 128 == 0:   # 1x128 / 128x128 blocks with fp32 scales (G:103-277)
+            for fn in ("deepseek_1x128_f", "deepseek_128x128_f", "deepseek_1x128_dim_m_f", "deepseek_1x128_dim_km_f"):
+                for i, o in enumerate(getattr(G, fn)(x)):
+                    out[f"{tag}/{fn}/{i}"] = raw(o)
         if M % 32 == 0:   # 32x32 blocks (G:753-959)
             for fn in ("mxfp8_32x32_f", "mxfp8_32x32_swizzle_f", "mxfp8_32x32_dim_m_swizzle_f", "mxfp8_32x32_dim_km_swizzle_f",
                        "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"):

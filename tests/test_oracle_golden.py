@@ -22,6 +22,29 @@ def test_single_input_recipes(tag, fn):
         assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
 
 
+DEEPSEEK = ["deepseek_1x128_f", "deepseek_128x128_f", "deepseek_1x128_dim_m_f", "deepseek_1x128_dim_km_f"]
+
+
+@pytest.mark.parametrize("tag", [t for t in golden_cases() if golden_n_outputs(t, "deepseek_1x128_f")])
+@pytest.mark.parametrize("fn", DEEPSEEK)
+def test_deepseek_recipes(tag, fn):
+    x = golden_x(tag)
+    outs = getattr(O, fn)(x)
+    assert len(outs) == golden_n_outputs(tag, fn) > 0
+    for i, o in enumerate(outs):
+        assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
+
+
+def test_deepseek_clamp_variants():
+    """An all-zero block takes the clamp: bf16(1e-12) in the single-direction recipes, fp32(1e-12) in dim_km."""
+    x = torch.zeros(128, 128, dtype=torch.bfloat16)
+    s_bf16 = O.deepseek_1x128_f(x)[1][0, 0]
+    s_f32 = O.deepseek_1x128_dim_km_f(x)[1][0, 0]
+    assert s_bf16 == torch.tensor(1e-12).to(torch.bfloat16).float() / 448.0
+    assert s_f32 == torch.tensor(1e-12, dtype=torch.float32) / 448.0
+    assert s_bf16 != s_f32
+
+
 B32 = ["mxfp8_32x32_f", "mxfp8_32x32_swizzle_f", "mxfp8_32x32_dim_m_swizzle_f", "mxfp8_32x32_dim_km_swizzle_f",
        "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"]
 

@@ -44,6 +44,41 @@ def _x(M, N, seed=0, **kw):
     return make_input(M, N, seed, **kw)
 
 
+DEEPSEEK = ["deepseek_1x128", "deepseek_128x128", "deepseek_1x128_dim_m", "deepseek_1x128_dim_km"]
+
+
+@pytest.mark.parametrize("tag", [t for t in golden_cases() if golden_n_outputs(t, "deepseek_1x128_f")])
+@pytest.mark.parametrize("fn", DEEPSEEK)
+def test_golden_deepseek(tag, fn):
+    x = golden_x(tag).cuda()
+    outs = cuda_fn(fn)(x)
+    assert len(outs) == golden_n_outputs(tag, fn + "_f") > 0
+    for i, o in enumerate(outs):
+        assert_same_bits(o, golden_out(tag, fn + "_f", i), f"{fn}[{i}] {tag}")
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (1024, 2048), (2176, 1152)])
+@pytest.mark.parametrize("fn", DEEPSEEK)
+def test_deepseek_matches_oracle(fn, shape):
+    x = _x(*shape, seed=shape[1] + 11)
+    same_outputs(cuda_fn(fn)(x.cuda()), oracle_fn(fn)(x), f"{fn} {shape}")
+
+
+def test_deepseek_ragged_and_zero_blocks():
+    """1x128 takes any row count, 128x1 any multiple of 8 columns; an all-zero input takes the clamp of each recipe."""
+    x = _x(96, 256, seed=2)
+    same_outputs(Q.deepseek_1x128_cuda(x.cuda()), O.deepseek_1x128_f(x), "1x128 at 96 rows")
+    x = _x(256, 200, seed=3)
+    same_outputs(Q.deepseek_1x128_dim_m_cuda(x.cuda()), O.deepseek_1x128_dim_m_f(x), "128x1 at 200 columns")
+    z = torch.zeros(256, 256, dtype=torch.bfloat16)
+    for fn in DEEPSEEK:
+        same_outputs(cuda_fn(fn)(z.cuda()), oracle_fn(fn)(z), f"{fn} zeros")
+    with pytest.raises(AssertionError):
+        Q.deepseek_1x128_cuda(_x(128, 160).cuda())
+    with pytest.raises(AssertionError):
+        Q.deepseek_128x128_cuda(_x(96, 256).cuda())
+
+
 B32 = ["mxfp8_32x32", "mxfp8_32x32_swizzle", "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle",
        "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle"]
 
@@ -399,10 +434,11 @@ def test_host_buffer_caster_matches_oracle(swizzle):
 
 def test_recipe_index_mirrors_reference_backends():
     names = [n for n, _ in Q.ALL_RECIPES]
-    assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "fp8_colwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "mxfp8_dim_m",
-                     "mxfp8_dim_m_swizzle", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "mxfp8_32x32", "mxfp8_32x32_swizzle",
+    assert names == ["fp8_tensorwise_precalc_scale", "fp8_rowwise_precalc_scale", "fp8_colwise_precalc_scale", "mxfp8", "mxfp8_swizzle", "fp8_deepseek_1x128", "mxfp8_dim_m",
+                     "mxfp8_dim_m_swizzle", "fp8_deepseek_1x128_dim_m", "mxfp8_dim_km", "mxfp8_dim_km_swizzle", "fp8_deepseek_1x128_dim_km",
+                     "mxfp8_32x32", "mxfp8_32x32_swizzle",
                      "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle", "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle",
-                     "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
+                     "fp8_deepseek_128x128", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
                      "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "bf16_rht"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
