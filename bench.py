@@ -483,6 +483,10 @@ def bench_other_casts(Q, x, dev, peak):
     out["mxfp8_32x32_dim_km_swizzle"] = timed(lambda: Q.mxfp8_32x32_dim_km_swizzle_cuda(x), 4 * e_ + e_ // 16)
     out["mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle"] = timed(
         lambda: Q.mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_cuda(x), 3 * e_ + e_ // 16)
+    out["fp8_deepseek_1x128"] = timed(lambda: Q.deepseek_1x128_cuda(x), 3 * e_ + e_ // 32)
+    out["fp8_deepseek_1x128_dim_m"] = timed(lambda: Q.deepseek_1x128_dim_m_cuda(x), 3 * e_ + e_ // 32)
+    out["fp8_deepseek_1x128_dim_km"] = timed(lambda: Q.deepseek_1x128_dim_km_cuda(x), 4 * e_ + e_ // 16)
+    out["fp8_deepseek_128x128"] = timed(lambda: Q.deepseek_128x128_cuda(x), 3 * e_ + e_ // 4096)
     # reference shape for the fp8 / nvfp4 rows as well (16384^2), then the smaller configurations
     s = Q.float8_tensorwise_scale_cuda(x)
     gs = Q.nvfp4_gs_scale_cuda(x)
