@@ -164,6 +164,10 @@ int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, void *qk, f
 /* 128x128 blocks: q (M, N), scale (M/128, N/128) fp32 (deepseek_128x128_f G:141-161).  M % 128 == 0, N % 128 == 0. */
 int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, void *q, float *scale, void *stream);
 
+/* out (M/128, N/128) fp32 = max |x| of every 128x128 block (QCC_AMAX_RAW) or that maximum / 2688
+ * (QCC_AMAX_NVFP4_SCALE: nvfp4_blocked_outer_scale G:1601-1606).  M % 128 == 0, N % 128 == 0. */
+int qcc_amax_block128x128(const void *x, int64_t M, int64_t N, int mode, float *out, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * mxfp8: 32-element blocks, e8m0 scales, e4m3 elements
  * ------------------------------------------------------------------------------------------- */
@@ -216,8 +220,9 @@ int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags, const int3
 /*
  * Rowwise: q (M, N/2) bytes, s the (M, N/16) e4m3 scales (plain or blocked).
  *   nvfp4_gs_f G:1494-1517, nvfp4_gs_swizzle_f G:1249-1266, nvfp4_gs_swizzle_sr_f G:1409-1426.
- * outer: device fp32; outer_per_row == 0 -> one value for the tensor, != 0 -> one per row (the
- * per-token form of G:1567-1571).  philox_key: device uint64[2] = {seed, offset}, read only when
+ * outer: device fp32; outer_per_row == 0 -> one value for the tensor, 1 -> one per row (the per-token
+ * form of G:1567-1571), 2 -> one per 128x128 block, the (M/128, N/128) grid of nvfp4_blocked_outer_f
+ * (G:1609-1634; needs M % 128 == 0, N % 128 == 0, no QCC_SR).  philox_key: device uint64[2] = {seed, offset}, read only when
  * QCC_SR is set; element (r, c) uses counter ((r * N + c) >> 2) + offset, output word (r * N + c) & 3,
  * and its low 22 bits as the dither of G:1401-1405.  Needs N % 16 == 0.
  */

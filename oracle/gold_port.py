@@ -40,6 +40,7 @@ def lib():
         _lib.qco_hadamard_rht.restype = ctypes.c_int
         _lib.qco_mxfp8_32x32.restype = ctypes.c_int
         _lib.qco_fp8_blockwise.restype = ctypes.c_int
+        _lib.qco_amax_block128x128.restype = ctypes.c_int
         _lib.qco_hadamard_rht_t.restype = ctypes.c_int
     return _lib
 
@@ -373,12 +374,14 @@ def mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f(x, **kwargs):
     return q, _expand_k(s), _expand_m(s)
 
 
-def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
+def _nvfp4(x, outer_scale, flags, key=None, transposed=False, outer_mode=None):
     _check_x(x)
     M, N = x.shape
     o = outer_scale.detach().float().contiguous().reshape(-1)
     per_row = int(outer_scale.ndim == 2)
-    if per_row:
+    if outer_mode is not None:
+        per_row = outer_mode
+    if per_row == 1:
         assert o.numel() == M and not transposed
     seed, off = key_words(key) if key is not None else (0, 0)
     swz = bool(flags & SWIZZLE)
@@ -400,6 +403,22 @@ def nvfp4_gs_f(x, outer_scale, **kwargs):
 
 def nvfp4_gs_swizzle_f(x, outer_scale, **kwargs):
     return _nvfp4(x, outer_scale, SWIZZLE)
+
+
+def nvfp4_blocked_outer_scale(x):
+    """G:1601-1606: per-128x128-block outer scale, (M/128, N/128) fp32."""
+    _check_x(x)
+    M, N = x.shape
+    out = torch.empty((M // 128, N // 128), dtype=torch.float32)
+    rc = lib().qco_amax_block128x128(_p(x), _i64(M), _i64(N), ctypes.c_float(2688.0), _p(out))
+    assert rc == 0
+    return out
+
+
+def nvfp4_blocked_outer_f(x, outer_blocked, **kwargs):
+    """G:1609-1634"""
+    assert outer_blocked.shape == (x.shape[0] // 128, x.shape[1] // 128)
+    return _nvfp4(x, outer_blocked, SWIZZLE, outer_mode=2)
 
 
 def nvfp4_gs_swizzle_sr_f(x, outer_scale, key, **kwargs):

@@ -299,6 +299,25 @@ void qco_fp8_tensorwise_scale(const uint16_t *x, int64_t n, int fmt, float *scal
     qco_fp8_scale_from_amax(amax, fmt, scale);
 }
 
+/* max |x| of every 128x128 block divided by `div` (2688: nvfp4_blocked_outer_scale G:1601-1606), (M/128, N/128) */
+int qco_amax_block128x128(const uint16_t *x, int64_t M, int64_t N, float div, float *out)
+{
+    if (M % 128 || N % 128) return -1;
+    int64_t nbc = N / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t bi = 0; bi < (M / 128) * nbc; bi++) {
+        int64_t br = bi / nbc, bc = bi % nbc;
+        uint16_t best = 0;
+        for (int r = 0; r < 128; r++)
+            for (int c = 0; c < 128; c++) {
+                uint16_t a = bf16_abs(x[(br * 128 + r) * N + bc * 128 + c]);
+                if (a > best) best = a;
+            }
+        out[bi] = bf16_to_f32(best) / div;
+    }
+    return 0;
+}
+
 /* amax -> nvfp4 per-tensor outer scale = amax / (448 * 6), no clamp.  G:1243-1246. */
 void qco_nvfp4_scale_from_amax(float amax, float *scale) { *scale = amax / 2688.0f; }
 
@@ -584,14 +603,17 @@ int qco_nvfp4(const uint16_t *x, int64_t M, int64_t N, const float *outer, int o
               int flags, uint64_t seed, uint64_t offset, uint8_t *q, uint8_t *s)
 {
     if (N % 16) return -1;
+    if (outer_per_row == 2 && (M % 128 || N % 128)) return -1;
     int swz = (flags & QC_SWIZZLE) != 0, sr = (flags & QC_SR) != 0;
     int64_t nb = N / 16;
     size_t ncb = (size_t)(nb + 3) / 4;
     if (swz) memset(s, 0, blocked_bytes((size_t)M, (size_t)nb));
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < M; r++) {
-        float o = outer_per_row ? outer[r] : outer[0];
+        float o = outer_per_row == 1 ? outer[r] : outer[0];
         for (int64_t b = 0; b < nb; b++) {
+            /* outer_per_row == 2: one outer scale per 128x128 block, nvfp4_blocked_outer_f G:1609-1634 */
+            if (outer_per_row == 2) o = outer[(r / 128) * (N / 128) + b / 8];
             const uint16_t *xb = x + r * N + b * 16;
             float v[16];
             uint16_t best = 0;

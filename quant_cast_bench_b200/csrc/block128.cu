@@ -63,8 +63,12 @@ fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t 
 // ---------------------------------------------------------------------------------------------
 // 128x128 blocks: register tile
 // ---------------------------------------------------------------------------------------------
+// AMAX_ONLY: no cast; scale receives the block maximum divided by `amax_div` (1: the maximum itself, 2688: the
+// per-block nvfp4 outer scale of nvfp4_blocked_outer_scale, G:1601-1606, which takes no clamp).
+template <bool AMAX_ONLY>
 __global__ void __launch_bounds__(128, 4)
-fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *__restrict__ q, float *__restrict__ scale)
+fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *__restrict__ q, float *__restrict__ scale,
+                   float amax_div)
 {
     __shared__ uint32_t s_max[4];
     const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
@@ -84,6 +88,10 @@ fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *
     if ((t & 31) == 0) s_max[t >> 5] = m;
     __syncthreads();
     m = max(max(s_max[0], s_max[1]), max(s_max[2], s_max[3]));
+    if (AMAX_ONLY) {
+        if (t == 0) scale[blockIdx.x] = __fdiv_rn(u2f(m), amax_div);
+        return;
+    }
     const float s = block_scale<false>(u2f(m));
     const float inv = __fdiv_rn(1.0f, s);
     uint8_t *qo = q + origin;
@@ -323,7 +331,19 @@ extern "C" int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, void *q
     if (M < 0 || N < 0 || M % 128 != 0 || N % 128 != 0 || N > 0x7FFFFF00 || (M / 128) * (N / 128) > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
     const int tiles_n = (int)(N / 128);
-    fp8_128x128_kernel<<<(unsigned)((M / 128) * tiles_n), 128, 0, (cudaStream_t)stream>>>((const uint16_t *)x, (int)N, tiles_n,
-                                                                                         (uint8_t *)q, scale);
+    fp8_128x128_kernel<false><<<(unsigned)((M / 128) * tiles_n), 128, 0, (cudaStream_t)stream>>>(
+        (const uint16_t *)x, (int)N, tiles_n, (uint8_t *)q, scale, 1.0f);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int qcc_amax_block128x128(const void *x, int64_t M, int64_t N, int mode, float *out, void *stream)
+{
+    if (M == 0 || N == 0) return 0;
+    if (!x || !out || (mode != QCC_AMAX_RAW && mode != QCC_AMAX_NVFP4_SCALE)) return QCC_ERR_ARG;
+    if (M < 0 || N < 0 || M % 128 != 0 || N % 128 != 0 || N > 0x7FFFFF00 || (M / 128) * (N / 128) > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    if (!aligned16(x)) return QCC_ERR_ALIGN;
+    const int tiles_n = (int)(N / 128);
+    fp8_128x128_kernel<true><<<(unsigned)((M / 128) * tiles_n), 128, 0, (cudaStream_t)stream>>>(
+        (const uint16_t *)x, (int)N, tiles_n, nullptr, out, mode == QCC_AMAX_NVFP4_SCALE ? 2688.0f : 1.0f);
     return (int)cudaGetLastError();
 }

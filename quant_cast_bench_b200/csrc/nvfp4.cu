@@ -57,7 +57,9 @@ __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer,
 constexpr int NV_THREADS = 256;
 constexpr int NV_UNROLL = 2;
 
-template <bool SWZ, bool SR, bool PER_ROW>
+// OUTER: 0 one outer scale for the tensor, 1 one per row (per token, G:1567-1571), 2 one per 128x128 block
+// (nvfp4_blocked_outer_f G:1609-1634; outer is then the (M/128, N/128) grid)
+template <bool SWZ, bool SR, int OUTER>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                      const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
@@ -71,7 +73,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
     // (a shared-memory table of the second division, as the transposed kernel uses, measured slower here:
     // its loads compete with the scale shuffles for the same issue queue)
     const float *lut = nullptr;
-    if (!PER_ROW) {
+    if (OUTER == 0) {
         o_all = __ldg(outer);
         inv_all = __fdiv_rn(1.0f, o_all);
     }
@@ -93,9 +95,10 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         const uint32_t bi = base + u * NV_THREADS;
         const bool ok = bi < nblocks;
         uint32_t row = 0, cb = 0;
-        if (SWZ || PER_ROW) { row = div_nb.div(ok ? bi : 0u); cb = (ok ? bi : 0u) - row * nb; }
+        if (SWZ || OUTER != 0) { row = div_nb.div(ok ? bi : 0u); cb = (ok ? bi : 0u) - row * nb; }
         float o = o_all, inv = inv_all;
-        if (PER_ROW) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
+        if (OUTER == 1) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
+        if (OUTER == 2) { o = __ldg(outer + (size_t)(row >> 7) * (nb >> 3) + (cb >> 3)); inv = __fdiv_rn(1.0f, o); }
         uint2 packed;
         const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, lut, (uint64_t)bi * 16u, seed, offset, packed);
         if (ok) __stcs(qv + bi, packed);
@@ -390,7 +393,9 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
     FastDiv32 dv;
     dv.init((uint32_t)nb);
     const unsigned grid = (nblocks + NV_THREADS * NV_UNROLL - 1) / (NV_THREADS * NV_UNROLL);
-    const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row != 0;
+    const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row == 1;
+    if (outer_per_row < 0 || outer_per_row > 2) return QCC_ERR_ARG;
+    if (outer_per_row == 2 && (sr || M % 128 != 0 || N % 128 != 0)) return sr ? QCC_ERR_ARG : QCC_ERR_SHAPE;
     const uint16_t *xp = (const uint16_t *)x;
     uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
     if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
@@ -400,12 +405,14 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
     }
 #define QCC_NV(SWZ_, SR_, PR_) \
     nvfp4_rowwise_kernel<SWZ_, SR_, PR_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp)
-    if (swz) {
-        if (sr) { if (pr) QCC_NV(true, true, true); else QCC_NV(true, true, false); }
-        else    { if (pr) QCC_NV(true, false, true); else QCC_NV(true, false, false); }
+    if (outer_per_row == 2) {
+        if (swz) QCC_NV(true, false, 2); else QCC_NV(false, false, 2);
+    } else if (swz) {
+        if (sr) { if (pr) QCC_NV(true, true, 1); else QCC_NV(true, true, 0); }
+        else    { if (pr) QCC_NV(true, false, 1); else QCC_NV(true, false, 0); }
     } else {
-        if (sr) { if (pr) QCC_NV(false, true, true); else QCC_NV(false, true, false); }
-        else    { if (pr) QCC_NV(false, false, true); else QCC_NV(false, false, false); }
+        if (sr) { if (pr) QCC_NV(false, true, 1); else QCC_NV(false, true, 0); }
+        else    { if (pr) QCC_NV(false, false, 1); else QCC_NV(false, false, 0); }
     }
 #undef QCC_NV
     return (int)cudaGetLastError();

@@ -417,6 +417,36 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
 
 
+def nvfp4_blocked_outer_scale_cuda(x, blk=128):
+    """gold nvfp4_blocked_outer_scale (G:1601-1606): max |x| / 2688 of every 128x128 block, (M/128, N/128) fp32."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert blk == 128 and M % 128 == 0 and N % 128 == 0, f"needs 128x128 blocks tiling the input, got {M}x{N}"
+    out = torch.empty((M // 128, N // 128), dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_amax_block128x128(_p(x), M, N, L.AMAX_NVFP4_SCALE, _p(out), _stream(x)), "amax_block128x128")
+    L.launch_count += 1
+    return out
+
+
+def nvfp4_blocked_outer_cuda(x, outer_blocked, **kwargs):
+    """gold nvfp4_blocked_outer_f (G:1609-1634): nvfp4 with one outer scale per 128x128 block, blocked inner scales."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert M % 128 == 0 and N % 128 == 0, f"needs 128x128 blocks tiling the input, got {M}x{N}"
+    assert outer_blocked.is_cuda and outer_blocked.dtype == torch.float32 and outer_blocked.shape == (M // 128, N // 128), (
+        "outer_blocked: (M/128, N/128) fp32 on the device")
+    q = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty(blocked_shape(M, N // 16), dtype=torch.uint8, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_nvfp4(_p(x), M, N, _p(outer_blocked.contiguous()), 2, L.SWIZZLE, None, _p(q), _p(s), _stream(x)),
+                "nvfp4 blocked outer")
+    L.launch_count += 1
+    return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
+
+
 def nvfp4_gs_cuda(x, outer_scale, **kwargs):
     """gold nvfp4_gs_f (G:1494-1517): (qdata (M, N/2) packed fp4, inner (M, N/16) e4m3); outer_scale a
     0-dim / (1,) per-tensor value or an (M, 1) per-token column."""
@@ -630,6 +660,11 @@ def _inputs_nvfp4(M, K):
     return (x, nvfp4_gs_scale_cuda(x))
 
 
+def _inputs_nvfp4_blocked_outer(M, K):
+    x = _x(M, K)
+    return (x, nvfp4_blocked_outer_scale_cuda(x))
+
+
 def _rht_matrix(x):
     return hadamard_rht_matrix_cuda(torch.tensor([1, -1] * 8), x.device, x.dtype)
 
@@ -682,6 +717,8 @@ _TABLE = [
      "(1,16) block, fp4 qdata, swizzle; dim-k (no RHT) + dim-m (RHT), two outer scales"),
     ("nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "Nvfp4GsSwizzle_DimKSR_DimMRHTSR_Gold", nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_cuda,
      _inputs_nvfp4_rht_sr, "(1,16) block, fp4 qdata (stochastic rounding), swizzle; dim-k (no RHT) + dim-m (RHT), two outer scales"),
+    ("nvfp4_blocked_outer", "Nvfp4BlockedOuterGold", nvfp4_blocked_outer_cuda, _inputs_nvfp4_blocked_outer,
+     "(1,16) block, fp4 qdata, swizzle, 128x128-blocked outer scale"),
     ("bf16_rht", "HadamardRht", hadamard_rht_cuda, _inputs_rht, "elementwise RHT"),
 ]
 

@@ -86,6 +86,11 @@ def main():
             for fn in ("deepseek_1x128_f", "deepseek_128x128_f", "deepseek_1x128_dim_m_f", "deepseek_1x128_dim_km_f"):
                 for i, o in enumerate(getattr(G, fn)(x)):
                     out[f"{tag}/{fn}/{i}"] = raw(o)
+            ob = G.nvfp4_blocked_outer_scale(x)
+            ob = torch.where(ob == 0, torch.full_like(ob, 2.0 ** -100), ob)   # an all-zero block: outer 0 divides 0 by 0
+            out[f"{tag}/nvfp4_blocked_outer_scale/0"] = raw(ob)
+            for i, o in enumerate(G.nvfp4_blocked_outer_f(x, ob)):
+                out[f"{tag}/nvfp4_blocked_outer_f/{i}"] = raw(o)
         if M % 32 == 0:   # 32x32 blocks (G:753-959)
             for fn in ("mxfp8_32x32_f", "mxfp8_32x32_swizzle_f", "mxfp8_32x32_dim_m_swizzle_f", "mxfp8_32x32_dim_km_swizzle_f",
                        "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"):

@@ -35,6 +35,15 @@ def test_deepseek_recipes(tag, fn):
         assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
 
 
+@pytest.mark.parametrize("tag", [t for t in golden_cases() if golden_n_outputs(t, "nvfp4_blocked_outer_f")])
+def test_nvfp4_blocked_outer(tag):
+    x = golden_x(tag)
+    ob = O.nvfp4_blocked_outer_scale(x)
+    assert_same_bits(ob, golden_out(tag, "nvfp4_blocked_outer_scale", 0), "blocked outer scale")
+    for i, o in enumerate(O.nvfp4_blocked_outer_f(x, ob)):
+        assert_same_bits(o, golden_out(tag, "nvfp4_blocked_outer_f", i), f"nvfp4_blocked_outer[{i}] {tag}")
+
+
 def test_deepseek_clamp_variants():
     """An all-zero block takes the clamp: bf16(1e-12) in the single-direction recipes, fp32(1e-12) in dim_km."""
     x = torch.zeros(128, 128, dtype=torch.bfloat16)

@@ -64,6 +64,23 @@ def test_deepseek_matches_oracle(fn, shape):
     same_outputs(cuda_fn(fn)(x.cuda()), oracle_fn(fn)(x), f"{fn} {shape}")
 
 
+@pytest.mark.parametrize("tag", [t for t in golden_cases() if golden_n_outputs(t, "nvfp4_blocked_outer_f")])
+def test_golden_nvfp4_blocked_outer(tag):
+    x = golden_x(tag).cuda()
+    ob = Q.nvfp4_blocked_outer_scale_cuda(x)
+    assert_same_bits(ob, golden_out(tag, "nvfp4_blocked_outer_scale", 0), "blocked outer scale")
+    for i, o in enumerate(Q.nvfp4_blocked_outer_cuda(x, ob)):
+        assert_same_bits(o, golden_out(tag, "nvfp4_blocked_outer_f", i), f"nvfp4_blocked_outer[{i}] {tag}")
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (1024, 2048), (2176, 1152)])
+def test_nvfp4_blocked_outer_matches_oracle(shape):
+    x = _x(*shape, seed=31, zero_row_p=0.0)
+    ob = Q.nvfp4_blocked_outer_scale_cuda(x.cuda())
+    assert_same_bits(ob, O.nvfp4_blocked_outer_scale(x), "blocked outer scale")
+    same_outputs(Q.nvfp4_blocked_outer_cuda(x.cuda(), ob), O.nvfp4_blocked_outer_f(x, ob.cpu()), f"blocked outer {shape}")
+
+
 def test_deepseek_ragged_and_zero_blocks():
     """1x128 takes any row count, 128x1 any multiple of 8 columns; an all-zero input takes the clamp of each recipe."""
     x = _x(96, 256, seed=2)
@@ -439,7 +456,7 @@ def test_recipe_index_mirrors_reference_backends():
                      "mxfp8_32x32", "mxfp8_32x32_swizzle",
                      "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle", "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle",
                      "fp8_deepseek_128x128", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
-                     "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "bf16_rht"]
+                     "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "nvfp4_blocked_outer", "bf16_rht"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
         outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
