@@ -195,6 +195,13 @@ int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk
               void *stream);
 
 /*
+ * mxfp4 (mxfp4_f G:607-617): 1x32 blocks along the rows, RCEIL e8m0 scale of amax / 6, elements e2m1 packed two
+ * per byte (even element in the low nibble).  q (M, N/2) bytes, s the (M, N/32) scales, plain or (QCC_SWIZZLE)
+ * blocked.  N % 32 == 0.
+ */
+int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, void *stream);
+
+/*
  * mxfp8 of token groups (MoE activations): x is (M, N) with G groups of consecutive rows, offs[g] = end row
  * of group g (device int32, ascending, every group a multiple of 32 rows).  Element bytes are those of
  * qcc_mxfp8; the blocked scales are laid out per group, as the grouped block-scaled GEMM reads them

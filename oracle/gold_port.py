@@ -39,6 +39,7 @@ def lib():
         _lib.qco_num_threads.restype = ctypes.c_int
         _lib.qco_hadamard_rht.restype = ctypes.c_int
         _lib.qco_mxfp8_32x32.restype = ctypes.c_int
+        _lib.qco_mxfp4.restype = ctypes.c_int
         _lib.qco_fp8_blockwise.restype = ctypes.c_int
         _lib.qco_amax_block128x128.restype = ctypes.c_int
         _lib.qco_hadamard_rht_t.restype = ctypes.c_int
@@ -328,6 +329,17 @@ def deepseek_1x128_dim_m_f(x, **kwargs):
 def deepseek_1x128_dim_km_f(x, **kwargs):
     """G:251-277 (amax clamped in fp32 there)"""
     return _fp8_blockwise(x, 1, 128, clamp_f32=True) + _fp8_blockwise(x, 128, 1, clamp_f32=True, transposed=True)
+
+
+def mxfp4_f(x, swizzle=False, **kwargs):
+    """gold mxfp4_f (G:607-617): (qdata (M, N/2) packed fp4, scale (M, N/32) e8m0); swizzle=True: blocked scale."""
+    _check_x(x)
+    M, N = x.shape
+    q = torch.empty((M, N // 2), dtype=torch.uint8)
+    s = torch.empty(blocked_shape(M, N // 32) if swizzle else (M, N // 32), dtype=torch.uint8)
+    rc = lib().qco_mxfp4(_p(x), _i64(M), _i64(N), SWIZZLE if swizzle else 0, _p(q), _p(s))
+    assert rc == 0, "mxfp4 needs N % 32 == 0"
+    return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e8m0fnu)
 
 
 # ------------------------------------------------------------------ mxfp8, 32x32 blocks

@@ -531,6 +531,45 @@ int qco_mxfp8(const uint16_t *x, int64_t M, int64_t N, int flags, uint8_t *qk, u
 }
 
 /*
+ * mxfp4 (mxfp4_f G:607-617): 1x32 blocks, RCEIL e8m0 scale with descale = amax * fp32(1/6) (G:504 with
+ * max_pos = 6), elements e2m1 (GU:15-57) packed even -> low nibble (GU:87-92).  q (M, N/2), s (M, N/32)
+ * plain or blocked.
+ */
+int qco_mxfp4(const uint16_t *x, int64_t M, int64_t N, int flags, uint8_t *q, uint8_t *s)
+{
+    if (N % 32) return -1;
+    int swz = (flags & QC_SWIZZLE) != 0;
+    int64_t nb = N / 32;
+    size_t ncb = (size_t)(nb + 3) / 4;
+    const float inv6 = u2f(0x3E2AAAABu);                    /* fp32(1.0 / 6.0) */
+    if (swz) memset(s, 0, blocked_bytes((size_t)M, (size_t)nb));
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < M; r++)
+        for (int64_t b = 0; b < nb; b++) {
+            const uint16_t *xb = x + r * N + b * 32;
+            uint16_t best = 0;
+            for (int i = 0; i < 32; i++) {
+                uint16_t a = bf16_abs(xb[i]);
+                if (a > best) best = a;
+            }
+            uint32_t bits = f2u(bf16_to_f32(best) * inv6);
+            uint8_t e;
+            if ((bits & 0x7F800000u) == 0x7F800000u) e = 255;
+            else {
+                uint32_t ex = (bits >> 23) & 0xFF, m = bits & 0x7FFFFFu;
+                e = (uint8_t)(ex + ((ex == 0) ? (m > 0x400000u) : (m != 0)));
+            }
+            float rcp = e8m0_to_recip(e, 0);
+            s[swz ? blocked_offset((size_t)r, (size_t)b, ncb) : (size_t)(r * nb + b)] = e;
+            for (int i = 0; i < 32; i += 2) {
+                uint8_t lo = f32_to_e2m1(bf16_to_f32(xb[i]) * rcp), hi = f32_to_e2m1(bf16_to_f32(xb[i + 1]) * rcp);
+                q[r * (N / 2) + b * 16 + i / 2] = (uint8_t)(lo | (hi << 4));
+            }
+        }
+    return 0;
+}
+
+/*
  * mxfp8 with one RCEIL e8m0 scale per 32x32 block (mxfp8_32x32_f G:753-773): q (M, N) in the
  * layout of x, s the plain (M/32, N/32) grid.  The expanded / blocked / transposed forms of the
  * other 32x32 recipes (G:809-815, G:856-862, G:900-910, G:946-959) are index permutations of these

@@ -154,12 +154,14 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(const float v[8])
 // amax (>= 0, an exact bf16 magnitude widened to fp32) -> e8m0 byte, RCEIL.  G:494-528:
 // descale = amax * fp32(1/448); byte = biased exponent, +1 if any mantissa bit is set (for an
 // fp32 subnormal: only above 2^-127); Inf/NaN -> 255.
-__device__ __forceinline__ uint32_t e8m0_rceil(float amax)
+// (inv_max_bits: fp32(1 / max_pos) of the element format, G:494-504: 1/448 for e4m3, 1/6 for e2m1)
+__device__ __forceinline__ uint32_t e8m0_rceil_of(float amax, uint32_t inv_max_bits)
 {
-    uint32_t b = f2u(__fmul_rn(amax, u2f(QCC_INV448_BITS)));
+    uint32_t b = f2u(__fmul_rn(amax, u2f(inv_max_bits)));
     uint32_t add = b < 0x00800000u ? 0x3FFFFFu : 0x7FFFFFu;
     return min((b + add) >> 23, 255u);
 }
+__device__ __forceinline__ uint32_t e8m0_rceil(float amax) { return e8m0_rceil_of(amax, QCC_INV448_BITS); }
 // FLOOR mode (OCP MX v1.0 6.3, not in the reference): exponent field of amax minus emax(e4m3)=8,
 // clamped at 0; Inf/NaN -> 255.
 __device__ __forceinline__ uint32_t e8m0_floor(float amax)

@@ -35,6 +35,33 @@ namespace qcc {
 constexpr int RS_THREADS = 256;
 constexpr int RS_UNROLL = 2;
 
+// Scale byte of block `bi` of the flat stream: plain (M, N/32) or blocked.  Called by every lane of the warp.
+template <bool SWZ>
+__device__ __forceinline__ void stream_scale_store(uint8_t *__restrict__ s, uint32_t bi, bool ok, uint32_t e, uint32_t nb,
+                                                   const FastDiv32 &div_nb, const int32_t *__restrict__ row_map)
+{
+    if (!SWZ) {
+        if (ok) s[bi] = (uint8_t)e;
+    } else if ((nb & 3) == 0) {
+        // four consecutive lanes hold the four scale columns of one (row, column block): one 4-byte store
+        uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 1) << 8);
+        v |= __shfl_down_sync(0xFFFFFFFFu, v, 2) << 16;
+        if (ok && (threadIdx.x & 3) == 0) {
+            uint32_t row = div_nb.div(bi);
+            const uint32_t cb = bi - row * nb;
+            int32_t dst = (int32_t)row;
+            if (row_map) dst = __ldg(row_map + row);      // token groups: row inside the padded, stacked groups
+            if (dst >= 0) *reinterpret_cast<uint32_t *>(s + blocked_offset((uint32_t)dst, cb, nb >> 2)) = v;
+        }
+    } else if (ok) {
+        uint32_t row = div_nb.div(bi);
+        const uint32_t cb = bi - row * nb;
+        int32_t dst = (int32_t)row;
+        if (row_map) dst = __ldg(row_map + row);
+        if (dst >= 0) s[blocked_offset((uint32_t)dst, cb, (nb + 3) >> 2)] = (uint8_t)e;
+    }
+}
+
 template <bool SWZ, bool FLOOR>
 __global__ void __launch_bounds__(RS_THREADS)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
@@ -67,27 +94,37 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             __stcs(qv + 2 * (size_t)bi, o0);
             __stcs(qv + 2 * (size_t)bi + 1, o1);
         }
-        if (!SWZ) {
-            if (ok) s[bi] = (uint8_t)e;
-        } else if ((nb & 3) == 0) {
-            // four consecutive lanes hold the four scale columns of one (row, column block): one 4-byte store
-            uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 1) << 8);
-            v |= __shfl_down_sync(0xFFFFFFFFu, v, 2) << 16;
-            if (ok && (threadIdx.x & 3) == 0) {
-                uint32_t row = div_nb.div(bi);
-                const uint32_t cb = bi - row * nb;
-                int32_t dst = (int32_t)row;
-                if (row_map) dst = __ldg(row_map + row);      // token groups: row inside the padded, stacked groups
-                if (dst >= 0) *reinterpret_cast<uint32_t *>(s + blocked_offset((uint32_t)dst, cb, nb >> 2)) = v;
-            }
-        } else if (ok) {
-            uint32_t row = div_nb.div(bi);
-            const uint32_t cb = bi - row * nb;
-            int32_t dst = (int32_t)row;
-            if (row_map) dst = __ldg(row_map + row);
-            if (dst >= 0) s[blocked_offset((uint32_t)dst, cb, (nb + 3) >> 2)] = (uint8_t)e;
-        }
+        stream_scale_store<SWZ>(s, bi, ok, e, nb, div_nb, row_map);
     }
+}
+
+// mxfp4 (gold mxfp4_f G:607-617): the same 1x32 blocks and RCEIL e8m0 scale, descaled by 6 instead of 448,
+// elements as e2m1 packed two per byte (even element in the low nibble).
+template <bool SWZ>
+__global__ void __launch_bounds__(RS_THREADS)
+mxfp4_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
+                            uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+{
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint4 *qv = reinterpret_cast<uint4 *>(q);
+    const uint32_t bi = blockIdx.x * RS_THREADS + threadIdx.x;
+    const bool ok = bi < nblocks;
+    uint4 c[4] = {};
+    if (ok) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = ld_v4(xv + 4 * (size_t)bi + i);
+    }
+    const uint32_t e = e8m0_rceil_of(amax_of_block(c), 0x3E2AAAABu);   // fp32(1 / 6)
+    const float rcp = e8m0_recip<false>(e);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float v[8] = {bf16lo(c[i].x) * rcp, bf16hi(c[i].x) * rcp, bf16lo(c[i].y) * rcp, bf16hi(c[i].y) * rcp,
+                      bf16lo(c[i].z) * rcp, bf16hi(c[i].z) * rcp, bf16lo(c[i].w) * rcp, bf16hi(c[i].w) * rcp};
+        o[i] = cvt_e2m1x8(v);
+    }
+    if (ok) __stcs(qv + bi, make_uint4(o[0], o[1], o[2], o[3]));
+    stream_scale_store<SWZ>(s, bi, ok, e, nb, div_nb, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -562,4 +599,28 @@ extern "C" int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags,
     group_tables_kernel<<<grid, 256, 0, st>>>(offs, (int)G, (int)M, (int)padded_c, row_map, mb_a, mb_b);
     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
     return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b});
+}
+
+extern "C" int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, void *stream)
+{
+    if (M == 0 || N == 0) return 0;
+    if (!x || !q || !s || (flags & ~QCC_SWIZZLE)) return QCC_ERR_ARG;
+    if (M < 0 || N < 0 || N % 32 != 0) return QCC_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
+    const int64_t nb = N / 32;
+    if (M * nb >= (1ll << 32) - RS_THREADS || M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t nblocks = (uint32_t)(M * nb);
+    FastDiv32 dv;
+    dv.init((uint32_t)nb);
+    const bool swz = flags & QCC_SWIZZLE;
+    if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
+        blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>((uint8_t *)s, (uint32_t)M, (uint32_t)nb);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    const unsigned grid = (nblocks + RS_THREADS - 1) / RS_THREADS;
+    if (swz) mxfp4_rowwise_stream_kernel<true><<<grid, RS_THREADS, 0, st>>>((const uint16_t *)x, nblocks, (uint32_t)nb, dv, (uint8_t *)q, (uint8_t *)s);
+    else mxfp4_rowwise_stream_kernel<false><<<grid, RS_THREADS, 0, st>>>((const uint16_t *)x, nblocks, (uint32_t)nb, dv, (uint8_t *)q, (uint8_t *)s);
+    return (int)cudaGetLastError();
 }

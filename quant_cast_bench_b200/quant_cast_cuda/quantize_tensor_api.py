@@ -9,7 +9,8 @@ the transposed and the bidirectional nvfp4 casts, stochastic rounding for nvfp4 
 
 3-D `(E, M, K)` inputs are quantised per expert (scaling never crosses the E dimension, blocked scales
 are per expert and returned flattened as `(E, flat_len)`), one launch per expert into slices of the
-stacked outputs.  The 32x32 block recipes of the reference are not part of this backend.
+stacked outputs.  BlockWise32x32 (one scale per 32x32 block, `skip_transposed_qdata` in the bidirectional call)
+and mxfp4 (fp4 data under an E8M0 scale) follow the reference's table as well.
 
 `quantize_tensor_grouped` / `quantize_tensor_grouped_bidirectional` (api.py:301-411) cast a `(total_M, C)`
 activation whose rows form token groups ending at `offs`: the data is cast as one matrix, the blocked
@@ -119,9 +120,16 @@ def quantize_tensor(input: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4
     if qdata_dtype == torch.float4_e2m1fn_x2:
         assert input.dim() == 2, "fp4 quantization is only supported for 2D input"
         assert input.is_contiguous(), "input must be contiguous"
+        if inner_scale_calc == InnerScaleCalc.E8M0_RCEIL:   # mxfp4 (api.py:124-135)
+            assert outer_scale is None, "outer_scale is only used by nvfp4 quantization"
+            if sr:
+                raise NotImplementedError("stochastic rounding is implemented for nvfp4 only")
+            if scaling_type != ScalingType.BlockWise1x32 or orientation != QuantOrientation.NATURAL:
+                raise ValueError(f"unsupported (scaling_type, orientation)=({scaling_type!r}, {orientation!r}) for mxfp4; "
+                                 "supported: (BlockWise1x32, NATURAL)")
+            return R.mxfp4_cuda(input, swizzle=swz)
         if inner_scale_calc != InnerScaleCalc.E4M3_NVFP4:
-            raise ValueError(f"float4_e2m1fn_x2 qdata requires inner_scale_calc=E4M3_NVFP4 here, got {inner_scale_calc!r} "
-                             "(mxfp4 is not part of this backend)")
+            raise ValueError(f"float4_e2m1fn_x2 qdata takes inner_scale_calc=E8M0_RCEIL (mxfp4) or E4M3_NVFP4, got {inner_scale_calc!r}")
         assert outer_scale is not None, "nvfp4 quantization requires a precomputed outer_scale"
         if scaling_type != ScalingType.BlockWise1x16:
             raise ValueError(f"unsupported scaling_type={scaling_type!r} for nvfp4; supported: BlockWise1x16")
@@ -139,8 +147,18 @@ def quantize_tensor(input: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4
     assert outer_scale is None, "outer_scale is only used by nvfp4 (float4_e2m1fn_x2) quantization"
     if sr:
         raise NotImplementedError("stochastic rounding is implemented for nvfp4 only")
+    if scaling_type == ScalingType.BlockWise32x32:   # api.py:203-206 plus the swizzled layouts of the gold index
+        assert input.dim() == 2 and input.is_contiguous(), "32x32 blocks take a contiguous 2D input"
+        if inner_scale_calc != InnerScaleCalc.E8M0_RCEIL:
+            raise ValueError("32x32 blocks take inner_scale_calc=E8M0_RCEIL")
+        if orientation == QuantOrientation.NATURAL:
+            return R._mxfp8_32x32(input, True, False, swz)
+        if orientation == QuantOrientation.TRANSPOSED and swz:
+            return R._mxfp8_32x32(input, False, True, True)
+        raise ValueError(f"unsupported (orientation, swizzle_type)=({orientation!r}, {swizzle_type!r}) for BlockWise32x32; "
+                         "supported: NATURAL with either layout, TRANSPOSED with SWIZZLE_32_4_4")
     if scaling_type != ScalingType.BlockWise1x32:
-        raise ValueError(f"unsupported scaling_type={scaling_type!r} for mxfp8; supported: BlockWise1x32")
+        raise ValueError(f"unsupported scaling_type={scaling_type!r} for mxfp8; supported: BlockWise1x32, BlockWise32x32")
     if orientation == QuantOrientation.NATURAL:
         direction = L.ROWWISE
     elif orientation == QuantOrientation.TRANSPOSED:
@@ -166,9 +184,9 @@ def quantize_tensor_bidirectional(input: Tensor, *, qdata_dtype: torch.dtype = t
     assert input.dim() in (2, 3), f"only 2D or 3D input supported, got {input.dim()}D"
     if rounding_mode == RoundingMode.STOCHASTIC or random_key is not None:
         raise NotImplementedError("stochastic rounding is not implemented for the bidirectional casts")
-    if skip_transposed_qdata:
-        raise NotImplementedError("skip_transposed_qdata belongs to the 32x32 block recipes, which this backend lacks")
     swz = _is_swz(swizzle_type)
+    if skip_transposed_qdata and (scaling_type != ScalingType.BlockWise32x32 or not swz or qdata_dtype != torch.float8_e4m3fn):
+        raise ValueError("skip_transposed_qdata is only supported for (BlockWise32x32, SWIZZLE_32_4_4) float8_e4m3fn")
     if qdata_dtype == torch.float4_e2m1fn_x2:
         assert input.dim() == 2 and input.is_contiguous(), "nvfp4 bidirectional takes a contiguous 2D input"
         if inner_scale_calc != InnerScaleCalc.E4M3_NVFP4 or scaling_type != ScalingType.BlockWise1x16:
@@ -179,8 +197,13 @@ def quantize_tensor_bidirectional(input: Tensor, *, qdata_dtype: torch.dtype = t
     if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
         raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
     assert outer_scale is None, "outer_scale is only used by nvfp4 (float4_e2m1fn_x2) quantization"
+    if scaling_type == ScalingType.BlockWise32x32:   # api.py:281-285; with the transposed data: gold G:900-910
+        assert input.dim() == 2 and input.is_contiguous(), "32x32 blocks take a contiguous 2D input"
+        if inner_scale_calc != InnerScaleCalc.E8M0_RCEIL or not swz:
+            raise ValueError("32x32 blocks take inner_scale_calc=E8M0_RCEIL and swizzle_type=SWIZZLE_32_4_4 here")
+        return R._mxfp8_32x32(input, True, True, True, transposed_data=not skip_transposed_qdata)
     if scaling_type != ScalingType.BlockWise1x32:
-        raise ValueError(f"unsupported scaling_type={scaling_type!r}; supported: BlockWise1x32")
+        raise ValueError(f"unsupported scaling_type={scaling_type!r}; supported: BlockWise1x32, BlockWise32x32")
     flags = L.ROWWISE | L.COLWISE | _mx_flags(inner_scale_calc, swz)
     if input.dim() == 3:
         if not swz:

@@ -250,6 +250,21 @@ def _mxfp8(x, flags, out=None):
     return tuple(outs)
 
 
+def mxfp4_cuda(x, swizzle=False, **kwargs):
+    """gold mxfp4_f (G:607-617): 1x32 blocks, e8m0 RCEIL scale of amax / 6, fp4 e2m1 data packed two per byte:
+    (qdata (M, N/2), scale (M, N/32)); swizzle=True gives the blocked scale layout (extension)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 32 == 0, f"mxfp4 needs N % 32 == 0, got N={N}"
+    q = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty(blocked_shape(M, N // 32) if swizzle else (M, N // 32), dtype=torch.uint8, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_mxfp4(_p(x), M, N, L.SWIZZLE if swizzle else 0, _p(q), _p(s), _stream(x)), "mxfp4")
+    L.launch_count += 1
+    return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e8m0fnu)
+
+
 def _fp8_block128(x, row, col):
     lib = L.load()
     _check_x(x)

@@ -96,6 +96,8 @@ def main():
                        "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f"):
                 for i, o in enumerate(getattr(G, fn)(x)):
                     out[f"{tag}/{fn}/{i}"] = raw(o)
+        for i, o in enumerate(G.mxfp4_f(x)):
+            out[f"{tag}/mxfp4_f/{i}"] = raw(o)
         gs = G.nvfp4_gs_scale(x)
         out[f"{tag}/nvfp4_gs_scale/0"] = raw(gs.reshape(1))
         for fn in ("nvfp4_gs_f", "nvfp4_gs_swizzle_f"):

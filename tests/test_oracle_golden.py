@@ -8,7 +8,7 @@ import torch
 from helpers import assert_same_bits, golden, golden_cases, golden_n_outputs, golden_out, golden_rht, golden_x
 from oracle import gold_port as O
 
-ONE_INPUT = ["rowwise_fp8_f", "colwise_fp8_f", "mxfp8_f", "mxfp8_swizzle_f", "mxfp8_dim_m_f",
+ONE_INPUT = ["rowwise_fp8_f", "colwise_fp8_f", "mxfp4_f", "mxfp8_f", "mxfp8_swizzle_f", "mxfp8_dim_m_f",
              "mxfp8_dim_m_swizzle_f", "mxfp8_dim_km_f", "mxfp8_dim_km_swizzle_f"]
 
 

@@ -81,6 +81,20 @@ def test_nvfp4_blocked_outer_matches_oracle(shape):
     same_outputs(Q.nvfp4_blocked_outer_cuda(x.cuda(), ob), O.nvfp4_blocked_outer_f(x, ob.cpu()), f"blocked outer {shape}")
 
 
+@pytest.mark.parametrize("tag", golden_cases())
+def test_golden_mxfp4(tag):
+    x = golden_x(tag).cuda()
+    for i, o in enumerate(Q.mxfp4_cuda(x)):
+        assert_same_bits(o, golden_out(tag, "mxfp4_f", i), f"mxfp4[{i}] {tag}")
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_mxfp4_matches_oracle(shape):
+    x = _x(*shape, seed=17)
+    for swz in (False, True):
+        same_outputs(Q.mxfp4_cuda(x.cuda(), swizzle=swz), O.mxfp4_f(x, swizzle=swz), f"mxfp4 {shape} swizzle={swz}")
+
+
 def test_deepseek_ragged_and_zero_blocks():
     """1x128 takes any row count, 128x1 any multiple of 8 columns; an all-zero input takes the clamp of each recipe."""
     x = _x(96, 256, seed=2)

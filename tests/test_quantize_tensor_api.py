@@ -44,6 +44,27 @@ def test_nvfp4_table():
                  O.nvfp4_gs_swizzle_f(x, gs.cpu()) + O.nvfp4_gs_swizzle_t_f(x, gs.cpu()), "nvfp4 bidirectional")
 
 
+def test_32x32_and_mxfp4_table():
+    x = make_input(256, 384, seed=6)
+    xc = x.cuda()
+    b32 = dict(scaling_type=A.ScalingType.BlockWise32x32)
+    same_outputs(A.quantize_tensor(xc, swizzle_type=NOSW, **b32), O.mxfp8_32x32_f(x), "32x32 plain")
+    same_outputs(A.quantize_tensor(xc, swizzle_type=SW, **b32), O.mxfp8_32x32_swizzle_f(x), "32x32 swizzle")
+    same_outputs(A.quantize_tensor(xc, swizzle_type=SW, orientation=TR, **b32), O.mxfp8_32x32_dim_m_swizzle_f(x), "32x32 transposed")
+    same_outputs(A.quantize_tensor_bidirectional(xc, **b32), O.mxfp8_32x32_dim_km_swizzle_f(x), "32x32 bidirectional")
+    same_outputs(A.quantize_tensor_bidirectional(xc, skip_transposed_qdata=True, **b32),
+                 O.mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f(x), "32x32 skip transposed qdata")
+    with pytest.raises(ValueError):
+        A.quantize_tensor(xc, swizzle_type=NOSW, orientation=TR, **b32)
+    with pytest.raises(ValueError):
+        A.quantize_tensor_bidirectional(xc, skip_transposed_qdata=True)
+    fp4 = dict(qdata_dtype=torch.float4_e2m1fn_x2, inner_scale_calc=A.InnerScaleCalc.E8M0_RCEIL)
+    same_outputs(A.quantize_tensor(xc, swizzle_type=NOSW, **fp4), O.mxfp4_f(x), "mxfp4")
+    same_outputs(A.quantize_tensor(xc, swizzle_type=SW, **fp4), O.mxfp4_f(x, swizzle=True), "mxfp4 swizzle")
+    with pytest.raises(ValueError):
+        A.quantize_tensor(xc, orientation=TR, **fp4)
+
+
 def test_per_expert_3d():
     E, M, K = 3, 160, 256
     x = make_input(E * M, K, seed=5).reshape(E, M, K)
@@ -66,13 +87,13 @@ def test_per_expert_3d():
 def test_unsupported_combinations_raise():
     x = torch.randn(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ValueError):
-        A.quantize_tensor(x, scaling_type=A.ScalingType.BlockWise32x32)
+        A.quantize_tensor(x, scaling_type=A.ScalingType.BlockWise128x128)
     with pytest.raises(ValueError):
         A.quantize_tensor(x, rounding_mode=A.RoundingMode.STOCHASTIC)
     with pytest.raises(AssertionError):
         A.quantize_tensor(x, qdata_dtype=torch.float4_e2m1fn_x2, inner_scale_calc=A.InnerScaleCalc.E4M3_NVFP4,
                           scaling_type=A.ScalingType.BlockWise1x16)            # no outer_scale
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):   # only with 32x32 blocks
         A.quantize_tensor_bidirectional(x, skip_transposed_qdata=True)
     with pytest.raises(ValueError):
         A.quantize_tensor(x.reshape(1, 64, 64), swizzle_type=NOSW)
