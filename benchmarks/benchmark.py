@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--K", type=int, default=16384)
     ap.add_argument("--recipe_name_filter", default=None)
+    ap.add_argument("--recipe_name_exact", default=None, help="run the one recipe of exactly this name")
     ap.add_argument("--mode", default="cuda")
     ap.add_argument("--csv", default=None)
     ap.add_argument("--iters", type=int, default=20)
@@ -86,9 +87,14 @@ def main():
     rows, csv_rows = [], []
     tile_kwargs = {"global_row": 0, "global_col": 0, "num_col": args.K}
 
+    def wanted(name):
+        if args.recipe_name_exact is not None:
+            return name == args.recipe_name_exact
+        return args.recipe_name_filter is None or args.recipe_name_filter in name
+
     cases = []
     for name, recipe in Q.ALL_RECIPES:
-        if name in _BENCH_SKIP and not args.include_skipped:
+        if (name in _BENCH_SKIP and not args.include_skipped) or not wanted(name):
             continue
         torch.manual_seed(0)
         inputs = recipe.example_input_fn(args.M, args.K)
@@ -96,11 +102,9 @@ def main():
     if args.extensions:
         torch.manual_seed(0)
         x = torch.randn(args.M, args.K, dtype=torch.bfloat16, device="cuda")
-        cases += [(n, i, f, "extension") for n, i, f in _extensions(x)]
-    if args.recipe_name_filter is not None:
-        cases = [c for c in cases if args.recipe_name_filter in c[0]]
-        if not cases:
-            raise ValueError(f"no recipe matched {args.recipe_name_filter!r}")
+        cases += [(n, i, f, "extension") for n, i, f in _extensions(x) if wanted(n)]
+    if not cases:
+        raise ValueError(f"no recipe matched {args.recipe_name_exact or args.recipe_name_filter!r}")
 
     for name, inputs, run, desc in cases:
         outputs = run()

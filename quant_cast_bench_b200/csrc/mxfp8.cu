@@ -383,8 +383,12 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
                 *reinterpret_cast<uint16_t *>(sm + off) = v;       // padding columns carry zeros (zero-filled x)
             } else if (Cn < N) {
                 uint8_t *dst = sm + (size_t)Cn * mb + tile_m * 2;
-                if (tile_m * 2 < mb) dst[0] = (uint8_t)v;
-                if (tile_m * 2 + 1 < mb) dst[1] = (uint8_t)(v >> 8);
+                if ((mb & 1) == 0) {
+                    *reinterpret_cast<uint16_t *>(dst) = v;       // both blocks inside, address even
+                } else {
+                    if (tile_m * 2 < mb) dst[0] = (uint8_t)v;
+                    if (tile_m * 2 + 1 < mb) dst[1] = (uint8_t)(v >> 8);
+                }
             }
         }
     }
