@@ -177,7 +177,7 @@ def run_reference(args):
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def time_kernel(fn, iters, warmup=3):
@@ -208,8 +208,6 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     from quant_cast_bench_b200 import quant_cast_cuda as Q
@@ -310,7 +308,7 @@ def run_ours(args):
         "c4_sharded": c4,
         "casts": casts,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def cpu_baseline():
@@ -528,7 +526,26 @@ def bench_other_casts(Q, x, dev, peak):
     return out
 
 
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    """Libraries loaded later (NCCL's version banner, for one) write to file descriptor 1.  The contract is ONE JSON
+    line on stdout, so fd 1 is pointed at stderr for the whole run and the line goes out through a saved copy."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(text):
+    out = _REAL_STDOUT if _REAL_STDOUT is not None else sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
 def main():
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

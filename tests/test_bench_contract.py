@@ -1,0 +1,40 @@
+"""bench.py prints exactly one JSON line on stdout, whatever the libraries it loads print (CPU: the reference arm;
+GPU: the default arm with a small step count)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REQUIRED = ["metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
+            "dtype", "data", "config", "cpu_baseline", "e2e"]
+
+
+def _run(args, timeout):
+    env = dict(os.environ, NCCL_DEBUG="VERSION")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py")] + args, cwd=ROOT, env=env, capture_output=True,
+                       text=True, timeout=timeout)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.split("\n") if ln.strip()]
+    assert len(lines) == 1, f"stdout must hold one line, got {len(lines)}: {p.stdout[:300]!r}"
+    return json.loads(lines[0])
+
+
+def test_reference_arm_prints_one_json_line():
+    line = _run(["--impl", "reference", "--steps", "1", "--warmup", "0"], 600)
+    assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port"
+    for k in REQUIRED:
+        assert k in line, k
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
+
+
+@pytest.mark.gpu
+def test_default_arm_prints_one_json_line():
+    line = _run(["--steps", "3", "--warmup", "3"], 900)
+    for k in REQUIRED + ["roofline", "gpu_launches", "clocks"]:
+        assert k in line, k
+    assert line["gpu_launches"] == 3 and line["n_gpus"] == 1
+    assert line["roofline"]["bound"] == "hbm" and 0.3 < line["roofline"]["frac"] < 1.2
+    assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
