@@ -304,12 +304,15 @@ static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scal
 // caller-supplied scratch of N words (atomic max on the bit patterns: exact and order independent), then
 // a tile kernel that casts and transposes; for matrices that fit in L2 the second pass never reaches HBM.
 // ---------------------------------------------------------------------------------------------
-constexpr int CW_AMAX_ROWS = 64;
+// rows per CTA of the column-maximum pass: 256 measured best at 16384^2 (211 us for both passes against 231 us
+// with 64, 128 or 512 rows)
+constexpr int CW_AMAX_ROWS = 256;
+constexpr int CW_AMAX_THREADS = 256;
 
-__global__ void __launch_bounds__(256) fp8_colwise_amax_kernel(const uint16_t *__restrict__ x, int M, int N,
+__global__ void __launch_bounds__(CW_AMAX_THREADS) fp8_colwise_amax_kernel(const uint16_t *__restrict__ x, int M, int N,
                                                               uint32_t *__restrict__ amax_bits)
 {
-    const int chunk = blockIdx.x * 256 + threadIdx.x;       // 8 adjacent columns
+    const int chunk = blockIdx.x * CW_AMAX_THREADS + threadIdx.x;       // 8 adjacent columns
     if (chunk * 8 >= N) return;
     const int r0 = blockIdx.y * CW_AMAX_ROWS;
     const int r1 = min(M, r0 + CW_AMAX_ROWS);
@@ -440,8 +443,8 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
     if (!PRECALC) {
         cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)N * 4, st);
         if (ce != cudaSuccess) return (int)ce;
-        dim3 grid((unsigned)((N / 8 + 255) / 256), (unsigned)((M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS));
-        fp8_colwise_amax_kernel<<<grid, 256, 0, st>>>((const uint16_t *)x, (int)M, (int)N, amax_bits);
+        dim3 grid((unsigned)((N / 8 + CW_AMAX_THREADS - 1) / CW_AMAX_THREADS), (unsigned)((M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS));
+        fp8_colwise_amax_kernel<<<grid, CW_AMAX_THREADS, 0, st>>>((const uint16_t *)x, (int)M, (int)N, amax_bits);
         ce = cudaGetLastError();
         if (ce != cudaSuccess) return (int)ce;
     }
