@@ -46,3 +46,30 @@ def config_input(name, seed=0, device="cpu", rows=None, row_offset=0):
     """Input of a named configuration; `rows` / `row_offset` select a row shard."""
     M, N, spread, p, mul, z = CONFIGS[name]
     return make_input(rows if rows is not None else M, N, seed, spread, p, mul, z, device, row_offset)
+
+
+def make_input_device(M, N, seed, device, spread=10.0, outlier_p=1e-3, outlier_mul=100.0, zero_row_p=0.01, row_offset=0,
+                      chunk_rows=2048):
+    """The same distribution drawn by the device's generator (full-size inputs in seconds instead of minutes).  Every
+    `chunk_rows`-row chunk has its own seed, so a row shard (offset and size multiples of `chunk_rows`) holds the
+    same values whatever the number of shards.  Not the same bytes as `make_input`."""
+    assert M % chunk_rows == 0 and row_offset % chunk_rows == 0
+    x = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    g = torch.Generator(device=device)
+    for r0 in range(0, M, chunk_rows):
+        g.manual_seed(seed * 1000003 + (row_offset + r0) // chunk_rows)
+        t = torch.randn(chunk_rows, N, generator=g, device=device)
+        if spread > 0:
+            t *= torch.exp2((torch.rand(chunk_rows, 1, generator=g, device=device) * 2 - 1) * spread)
+        if outlier_p > 0:
+            t = torch.where(torch.rand(chunk_rows, N, generator=g, device=device) < outlier_p, t * outlier_mul, t)
+        if zero_row_p > 0:
+            t[torch.rand(chunk_rows, generator=g, device=device) < zero_row_p] = 0
+        x[r0:r0 + chunk_rows] = t.to(torch.bfloat16)
+    return x
+
+
+def config_input_device(name, device, seed=0):
+    M, N, spread, p, mul, z = CONFIGS[name]
+    return make_input_device(M, N, seed, device, spread, p, mul, z)
+
