@@ -117,6 +117,39 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
     }
 }
 
+// The common case -- blocked scales, round to nearest, one outer scale, N % 64 == 0 -- with two adjacent blocks per thread: 64
+// contiguous input bytes (four 16-byte loads that share sectors through L1), one 16-byte store of packed nibbles,
+// and one blocked-offset computation per four scale bytes (a lane pair) instead of per byte.  (Four blocks per
+// thread measured 33 % slower: 128-byte strides between lanes defeat coalescing.)
+__global__ void __launch_bounds__(NV_THREADS)
+nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint32_t nb, FastDiv32 div_np,
+                          const float *__restrict__ outer, uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+{
+    const uint32_t pi = blockIdx.x * NV_THREADS + threadIdx.x;   // blocks 2 pi and 2 pi + 1 of the flat stream
+    const bool ok = pi < npairs;
+    const float o = __ldg(outer);
+    const float inv = __fdiv_rn(1.0f, o);
+    uint4 c[4] = {};
+    if (ok) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(x) + 4 * (size_t)pi;
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = ld_v4(p + i);
+    }
+    uint2 p0, p1;
+    const uint32_t b0 = nvfp4_quant16<false>(c[0], c[1], o, inv, nullptr, 0, 0, 0, p0);
+    const uint32_t b1 = nvfp4_quant16<false>(c[2], c[3], o, inv, nullptr, 0, 0, 0, p1);
+    if (ok) __stcs(reinterpret_cast<uint4 *>(q) + pi, make_uint4(p0.x, p0.y, p1.x, p1.y));
+    // an even lane and its neighbour hold the four scale columns of one (row, column block)
+    const uint32_t b01 = b0 | (b1 << 8);
+    const uint32_t v = b01 | (__shfl_down_sync(0xFFFFFFFFu, b01, 1) << 16);
+    if (ok && (threadIdx.x & 1) == 0) {
+        const uint32_t np = nb >> 1;
+        const uint32_t row = div_np.div(pi);
+        const uint32_t cb = (pi - row * np) << 1;
+        *reinterpret_cast<uint32_t *>(s + blocked_offset(row, cb, nb >> 2)) = v;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // transposed cast: one-shot tile kernel
 // ---------------------------------------------------------------------------------------------
@@ -402,6 +435,14 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
         blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(sp, (uint32_t)M, (uint32_t)nb);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
+    }
+    if (swz && !sr && outer_per_row == 0 && (nb & 3) == 0) {   // (the plain layout gains nothing from pairing)
+        const uint32_t npairs = nblocks >> 1;
+        FastDiv32 dp;
+        dp.init((uint32_t)(nb >> 1));
+        const unsigned pgrid = (npairs + NV_THREADS - 1) / NV_THREADS;
+        nvfp4_rowwise_pair_kernel<<<pgrid, NV_THREADS, 0, st>>>(xp, npairs, (uint32_t)nb, dp, outer, qp, sp);
+        return (int)cudaGetLastError();
     }
 #define QCC_NV(SWZ_, SR_, PR_) \
     nvfp4_rowwise_kernel<SWZ_, SR_, PR_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp)
