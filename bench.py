@@ -425,9 +425,9 @@ def bench_other_casts(Q, x, dev, peak):
             torch.cuda.synchronize()
             ts.append(a.elapsed_time(b))
         ms = statistics.median(ts)
-        if flush_l2:
-            # data fit in L2: kernel time with a cold L2 but without launch latency = (10 x [flush, cast]) - (10 x flush),
-            # both replayed from graphs
+        if True:
+            # kernel time with a cold L2 but without launch latency = (10 x [flush, cast]) - (10 x flush), both replayed
+            # from graphs: the figure to hold against profiler-timed kernels (the reference's tables)
             gfk = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gfk, stream=side):
                 for _ in range(10):
@@ -454,12 +454,11 @@ def bench_other_casts(Q, x, dev, peak):
         ms_sus = a.elapsed_time(b) / 10
         gbs = nbytes / (ms * 1e-3) / 1e9
         res = {"ms": ms, "GBps": gbs, "frac_measured_peak": gbs / peak, "frac_8TBps": gbs / 8000.0}
-        if not flush_l2:
+        if not flush_l2:      # back-to-back launches only mean something when the data exceed L2
             res["ms_sustained"] = ms_sus
             res["GBps_sustained"] = nbytes / (ms_sus * 1e-3) / 1e9
-        else:
-            res["ms_cold_in_graph"] = ms_cold
-            res["GBps_cold_in_graph"] = nbytes / (ms_cold * 1e-3) / 1e9
+        res["ms_cold_in_graph"] = ms_cold
+        res["GBps_cold_in_graph"] = nbytes / (ms_cold * 1e-3) / 1e9
         del g1, g10
         return res
 
