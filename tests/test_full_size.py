@@ -171,3 +171,41 @@ def test_c5_nvfp4_sr_8192x16384():
     xf = x.float()
     rel = float((mean - xf).sum().abs() / xf.abs().sum())
     assert rel <= 1e-3, f"mean error of 16 seeds {rel:.2e}"
+
+
+def test_addressing_beyond_2_31_elements():
+    """131072 x 16384 = 2^31 elements (4 GiB of bf16): byte offsets of every output pass 2^31, element offsets of the
+    input pass 2^31 - 1.  Slabs at the far end must still match the oracle."""
+    from quant_cast_bench_b200.workloads import make_input_device
+    M, N = 131072, 16384
+    x = make_input_device(M, N, seed=9, device="cuda", spread=4.0, outlier_p=0.0, zero_row_p=0.0)
+    qk, sk, qm, sm = Q.mxfp8_dim_km_swizzle_cuda(x)
+    for r0 in (0, M - 128):
+        want = O.mxfp8_dim_km_swizzle_f(x[r0:r0 + 128].cpu())
+        assert_same_bits(qk[r0:r0 + 128], want[0], f"qk slab {r0}")
+        assert_same_bits(sk[r0 // 128], want[1][0], f"sk slab {r0}")
+        assert_same_bits(qm[:, r0:r0 + 128], want[2], f"qm slab {r0}")
+        assert_same_bits(sm[:, r0 // 128], want[3][:, 0], f"sm slab {r0}")
+    del qk, sk, qm, sm
+    gs = Q.nvfp4_gs_scale_cuda(x)
+    q4, s4 = Q.nvfp4_gs_swizzle_cuda(x, gs)
+    qt, st = Q.nvfp4_gs_swizzle_t_cuda(x, gs)
+    r0 = M - 128
+    xs = x[r0:].cpu()
+    w = O.nvfp4_gs_swizzle_f(xs, gs.cpu())
+    assert_same_bits(q4[r0:], w[0], "nvfp4 last slab")
+    assert_same_bits(s4[r0 // 128], w[1][0], "nvfp4 scale last slab")
+    wt = O.nvfp4_gs_swizzle_t_f(xs, gs.cpu())
+    assert_same_bits(qt[:, r0 // 2:], wt[0], "nvfp4 transposed last slab")
+    assert_same_bits(st[:, r0 // 64:], wt[1], "nvfp4 transposed scale last slab")
+    (q8,) = Q.float8_tensorwise_cuda(x, Q.float8_tensorwise_scale_cuda(x))
+    assert_same_bits(q8[r0:], O.float8_tensorwise_f(xs, Q.float8_tensorwise_scale_cuda(x).cpu())[0], "tensorwise last slab")
+    # shapes past the 32-bit block counters are refused before anything is launched (no memory is touched: the
+    # pointers only have to be non-null and aligned)
+    from quant_cast_bench_b200.quant_cast_cuda import _lib as L
+    lib = L.load()
+    p = x.data_ptr()
+    big_m = (1 << 32) // (N // 32) + 128
+    assert lib.qcc_mxfp8(p, big_m, N, L.ROWWISE, p, p, None, None, None) == -1          # QCC_ERR_SHAPE
+    assert lib.qcc_nvfp4(p, (1 << 32) // (N // 16) + 128, N, p, 0, 0, None, p, p, None) == -1
+    assert lib.qcc_fp8_block128(p, big_m, N, L.ROWWISE, p, p, None, None, None) == -1
