@@ -449,6 +449,45 @@ def test_rejected_arguments():
     assert q.shape == (0, 64) and s.shape == (0, 2)
 
 
+def test_rejected_arguments_of_the_block_and_transform_entries():
+    """Every entry point returns its error code before anything is launched: -1 shape, -2 alignment, -3 argument,
+    -4 workspace."""
+    lib = L.load()
+    x = torch.randn(256, 256, dtype=torch.bfloat16, device="cuda")
+    p = x.data_ptr()
+    B32 = L.BLOCK32
+    assert lib.qcc_mxfp8(p, 48, 64, L.ROWWISE | B32, p, p, None, None, None) == -1               # M % 32 with 32x32 blocks
+    assert lib.qcc_mxfp8(p, 64, 64, L.ROWWISE | B32 | L.FLOOR, p, p, None, None, None) == -3     # FLOOR with 32x32 blocks
+    assert lib.qcc_mxfp8(p, 64, 64, L.COLWISE | B32, None, None, p, p, None) == -3               # transposed 32x32 needs SWIZZLE
+    assert lib.qcc_mxfp8(p, 64, 64, L.ROWWISE | L.COLWISE | L.SWIZZLE, p, p, None, p, None) == -3  # qm may be NULL with BLOCK32 only
+    assert lib.qcc_mxfp4(p, 64, 48, 0, p, p, None) == -1
+    assert lib.qcc_mxfp4(p, 64, 64, L.ROWWISE, p, p, None) == -3                                  # only QCC_SWIZZLE is a valid flag
+    assert lib.qcc_fp8_block128(p, 128, 160, L.ROWWISE, p, p, None, None, None) == -1             # N % 128
+    assert lib.qcc_fp8_block128(p, 96, 128, L.COLWISE, None, None, p, p, None) == -1              # M % 128
+    assert lib.qcc_fp8_block128(p, 128, 128, 0, p, p, p, p, None) == -3
+    assert lib.qcc_fp8_block128(p, 128, 128, L.ROWWISE, p + 4, p, None, None, None) == -2
+    assert lib.qcc_fp8_block128x128(p, 128, 192, p, p, None) == -1
+    assert lib.qcc_amax_block128x128(p, 128, 128, 1, p, None) == -3                                # FP8_SCALE is not a mode here
+    assert lib.qcc_nvfp4(p, 128, 128, p, 3, 0, None, p, p, None) == -3                             # outer mode 0..2
+    assert lib.qcc_nvfp4(p, 96, 128, p, 2, L.SWIZZLE, None, p, p, None) == -1                      # blocked outer needs M % 128
+    assert lib.qcc_nvfp4(p, 128, 128, p, 2, L.SWIZZLE | L.SR, p, p, p, None) == -3                 # no SR with a blocked outer
+    assert lib.qcc_hadamard_rht(p, 64, 40, p, p, None) == -1
+    assert lib.qcc_hadamard_rht(p, 64, 64, None, p, None) == -3
+    assert lib.qcc_nvfp4_rht_amax(p, 40, 64, p, 0, p, None) == -1
+    assert lib.qcc_nvfp4_rht_amax(p, 64, 64, p, 1, p, None) == -3
+    assert lib.qcc_nvfp4_rht(p, 48, 64, p, p, p, L.SWIZZLE, None, None, p, p, p, p, None) == -1
+    assert lib.qcc_nvfp4_rht(p, 64, 64, p, p, None, L.SWIZZLE, None, None, p, p, p, p, None) == -3
+    assert lib.qcc_nvfp4_rht(p, 64, 64, p, p, p, L.SWIZZLE | L.SR, None, None, p, p, p, p, None) == -3   # SR without keys
+    offs = torch.tensor([64], dtype=torch.int32, device="cuda")
+    need = lib.qcc_mxfp8_grouped_workspace_bytes(64)
+    assert lib.qcc_mxfp8_grouped(p, 64, 128, L.ROWWISE | L.SWIZZLE, offs.data_ptr(), 1, p, p, None, None, p, need - 1, None) == -4
+    assert lib.qcc_mxfp8_grouped(p, 64, 128, L.ROWWISE, offs.data_ptr(), 1, p, p, None, None, p, need, None) == -3   # needs SWIZZLE
+    assert lib.qcc_mxfp8_grouped(p, 64, 96, L.ROWWISE | L.SWIZZLE, offs.data_ptr(), 1, p, p, None, None, p, need, None) == -1
+    assert lib.qcc_mxfp8_grouped(p, 64, 128, L.ROWWISE | L.SWIZZLE, offs.data_ptr(), 5000, p, p, None, None, p, need, None) == -1
+    torch.cuda.synchronize()
+    assert L.device_error() == 0
+
+
 @pytest.mark.parametrize("swizzle", [True, False])
 def test_host_buffer_caster_matches_oracle(swizzle):
     """The chunked, pipelined host-buffer call returns the bytes of the one-shot cast."""
