@@ -34,7 +34,7 @@ __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer,
     float v[16] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w),
                    bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
 #pragma unroll
-    for (int i = 0; i < 16; i++) v[i] *= recip;
+    for (int i = 0; i < 16; i += 2) mul2(v[i], v[i + 1], recip, v[i], v[i + 1]);   // packed fp32x2 multiply
     // the clamp to +-6 of G:1513 is what the saturating conversion does; it only has to be explicit
     // ahead of the dither
     if (SR) {
@@ -305,10 +305,9 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             sc[k][h] = nvfp4_inner_lut(am[k], outer, lut, recip);
             float v[16];
 #pragma unroll
-            for (int r = 0; r < 16; r++) {
-                const uint32_t word = (k < 2) ? w[r].x : w[r].y;
-                const float f = (k & 1) ? bf16hi(word) : bf16lo(word);
-                v[r] = f * recip;
+            for (int r = 0; r < 16; r += 2) {
+                const uint32_t w0 = (k < 2) ? w[r].x : w[r].y, w1 = (k < 2) ? w[r + 1].x : w[r + 1].y;
+                mul2((k & 1) ? bf16hi(w0) : bf16lo(w0), (k & 1) ? bf16hi(w1) : bf16lo(w1), recip, v[r], v[r + 1]);
             }
             if (SR) {
 #pragma unroll
