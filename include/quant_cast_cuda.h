@@ -59,7 +59,7 @@ int qcc_version(void);
 
 /* Reads and clears the device-side error word of the current device.  Non-zero: a kernel gave up a
  * bounded wait on a TMA barrier (codes 1..15), or qcc_mxfp8_grouped was given group offsets that are
- * not ascending multiples of 32 ending at M (code 16; the scale buffers then hold zeros only), or a
+ * not ascending multiples of 32 inside M (code 16; the scale buffers then hold zeros only), or a
  * transform matrix that is not diag(+-1) @ H16 / 4 was passed to one of the qcc_*rht* calls (code 17;
  * the outputs then follow the signs of its first column).  Synchronises the device. */
 int qcc_device_error(unsigned int *out);
@@ -203,7 +203,8 @@ int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, 
 
 /*
  * mxfp8 of token groups (MoE activations): x is (M, N) with G groups of consecutive rows, offs[g] = end row
- * of group g (device int32, ascending, every group a multiple of 32 rows).  Element bytes are those of
+ * of group g (device int32, ascending, every group a multiple of 32 rows; rows after the last group belong to no
+ * group and get no scale).  Element bytes are those of
  * qcc_mxfp8; the blocked scales are laid out per group, as the grouped block-scaled GEMM reads them
  * (experiments/quantize_tensor_api/api.py:301-411, moe_utils.py:62-128 of the reference):
  *   sk: (M + G * 128, N / 32) bytes -- each group's (rows, N/32) scales blocked on their own, padded to 128
@@ -212,12 +213,33 @@ int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, 
  *       own, columns padded to 4, stored group after group (_to_blocked_2d_k_groups).
  * flags must contain QCC_SWIZZLE; QCC_ROWWISE needs N % 128 == 0 (as the reference's reshape does).  workspace: qcc_mxfp8_grouped_workspace_bytes(M) bytes of scratch.  At most
  * 4096 groups.  Both scale buffers are cleared by the call.  offs lives on the device, so it is checked
- * there: offsets that are not ascending multiples of 32 ending at M leave the scale buffers zero and
+ * there: offsets that are not ascending multiples of 32 within M leave the scale buffers zero and
  * set code 16 in the word qcc_device_error reads (the data outputs do not depend on the groups).
  */
 size_t qcc_mxfp8_grouped_workspace_bytes(int64_t M);
 int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G, void *qk,
                       void *sk, void *qm, void *sm, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Token groups of ANY size (offs[g] = end row of group g, ascending, last = M): what the reference does in two steps --
+ * pad every group with zero rows to a multiple of 32 (_pad_token_groups, experiments/quantize_tensor_api/
+ * moe_utils.py:35-59, used by moe_main.py:178-188), then quantize_tensor_grouped* -- without the padded bf16 copy.
+ * The padded frame has R = qcc_padded_token_rows(M, G) = ceil32(M + 32 G) rows (the reference's upper bound, so no
+ * size has to come back from the device); rows after the last padded group are zero.
+ *   qcc_pad_token_groups:  out (R, row_bytes) = the padded rows themselves (any element type, row_bytes % 16 == 0);
+ *   qcc_mxfp8_grouped_pad: the outputs of qcc_mxfp8_grouped on that padded matrix: qk (R, N), sk (R + 128 G, N/32),
+ *                          qm (N, R), sm (ceil128(N), R/32 + 4 G); x is read once, from its unpadded rows.
+ * padded_offs (device int32[G], may be NULL): group ends in the padded frame, the `offs` of the grouped GEMM.
+ * workspace: qcc_token_pad_workspace_bytes(M, G) bytes.  At most 2048 groups.  Offsets that are not ascending or do
+ * not end at M: code 16 in the device error word, scales zero, padded_offs zero.
+ */
+int64_t qcc_padded_token_rows(int64_t M, int64_t G);
+size_t qcc_token_pad_workspace_bytes(int64_t M, int64_t G);
+int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
+                         int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream);
+int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G, void *qk,
+                          void *sk, void *qm, void *sm, int32_t *padded_offs, void *workspace, size_t workspace_bytes,
+                          void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * nvfp4: 16-element blocks, e4m3 block scales relative to an fp32 outer scale, e2m1 elements

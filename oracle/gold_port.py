@@ -552,6 +552,27 @@ def to_blocked_2d_k_groups(scales, offs):
     return out.view(Hp, W + len(ends) * 4).view(scales.dtype)
 
 
+def pad_token_groups(x, offs, alignment=32):
+    """moe_utils.py:35-59 (_pad_token_groups): each group's rows at the start of its `alignment`-aligned slot of a zero
+    matrix with ceil(total + G * alignment) rows.  Returns (padded, padded_start_offsets, padded_offsets)."""
+    ends = [int(v) for v in offs.tolist()]
+    M, C = x.shape
+    G = len(ends)
+    rows_out = _cdiv(M + G * alignment, alignment) * alignment
+    out = torch.zeros((rows_out, C), dtype=x.dtype)
+    starts, pends = [], []
+    start = pstart = 0
+    for end in ends:
+        size = end - start
+        psize = _cdiv(size, alignment) * alignment
+        out[pstart:pstart + size] = x[start:end]
+        starts.append(pstart)
+        pstart += psize
+        pends.append(pstart)
+        start = end
+    return out, torch.tensor(starts, dtype=torch.int32), torch.tensor(pends, dtype=torch.int32)
+
+
 def quantize_grouped(x, offs, mode="rceil"):
     """(q (M, C), sk grouped, q_t (C, M), sm grouped): api.py:301-411 (quantize_tensor_grouped_bidirectional)."""
     qk, sk, qm, sm = _mxfp8(x, ROWWISE | COLWISE | _mode(mode))

@@ -35,6 +35,23 @@ namespace qcc {
 constexpr int RS_THREADS = 256;
 constexpr int RS_UNROLL = 2;
 
+// Tables of the token-group casts (all null for the plain casts).  Rows are rows of the OUTPUT frame.
+//   row_map[r]  row -> row inside the 128-padded, stacked groups (-1: not in any group)
+//   mb_a[b]     32-row block b -> byte offset of its scale column inside its group's blocked matrix
+//               (group base + (column / 4) * 512 + column % 4), 0xFFFFFFFF: not in any group
+//   mb_b[b]     bytes between consecutive 128-row blocks of that group's blocked matrix
+// and, when the cast also pads every group to a multiple of 32 rows (the input then has src_rows unpadded rows):
+//   blk_src[b]    first source row of output block b (src_rows, i.e. past the end, where there is none)
+//   blk_valid[b]  how many of its 32 rows come from the input; the others are zero
+struct GroupTables {
+    const int32_t *row_map;
+    const uint32_t *mb_a;
+    const uint32_t *mb_b;
+    const int32_t *blk_src;
+    const int32_t *blk_valid;
+    int src_rows;
+};
+
 // Scale byte of block `bi` of the flat stream: plain (M, N/32) or blocked.  Called by every lane of the warp.
 template <bool SWZ>
 __device__ __forceinline__ void stream_scale_store(uint8_t *__restrict__ s, uint32_t bi, bool ok, uint32_t e, uint32_t nb,
@@ -65,8 +82,9 @@ __device__ __forceinline__ void stream_scale_store(uint8_t *__restrict__ s, uint
 template <bool SWZ, bool FLOOR>
 __global__ void __launch_bounds__(RS_THREADS)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
-                            uint8_t *__restrict__ q, uint8_t *__restrict__ s, const int32_t *__restrict__ row_map)
+                            uint8_t *__restrict__ q, uint8_t *__restrict__ s, GroupTables g)
 {
+    const int32_t *__restrict__ row_map = g.row_map;
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint4 *qv = reinterpret_cast<uint4 *>(q);
     const uint32_t base = blockIdx.x * (RS_THREADS * RS_UNROLL) + threadIdx.x;
@@ -74,9 +92,17 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
 #pragma unroll
     for (int u = 0; u < RS_UNROLL; u++) {
         const uint32_t bi = base + u * RS_THREADS;
-        if (bi < nblocks) {
+        size_t src = bi;                      // block index inside x
+        bool have = bi < nblocks;
+        if (have && g.blk_src) {              // padded token groups: the row comes from another place, or is padding
+            const uint32_t row = div_nb.div(bi);
+            const uint32_t rb = row >> 5, ri = row & 31u;
+            have = (int32_t)ri < __ldg(g.blk_valid + rb);
+            src = (size_t)((uint32_t)__ldg(g.blk_src + rb) + ri) * nb + (bi - row * nb);
+        }
+        if (have) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) c[u][i] = ld_v4(xv + 4 * (size_t)bi + i);
+            for (int i = 0; i < 4; i++) c[u][i] = ld_v4(xv + 4 * src + i);
         } else {
 #pragma unroll
             for (int i = 0; i < 4; i++) c[u][i] = make_uint4(0, 0, 0, 0);
@@ -136,16 +162,6 @@ mxfp4_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
 // sweep is row-major, which measured best on B200 (the 128-byte segments of x rows and of the
 // rowwise output written at the same time are neighbours; taller groups favour the transposed
 // output instead).
-// Scale placement tables of the token-group casts (all null for the plain casts).
-//   row_map[r]  row of x -> row inside the 128-padded, stacked groups (-1: not in any group)
-//   mb_a[b]     32-row block b of x -> byte offset of its scale column inside its group's blocked matrix
-//               (group base + (column / 4) * 512 + column % 4), 0xFFFFFFFF: not in any group
-//   mb_b[b]     bytes between consecutive 128-row blocks of that group's blocked matrix
-struct GroupTables {
-    const int32_t *row_map;
-    const uint32_t *mb_a;
-    const uint32_t *mb_b;
-};
 
 #ifndef QCC_MX_GROUP_M
 #define QCC_MX_GROUP_M 1
@@ -181,7 +197,9 @@ struct T64 {
 // maximum over the 32 lanes of a row warp, or over the eight lanes (32 columns) of a column warp; both give the
 // same byte, which is then stored once per row / per column in the expanded 1x32 and 32x1 scale frames.  The
 // rowwise form (DO_M false) can also write the transposed frame's scales (sm non-null) without the transposed data.
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32>
+// PAD (token groups padded by the cast itself): the two 32-row slabs of a tile are fetched from their own source rows
+// and the rows past a group's end read as zero.
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32, bool PAD>
 __global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS, T64<DO_K, DO_M>::MIN_CTAS)
 mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
                     uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n, GroupTables g)
@@ -200,15 +218,30 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
         fence_barrier_init();
     }
     __syncthreads();
+    const int nblk = (M + 31) >> 5;
     if (threadIdx.x == 0) {
         mbar_expect_tx(bar, 2 * T64_PANEL);
-        tma_load_2d(sbase + L::X_OFF, &tm_x, bar, tile_n * 128, tile_m * T64_ROWS);
-        tma_load_2d(sbase + L::X_OFF + T64_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * T64_ROWS);
+        if (PAD) {
+            // padded token groups: each 32-row slab of the tile has its own source rows (the tensor map's box is 32 rows)
+#pragma unroll
+            for (int sl = 0; sl < 2; sl++) {
+                const int ob = tile_m * 2 + sl;
+                const int src = ob < nblk ? __ldg(g.blk_src + ob) : g.src_rows;   // past the end: zero fill
+                tma_load_2d(sbase + L::X_OFF + sl * 4096, &tm_x, bar, tile_n * 128, src);
+                tma_load_2d(sbase + L::X_OFF + T64_PANEL + sl * 4096, &tm_x, bar, tile_n * 128 + 64, src);
+            }
+        } else {
+            tma_load_2d(sbase + L::X_OFF, &tm_x, bar, tile_n * 128, tile_m * T64_ROWS);
+            tma_load_2d(sbase + L::X_OFF + T64_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * T64_ROWS);
+        }
     }
     const bool is_row = DO_K && warp < 2;
     const int b = warp & 1;                        // 32-row slab of this warp
     const int nb = N >> 5, mb = M >> 5;
     const uint32_t xs = base + L::X_OFF;
+    // rows of this warp's slab that hold input (the rest of a padded token group's last block reads as zero)
+    int valid = 32;
+    if (PAD) valid = (tile_m * 2 + b) < nblk ? __ldg(g.blk_valid + tile_m * 2 + b) : 0;
     mbar_wait(bar, 0, 4u);
 
     if (is_row) {
@@ -225,6 +258,7 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
             uint4 c[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) c[i] = lds_v4(prow + (((j0 + i) ^ key) << 4));
+            if (PAD && lane >= valid) c[0] = c[1] = c[2] = c[3] = make_uint4(0, 0, 0, 0);
             float am = amax_of_block(c);
             if (B32) am = u2f(__reduce_max_sync(0xFFFFFFFFu, f2u(am)));   // non-negative floats order like integers
             const uint32_t e = e8m0_from_amax<FLOOR>(am);
@@ -298,6 +332,7 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
 #pragma unroll
         for (int r = 0; r < 32; r++) {
             w[r] = lds_v2(pbase + r * 128 + ((j ^ (r & 7)) << 4));
+            if (PAD && r >= valid) w[r] = make_uint2(0, 0);
             a0 = absmax2_acc(a0, w[r].x);
             a1 = absmax2_acc(a1, w[r].y);
         }
@@ -394,12 +429,12 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
     }
 }
 
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32 = false>
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32 = false, bool PAD = false>
 static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st,
                       GroupTables g)
 {
     using L = T64<DO_K, DO_M>;
-    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32>;
+    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32, PAD>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -477,11 +512,11 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
         if (swz) {
-            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
-            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
+            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
+            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
         } else {
-            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
-            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g.row_map);
+            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
+            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
         }
         return (int)cudaGetLastError();
     }
@@ -489,9 +524,10 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
     uint8_t *qkp = (uint8_t *)qk, *qmp = (uint8_t *)qm;
     {
         CUtensorMap t64;
-        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        // padded token groups: M counts output rows, the input has g.src_rows of them and is fetched by 32-row boxes
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)(g.blk_src ? g.src_rows : M)};
         uint64_t strides[1] = {(uint64_t)N * 2};
-        uint32_t box[2] = {64, 64};
+        uint32_t box[2] = {64, g.blk_src ? 32u : 64u};
         int e = make_tensor_map(&t64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (e) return e;
 #define QCC_T64(DO_K)                                                                                        \
@@ -499,6 +535,12 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
                : launch_t64<DO_K, true, true, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g))           \
          : (fl ? launch_t64<DO_K, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)            \
                : launch_t64<DO_K, true, false, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)))
+        if (g.blk_src) {   // padded token groups (blocked scales only)
+            if (row) return fl ? launch_t64<true, true, true, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)
+                               : launch_t64<true, true, true, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
+            return fl ? launch_t64<false, true, true, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)
+                      : launch_t64<false, true, true, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
+        }
         if (row) return QCC_T64(true);
         return QCC_T64(false);
 #undef QCC_T64
@@ -508,7 +550,7 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
 extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
                          void *stream)
 {
-    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr});
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0});
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -517,41 +559,63 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
 namespace qcc {
 
 constexpr int GROUPS_MAX = 4096;
+constexpr int GROUPS_MAX_PAD = 2048;                // the padding form keeps two more per-group arrays in shared memory
 constexpr unsigned int QCC_DEVERR_GROUPS = 16u;   // reported by qcc_device_error
 
-// offs[g] = end row of group g (ascending, multiples of 32).  Fills the three tables of GroupTables.
+// offs[g] = end row of group g in x (ascending, last = src_rows).  Fills the tables of GroupTables for an output frame
+// of M rows.  PAD false: the groups are multiples of 32 rows already and M = src_rows.  PAD true: every group is
+// padded to a multiple of 32 rows on the way (torch_pad_token_groups of torchao / _pad_token_groups of the reference,
+// experiments/quantize_tensor_api/moe_utils.py:35-59), M is the upper bound ceil32(src_rows + G * 32) and
+// padded_offs[g] receives the group ends of the padded frame.
 // Every CTA recomputes the (short) prefix sums over the groups, then fills its share of the tables.
-__global__ void __launch_bounds__(256) group_tables_kernel(const int32_t *__restrict__ offs, int G, int M, int padded_c,
-                                                          int32_t *__restrict__ row_map, uint32_t *__restrict__ mb_a,
-                                                          uint32_t *__restrict__ mb_b)
+template <bool PAD>
+__global__ void __launch_bounds__(256) group_tables_kernel(const int32_t *__restrict__ offs, int G, int M, int src_rows,
+                                                          int padded_c, int32_t *__restrict__ row_map,
+                                                          uint32_t *__restrict__ mb_a, uint32_t *__restrict__ mb_b,
+                                                          int32_t *__restrict__ blk_src, int32_t *__restrict__ blk_valid,
+                                                          int32_t *__restrict__ padded_offs)
 {
-    __shared__ int32_t s_end[GROUPS_MAX];
-    __shared__ int32_t s_prow[GROUPS_MAX];     // first row of the group inside the stacked, 128-padded groups
-    __shared__ uint32_t s_pcol[GROUPS_MAX];    // first scale column of the group after padding each group to 4
+    constexpr int GMAX = PAD ? GROUPS_MAX_PAD : GROUPS_MAX;
+    __shared__ int32_t s_end[GMAX];       // group ends in the output frame
+    __shared__ int32_t s_prow[GMAX];      // first row of the group inside the stacked, 128-padded groups
+    __shared__ uint32_t s_pcol[GMAX];     // first scale column of the group after padding each group to 4
+    __shared__ int32_t s_shift[PAD ? GMAX : 1];   // source row minus output row inside the group
+    __shared__ int32_t s_size[PAD ? GMAX : 1];    // rows the group really has
     for (int i = threadIdx.x; i < G; i += blockDim.x) s_end[i] = offs[i];
     __syncthreads();
     int bad = 0;
     if (threadIdx.x == 0) {
-        int32_t prow = 0, start = 0;
+        int32_t prow = 0, start = 0, pstart = 0;
         uint32_t pcol = 0;
         for (int i = 0; i < G; i++) {
-            const int32_t size = s_end[i] - start;
-            bad |= (size < 0) | (s_end[i] & 31) | (s_end[i] > M);
+            const int32_t end = s_end[i];
+            const int32_t size = end - start;
+            bad |= (size < 0) | (end > src_rows) | (PAD ? 0 : (end & 31));
+            const int32_t psize = PAD ? ((max(size, 0) + 31) & ~31) : size;
             s_prow[i] = prow;
             s_pcol[i] = pcol;
+            if (PAD) {
+                s_shift[i] = start - pstart;
+                s_size[i] = size;
+                s_end[i] = pstart + psize;
+            }
             if (size > 0) {
-                prow += ((size + 127) >> 7) << 7;
-                pcol += (uint32_t)((((size >> 5) + 3) >> 2) << 2);
-                start = s_end[i];
+                prow += ((psize + 127) >> 7) << 7;
+                pcol += (uint32_t)((((psize >> 5) + 3) >> 2) << 2);
+                start = end;
+                pstart += psize;
             }
         }
-        bad |= (start != M);
+        // the padding form consumes every input row; without padding rows after the last group simply belong to none
+        bad |= (PAD ? (start != src_rows) : 0) | (pstart > M);
         if (bad && blockIdx.x == 0) atomicMax(&g_qcc_error, QCC_DEVERR_GROUPS);
     }
-    // offsets that are not ascending multiples of 32 ending at M: no scale is written at all
+    // offsets that are not ascending (multiples of 32) ending at the last row: no scale is written at all
     const int total = __syncthreads_or(bad) ? 0 : s_end[G - 1];
+    if (PAD && padded_offs && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < G; i += blockDim.x) padded_offs[i] = total ? s_end[i] : 0;
     for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
-        int32_t dst = -1;
+        int32_t dst = -1, src = src_rows, nvalid = 0;
         uint32_t a = 0xFFFFFFFFu, bstride = 0;
         if (r < total) {
             int lo = 0, hi = G - 1;                 // first group whose end is above r
@@ -566,9 +630,34 @@ __global__ void __launch_bounds__(256) group_tables_kernel(const int32_t *__rest
             const uint32_t ncb = (uint32_t)(((size >> 5) + 3) >> 2);
             a = s_pcol[lo] * (uint32_t)padded_c + (cg >> 2) * 512u + (cg & 3u);
             bstride = ncb * 512u;
+            if (PAD) {
+                src = r + s_shift[lo];
+                nvalid = min(32, max(0, s_size[lo] - (r - start)));
+            }
         }
         row_map[r] = dst;
-        if ((r & 31) == 0) { mb_a[r >> 5] = a; mb_b[r >> 5] = bstride; }
+        if ((r & 31) == 0) {
+            mb_a[r >> 5] = a;
+            mb_b[r >> 5] = bstride;
+            if (PAD) { blk_src[r >> 5] = src; blk_valid[r >> 5] = nvalid; }
+        }
+    }
+}
+
+// out (rows_out, row_bytes) = the rows of x moved to their padded places, zeros elsewhere; one 16-byte piece per thread
+__global__ void __launch_bounds__(256) pad_rows_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ out, int rows_out,
+                                                      uint32_t vec_per_row, FastDiv32 div_vec,
+                                                      const int32_t *__restrict__ blk_src, const int32_t *__restrict__ blk_valid)
+{
+    const uint64_t total = (uint64_t)rows_out * vec_per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (uint64_t)gridDim.x * 256) {
+        // i < 2^32 is checked by the launcher
+        const uint32_t row = div_vec.div((uint32_t)i);
+        const uint32_t v = (uint32_t)i - row * vec_per_row;
+        const uint32_t rb = row >> 5, ri = row & 31u;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if ((int32_t)ri < __ldg(blk_valid + rb)) val = ld_nc_v4(x + (size_t)((uint32_t)__ldg(blk_src + rb) + ri) * vec_per_row + v);
+        __stcs(out + i, val);
     }
 }
 
@@ -600,9 +689,90 @@ extern "C" int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags,
     if (col && sm && (e = cudaMemsetAsync(sm, 0, (size_t)padded_c * (mb + G * 4), st)) != cudaSuccess) return (int)e;
     int grid = (int)((M + 255) / 256);
     if (grid > sm_count()) grid = sm_count();
-    group_tables_kernel<<<grid, 256, 0, st>>>(offs, (int)G, (int)M, (int)padded_c, row_map, mb_a, mb_b);
+    group_tables_kernel<false><<<grid, 256, 0, st>>>(offs, (int)G, (int)M, (int)M, (int)padded_c, row_map, mb_a, mb_b, nullptr,
+                                                    nullptr, nullptr);
     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b});
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b, nullptr, nullptr, 0});
+}
+
+// ---- token groups of any size: pad to multiples of 32 rows and cast in one pass -----------------------------------
+extern "C" int64_t qcc_padded_token_rows(int64_t M, int64_t G) { return ((M + G * 32 + 31) / 32) * 32; }
+
+extern "C" size_t qcc_token_pad_workspace_bytes(int64_t M, int64_t G)
+{
+    const int64_t R = qcc_padded_token_rows(M, G);
+    return (size_t)(R * 4 + 4 * (R / 32) * 4 + 64);
+}
+
+namespace {
+struct PadTables {
+    int32_t *row_map, *blk_src, *blk_valid;
+    uint32_t *mb_a, *mb_b;
+};
+// carves the workspace and launches the table kernel for the padded frame of R rows
+int build_pad_tables(const int32_t *offs, int64_t G, int64_t M, int64_t R, int64_t padded_c, int32_t *padded_offs,
+                     void *workspace, cudaStream_t st, PadTables &t)
+{
+    t.row_map = (int32_t *)workspace;
+    t.mb_a = (uint32_t *)(t.row_map + R);
+    t.mb_b = t.mb_a + R / 32;
+    t.blk_src = (int32_t *)(t.mb_b + R / 32);
+    t.blk_valid = t.blk_src + R / 32;
+    int grid = (int)((R + 255) / 256);
+    if (grid > sm_count()) grid = sm_count();
+    group_tables_kernel<true><<<grid, 256, 0, st>>>(offs, (int)G, (int)R, (int)M, (int)padded_c, t.row_map, t.mb_a, t.mb_b,
+                                                   t.blk_src, t.blk_valid, padded_offs);
+    return (int)cudaGetLastError();
+}
+}  // namespace
+
+extern "C" int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
+                                    int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!x || !offs || !out || !workspace || G <= 0 || M < 0 || row_bytes <= 0) return QCC_ERR_ARG;
+    if (G > GROUPS_MAX_PAD || row_bytes % 16 != 0 || M > 0x7FFFF000) return QCC_ERR_SHAPE;
+    const int64_t R = qcc_padded_token_rows(M, G);
+    if (R * (row_bytes / 16) >= (1ll << 32)) return QCC_ERR_SHAPE;
+    if (workspace_bytes < qcc_token_pad_workspace_bytes(M, G)) return QCC_ERR_WORKSPACE;
+    if (!aligned16(x) || !aligned16(out) || !aligned16(workspace)) return QCC_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    PadTables t;
+    int e = build_pad_tables(offs, G, M, R, 128, padded_offs, workspace, st, t);
+    if (e) return e;
+    FastDiv32 dv;
+    dv.init((uint32_t)(row_bytes / 16));
+    const uint64_t total = (uint64_t)R * (uint64_t)(row_bytes / 16);
+    uint64_t grid = (total + 255) / 256;
+    const uint64_t cap = (uint64_t)sm_count() * 32;
+    if (grid > cap) grid = cap;
+    pad_rows_kernel<<<(unsigned)grid, 256, 0, st>>>((const uint4 *)x, (uint4 *)out, (int)R, (uint32_t)(row_bytes / 16), dv,
+                                                   t.blk_src, t.blk_valid);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G,
+                                     void *qk, void *sk, void *qm, void *sm, int32_t *padded_offs, void *workspace,
+                                     size_t workspace_bytes, void *stream)
+{
+    const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
+    if (N == 0) return 0;
+    if (!offs || !workspace || G <= 0 || M < 0 || !(flags & QCC_SWIZZLE)) return QCC_ERR_ARG;
+    if (G > GROUPS_MAX_PAD || M > 0x7FFFF000) return QCC_ERR_SHAPE;
+    if (row && N % 128 != 0) return QCC_ERR_SHAPE;
+    if (workspace_bytes < qcc_token_pad_workspace_bytes(M, G)) return QCC_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return QCC_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t R = qcc_padded_token_rows(M, G);
+    const int64_t nb = N / 32, mb = R / 32, padded_c = ((N + 127) / 128) * 128;
+    if ((uint64_t)padded_c * (uint64_t)(mb + G * 4) >= (1ull << 32)) return QCC_ERR_SHAPE;
+    cudaError_t ce;
+    if (row && sk && (ce = cudaMemsetAsync(sk, 0, (size_t)(R + G * 128) * nb, st)) != cudaSuccess) return (int)ce;
+    if (col && sm && (ce = cudaMemsetAsync(sm, 0, (size_t)padded_c * (mb + G * 4), st)) != cudaSuccess) return (int)ce;
+    PadTables t;
+    int e = build_pad_tables(offs, G, M, R, padded_c, padded_offs, workspace, st, t);
+    if (e) return e;
+    return mxfp8_entry(x, R, N, flags, qk, sk, qm, sm, stream,
+                       GroupTables{t.row_map, t.mb_a, t.mb_b, t.blk_src, t.blk_valid, (int)M});
 }
 
 extern "C" int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, void *stream)

@@ -38,6 +38,10 @@ SIGNATURES = {
     "qcc_fp8_colwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "qcc_fp8_colwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
     "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "qcc_padded_token_rows": (_i64, [_i64, _i64]),
+    "qcc_token_pad_workspace_bytes": (_sz, [_i64, _i64]),
+    "qcc_pad_token_groups": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "qcc_mxfp8_grouped_pad": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "qcc_mxfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_mxfp8_grouped_workspace_bytes": (_sz, [_i64]),
     "qcc_mxfp8_grouped": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -290,3 +290,83 @@ def quantize_tensor_grouped_bidirectional(input: Tensor, offs: Tensor, *, qdata_
     if skip_transposed_qdata:
         raise NotImplementedError("skip_transposed_qdata is not supported by quantize_tensor_grouped_bidirectional")
     return _grouped(input, offs, L.ROWWISE | L.COLWISE | _mx_flags(inner_scale_calc, True))
+
+
+def pad_token_groups(input: Tensor, offs: Tensor):
+    """`_pad_token_groups` of the reference (experiments/quantize_tensor_api/moe_utils.py:35-59) as one kernel and
+    without the host sync on the group sizes: every group's rows moved to the start of its 32-row-aligned slot of a
+    zero matrix with ceil32(total_M + 32 G) rows.  Returns (padded_tokens, padded_start_offsets, padded_offsets)."""
+    lib = L.load()
+    assert input.dim() == 2 and input.is_cuda, "a 2D CUDA tensor"
+    x = input.contiguous()
+    M, C = x.shape
+    row_bytes = C * x.element_size()
+    assert row_bytes % 16 == 0, f"rows must be a multiple of 16 bytes, got {row_bytes}"
+    offs32 = offs.to(torch.int32).contiguous()
+    G = offs32.numel()
+    rows_out = lib.qcc_padded_token_rows(M, G)
+    out = torch.empty((rows_out, C), dtype=x.dtype, device=x.device)
+    padded_offs = torch.empty(G, dtype=torch.int32, device=x.device)
+    nws = lib.qcc_token_pad_workspace_bytes(M, G)
+    ws = torch.empty(nws, dtype=torch.uint8, device=x.device)
+    with R._on_device(x.device):
+        L.check(lib.qcc_pad_token_groups(R._p(x), M, row_bytes, R._p(offs32), G, R._p(out), R._p(padded_offs), R._p(ws), nws,
+                                         R._stream(x)), "pad_token_groups")
+    L.launch_count += 2
+    sizes = torch.diff(offs32, prepend=offs32.new_zeros(1))
+    padded_sizes = (sizes + 31) // 32 * 32
+    return out, padded_offs - padded_sizes, padded_offs
+
+
+def _grouped_pad(x, offs, flags):
+    lib = L.load()
+    assert x.dim() == 2, f"grouped casts take a 2D (total_M, C) input, got {x.dim()}D"
+    x = x.contiguous()
+    R._check_x(x)
+    M, C = x.shape
+    row, col = bool(flags & L.ROWWISE), bool(flags & L.COLWISE)
+    assert C % 32 == 0 and (not row or C % 128 == 0), f"needs C % 32 == 0 (C % 128 == 0 for the natural orientation), got C={C}"
+    assert offs.dim() == 1 and offs.device == x.device, "offs: 1-D tensor of group ends on the input's device"
+    offs32 = offs.to(torch.int32).contiguous()
+    G = offs32.numel()
+    Rr = lib.qcc_padded_token_rows(M, G)
+    dev, u8 = x.device, torch.uint8
+    qk = torch.empty((Rr, C), dtype=u8, device=dev) if row else None
+    sk = torch.empty((Rr + G * 128, C // 32), dtype=u8, device=dev) if row else None
+    qm = torch.empty((C, Rr), dtype=u8, device=dev) if col else None
+    sm = torch.empty((-(-C // 128) * 128, Rr // 32 + G * 4), dtype=u8, device=dev) if col else None
+    padded_offs = torch.empty(G, dtype=torch.int32, device=dev)
+    nws = lib.qcc_token_pad_workspace_bytes(M, G)
+    ws = torch.empty(nws, dtype=u8, device=dev)
+    with R._on_device(dev):
+        L.check(lib.qcc_mxfp8_grouped_pad(R._p(x), M, C, flags, R._p(offs32), G, R._p(qk), R._p(sk), R._p(qm), R._p(sm),
+                                          R._p(padded_offs), R._p(ws), nws, R._stream(x)), "mxfp8_grouped_pad")
+    L.launch_count += 2
+    f8, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    outs = []
+    if row:
+        outs += [qk.view(f8), sk.view(e8)]
+    if col:
+        outs += [qm.view(f8), sm.view(e8)]
+    return tuple(outs) + (padded_offs,)
+
+
+def quantize_tensor_grouped_padded(input: Tensor, offs: Tensor, *, orientation: QuantOrientation = QuantOrientation.NATURAL,
+                                   inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL):
+    """`quantize_tensor_grouped(*_pad_token_groups(input, offs)[::2])` in one pass over the unpadded input (the call
+    pattern of moe_main.py:178-188): token groups of any size; returns (qdata, blocked scales, padded_offsets)."""
+    if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
+        raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
+    if orientation not in (QuantOrientation.NATURAL, QuantOrientation.TRANSPOSED):
+        raise ValueError(f"orientation={orientation!r} is not supported; supported: NATURAL, TRANSPOSED")
+    direction = L.ROWWISE if orientation == QuantOrientation.NATURAL else L.COLWISE
+    return _grouped_pad(input, offs, direction | _mx_flags(inner_scale_calc, True))
+
+
+def quantize_tensor_grouped_padded_bidirectional(input: Tensor, offs: Tensor, *,
+                                                 inner_scale_calc: InnerScaleCalc = InnerScaleCalc.E8M0_RCEIL):
+    """Both orientations of the padded grouped cast from one read: (q_nat, sb_nat, q_t, sb_t, padded_offsets)."""
+    if inner_scale_calc not in (InnerScaleCalc.E8M0_RCEIL, InnerScaleCalc.E8M0_FLOOR):
+        raise ValueError(f"float8_e4m3fn qdata takes an E8M0 inner scale, got {inner_scale_calc!r}")
+    return _grouped_pad(input, offs, L.ROWWISE | L.COLWISE | _mx_flags(inner_scale_calc, True))
+

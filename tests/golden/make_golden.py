@@ -176,6 +176,15 @@ def main():
         sct = torch.randint(1, 256, (W * 16, M // 32), generator=g, dtype=torch.uint8)   # (C, M/32) transposed scales
         out[f"kat/kgroups_{name}_in"] = raw(sct)
         out[f"kat/kgroups_{name}_out"] = raw(MU._to_blocked_2d_k_groups(sct, o // 32))
+    for name, M, C, offs in (("a", 100, 16, [7, 7, 40, 100]), ("b", 64, 8, [64]), ("c", 131, 24, [1, 33, 131])):
+        xin = torch.randn(M, C, generator=g).to(torch.bfloat16)
+        o = torch.tensor(offs, dtype=torch.int32)
+        padded, pstarts, pends = MU._pad_token_groups(xin, o)
+        out[f"kat/padgroups_{name}_in"] = raw(xin)
+        out[f"kat/padgroups_{name}_offs"] = o.numpy()
+        out[f"kat/padgroups_{name}_out"] = raw(padded)
+        out[f"kat/padgroups_{name}_starts"] = pstarts.to(torch.int32).numpy()
+        out[f"kat/padgroups_{name}_ends"] = pends.to(torch.int32).numpy()
     out["kat/bf16_clamp_min"] = raw(torch.zeros(1, dtype=torch.bfloat16).clamp(min=1e-12))
 
     np.savez_compressed(args.out, **out)

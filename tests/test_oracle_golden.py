@@ -165,6 +165,17 @@ def test_token_group_layouts():
         assert_same_bits(O.to_blocked_2d_k_groups(sct, offs // 32), torch.from_numpy(g[f"kat/kgroups_{name}_out"].copy()), f"k groups {name}")
 
 
+def test_pad_token_groups():
+    g = golden()
+    for name in ("a", "b", "c"):
+        x = torch.from_numpy(g[f"kat/padgroups_{name}_in"].copy()).view(torch.bfloat16)
+        offs = torch.from_numpy(g[f"kat/padgroups_{name}_offs"].copy())
+        padded, starts, ends = O.pad_token_groups(x, offs)
+        assert_same_bits(padded, torch.from_numpy(g[f"kat/padgroups_{name}_out"].copy()), f"padded {name}")
+        assert starts.tolist() == g[f"kat/padgroups_{name}_starts"].tolist()
+        assert ends.tolist() == g[f"kat/padgroups_{name}_ends"].tolist()
+
+
 def test_philox_known_answers():
     """Random123 known-answer vectors for Philox4x32-10."""
     kat = [

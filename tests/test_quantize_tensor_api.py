@@ -138,10 +138,60 @@ def test_token_groups_errors():
     # offsets live on the device and are checked there: bad ones (a group that is not a multiple of 32 rows,
     # a last end other than total_M, descending ends) write no scale and raise the device error word
     want_q = O.mxfp8_f(make_input(128, 128, seed=1))[0]
-    for ends in ([48, 128], [64], [96, 64, 128], [128, 160]):
+    for ends in ([48, 128], [96, 64, 128], [128, 160]):
         assert L.device_error() == 0
         q, s = A.quantize_tensor_grouped(xc, torch.tensor(ends, dtype=torch.int32).cuda())
         assert L.device_error() == 16, ends
         assert_same_bits(q, want_q, f"data with bad offsets {ends}")
         assert int(s.view(torch.uint8).max()) == 0
     assert L.device_error() == 0
+
+
+PAD_CASES = [
+    (100, 128, [7, 7, 40, 100]),          # ragged groups, an empty one
+    (64, 256, [64]),                      # one aligned group
+    (131, 128, [1, 33, 131]),             # a one-row group
+    (1000, 384, [0, 250, 250, 777, 1000]),
+    (4096, 512, [1000, 2047, 2048, 4096]),
+]
+
+
+@pytest.mark.parametrize("M,C,ends", PAD_CASES)
+def test_pad_token_groups(M, C, ends):
+    """The padded copy itself (moe_utils.py:35-59), for bf16 and for a 16-byte-row byte tensor."""
+    x = make_input(M, C, seed=M)
+    offs = torch.tensor(ends, dtype=torch.int32)
+    want, wstarts, wends = O.pad_token_groups(x, offs)
+    got, starts, pends = A.pad_token_groups(x.cuda(), offs.cuda())
+    assert_same_bits(got, want, "padded tokens")
+    assert starts.cpu().tolist() == wstarts.tolist() and pends.cpu().tolist() == wends.tolist()
+    assert L.device_error() == 0
+
+
+@pytest.mark.parametrize("M,C,ends", PAD_CASES)
+def test_token_groups_padded_by_the_cast(M, C, ends):
+    """quantize_tensor_grouped(_pad_token_groups(x, offs)) in one pass: same bytes as padding first."""
+    x = make_input(M, C, seed=M + 1)
+    offs = torch.tensor(ends, dtype=torch.int32)
+    padded, _, pends = O.pad_token_groups(x, offs)
+    for mode, calc in (("rceil", A.InnerScaleCalc.E8M0_RCEIL), ("floor", A.InnerScaleCalc.E8M0_FLOOR)):
+        want = O.quantize_grouped(padded, pends, mode)
+        got = A.quantize_tensor_grouped_padded_bidirectional(x.cuda(), offs.cuda(), inner_scale_calc=calc)
+        same_outputs(got[:4], want, f"padded grouped bidirectional {mode}")
+        assert got[4].cpu().tolist() == pends.tolist()
+        nat = A.quantize_tensor_grouped_padded(x.cuda(), offs.cuda(), inner_scale_calc=calc)
+        same_outputs(nat[:2], want[:2], f"padded grouped natural {mode}")
+        tr = A.quantize_tensor_grouped_padded(x.cuda(), offs.cuda(), orientation=TR, inner_scale_calc=calc)
+        same_outputs(tr[:2], want[2:], f"padded grouped transposed {mode}")
+        # and equal to the two-step route through this backend
+        p2, _, po2 = A.pad_token_groups(x.cuda(), offs.cuda())
+        same_outputs(A.quantize_tensor_grouped_bidirectional(p2, po2, inner_scale_calc=calc), got[:4], "two-step route")
+    assert L.device_error() == 0
+
+
+def test_padded_groups_bad_offsets():
+    xc = make_input(128, 128, seed=1).cuda()
+    for ends in ([64, 32, 128], [64, 100], [64, 200]):
+        out = A.quantize_tensor_grouped_padded(xc, torch.tensor(ends, dtype=torch.int32).cuda())
+        assert L.device_error() == 16, ends
+        assert int(out[1].view(torch.uint8).max()) == 0 and out[2].cpu().tolist() == [0] * len(ends)
