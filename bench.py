@@ -284,9 +284,13 @@ def run_ours(args):
     torch.cuda.empty_cache()
     c4 = bench_c4_sharded(dev, world, rank, peak)
     casts = {}
+    moe = None
     cpu = None
     if rank == 0:
         casts = bench_other_casts(Q, x, dev, peak)
+        del x
+        torch.cuda.empty_cache()
+        moe = bench_moe_token_groups(dev)
         clocks = sampler.stop()
         cpu = cpu_baseline()
     if world > 1:
@@ -313,6 +317,7 @@ def run_ours(args):
         "clocks": clocks,
         "c4_sharded": c4,
         "casts": casts,
+        "moe_token_groups": moe,
     }
     emit(json.dumps(line))
 
@@ -384,6 +389,45 @@ def bench_c4_sharded(dev, world, rank, peak, iters=10):
             "ms_per_iter": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "bytes": nbytes, "n_gpus": world,
             "frac_measured_peak_per_gpu": nbytes / (ms * 1e-3) / 1e9 / world / peak,
             "output_checksum": int(chk.item()), "outer_scale": outer}
+
+
+def bench_moe_token_groups(dev, iters=10):
+    """Config-4-shaped MoE activation, 64 ragged token groups: pad every group to 32 rows + mxfp8 both orientations with
+    per-group blocked scales -- as two steps (padded bf16 copy, then the grouped cast) and as the one fused cast."""
+    import torch
+    from quant_cast_bench_b200.quant_cast_cuda import quantize_tensor_api as A
+    from quant_cast_bench_b200.workloads import make_input_device
+    M, C, G = 131072, 7168, 64
+    x = make_input_device(M, C, seed=4, device=dev, spread=6.0, outlier_p=0.0, zero_row_p=0.0)
+    cuts = torch.sort(torch.randint(0, M, (G - 1,), generator=torch.Generator().manual_seed(0))).values
+    offs = torch.cat([cuts, torch.tensor([M])]).to(torch.int32).to(dev)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    def two_step():
+        p, _, po = A.pad_token_groups(x, offs)
+        return A.quantize_tensor_grouped_bidirectional(p, po)
+
+    ms_two = timed(two_step)
+    ms_fused = timed(lambda: A.quantize_tensor_grouped_padded_bidirectional(x, offs))
+    ms_dense = timed(lambda: A.quantize_tensor_bidirectional(x))
+    rows = int(A.L.load().qcc_padded_token_rows(M, G))
+    nbytes = 2 * M * C + 2 * rows * C + 2 * rows * C // 32     # unpadded input + both padded outputs + both scale sets
+    del x
+    torch.cuda.empty_cache()
+    return {"workload": "bf16[131072,7168], 64 ragged token groups: pad to 32 rows + mxfp8 both orientations, per-group blocked scales",
+            "ms_pad_then_cast": ms_two, "ms_fused": ms_fused, "ms_dense_no_groups": ms_dense,
+            "GBps_fused": nbytes / (ms_fused * 1e-3) / 1e9, "bytes": nbytes}
 
 
 def bench_other_casts(Q, x, dev, peak):

@@ -403,13 +403,18 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
             const uint16_t v = *reinterpret_cast<const uint16_t *>(sms + c * 2);
             if (SWZ && g.mb_a) {
                 // token groups: every 32-row block of x has its own place (group base, column inside the group)
-#pragma unroll
-                for (int hb = 0; hb < 2; hb++) {
-                    const int mblk = tile_m * 2 + hb;
-                    if (Cn < N && mblk < mb) {
-                        const uint32_t a = __ldg(g.mb_a + mblk);
-                        if (a != 0xFFFFFFFFu)
-                            sm[(size_t)a + (size_t)tile_n * __ldg(g.mb_b + mblk) + (c & 31) * 16u + (c >> 5) * 4u] = (uint8_t)(v >> (8 * hb));
+                const int m0 = tile_m * 2;
+                const uint32_t a0 = m0 < mb ? __ldg(g.mb_a + m0) : 0xFFFFFFFFu;
+                const uint32_t a1 = m0 + 1 < mb ? __ldg(g.mb_a + m0 + 1) : 0xFFFFFFFFu;
+                const uint32_t b0 = m0 < mb ? __ldg(g.mb_b + m0) : 0u, b1 = m0 + 1 < mb ? __ldg(g.mb_b + m0 + 1) : 0u;
+                const uint32_t lane_off = (c & 31) * 16u + (c >> 5) * 4u;
+                if (Cn < N) {
+                    if (a0 != 0xFFFFFFFFu && a1 == a0 + 1u && b1 == b0 && (a0 & 1u) == 0u) {
+                        // both blocks in one group, in neighbouring scale columns of one atom: one 2-byte store
+                        *reinterpret_cast<uint16_t *>(sm + (size_t)a0 + (size_t)tile_n * b0 + lane_off) = v;
+                    } else {
+                        if (a0 != 0xFFFFFFFFu) sm[(size_t)a0 + (size_t)tile_n * b0 + lane_off] = (uint8_t)v;
+                        if (a1 != 0xFFFFFFFFu) sm[(size_t)a1 + (size_t)tile_n * b1 + lane_off] = (uint8_t)(v >> 8);
                     }
                 }
             } else if (SWZ) {
