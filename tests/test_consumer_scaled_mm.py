@@ -52,3 +52,51 @@ def test_nvfp4_blocked_scales_feed_scaled_mm():
     ref = a.float() @ b.float().t()
     got = y.float() * (ga * gb)      # the per-tensor outer scales are applied outside the GEMM
     assert _sqnr(ref, got) > 12.0
+
+
+def _scaled_grouped_mm(a, b, sa, sb, offs):
+    if not hasattr(torch, "_scaled_grouped_mm"):
+        pytest.skip("this torch build has no torch._scaled_grouped_mm")
+    try:
+        return torch._scaled_grouped_mm(a, b, sa, sb, offs=offs, out_dtype=torch.bfloat16)
+    except (RuntimeError, NotImplementedError, TypeError) as e:
+        pytest.skip(f"torch._scaled_grouped_mm does not take these operands here: {str(e).splitlines()[0][:160]}")
+
+
+def test_grouped_casts_feed_the_grouped_gemm():
+    """The MoE flow of the reference (experiments/quantize_tensor_api/moe_main.py:71-162): token groups of any size,
+    padded and cast in one pass, multiplied per expert by torch._scaled_grouped_mm; forward (2d-3d) and weight
+    gradient (2d-2d), each against the bf16 product of the same groups."""
+    from quant_cast_bench_b200.quant_cast_cuda import quantize_tensor_api as A
+    torch.manual_seed(2)
+    E, K, N = 4, 256, 384
+    ends = [100, 100, 333, 512]                      # one empty group, ragged sizes
+    M = ends[-1]
+    act = torch.randn(M, K, dtype=torch.bfloat16, device="cuda")
+    weight_t = torch.randn(E, K, N, dtype=torch.bfloat16, device="cuda")
+    offs = torch.tensor(ends, dtype=torch.int32, device="cuda")
+
+    qa, sa, padded_offs = A.quantize_tensor_grouped_padded(act, offs)                       # (Mp, K), M-groups scales
+    wq, ws = A.quantize_tensor(weight_t, orientation=A.QuantOrientation.TRANSPOSED)          # (E, N, K), per-expert scales
+    out = _scaled_grouped_mm(qa, wq.transpose(-2, -1), sa, ws, padded_offs)                  # (Mp, N)
+    pends = padded_offs.cpu().tolist()
+    start, pstart = 0, 0
+    for e, end in enumerate(ends):
+        size = end - start
+        if size:
+            ref = act[start:end].float() @ weight_t[e].float()
+            got = out[pstart:pstart + size].float()
+            assert _sqnr(ref, got) > 25.0, f"forward, expert {e}"
+        start, pstart = end, pends[e]
+
+    # weight gradient: grad_output^T @ act per group, both operands cast along the (padded) token dimension
+    go = torch.randn(M, N, dtype=torch.bfloat16, device="cuda")
+    go_t, go_ts, po2 = A.quantize_tensor_grouped_padded(go, offs, orientation=A.QuantOrientation.TRANSPOSED)   # (N, Mp)
+    ia_t, ia_ts, _ = A.quantize_tensor_grouped_padded(act, offs, orientation=A.QuantOrientation.TRANSPOSED)    # (K, Mp)
+    gw = _scaled_grouped_mm(go_t, ia_t.transpose(-2, -1), go_ts, ia_ts, po2)                                   # (E, N, K)
+    start = 0
+    for e, end in enumerate(ends):
+        if end > start:
+            ref = go[start:end].float().t() @ act[start:end].float()
+            assert _sqnr(ref, gw[e].float()) > 25.0, f"weight gradient, expert {e}"
+        start = end
