@@ -237,6 +237,10 @@ int64_t qcc_padded_token_rows(int64_t M, int64_t G);
 size_t qcc_token_pad_workspace_bytes(int64_t M, int64_t G);
 int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
                          int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream);
+/* The inverse of qcc_pad_token_groups (_unpad_token_groups, moe_main.py:54-68): out (M, row_bytes) = the real rows of
+ * `padded` (qcc_padded_token_rows(M, G) rows); offs are the UNPADDED group ends, as above. */
+int qcc_unpad_token_groups(const void *padded, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
+                           void *workspace, size_t workspace_bytes, void *stream);
 int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G, void *qk,
                           void *sk, void *qm, void *sm, int32_t *padded_offs, void *workspace, size_t workspace_bytes,
                           void *stream);

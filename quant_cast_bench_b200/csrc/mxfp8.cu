@@ -649,20 +649,29 @@ __global__ void __launch_bounds__(256) group_tables_kernel(const int32_t *__rest
     }
 }
 
-// out (rows_out, row_bytes) = the rows of x moved to their padded places, zeros elsewhere; one 16-byte piece per thread
-__global__ void __launch_bounds__(256) pad_rows_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ out, int rows_out,
+// PAD: out (rows_padded, row_bytes) = the rows of x moved to their padded places, zeros elsewhere.
+// !PAD (the inverse, _unpad_token_groups of moe_main.py:54-68): out (unpadded rows) = the real rows of the padded x.
+// One 16-byte piece per thread, indexed in the padded frame.
+template <bool PAD>
+__global__ void __launch_bounds__(256) pad_rows_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ out, int rows_padded,
                                                       uint32_t vec_per_row, FastDiv32 div_vec,
                                                       const int32_t *__restrict__ blk_src, const int32_t *__restrict__ blk_valid)
 {
-    const uint64_t total = (uint64_t)rows_out * vec_per_row;
+    const uint64_t total = (uint64_t)rows_padded * vec_per_row;
     for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (uint64_t)gridDim.x * 256) {
         // i < 2^32 is checked by the launcher
         const uint32_t row = div_vec.div((uint32_t)i);
         const uint32_t v = (uint32_t)i - row * vec_per_row;
         const uint32_t rb = row >> 5, ri = row & 31u;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if ((int32_t)ri < __ldg(blk_valid + rb)) val = ld_nc_v4(x + (size_t)((uint32_t)__ldg(blk_src + rb) + ri) * vec_per_row + v);
-        __stcs(out + i, val);
+        const bool real = (int32_t)ri < __ldg(blk_valid + rb);
+        const size_t other = (size_t)((uint32_t)__ldg(blk_src + rb) + ri) * vec_per_row + v;   // place in the unpadded frame
+        if (PAD) {
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (real) val = ld_nc_v4(x + other);
+            __stcs(out + i, val);
+        } else if (real) {
+            __stcs(out + other, ld_nc_v4(x + i));
+        }
     }
 }
 
@@ -731,8 +740,8 @@ int build_pad_tables(const int32_t *offs, int64_t G, int64_t M, int64_t R, int64
 }
 }  // namespace
 
-extern "C" int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
-                                    int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream)
+static int pad_or_unpad(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
+                        int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream, bool unpad)
 {
     if (!x || !offs || !out || !workspace || G <= 0 || M < 0 || row_bytes <= 0) return QCC_ERR_ARG;
     if (G > GROUPS_MAX_PAD || row_bytes % 16 != 0 || M > 0x7FFFF000) return QCC_ERR_SHAPE;
@@ -750,9 +759,25 @@ extern "C" int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes,
     uint64_t grid = (total + 255) / 256;
     const uint64_t cap = (uint64_t)sm_count() * 32;
     if (grid > cap) grid = cap;
-    pad_rows_kernel<<<(unsigned)grid, 256, 0, st>>>((const uint4 *)x, (uint4 *)out, (int)R, (uint32_t)(row_bytes / 16), dv,
-                                                   t.blk_src, t.blk_valid);
+    if (unpad)
+        pad_rows_kernel<false><<<(unsigned)grid, 256, 0, st>>>((const uint4 *)x, (uint4 *)out, (int)R, (uint32_t)(row_bytes / 16),
+                                                              dv, t.blk_src, t.blk_valid);
+    else
+        pad_rows_kernel<true><<<(unsigned)grid, 256, 0, st>>>((const uint4 *)x, (uint4 *)out, (int)R, (uint32_t)(row_bytes / 16),
+                                                             dv, t.blk_src, t.blk_valid);
     return (int)cudaGetLastError();
+}
+
+extern "C" int qcc_pad_token_groups(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
+                                    int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream)
+{
+    return pad_or_unpad(x, M, row_bytes, offs, G, out, padded_offs, workspace, workspace_bytes, stream, false);
+}
+
+extern "C" int qcc_unpad_token_groups(const void *padded, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G,
+                                      void *out, void *workspace, size_t workspace_bytes, void *stream)
+{
+    return pad_or_unpad(padded, M, row_bytes, offs, G, out, nullptr, workspace, workspace_bytes, stream, true);
 }
 
 extern "C" int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const int32_t *offs, int64_t G,

@@ -318,6 +318,29 @@ def pad_token_groups(input: Tensor, offs: Tensor):
     return out, padded_offs - padded_sizes, padded_offs
 
 
+def unpad_token_groups(padded: Tensor, offs: Tensor):
+    """`_unpad_token_groups` (moe_main.py:54-68): the (total_M, C) rows of a tensor in the padded frame of
+    `pad_token_groups`; `offs` are the unpadded group ends."""
+    lib = L.load()
+    assert padded.dim() == 2 and padded.is_cuda, "a 2D CUDA tensor"
+    p = padded.contiguous()
+    offs32 = offs.to(torch.int32).contiguous()
+    G = offs32.numel()
+    C = p.shape[1]
+    row_bytes = C * p.element_size()
+    # total_M is the last offset; it fixes the output shape, so it is read back once (the reference does the same)
+    M = int(offs32[-1].item())
+    assert p.shape[0] == lib.qcc_padded_token_rows(M, G), "padded must have qcc_padded_token_rows(total_M, G) rows"
+    out = torch.empty((M, C), dtype=p.dtype, device=p.device)
+    nws = lib.qcc_token_pad_workspace_bytes(M, G)
+    ws = torch.empty(nws, dtype=torch.uint8, device=p.device)
+    with R._on_device(p.device):
+        L.check(lib.qcc_unpad_token_groups(R._p(p), M, row_bytes, R._p(offs32), G, R._p(out), R._p(ws), nws, R._stream(p)),
+                "unpad_token_groups")
+    L.launch_count += 2
+    return out
+
+
 def _grouped_pad(x, offs, flags):
     lib = L.load()
     assert x.dim() == 2, f"grouped casts take a 2D (total_M, C) input, got {x.dim()}D"

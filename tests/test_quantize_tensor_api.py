@@ -165,6 +165,7 @@ def test_pad_token_groups(M, C, ends):
     got, starts, pends = A.pad_token_groups(x.cuda(), offs.cuda())
     assert_same_bits(got, want, "padded tokens")
     assert starts.cpu().tolist() == wstarts.tolist() and pends.cpu().tolist() == wends.tolist()
+    assert_same_bits(A.unpad_token_groups(got, offs.cuda()), x, "unpad(pad(x))")
     assert L.device_error() == 0
 
 
