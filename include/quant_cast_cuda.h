@@ -195,6 +195,17 @@ int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk
               void *stream);
 
 /*
+ * E independent (M, N) matrices stacked in x, e.g. per-expert weights (the 3-D branch of quantize_tensor,
+ * experiments/quantize_tensor_api/api.py:171-190, with _to_blocked_per_group_3d of moe_utils.py:84-90): the casts of
+ * qcc_mxfp8 applied to every matrix, outputs stacked, scale grids per matrix.  One call: a single launch for the
+ * whole stack when the scales are plain and only rowwise outputs are asked for, or when the scales are blocked and
+ * M % 128 == 0 (every matrix is whole scale atoms; the transposed outputs are placed per matrix inside the kernel);
+ * otherwise one launch per matrix.
+ */
+int qcc_mxfp8_batched(const void *x, int64_t E, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
+                      void *stream);
+
+/*
  * mxfp4 (mxfp4_f G:607-617): 1x32 blocks along the rows, RCEIL e8m0 scale of amax / 6, elements e2m1 packed two
  * per byte (even element in the low nibble).  q (M, N/2) bytes, s the (M, N/32) scales, plain or (QCC_SWIZZLE)
  * blocked.  N % 32 == 0.

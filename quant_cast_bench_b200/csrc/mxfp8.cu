@@ -50,6 +50,10 @@ struct GroupTables {
     const int32_t *blk_src;
     const int32_t *blk_valid;
     int src_rows;
+    // stacked matrices (per-expert weights) cast by one launch: rows of one matrix (a multiple of 128) and the bytes
+    // of one matrix's transposed scale grid; 0 when x is a single matrix
+    int rows_per_mat;
+    uint32_t sm_bytes_per_mat;
 };
 
 // Scale byte of block `bi` of the flat stream: plain (M, N/32) or blocked.  Called by every lane of the warp.
@@ -199,7 +203,10 @@ struct T64 {
 // rowwise form (DO_M false) can also write the transposed frame's scales (sm non-null) without the transposed data.
 // PAD (token groups padded by the cast itself): the two 32-row slabs of a tile are fetched from their own source rows
 // and the rows past a group's end read as zero.
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32, bool PAD>
+// BATCHED (blocked scales, no groups): x is E matrices of g.rows_per_mat rows stacked; loads and rowwise outputs
+// address the stack as one tall matrix (its blocked scale grid is the E grids one after the other), the transposed
+// outputs go to matrix e's own (N, rows_per_mat) frame and scale grid.
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32, bool PAD, bool BATCHED>
 __global__ void __launch_bounds__(T64<DO_K, DO_M>::THREADS, T64<DO_K, DO_M>::MIN_CTAS)
 mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk,
                     uint8_t *__restrict__ qm, uint8_t *__restrict__ sm, int M, int N, int tiles_m, int tiles_n, GroupTables g)
@@ -382,17 +389,28 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
 #pragma unroll
         for (int kk = 0; kk < 4; kk++) sms[(4 * lane + kk) * 2 + b] = (uint8_t)e[kk];
         named_barrier(1, 64);
+        // frame of the transposed outputs: the whole matrix, or matrix e of a stack
+        int tm = tile_m, Mq = M;
+        uint8_t *qmp = qm, *smp = sm;
+        if (BATCHED) {
+            const int tpm = g.rows_per_mat >> 6;
+            const int e = tile_m / tpm;
+            tm = tile_m - e * tpm;
+            Mq = g.rows_per_mat;
+            qmp = qm + (size_t)e * N * Mq;
+            smp = sm + (size_t)e * g.sm_bytes_per_mat;
+        }
         // write-out: col warp b takes sub-tiles 2b and 2b+1; four lanes move one 64-byte row segment
         {
             const int jj = lane & 3;
-            const int mcol = tile_m * T64_ROWS + jj * 16;
+            const int mcol = tm * T64_ROWS + jj * 16;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const int kk = 2 * b + (i >> 2);
                 const int l = (i & 3) * 8 + (lane >> 2);
                 const int Cn = tile_n * 128 + 4 * l + kk;
                 const uint4 v = lds_v4(qms + kk * 2048 + l * 64 + ((jj ^ ((l >> 1) & 3)) << 4));
-                if (Cn < N && mcol < M) *reinterpret_cast<uint4 *>(qm + (size_t)Cn * M + mcol) = v;
+                if (Cn < N && mcol < Mq) *reinterpret_cast<uint4 *>(qmp + (size_t)Cn * Mq + mcol) = v;
             }
         }
         // scales: thread (b, lane) writes the two bytes (m-blocks 2 tile_m, 2 tile_m + 1) of columns 2t, 2t+1
@@ -418,9 +436,9 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
                     }
                 }
             } else if (SWZ) {
-                const uint32_t ncb = (mb + 3) >> 2;
-                const size_t off = ((size_t)tile_n * ncb + (tile_m >> 1)) * 512u + (c & 31) * 16u + (c >> 5) * 4u + (tile_m & 1) * 2u;
-                *reinterpret_cast<uint16_t *>(sm + off) = v;       // padding columns carry zeros (zero-filled x)
+                const uint32_t ncb = (uint32_t)((Mq >> 5) + 3) >> 2;
+                const size_t off = ((size_t)tile_n * ncb + (tm >> 1)) * 512u + (c & 31) * 16u + (c >> 5) * 4u + (tm & 1) * 2u;
+                *reinterpret_cast<uint16_t *>(smp + off) = v;      // padding columns carry zeros (zero-filled x)
             } else if (Cn < N) {
                 uint8_t *dst = sm + (size_t)Cn * mb + tile_m * 2;
                 if ((mb & 1) == 0) {
@@ -434,12 +452,12 @@ mxfp8_tile64_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restric
     }
 }
 
-template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32 = false, bool PAD = false>
+template <bool DO_K, bool DO_M, bool SWZ, bool FLOOR, bool B32 = false, bool PAD = false, bool BATCHED = false>
 static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *qm, uint8_t *sm, int M, int N, cudaStream_t st,
                       GroupTables g)
 {
     using L = T64<DO_K, DO_M>;
-    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32, PAD>;
+    auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32, PAD, BATCHED>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -540,6 +558,12 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
                : launch_t64<DO_K, true, true, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g))           \
          : (fl ? launch_t64<DO_K, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)            \
                : launch_t64<DO_K, true, false, false>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)))
+        if (g.rows_per_mat) {   // stacked matrices (blocked scales only)
+            if (row) return fl ? launch_t64<true, true, true, true, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)
+                               : launch_t64<true, true, true, false, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
+            return fl ? launch_t64<false, true, true, true, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)
+                      : launch_t64<false, true, true, false, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
+        }
         if (g.blk_src) {   // padded token groups (blocked scales only)
             if (row) return fl ? launch_t64<true, true, true, true, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g)
                                : launch_t64<true, true, true, false, false, true>(t64, qkp, skp, qmp, smp, (int)M, (int)N, st, g);
@@ -555,7 +579,42 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
 extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
                          void *stream)
 {
-    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0});
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0});
+}
+
+// E independent (M, N) matrices stacked in x (per-expert weights): one launch per matrix, issued from here so that
+// the caller pays one call instead of E.  Outputs are stacked the same way; blocked scale grids are per matrix.
+extern "C" int qcc_mxfp8_batched(const void *x, int64_t E, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm,
+                                 void *sm, void *stream)
+{
+    if (E < 0) return QCC_ERR_ARG;
+    if (E == 0 || M == 0 || N == 0) return 0;
+    const bool swz = flags & QCC_SWIZZLE, b32 = flags & QCC_BLOCK32;
+    const int64_t nb = N / 32, mb = M / 32;
+    const size_t sk_bytes = b32 && !swz ? (size_t)mb * nb
+                                        : swz ? (size_t)((M + 127) / 128) * ((nb + 3) / 4) * 512 : (size_t)M * nb;
+    const size_t sm_bytes = swz ? (size_t)((N + 127) / 128) * ((mb + 3) / 4) * 512 : (size_t)N * mb;
+    // every slice must start 16-byte aligned
+    if ((((size_t)M * N) & 15) || (sk && (sk_bytes & 15)) || (sm && (sm_bytes & 15))) return QCC_ERR_SHAPE;
+    // One launch for the whole stack where the stacked outputs are those of one tall matrix: always for the plain
+    // rowwise cast, for blocked scales when every matrix is whole 128-row atoms (the transposed outputs then go to
+    // their own frames inside the kernel).
+    const bool col = flags & QCC_COLWISE;
+    const int64_t ME = E * M;
+    if (!b32 && ME <= 0x7FFFFF00 && sm_bytes < (1ull << 32)) {
+        if (!col && (!swz || M % 128 == 0)) return qcc_mxfp8(x, ME, N, flags, qk, sk, nullptr, nullptr, stream);
+        if (col && swz && M % 128 == 0)
+            return mxfp8_entry(x, ME, N, flags, qk, sk, qm, sm, stream,
+                               GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0, (int)M, (uint32_t)sm_bytes});
+    }
+    for (int64_t e = 0; e < E; e++) {
+        const int rc = qcc_mxfp8((const uint16_t *)x + (size_t)e * M * N, M, N, flags,
+                                 qk ? (uint8_t *)qk + (size_t)e * M * N : nullptr, sk ? (uint8_t *)sk + e * sk_bytes : nullptr,
+                                 qm ? (uint8_t *)qm + (size_t)e * M * N : nullptr, sm ? (uint8_t *)sm + e * sm_bytes : nullptr,
+                                 stream);
+        if (rc) return rc;
+    }
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -706,7 +765,7 @@ extern "C" int qcc_mxfp8_grouped(const void *x, int64_t M, int64_t N, int flags,
     group_tables_kernel<false><<<grid, 256, 0, st>>>(offs, (int)G, (int)M, (int)M, (int)padded_c, row_map, mb_a, mb_b, nullptr,
                                                     nullptr, nullptr);
     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b, nullptr, nullptr, 0});
+    return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{row_map, mb_a, mb_b, nullptr, nullptr, 0, 0, 0});
 }
 
 // ---- token groups of any size: pad to multiples of 32 rows and cast in one pass -----------------------------------
@@ -802,7 +861,7 @@ extern "C" int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int fl
     int e = build_pad_tables(offs, G, M, R, padded_c, padded_offs, workspace, st, t);
     if (e) return e;
     return mxfp8_entry(x, R, N, flags, qk, sk, qm, sm, stream,
-                       GroupTables{t.row_map, t.mb_a, t.mb_b, t.blk_src, t.blk_valid, (int)M});
+                       GroupTables{t.row_map, t.mb_a, t.mb_b, t.blk_src, t.blk_valid, (int)M, 0, 0});
 }
 
 extern "C" int qcc_mxfp4(const void *x, int64_t M, int64_t N, int flags, void *q, void *s, void *stream)

@@ -43,6 +43,7 @@ SIGNATURES = {
     "qcc_pad_token_groups": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     "qcc_unpad_token_groups": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
     "qcc_mxfp8_grouped_pad": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "qcc_mxfp8_batched": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "qcc_mxfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_mxfp8_grouped_workspace_bytes": (_sz, [_i64]),
     "qcc_mxfp8_grouped": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -82,6 +82,8 @@ def _mx_flags(inner_scale_calc, swz):
 
 def _per_expert(x, flags):
     """mxfp8 of every (M, K) slice of a contiguous (E, M, K) tensor into stacked outputs."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()):
+        raise ValueError("per-expert casts take a contiguous CUDA bf16 (E, M, K) tensor (quant_cast_cuda has no CPU path)")
     E, M, K = x.shape
     dev, u8 = x.device, torch.uint8
     swz = bool(flags & L.SWIZZLE)
@@ -92,9 +94,12 @@ def _per_expert(x, flags):
     nm = R.blocked_shape(K, M // 32) if swz else (K, M // 32)
     sk = torch.empty((E,) + tuple(nk), dtype=u8, device=dev) if row else None
     sm = torch.empty((E,) + tuple(nm), dtype=u8, device=dev) if col else None
-    for e in range(E):
-        R._mxfp8(x[e], flags, out=(qk[e] if row else None, sk[e] if row else None, qm[e] if col else None,
-                                   sm[e] if col else None))
+    assert M % 32 == 0 or not col, f"the transposed cast needs M % 32 == 0, got M={M}"
+    assert K % 32 == 0, f"mxfp8 needs K % 32 == 0, got K={K}"
+    with R._on_device(dev):
+        L.check(L.load().qcc_mxfp8_batched(R._p(x), E, M, K, flags, R._p(qk), R._p(sk), R._p(qm), R._p(sm), R._stream(x)),
+                "mxfp8_batched")
+    L.launch_count += E
     f8, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
     outs = []
     if row:

@@ -65,8 +65,11 @@ def test_32x32_and_mxfp4_table():
         A.quantize_tensor(xc, orientation=TR, **fp4)
 
 
-def test_per_expert_3d():
-    E, M, K = 3, 160, 256
+@pytest.mark.parametrize("E,M,K", [(3, 160, 256),      # ragged experts: one launch per expert
+                                   (4, 256, 384),      # whole 128-row atoms: the stack is cast by one launch
+                                   (5, 128, 160),      # ... with a ragged column count
+                                   (2, 1024, 2048)])
+def test_per_expert_3d(E, M, K):
     x = make_input(E * M, K, seed=5).reshape(E, M, K)
     xc = x.cuda()
     q, s = A.quantize_tensor(xc)
@@ -82,6 +85,12 @@ def test_per_expert_3d():
         assert_same_bits(st[e], wst.reshape(-1), f"expert {e} transposed scale")
         assert_same_bits(qk[e], wq, "bidir qk"); assert_same_bits(sk[e], ws.reshape(-1), "bidir sk")
         assert_same_bits(qm[e], wqt, "bidir qm"); assert_same_bits(sm[e], wst.reshape(-1), "bidir sm")
+    fl = A.InnerScaleCalc.E8M0_FLOOR
+    qk, sk, qm, sm = A.quantize_tensor_bidirectional(xc, inner_scale_calc=fl)
+    for e in range(E):
+        want = O.mxfp8_dim_km_swizzle_f(x[e].contiguous(), mode="floor")
+        for got, w in zip((qk[e], sk[e], qm[e], sm[e]), want):
+            assert_same_bits(got, w.reshape(got.shape), f"floor expert {e}")
 
 
 def test_unsupported_combinations_raise():
