@@ -15,7 +15,6 @@ Reference functions mirrored (quant_cast_bench/quant_cast_gold/recipes.py = "G")
 Extensions without a reference counterpart take `fmt="e5m2"`, `mode="floor"`, or a Philox key.
 """
 import ctypes
-import os
 
 import torch
 

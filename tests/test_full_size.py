@@ -15,7 +15,7 @@ import torch
 from helpers import assert_same_bits
 from oracle import gold_port as O
 from quant_cast_bench_b200 import quant_cast_cuda as Q
-from quant_cast_bench_b200.workloads import CONFIGS, config_input_device
+from quant_cast_bench_b200.workloads import config_input_device
 
 pytestmark = pytest.mark.gpu
 
