@@ -160,23 +160,24 @@ constexpr int NVT_Q_OFF = 2 * NVT_PANEL_BYTES;     // staging: 4 sub-tiles x 32 
 constexpr int NVT_S_OFF = NVT_Q_OFF + 4 * 32 * 64; // 128 columns x 8 block scales
 constexpr int NVT_LUT_OFF = NVT_S_OFF + 1024;      // 128 multipliers, one per inner-scale byte
 constexpr int NVT_BAR_OFF = NVT_LUT_OFF + 512;
-constexpr int NVT_QK_OFF = NVT_BAR_OFF + 512;      // rowwise staging (fused form only): 128 rows x 64 B
-constexpr int nvt_alloc(bool do_k) { return NVT_QK_OFF + (do_k ? 128 * 64 : 0) + 1024; }
+constexpr int NVT_QK_OFF = NVT_Q_OFF;              // rowwise staging (fused form): reuses the transposed staging
+constexpr int NVT_ALLOC = NVT_BAR_OFF + 512 + 1024;
 
-// Row-major tile order (column tiles fastest), as in the mxfp8 tile kernel.  Warps 0-3 quantise down the
-// rows (transposed outputs q, s); with DO_K warps 4-7 also quantise along the rows (outputs qk, sk), so both
-// orientations come from one read of x.
-// RHT (transposed outputs only): the 16-row blocks going down the rows pass through the 16-point randomised
-// Hadamard transform before they are quantised -- the dim-m half of nvfp4_gs_swizzle_dim_k_dim_m_rht_f
-// (G:1324-1333) and of its stochastic form (G:1429-1438).
+// Row-major tile order (column tiles fastest), as in the mxfp8 tile kernel.  The four warps quantise down the
+// rows (transposed outputs q, s); with DO_K they then also quantise along the rows of the same tile (outputs qk, sk),
+// so both orientations come from one read of x.
+// RHT: the 16-row blocks going down the rows pass through the 16-point randomised Hadamard transform before they
+// are quantised -- the dim-m half of nvfp4_gs_swizzle_dim_k_dim_m_rht_f (G:1324-1333) and of its stochastic form
+// (G:1429-1438); the rowwise half is not transformed and has its own outer scale and Philox key.
+
 template <bool DO_K, bool SWZ, bool SR, bool RHT>
-__global__ void __launch_bounds__(DO_K ? 256 : 128, DO_K ? 3 : ((RHT && SR) ? 4 : 5))
+__global__ void __launch_bounds__(128, (RHT && SR) ? 4 : 5)
 nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *__restrict__ outer_p,
-                        const uint64_t *__restrict__ key, const uint16_t *__restrict__ rht, uint8_t *__restrict__ q,
+                        const float *__restrict__ outer_k_p, const uint64_t *__restrict__ key,
+                        const uint64_t *__restrict__ key_k, const uint16_t *__restrict__ rht, uint8_t *__restrict__ q,
                         uint8_t *__restrict__ s, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk, int M, int N,
                         int tiles_n)
 {
-    static_assert(!(DO_K && (RHT || SR)), "the fused rowwise half is round-to-nearest without transform");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
@@ -207,9 +208,9 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
 
     mbar_wait(bar, 0, 2u);
 
-    if (DO_K && b >= 4) {
-        // ------------------------------------------------------------------ along the row (fused form)
-        const int rw = b - 4;
+    // ---------------------------------------------------------------------- along the row (fused form)
+    auto row_phase = [&](const int rw, const float outer_k, const float inv_outer_k, const uint64_t seed_k,
+                         const uint64_t offset_k) {
         const int row_t = rw * 32 + lane;
         const int R = tile_m * NVT_TILE_M + row_t;
         const int nb16 = N >> 4, halfN = N >> 1;
@@ -225,7 +226,8 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             const uint4 a4 = lds_v4(prow + (((j0) ^ key7) << 4));
             const uint4 b4 = lds_v4(prow + (((j0 + 1) ^ key7) << 4));
             uint2 packed;
-            uint32_t byte = nvfp4_quant16<false>(a4, b4, outer, inv_outer, lut, 0, 0, 0, packed);
+            const uint64_t flat0 = (uint64_t)R * (uint64_t)N + (uint64_t)(tile_n * 128 + kb * 16);
+            uint32_t byte = nvfp4_quant16<SR>(a4, b4, outer_k, inv_outer_k, lut, flat0, seed_k, offset_k, packed);
             const bool ok = R < M && (tile_n * 8 + kb) < nb16;
             sb[kb >> 2] |= (ok ? byte : 0u) << (8 * (kb & 3));
             asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(qrow + ((kb ^ key2) << 3)), "r"(packed.x), "r"(packed.y) : "memory");
@@ -261,8 +263,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
                     if (tile_n * 8 + kb < nb16) dst[kb] = (uint8_t)(sb[kb >> 2] >> (8 * (kb & 3)));
             }
         }
-        return;
-    }
+    };
 
     const uint32_t pbase = base + NVT_X_OFF + (lane >> 4) * NVT_PANEL_BYTES + (b * 32) * 128 + (lane & 1) * 8;
     const uint32_t j = (lane & 15) >> 1;
@@ -386,6 +387,21 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             }
         }
     }
+    if (DO_K) {
+        // The same four warps, after their column work (four more warps for this half measured 14 % slower: they sit
+        // idle while the column warps finish, and eight warps at 80 registers allow 3 CTAs per SM instead of 5).
+        float outer_k = outer, inv_outer_k = inv_outer;
+        uint64_t seed_k = 0, offset_k = 0;
+        if (SR) { seed_k = key_k[0]; offset_k = key_k[1]; }
+        __syncthreads();                     // the staging tile and the multiplier table are about to be reused
+        if (RHT) {                           // the two halves have their own outer scales
+            outer_k = __ldg(outer_k_p);
+            inv_outer_k = __fdiv_rn(1.0f, outer_k);
+            nvfp4_fill_recip_lut(lut, inv_outer_k);
+            __syncthreads();
+        }
+        row_phase(b, outer_k, inv_outer_k, seed_k, offset_k);
+    }
 }
 
 // rht must be diag(sign) @ H / 4 in bf16: entry (i, j) = +-0.25 with the sign of row i times (-1)^popcount(i & j)
@@ -459,9 +475,9 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
 }
 
 struct NvtArgs {
-    const float *outer;
-    const uint64_t *key;
-    const uint16_t *rht;     // non-null: transform down the rows (transposed outputs only)
+    const float *outer, *outer_k;          // down the rows / along the rows (fused forms)
+    const uint64_t *key, *key_k;
+    const uint16_t *rht;                   // non-null: transform down the rows
     uint8_t *q, *s, *qk, *sk;
 };
 
@@ -469,12 +485,11 @@ template <bool DO_K, bool SWZ, bool SR, bool RHT>
 static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cudaStream_t st)
 {
     auto kern = nvfp4_transposed_kernel<DO_K, SWZ, SR, RHT>;
-    constexpr int ALLOC = nvt_alloc(DO_K);
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ALLOC);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, NVT_ALLOC);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
@@ -483,23 +498,24 @@ static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cud
     const int tiles_n = (N + 127) / 128, tiles_m = (M + NVT_TILE_M - 1) / NVT_TILE_M;
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, DO_K ? 256 : 128, ALLOC, st>>>(tx, a.outer, a.key, a.rht, a.q, a.s, a.qk, a.sk, M, N, tiles_n);
+    kern<<<(unsigned)num_tiles, 128, NVT_ALLOC, st>>>(tx, a.outer, a.outer_k, a.key, a.key_k, a.rht, a.q, a.s, a.qk, a.sk, M, N,
+                                                     tiles_n);
     return (int)cudaGetLastError();
 }
 
-template <bool RHT>
-static int launch_nvt_t(const CUtensorMap &tx, const NvtArgs &a, bool swz, bool sr, int M, int N, cudaStream_t st)
+template <bool DO_K, bool RHT>
+static int launch_nvt_flags(const CUtensorMap &tx, const NvtArgs &a, bool swz, bool sr, int M, int N, cudaStream_t st)
 {
-    if (swz) return sr ? launch_nvt<false, true, true, RHT>(tx, a, M, N, st) : launch_nvt<false, true, false, RHT>(tx, a, M, N, st);
-    return sr ? launch_nvt<false, false, true, RHT>(tx, a, M, N, st) : launch_nvt<false, false, false, RHT>(tx, a, M, N, st);
+    if (swz) return sr ? launch_nvt<DO_K, true, true, RHT>(tx, a, M, N, st) : launch_nvt<DO_K, true, false, RHT>(tx, a, M, N, st);
+    return sr ? launch_nvt<DO_K, false, true, RHT>(tx, a, M, N, st) : launch_nvt<DO_K, false, false, RHT>(tx, a, M, N, st);
 }
 
 static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &a, int flags, bool both, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || a.rht)) || (flags & ~(QCC_SWIZZLE | QCC_SR)))
+    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || !a.outer_k)) || (flags & ~(QCC_SWIZZLE | QCC_SR)))
         return QCC_ERR_ARG;
-    if ((flags & QCC_SR) && (!a.key || both)) return QCC_ERR_ARG;
+    if ((flags & QCC_SR) && (!a.key || (both && !a.key_k))) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     // output rows of M / 2 bytes are written in 16-byte pieces: M % 32 == 0; the TMA load needs N % 8 == 0
     if (M % 32 != 0 || N % 8 != 0 || (both && N % 32 != 0)) return QCC_ERR_SHAPE;
@@ -514,46 +530,37 @@ static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &
         if (e) return e;
     }
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR;
-    if (both)
-        return swz ? launch_nvt<true, true, false, false>(tx, a, (int)M, (int)N, st)
-                   : launch_nvt<true, false, false, false>(tx, a, (int)M, (int)N, st);
     if (a.rht) {
         int e = launch_rht_check(a.rht, st);
         if (e) return e;
-        return launch_nvt_t<true>(tx, a, swz, sr, (int)M, (int)N, st);
+        return both ? launch_nvt_flags<true, true>(tx, a, swz, sr, (int)M, (int)N, st)
+                    : launch_nvt_flags<false, true>(tx, a, swz, sr, (int)M, (int)N, st);
     }
-    return launch_nvt_t<false>(tx, a, swz, sr, (int)M, (int)N, st);
+    return both ? launch_nvt_flags<true, false>(tx, a, swz, sr, (int)M, (int)N, st)
+                : launch_nvt_flags<false, false>(tx, a, swz, sr, (int)M, (int)N, st);
 }
 
 extern "C" int qcc_nvfp4_transposed(const void *x, int64_t M, int64_t N, const float *outer, int flags,
                                     const uint64_t *philox_key, void *q, void *s, void *stream)
 {
-    NvtArgs a = {outer, philox_key, nullptr, (uint8_t *)q, (uint8_t *)s, nullptr, nullptr};
+    NvtArgs a = {outer, nullptr, philox_key, nullptr, nullptr, (uint8_t *)q, (uint8_t *)s, nullptr, nullptr};
     return nvfp4_tile_entry(x, M, N, a, flags, false, stream);
 }
 
 extern "C" int qcc_nvfp4_both(const void *x, int64_t M, int64_t N, const float *outer, int flags, void *qk, void *sk,
                               void *qm, void *sm, void *stream)
 {
-    NvtArgs a = {outer, nullptr, nullptr, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
+    if (flags & QCC_SR) return QCC_ERR_ARG;   // one key cannot serve two streams; the transform form takes two
+    NvtArgs a = {outer, outer, nullptr, nullptr, nullptr, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
     return nvfp4_tile_entry(x, M, N, a, flags, true, stream);
 }
 
-// Two launches when both halves are asked for: the rowwise stream cast, then the tile kernel with the transform
-// for the dim-m half.  (A single kernel doing both from one read exists for the transform-free pair,
-// qcc_nvfp4_both; with the transform in the column warps it ran slower than these two.)
 extern "C" int qcc_nvfp4_rht(const void *x, int64_t M, int64_t N, const float *outer_k, const float *outer_m,
                              const void *rht, int flags, const uint64_t *key_k, const uint64_t *key_m, void *qk, void *sk,
                              void *qm, void *sm, void *stream)
 {
-    if (M == 0 || N == 0) return 0;
-    if (!rht || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if (!rht) return QCC_ERR_ARG;
     const bool both = qk != nullptr || sk != nullptr;
-    if (M % 32 != 0 || N % 8 != 0 || (both && N % 32 != 0)) return QCC_ERR_SHAPE;
-    if (both) {
-        int e = qcc_nvfp4(x, M, N, outer_k, 0, flags, key_k, qk, sk, stream);
-        if (e) return e;
-    }
-    NvtArgs a = {outer_m, key_m, (const uint16_t *)rht, (uint8_t *)qm, (uint8_t *)sm, nullptr, nullptr};
-    return nvfp4_tile_entry(x, M, N, a, flags, false, stream);
+    NvtArgs a = {outer_m, outer_k, key_m, key_k, (const uint16_t *)rht, (uint8_t *)qm, (uint8_t *)sm, (uint8_t *)qk, (uint8_t *)sk};
+    return nvfp4_tile_entry(x, M, N, a, flags, both, stream);
 }
