@@ -7,7 +7,7 @@
 //    CTA per 128x128 tile fetched by TMA (two 64-column boxes, 128-byte swizzle, bounded mbarrier wait).  Four
 //    column warps each hold a 32-row slab in registers (lane = four adjacent columns), exchange their column
 //    maxima through shared memory, quantise and stage the transposed bytes in a swizzled tile that leaves as
-//    coalesced 16-byte stores; with both directions four more warps quantise along the rows (lane = row).
+//    coalesced 16-byte stores; with both directions the same warps then quantise along the rows (lane = row).
 //  * 128x128: one CTA of 128 threads per block, the block held in registers (16 x 16 bytes per thread), one
 //    CTA-wide maximum, 8-byte stores.
 //
@@ -113,8 +113,8 @@ constexpr int BT_X_OFF = 0;
 constexpr int BT_QM_OFF = 2 * BT_PANEL;             // transposed staging: 4 sub-tiles x 32 output rows x 128 B
 constexpr int BT_AM_OFF = BT_QM_OFF + 4 * 32 * 128; // column maxima of the four slabs: 4 x 32 lanes x 8 B
 constexpr int BT_BAR_OFF = BT_AM_OFF + 1024;
-constexpr int BT_QK_OFF = BT_BAR_OFF + 64;          // rowwise staging (fused form): 128 rows x 128 B
-constexpr int bt_alloc(bool do_k) { return BT_QK_OFF + (do_k ? 128 * 128 : 0) + 1024; }
+constexpr int BT_QK_OFF = BT_QM_OFF;                // rowwise staging (fused form): reuses the transposed staging
+constexpr int BT_ALLOC = BT_BAR_OFF + 64 + 1024;
 
 // 16 bf16 in two 16-byte chunks -> 16 e4m3 bytes
 __device__ __forceinline__ uint4 quant16(uint4 a, uint4 b, float inv)
@@ -128,7 +128,7 @@ __device__ __forceinline__ uint4 quant16(uint4 a, uint4 b, float inv)
 }
 
 template <bool DO_K, bool CLAMP_F32>
-__global__ void __launch_bounds__(DO_K ? 256 : 128, DO_K ? 3 : 4)
+__global__ void __launch_bounds__(128, 4)
 fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, float *__restrict__ sk,
                          uint8_t *__restrict__ qm, float *__restrict__ sm, int M, int N, int tiles_n)
 {
@@ -151,9 +151,8 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
     }
     mbar_wait(bar, 0, 5u);
 
-    if (DO_K && b >= 4) {
-        // ------------------------------------------------------------------ along the row: lane = row
-        const int rw = b - 4;
+    // ---------------------------------------------------------------------- along the row: lane = row
+    auto row_phase = [&](const int rw) {
         const int row_t = rw * 32 + lane;
         const int R = tile_m * 128 + row_t;
         const uint32_t xrow = base + BT_X_OFF + row_t * 128;
@@ -189,8 +188,7 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
             }
         }
         if (R < M) sk[(size_t)R * (N >> 7) + tile_n] = s;
-        return;
-    }
+    };
 
     // ---------------------------------------------------------------------- down the rows: lane = 4 columns
     const uint32_t pbase = base + BT_X_OFF + (lane >> 4) * BT_PANEL + (b * 32) * 128 + (lane & 1) * 8;
@@ -266,13 +264,19 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
             if (Cn < N) sm[(size_t)Cn * (M >> 7) + tile_m] = s[kk];
         }
     }
+    if (DO_K) {
+        // the same four warps take the rows once the staging tile has been drained (four extra warps for this half
+        // left 3 CTAs per SM and idled while the column warps finished)
+        __syncthreads();
+        row_phase(b);
+    }
 }
 
 template <bool DO_K, bool CLAMP_F32>
 static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, uint8_t *qm, float *sm, int M, int N, cudaStream_t st)
 {
     auto kern = fp8_block128_tile_kernel<DO_K, CLAMP_F32>;
-    constexpr int ALLOC = bt_alloc(DO_K);
+    constexpr int ALLOC = BT_ALLOC;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -286,7 +290,7 @@ static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, u
     const int tiles_n = (N + 127) / 128, tiles_m = M / 128;
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, DO_K ? 256 : 128, ALLOC, st>>>(tx, qk, sk, qm, sm, M, N, tiles_n);
+    kern<<<(unsigned)num_tiles, 128, ALLOC, st>>>(tx, qk, sk, qm, sm, M, N, tiles_n);
     return (int)cudaGetLastError();
 }
 
