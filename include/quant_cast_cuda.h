@@ -321,8 +321,9 @@ int qcc_nvfp4_rht_amax(const void *x, int64_t M, int64_t N, const void *rht, int
  * G:1429-1438):
  *   (qk, sk) = qcc_nvfp4(x, outer_k)                       -- no transform
  *   (qm, sm) = nvfp4 along M of RHT(x.t()) under outer_m   -- q (N, M/2), scales over the (N, M/16) frame
- * One read of x: the four warps of a tile first transform and quantise down the rows, then quantise along the rows
- * of the same tile.  qk == sk == NULL gives the dim-m half alone.  flags: QCC_SWIZZLE, QCC_SR (key_k / key_m: device uint64[2]
+ * Round to nearest: one read of x, the four warps of a tile first transform and quantise down the rows, then quantise
+ * along the rows of the same tile.  With QCC_SR: two launches (both halves are bound by the Philox arithmetic and the
+ * fused kernel measured slower).  qk == sk == NULL gives the dim-m half alone.  flags: QCC_SWIZZLE, QCC_SR (key_k / key_m: device uint64[2]
  * each, the stream of a half indexed by the row-major position in that half's own frame).
  * Needs M % 32 == 0, N % 8 == 0, and N % 32 == 0 when the dim-k half is requested.
  */

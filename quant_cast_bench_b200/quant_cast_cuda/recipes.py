@@ -596,7 +596,7 @@ def _nvfp4_rht(x, outer_scale_k, outer_scale_m, rht, flags, key_k=None, key_m=No
     with _on_device(dev):
         L.check(lib.qcc_nvfp4_rht(_p(x), M, N, _p(outer_scale_k.contiguous()) if both else None, _p(outer_scale_m.contiguous()),
                                   _p(rht), flags, _p(key_k), _p(key_m), _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "nvfp4_rht")
-    L.launch_count += 2
+    L.launch_count += 3 if (both and flags & L.SR) else 2
     f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
     if both:
         return qk.view(f4), sk.view(e4), qm.view(f4), sm.view(e4)
