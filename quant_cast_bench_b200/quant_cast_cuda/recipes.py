@@ -219,9 +219,7 @@ def colwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
 # --------------------------------------------------------------------------------------------
 # mxfp8
 # --------------------------------------------------------------------------------------------
-def _mxfp8(x, flags, out=None):
-    """`out`: optional preallocated uint8 (qk, sk, qm, sm) (None for a direction that is not requested), each
-    contiguous with the byte count of the output it receives; used to fill slices of stacked outputs."""
+def _mxfp8(x, flags):
     lib = L.load()
     _check_x(x)
     M, N = x.shape
@@ -231,12 +229,10 @@ def _mxfp8(x, flags, out=None):
     swz = bool(flags & L.SWIZZLE)
     dev = x.device
     qk = sk = qm = sm = None
-    if out is not None:
-        qk, sk, qm, sm = out
-    elif flags & L.ROWWISE:
+    if flags & L.ROWWISE:
         qk = torch.empty((M, N), dtype=torch.uint8, device=dev)
         sk = torch.empty(blocked_shape(M, N // 32) if swz else (M, N // 32), dtype=torch.uint8, device=dev)
-    if out is None and flags & L.COLWISE:
+    if flags & L.COLWISE:
         qm = torch.empty((N, M), dtype=torch.uint8, device=dev)
         sm = torch.empty(blocked_shape(N, M // 32) if swz else (N, M // 32), dtype=torch.uint8, device=dev)
     with _on_device(dev):
