@@ -233,16 +233,40 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
+    # The K timed steps are captured into one CUDA graph (K launches of the cast through the recipe layer, outputs
+    # allocated per step from the graph's pool) and replayed once: the device then runs K back-to-back steps whatever
+    # the host is doing -- with 8 ranks on one box, host scheduling jitter between launches otherwise shows up as
+    # idle gaps on the slowest rank.  If capture is not possible the steps are issued eagerly.
+    graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        L.launch_count = 0
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(args.steps):
+                step()
+        captured_launches = L.launch_count
+        torch.cuda.synchronize()
+    except Exception as exc:   # pragma: no cover
+        print(f"bench: CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+        graph = None
+    barrier()
+    torch.cuda.synchronize()
     L.launch_count = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # The start event is queued behind a ~200 us device-side delay: while it runs the host enqueues the first step,
+    # The start event is queued behind a ~200 us device-side delay: while it runs the host enqueues the work,
     # so the device-timed region holds K back-to-back steps and not the host's launch latency for the first one
-    # (which cost 3 % at K = 5 and 10 % at K = 2).
+    # (which cost 3 % at K = 5 and 10 % at K = 2 when the steps were issued eagerly).
     if hasattr(torch.cuda, "_sleep"):
         torch.cuda._sleep(400_000)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    if graph is not None:
+        graph.replay()
+        L.launch_count = captured_launches
+    else:
+        for _ in range(args.steps):
+            step()
     e1.record()
     torch.cuda.synchronize()
     barrier()
@@ -303,6 +327,7 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": (value / 4987.5) if world == 1 else None,
         "dtype": "bf16->e4m3+e8m0 (fp32 scale math)", "data": "synthetic",
+        "timed_region": "one CUDA graph of K steps" if graph is not None else "K eager launches",
         "config": {"workload": WORKLOAD, "rows_per_gpu": M_STEP, "cols": N_STEP, "bytes_per_step_per_gpu": nbytes,
                    "l2": "inputs (512 MiB) and outputs (528 MiB) exceed the 126 MB L2; no flush between iterations",
                    "vs_baseline_ref": "reference CuTe kernel on one B200, 4987.5 GB/s (benchmarks/bench_results.csv:34); "

@@ -30,6 +30,20 @@ def test_reference_arm_prints_one_json_line():
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
 
 
+def test_reference_arm_under_torchrun_prints_once():
+    """N > 1: the launcher starts N processes; rank 0 alone measures and prints, the others exit 0 without work."""
+    env = dict(os.environ, NCCL_DEBUG="VERSION")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+           "--warmup", "0"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.split("\n") if ln.strip().startswith("{")]
+    assert len(lines) == 1, p.stdout[:500]
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2
+
+
 @pytest.mark.gpu
 def test_default_arm_prints_one_json_line():
     line = _run(["--steps", "3", "--warmup", "3"], 900)
