@@ -33,8 +33,24 @@ def cuda_ops():
         rowwise_fp8=R.rowwise_fp8_cuda, mxfp8=R._mxfp8, nvfp4=R._nvfp4)
 
 
+def new_amax_group(ranks=None):
+    """A process group for the amax all-reduce.  Under NCCL its stream gets high priority: the all-reduce kernel
+    becomes ready together with a cast that fills every SM, and at default priority it is scheduled only once that
+    cast's grid has drained, which puts the collective's latency (about 30 us over 8 GPUs) after the cast instead of
+    under it.  Collective: every rank of the default group must call it."""
+    if dist.get_backend() == "nccl":
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        return dist.new_group(ranks, backend="nccl", pg_options=opts)
+    return dist.new_group(ranks)
+
+
 class ShardedCaster:
+    """`group=None` with more than one rank creates the group with `new_amax_group()`, so constructing a caster is
+    then a collective call."""
+
     def __init__(self, group=None, ops=None):
+        if group is None and dist.is_initialized() and dist.get_world_size() > 1:
+            group = new_amax_group()
         self.group = group
         self.ops = ops if ops is not None else cuda_ops()
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
