@@ -61,7 +61,8 @@ int qcc_version(void);
  * bounded wait on a TMA barrier (codes 1..15), or qcc_mxfp8_grouped was given group offsets that are
  * not ascending multiples of 32 inside M (code 16; the scale buffers then hold zeros only), or a
  * transform matrix that is not diag(+-1) @ H16 / 4 was passed to one of the qcc_*rht* calls (code 17;
- * the outputs then follow the signs of its first column).  Synchronises the device. */
+ * the outputs then follow the signs of its first column), or a cast tile of qcc_fp8_colwise gave up waiting for the
+ * column maxima of its panel (code 18).  Synchronises the device. */
 int qcc_device_error(unsigned int *out);
 
 /* Number of SMs of the current device (cached per device). */
@@ -138,8 +139,11 @@ int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
                             void *stream);
 
 /* One scale per column (amax over all rows), outputs transposed: q (N, M), scale[c] for column c.
- * colwise_fp8_f, G:339-349.  workspace: N * 4 bytes of scratch (column maxima; cleared by the call).
+ * colwise_fp8_f, G:339-349.  workspace: qcc_fp8_colwise_workspace_bytes(M, N) bytes of scratch, 16-byte aligned
+ * (column maxima and the work counters of the launch; cleared by the call).  One launch: x is cut into column
+ * panels that stay in L2 between their maximum pass and their cast, so HBM sees x once.
  * Needs N % 8 == 0 and M % 16 == 0. */
+size_t qcc_fp8_colwise_workspace_bytes(int64_t M, int64_t N);
 int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *workspace,
                     size_t workspace_bytes, void *stream);
 

@@ -300,9 +300,10 @@ static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scal
 
 // ---------------------------------------------------------------------------------------------
 // colwise cast: one scale per column, transposed outputs q (N, M), scale (N, 1).
-// colwise_fp8_f G:339-349, colwise_precalc_f G:445-449.  Two passes over x: column maxima into a
-// caller-supplied scratch of N words (atomic max on the bit patterns: exact and order independent), then
-// a tile kernel that casts and transposes; for matrices that fit in L2 the second pass never reaches HBM.
+// colwise_fp8_f G:339-349, colwise_precalc_f G:445-449.  The kernels here are the two-launch form: column maxima into
+// a caller-supplied scratch of N words (atomic max on the bit patterns: exact and order independent), then a tile
+// kernel that casts and transposes.  It serves the cast with given scales and matrices too tall for the one-launch
+// form of colwise.cu, which is tried first.
 // ---------------------------------------------------------------------------------------------
 // rows per CTA of the column-maximum pass: 256 measured best at 16384^2 (211 us for both passes against 231 us
 // with 64, 128 or 512 rows)
@@ -346,32 +347,17 @@ __global__ void __launch_bounds__(CW_AMAX_THREADS) fp8_colwise_amax_kernel(const
 constexpr int CW_PANEL = 64 * 128;                // one 64-column panel of a 64-row tile
 constexpr int CW_Q_OFF = 2 * CW_PANEL;            // staging: 4 sub-tiles x 32 rows x 64 B
 constexpr int CW_BAR_OFF = CW_Q_OFF + 4 * 32 * 64;
-constexpr int CW_ALLOC = CW_BAR_OFF + 16 + 1024;
+constexpr int CW_ALLOC = CW_BAR_OFF + 32 + 1024;     // four barriers
 
-// One CTA (two warps) per 64-row x 128-column tile; warp b owns the 32-row slab b, lane = four adjacent columns.
+// One 64-row x 128-column tile by one CTA of two warps; warp b owns the 32-row slab b, lane = four adjacent columns.
 // PRECALC: per-column scale given, true division (G:448); otherwise scale = f(column amax), multiply by 1/scale.
+// The caller has issued the two TMA loads of the tile on `bar`; `parity` is the phase to wait for.
 template <int FMT, bool PRECALC>
-__global__ void __launch_bounds__(64, 8)
-fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t *__restrict__ amax_bits,
-                        const float *__restrict__ scale_in, uint8_t *__restrict__ q, float *__restrict__ scale_out, int M,
-                        int N, int tiles_n)
+__device__ __forceinline__ void colwise_cast_tile(uint32_t base, uint64_t *bar, uint32_t parity, const uint32_t *amax_bits,
+                                                  const float *__restrict__ scale_in, uint8_t *__restrict__ q,
+                                                  float *__restrict__ scale_out, int M, int N, int tile_m, int tile_n)
 {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + CW_BAR_OFF);
-    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
     const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        mbar_init(bar, 1);
-        fence_barrier_init();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        mbar_expect_tx(bar, 2 * CW_PANEL);
-        tma_load_2d(sbase, &tm_x, bar, tile_n * 128, tile_m * 64);
-        tma_load_2d(sbase + CW_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * 64);
-    }
     float sc[4];   // multiplier (or divisor when PRECALC) of the four columns
 #pragma unroll
     for (int k = 0; k < 4; k++) {
@@ -381,13 +367,13 @@ fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t
             if (PRECALC) {
                 s = __ldg(scale_in + Cn);
             } else {
-                s = fp8_scale_from_amax<FMT>(u2f(__ldg(amax_bits + Cn)));
+                s = fp8_scale_from_amax<FMT>(u2f(__ldcg(amax_bits + Cn)));
                 if (tile_m == 0 && b == 0) scale_out[Cn] = s;
             }
         }
         sc[k] = PRECALC ? s : __fdiv_rn(1.0f, s);
     }
-    mbar_wait(bar, 0, 5u);
+    mbar_wait(bar, parity, 5u);
     const uint32_t pbase = base + (lane >> 4) * CW_PANEL + (b * 32) * 128 + (lane & 1) * 8;
     const uint32_t j = (lane & 15) >> 1;
     const uint32_t qs = base + CW_Q_OFF;
@@ -430,6 +416,31 @@ fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t
     }
 }
 
+// One CTA per tile: the cast with given scales, or the second pass of the two-launch form.
+template <int FMT, bool PRECALC>
+__global__ void __launch_bounds__(64, 8)
+fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t *__restrict__ amax_bits,
+                        const float *__restrict__ scale_in, uint8_t *__restrict__ q, float *__restrict__ scale_out, int M,
+                        int N, int tiles_n)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + CW_BAR_OFF);
+    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(bar, 2 * CW_PANEL);
+        tma_load_2d(sbase, &tm_x, bar, tile_n * 128, tile_m * 64);
+        tma_load_2d(sbase + CW_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * 64);
+    }
+    colwise_cast_tile<FMT, PRECALC>(base, bar, 0, amax_bits, scale_in, q, scale_out, M, N, tile_m, tile_n);
+}
+
 template <int FMT, bool PRECALC>
 static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scale_in, void *q, float *scale_out,
                           uint32_t *amax_bits, cudaStream_t st)
@@ -440,6 +451,11 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
     uint32_t box[2] = {64, 64};
     int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (e) return e;
+    if (!PRECALC) {
+        // one launch with the panel resident in shared memory where the shape allows it (colwise.cu)
+        const int rc = qcc_colwise_resident(x, M, N, FMT, q, scale_out, amax_bits, st);
+        if (rc != 1) return rc;
+    }
     if (!PRECALC) {
         cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)N * 4, st);
         if (ce != cudaSuccess) return (int)ce;
@@ -474,6 +490,7 @@ using namespace qcc;
 extern "C" int qcc_mxfp8_device_error(unsigned int *out);
 extern "C" int qcc_nvfp4_device_error(unsigned int *out);
 extern "C" int qcc_block128_device_error(unsigned int *out);
+extern "C" int qcc_colwise_device_error(unsigned int *out);
 
 extern "C" {
 
@@ -488,6 +505,8 @@ int qcc_device_error(unsigned int *out)
     if ((e = qcc_nvfp4_device_error(&c)) != 0) return e;
     unsigned int d = 0;
     if ((e = qcc_block128_device_error(&d)) != 0) return e;
+    c = c > d ? c : d;
+    if ((e = qcc_colwise_device_error(&d)) != 0) return e;
     c = c > d ? c : d;
     if (out) *out = a > b ? (a > c ? a : c) : (b > c ? b : c);
     return 0;
@@ -609,6 +628,13 @@ int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
                                : launch_rowwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, st);
 }
 
+size_t qcc_fp8_colwise_workspace_bytes(int64_t M, int64_t N)
+{
+    (void)M;
+    if (N <= 0) return 0;
+    return (size_t)N * 4 + 128 + 128 * (1 + (size_t)((N + 63) / 64));   // column maxima, then one counter per panel on a 128-byte line of its own
+}
+
 int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *workspace,
                     size_t workspace_bytes, void *stream)
 {
@@ -618,7 +644,7 @@ int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
     if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00 || (M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS > 65535)
         return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q) || !aligned16(workspace)) return QCC_ERR_ALIGN;
-    if (workspace_bytes < (size_t)N * 4) return QCC_ERR_WORKSPACE;
+    if (workspace_bytes < qcc_fp8_colwise_workspace_bytes(M, N)) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st)
                                : launch_colwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st);

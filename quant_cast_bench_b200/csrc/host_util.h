@@ -65,3 +65,8 @@ inline int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, c
 int launch_rht_check(const void *rht, cudaStream_t st);
 
 }  // namespace qcc
+
+// fp8 colwise cast with the panel resident in shared memory (colwise.cu).  1: the shape does not fit that form.
+int qcc_colwise_resident(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale_out, uint32_t *amax_bits,
+                         cudaStream_t st);
+

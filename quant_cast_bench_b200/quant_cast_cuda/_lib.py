@@ -35,6 +35,7 @@ SIGNATURES = {
     "qcc_fp8_tensorwise": (_int, [_vp, _i64, _vp, _int, _vp, _vp]),
     "qcc_fp8_rowwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_fp8_rowwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
+    "qcc_fp8_colwise_workspace_bytes": (_sz, [_i64, _i64]),
     "qcc_fp8_colwise": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "qcc_fp8_colwise_precalc": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
     "qcc_mxfp8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),

@@ -189,10 +189,11 @@ def colwise_fp8_cuda(x, fmt="e4m3", **kwargs):
     assert N % 8 == 0 and M % 16 == 0, f"colwise fp8 needs N % 8 == 0 and M % 16 == 0, got {M}x{N}"
     q = torch.empty((N, M), dtype=torch.uint8, device=x.device)
     s = torch.empty((N, 1), dtype=torch.float32, device=x.device)
-    ws = torch.empty(N, dtype=torch.int32, device=x.device)
+    ws_bytes = int(lib.qcc_fp8_colwise_workspace_bytes(M, N))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_colwise(_p(x), M, N, f, _p(q), _p(s), _p(ws), N * 4, _stream(x)), "fp8_colwise")
-    L.launch_count += 3
+        L.check(lib.qcc_fp8_colwise(_p(x), M, N, f, _p(q), _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise")
+    L.launch_count += 2
     return q.view(_FP8_DTYPE[f]), s
 
 
