@@ -91,7 +91,8 @@ def check(rc, what):
 
 def device_error():
     """Reads and clears the device-side error word of the current CUDA device (synchronises): 0 when no kernel
-    reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets, 17 an unsupported transform matrix."""
+    reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets, 17 an unsupported transform matrix, 18 a colwise cast
+    that gave up waiting for the column maxima of a panel."""
     v = ctypes.c_uint(0)
     check(load().qcc_device_error(ctypes.byref(v)), "device_error")
     return int(v.value)
