@@ -209,3 +209,21 @@ def test_addressing_beyond_2_31_elements():
     assert lib.qcc_mxfp8(p, big_m, N, L.ROWWISE, p, p, None, None, None) == -1          # QCC_ERR_SHAPE
     assert lib.qcc_nvfp4(p, (1 << 32) // (N // 16) + 128, N, p, 0, 0, None, p, p, None) == -1
     assert lib.qcc_fp8_block128(p, big_m, N, L.ROWWISE, p, p, None, None, None) == -1
+
+
+@pytest.mark.parametrize("config", ["c2_mxfp8_16384", "c3_nvfp4_8192", "c4_moe_131072x7168"])
+def test_fp8_colwise_full_size(config):
+    """fp8 colwise is invariant under COLUMN slabs (every column has its own scale): 128 columns of the full-size
+    outputs equal the oracle's outputs for those columns alone, all rows included."""
+    x = config_input_device(config, "cuda")
+    M, N = x.shape
+    q, s = Q.colwise_fp8_cuda(x)
+    q2, s2 = Q.colwise_fp8_cuda(x)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2), "colwise is not deterministic"
+    for c0 in (0, (N // 2 // 128) * 128, N - 128):
+        qo, so = O.colwise_fp8_f(x[:, c0:c0 + 128].contiguous().cpu())
+        assert_same_bits(q[c0:c0 + 128], qo, f"colwise q, columns {c0}..")
+        assert_same_bits(s[c0:c0 + 128], so, f"colwise scale, columns {c0}..")
+    # every column's scale by gold's formula (the division on the CPU: torch's CUDA kernel multiplies by 1/448 instead)
+    amax = x.abs().amax(dim=0).clamp(min=1e-12).float().cpu()
+    assert torch.equal(s.reshape(-1).cpu(), amax / 448.0)

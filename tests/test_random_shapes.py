@@ -89,3 +89,14 @@ def test_random_token_groups(seed):
     pt, _, po = A.pad_token_groups(x.cuda(), offs.cuda())
     same_outputs((pt,), (padded,), "padded copy")
     same_outputs((A.unpad_token_groups(pt, offs.cuda()),), (x,), "unpad")
+
+
+@pytest.mark.parametrize("shape", [(66304, 128), (66320, 64), (40000, 200), (16, 8), (9472, 1096), (148 * 7 * 64, 72)], ids=str)
+def test_colwise_tall_and_ragged(shape):
+    """fp8 colwise at the edges of its one-launch form: the tallest matrix it takes (66304 rows = 148 SMs x 7 tiles of
+    64 rows), one that is 16 rows taller (two-launch form), a last panel that is cut by the matrix edge, and row counts
+    that leave some CTAs without tiles."""
+    x = make_input(*shape, seed=shape[0] + shape[1])
+    xc = x.cuda()
+    for fmt in ("e4m3", "e5m2"):
+        same_outputs(Q.colwise_fp8_cuda(xc, fmt), O.colwise_fp8_f(x, fmt), f"colwise {fmt} {shape}")
