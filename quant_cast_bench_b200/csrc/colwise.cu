@@ -59,14 +59,20 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Waits of this kernel give up after 50 ms of wall time, and at once when any wait has given up before: a launch that
-// goes wrong ends within a fraction of a second.
+// Waits of this kernel give up after 50 ms of wall time, and at once when a wait of the same launch has given up before
+// (`abort_word`, cleared with the counters before every launch): a launch that goes wrong ends within a fraction of a
+// second.  The code of the first failure also goes to the device error word, which stays set until it is read.
 constexpr uint64_t CWR_WAIT_NS = 50ull * 1000 * 1000;
-__device__ __forceinline__ void mbar_wait_timed(uint64_t *bar, uint32_t parity, unsigned int err_code)
+__device__ __forceinline__ void give_up(uint32_t *abort_word, unsigned int err_code)
+{
+    atomicMax(abort_word, err_code);
+    atomicMax(&g_qcc_error, err_code);
+}
+__device__ __forceinline__ void mbar_wait_timed(uint64_t *bar, uint32_t parity, uint32_t *abort_word, unsigned int err_code)
 {
     const uint32_t a = smem_u32(bar);
     const uint64_t start = global_timer_ns();
-    for (;;) {
+    for (uint32_t n = 1;; n++) {
         uint32_t ok;
         asm volatile(
             "{\n.reg .pred p;\n"
@@ -76,10 +82,11 @@ __device__ __forceinline__ void mbar_wait_timed(uint64_t *bar, uint32_t parity, 
             : "r"(a), "r"(parity)
             : "memory");
         if (ok) return;
-        if (*(volatile unsigned int *)&g_qcc_error != 0) return;
+        if (n & 15) continue;                                   // a try_wait itself blocks for a while: look up rarely
+        if (*(volatile uint32_t *)abort_word != 0) return;
         if (global_timer_ns() - start > CWR_WAIT_NS) break;
     }
-    atomicMax(&g_qcc_error, err_code);
+    give_up(abort_word, err_code);
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first()
 {
@@ -109,7 +116,8 @@ __device__ __forceinline__ void fence_proxy_async_smem()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// done[32 p]: CTAs that have merged their maxima of panel p (one counter per 128-byte line: they are polled).
+// done[32 p]: CTAs that have merged their maxima of panel p (one counter per 128-byte line: they are polled);
+// done[32 np]: the launch's abort word.
 template <int FMT>
 __global__ void __launch_bounds__(CWR_THREADS, 1)
 fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *amax_bits, uint32_t *done,
@@ -122,6 +130,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
     float *s_rcp = reinterpret_cast<float *>(sbase + CWR_RCP_OFF);
     uint64_t *bar = reinterpret_cast<uint64_t *>(sbase + CWR_BAR_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t *abort_word = done + 32 * np;
     const uint64_t pol_first = l2_policy_evict_first();
 
     // this CTA: one 64-column strip of every panel, a run of row tiles of it
@@ -192,7 +201,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
                 const int bx = i & 1;
                 const int cg = lane & 7, rg = lane >> 3;
                 uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-                mbar_wait_timed(bar + bx, (uint32_t)(i >> 1) & 1u, QCC_DEVERR_COLWISE_TMA);
+                mbar_wait_timed(bar + bx, (uint32_t)(i >> 1) & 1u, abort_word, QCC_DEVERR_COLWISE_TMA);
                 const uint32_t src = base + bx * CWR_BUF_BYTES + (RW * (warp - 1) + rg) * 128;
                 for (int k = 0; k < nt; k++) {
 #pragma unroll
@@ -218,9 +227,9 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
                 if (lane == 0) {
                     const uint64_t start = global_timer_ns();
                     while (ld_acquire_u32(done + 32 * pn) < gridDim.x) {
-                        if (*(volatile unsigned int *)&g_qcc_error != 0) break;
+                        if (*(volatile uint32_t *)abort_word != 0) break;
                         if (global_timer_ns() - start > CWR_WAIT_NS) {
-                            atomicMax(&g_qcc_error, QCC_DEVERR_COLWISE_WAIT);
+                            give_up(abort_word, QCC_DEVERR_COLWISE_WAIT);
                             break;
                         }
                         __nanosleep(100);
@@ -245,7 +254,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
             const int tk = (warp - 1) >> 1, hb = (warp - 1) & 1;
             const int l16 = lane & 15, rh = lane >> 4;
             const float4 sc = *reinterpret_cast<const float4 *>(s_rcp + (p & 1) * 64 + 4 * l16);
-            mbar_wait_timed(bar + 2 + (p & 1), (uint32_t)(p >> 1) & 1u, QCC_DEVERR_COLWISE_TMA);
+            mbar_wait_timed(bar + 2 + (p & 1), (uint32_t)(p >> 1) & 1u, abort_word, QCC_DEVERR_COLWISE_TMA);
             const uint32_t slab = base + (2 + (p & 1)) * CWR_BUF_BYTES + tk * CWR_TILE_BYTES + hb * 4096;
             const uint32_t pbase = slab + (rh * 16) * 128 + (l16 & 1) * 8;
             const uint32_t j = l16 >> 1;
@@ -324,7 +333,8 @@ static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t 
 using namespace qcc;
 
 // Returns 1 when the shape does not fit the resident form (the caller then takes the two-pass form), 0 on success,
-// else an error.  amax_bits: N words followed by 128 + 128 * ceil(N / 64) bytes for the panel counters.
+// else an error.  amax_bits: N words followed by 128 + 128 * (1 + ceil(N / 64)) bytes for the panel counters and the
+// abort word.
 int qcc_colwise_resident(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale_out, uint32_t *amax_bits,
                          cudaStream_t st)
 {
@@ -339,7 +349,7 @@ int qcc_colwise_resident(const void *x, int64_t M, int64_t N, int fmt, void *q, 
     if (e) return e;
     const int np = (int)((N + 64 * strips - 1) / (64 * strips));
     uint32_t *done = (uint32_t *)(((uintptr_t)(amax_bits + N) + 127) & ~(uintptr_t)127);
-    cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)((uint8_t *)(done + 32 * np) - (uint8_t *)amax_bits), st);
+    cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)((uint8_t *)(done + 32 * (np + 1)) - (uint8_t *)amax_bits), st);
     if (ce != cudaSuccess) return (int)ce;
     return fmt == QCC_FMT_E5M2 ? launch_resident<QCC_FMT_E5M2>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, st)
                                : launch_resident<QCC_FMT_E4M3>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, st);
