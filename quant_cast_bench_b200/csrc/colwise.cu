@@ -325,7 +325,12 @@ static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t 
     uint8_t *qp = (uint8_t *)q;
     int Mi = (int)M, Ni = (int)N;
     void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np};
-    return (int)cudaLaunchCooperativeKernel((const void *)kern, dim3((unsigned)grid), dim3(CWR_THREADS), args, CWR_ALLOC, st);
+    const cudaError_t ce = cudaLaunchCooperativeKernel((const void *)kern, dim3((unsigned)grid), dim3(CWR_THREADS), args, CWR_ALLOC, st);
+    if (ce == cudaErrorCooperativeLaunchTooLarge) {         // fewer SMs available than the device reports: two-launch form
+        cudaGetLastError();
+        return 1;
+    }
+    return (int)ce;
 }
 
 }  // namespace qcc
