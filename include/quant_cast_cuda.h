@@ -140,8 +140,9 @@ int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
 
 /* One scale per column (amax over all rows), outputs transposed: q (N, M), scale[c] for column c.
  * colwise_fp8_f, G:339-349.  workspace: qcc_fp8_colwise_workspace_bytes(M, N) bytes of scratch, 16-byte aligned
- * (column maxima and the work counters of the launch; cleared by the call).  One launch: x is cut into column
- * panels that stay in L2 between their maximum pass and their cast, so HBM sees x once.
+ * (column maxima and the panel counters of the launch; cleared by the call).  One persistent launch: x is cut into
+ * column panels that stay in L2 between their maximum pass and their cast, so HBM sees x once; matrices with more
+ * than 448 rows per SM (66304 rows on 148 SMs) take two launches and read x twice.
  * Needs N % 8 == 0 and M % 16 == 0. */
 size_t qcc_fp8_colwise_workspace_bytes(int64_t M, int64_t N);
 int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *workspace,
