@@ -7,11 +7,11 @@
 // tiles of one 64-column strip of every panel, and per step i
 //     1. reduces its tiles of panel i (TMA loads from HBM, two buffers) to 64 column maxima, which warp 0 merges into
 //        the global maxima (64 atomics per CTA) before it adds one to the panel's counter;
-//     2. casts its tiles of panel i - CWR_LAG (TMA loads again, now L2 hits, two more buffers) with the final maxima,
+//     2. casts its tiles of panel i - lag (TMA loads again, now L2 hits, two more buffers) with the final maxima,
 //        transposes them in place and writes them out;
 //     3. issues the loads of both streams two steps ahead.
 // A signal takes 2 to 3 us from one SM through L2 to all others, longer than a step (about 2 us); with the cast
-// CWR_LAG steps behind the maxima, the counter a cast depends on was completed long before, and the wait for it
+// lag = 4 or 5 steps behind the maxima, the counter a cast depends on was completed long before, and the wait for it
 // (bounded) costs nothing.  That wait, the read of the final maxima and their turn into reciprocal scales are done a
 // step ahead by a warp of their own, so that the cast warps never see an L2 latency.
 //
@@ -28,7 +28,9 @@ namespace qcc {
 
 constexpr int CWR_TILES = 7;                       // 64 x 64 tiles per CTA and panel
 constexpr int CWR_NBUF = 4;                        // two buffers for the maxima stream, two for the cast stream
-constexpr int CWR_LAG = 5;                         // a panel is cast this many steps after its maxima (measured best of 2..7)
+constexpr int CWR_LAG = 5;                         // a panel is cast this many steps after its maxima (measured best of 2..7
+                                                   // at 64 panels; 4 with fewer than 40 panels); the load prologue needs >= 2
+static_assert(CWR_LAG >= 3, "the cast stream's first loads are issued in steps lag - 2 and lag - 1");
 constexpr int CWR_TILE_BYTES = 64 * 128;
 constexpr int CWR_BUF_BYTES = CWR_TILES * CWR_TILE_BYTES;
 constexpr int CWR_WARPS = 16;
@@ -121,7 +123,7 @@ __device__ __forceinline__ void fence_proxy_async_smem()
 template <int FMT>
 __global__ void __launch_bounds__(CWR_THREADS, 1)
 fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *amax_bits, uint32_t *done,
-                            uint8_t *__restrict__ q, float *__restrict__ scale_out, int M, int N, int strips, int np)
+                            uint8_t *__restrict__ q, float *__restrict__ scale_out, int M, int N, int strips, int np, int lag)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -160,8 +162,8 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
     if (tid == 32)
         for (int p = 0; p < 2 && p < np; p++) issue(p, p);
 
-    for (int i = 0; i < np + CWR_LAG; i++) {
-        const int p = i - CWR_LAG;                                              // the panel cast in this step
+    for (int i = 0; i < np + lag; i++) {
+        const int p = i - lag;                                              // the panel cast in this step
         const int col0_x = (i * strips + strip) * 64, col0_c = (p * strips + strip) * 64;
         const bool have_x = i < np && col0_x < N && nt > 0;
         const bool have_c = p >= 0 && col0_c < N && nt > 0;
@@ -220,7 +222,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
             named_barrier(1, 32 * (1 + CWR_XWARPS));                            // also: warp 0 has read the scratch of two steps ago
         }
         if (warp == CWR_WARPS - 1) {
-            // ---- scale warp: when the counter of the panel cast in the NEXT step (signalled CWR_LAG - 1 steps ago) shows
+            // ---- scale warp: when the counter of the panel cast in the NEXT step (signalled lag - 1 steps ago) shows
             //      every CTA, turn its 64 final maxima into reciprocal scales for the cast warps
             const int pn = p + 1, col0_n = (pn * strips + strip) * 64;
             if (pn >= 0 && pn < np && col0_n < N && nt > 0) {
@@ -324,7 +326,8 @@ static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t 
     }
     uint8_t *qp = (uint8_t *)q;
     int Mi = (int)M, Ni = (int)N;
-    void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np};
+    int lag = np >= 40 ? CWR_LAG : CWR_LAG - 1;               // few panels: the steps that only drain the pipeline weigh more
+    void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np, &lag};
     const cudaError_t ce = cudaLaunchCooperativeKernel((const void *)kern, dim3((unsigned)grid), dim3(CWR_THREADS), args, CWR_ALLOC, st);
     if (ce == cudaErrorCooperativeLaunchTooLarge) {         // fewer SMs available than the device reports: two-launch form
         cudaGetLastError();
