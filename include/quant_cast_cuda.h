@@ -46,6 +46,19 @@ extern "C" {
 #define QCC_AMAX_FP8_SCALE 1  /* max(amax, bf16(1e-12)) / fp8_max     G:1179-1183        */
 #define QCC_AMAX_NVFP4_SCALE 2 /* amax / (448 * 6)                    G:1243-1246        */
 
+/* OR'ed into `mode` of qcc_amax_bf16: the workspace was prepared by qcc_amax_workspace_init and has since been used
+ * by amax calls only, issued in stream order -> one launch instead of two */
+#define QCC_AMAX_ONE_LAUNCH 0x100
+
+/* where a cast takes its per-tensor scale from (library internal; see qcc_*_from_amax) */
+#define QCC_SRC_SCALE 0 /* a device fp32 holding the scale                                                   */
+#define QCC_SRC_AMAX 1  /* a device fp32 holding the raw amax; the cast forms the scale in its prologue      */
+
+/* amax exchange between the GPUs of one box */
+#define QCC_XCHG_MAX_RANKS 16
+#define QCC_XCHG_STATE_BYTES 1024
+#define QCC_XCHG_HANDLE_BYTES 64
+
 /* argument errors */
 #define QCC_ERR_SHAPE -1     /* a dimension violates the divisibility the cast needs */
 #define QCC_ERR_ALIGN -2     /* a pointer is not 16-byte aligned                     */
@@ -82,10 +95,17 @@ int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pi
 /* Bytes of scratch qcc_amax_bf16 needs (independent of n). */
 size_t qcc_amax_workspace_bytes(void);
 
+/* Clears a workspace (one small memset on `stream`) so that it can be used with QCC_AMAX_ONE_LAUNCH.  Every such
+ * call leaves the workspace cleared again, so this is needed once per workspace, not once per call.  Calls that
+ * share a workspace must not overlap on the GPU. */
+int qcc_amax_workspace_init(void *workspace, size_t workspace_bytes, void *stream);
+
 /*
  * out[0] = f(max |x[i]|) over n bf16 values, f selected by `mode` (QCC_AMAX_*), `fmt` used by
- * QCC_AMAX_FP8_SCALE only.  Two launches: per-CTA partial maxima into `workspace`, then a
- * one-CTA finish.  The maximum is exact (a bf16 magnitude), so any partition of x gives the same
+ * QCC_AMAX_FP8_SCALE only.  Two launches: per-CTA partial maxima into `workspace` (any contents), then a
+ * one-CTA finish.  With mode | QCC_AMAX_ONE_LAUNCH: one launch of a one-shot grid whose CTAs merge their maxima
+ * into one word of the (prepared) workspace; the CTA that finishes last writes out[0].  The maximum is exact
+ * (a bf16 magnitude), so any partition of x gives the same
  * result.  Replaces float8_tensorwise_scale (G:1179-1183) and nvfp4_gs_scale (G:1243-1246).
  */
 int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace,
@@ -122,11 +142,62 @@ int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *ou
 int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * amax exchange: the tensor-wide amax of a row-sharded tensor, one process per GPU of one box
+ *
+ * (No counterpart in the reference, which is single GPU.  It does the job of ncclAllReduce(MAX) on the per-shard
+ * amax over peer memory, without a collective call and without a second stream.)
+ *
+ * A PRODUCER (qcc_amax_bf16_xchg, or the cast qcc_mxfp8_amax_xchg, which has every block maximum in registers anyway)
+ * leaves the shard's amax in the rank's own exchange state; its CTAs wait for nothing.  qcc_xchg_resolve, one warp
+ * launched next on the same stream, stores that value, tagged with the exchange number, into every rank's state over
+ * NVLink (plain 8-byte peer stores), reads the `world` tagged values from its own memory, waits for any that have not
+ * arrived (bounded by the state's timeout; code 19 of qcc_device_error), and writes f(global amax) for the casts that
+ * follow.  The maximum is exact and order independent, so every rank derives the bits a single GPU would.
+ *
+ * Rules: every rank owns one state of QCC_XCHG_STATE_BYTES in device memory.  Set-up, once: qcc_xchg_alloc (or own
+ * memory + qcc_xchg_state_init), qcc_xchg_ipc_export, hand the 64 handle bytes to the other ranks' processes by any
+ * host channel, qcc_xchg_ipc_open on each; states[0..world) then holds the addresses, valid on this GPU, of all
+ * ranks' states, states[rank] being the rank's own.  With several GPUs in one process the peers' states are used
+ * directly (peer access enabled by the caller).  All ranks must issue the same sequence of producing calls, each
+ * followed by one publishing resolve before the rank's next producing call, all on one stream.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qcc_xchg_ref {
+    void *const *states; /* [world] device addresses of the ranks' states as seen from this GPU */
+    int world;           /* 1..QCC_XCHG_MAX_RANKS                                             */
+    int rank;            /* this rank                                                         */
+    int publish;         /* qcc_xchg_resolve: 1 = hand this rank's amax to all ranks first (the normal call);
+                            0 = only read an exchange that was published before                */
+} qcc_xchg_ref;
+
+int qcc_xchg_alloc(void **state);   /* cudaMalloc + clear, timeout 1 s; set-up path, the only allocating call */
+int qcc_xchg_free(void *state);
+int qcc_xchg_state_init(void *state, unsigned int timeout_us, void *stream);   /* clear caller-owned memory */
+int qcc_xchg_ipc_export(void *state, void *handle /* QCC_XCHG_HANDLE_BYTES */);
+int qcc_xchg_ipc_open(const void *handle, void **peer_state);
+int qcc_xchg_ipc_close(void *peer_state);
+
+/* Producer: max |x| of this rank's shard into the rank's own state; one launch, no CTA waits for anything. */
+int qcc_amax_bf16_xchg(const void *x, int64_t n, void *state, void *stream);
+
+/* The publishing half of qcc_xchg_resolve on its own (one warp that waits for nothing; ref->publish is ignored):
+ * for driving several ranks' states from one stream, where every rank must have published before any rank waits. */
+int qcc_xchg_publish(const qcc_xchg_ref *ref, void *stream);
+
+/* out[0] = f(maximum over the ranks of the exchange), f by `mode` / `fmt` as in qcc_amax_bf16.  One warp. */
+int qcc_xchg_resolve(const qcc_xchg_ref *ref, int mode, int fmt, float *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * fp8 casts
  * ------------------------------------------------------------------------------------------- */
 
 /* q[i] = fp8(float(x[i]) * (1 / scale[0])), saturating.  float8_tensorwise_f, G:1186-1191. */
 int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream);
+
+/* The same cast from a raw amax (device fp32, e.g. max-reduced over shards): the scale
+ * max(amax, bf16(1e-12)) / fp8_max of G:1179-1183 is formed in the kernel's prologue and also written to scale_out
+ * (device, may be NULL) -- float8_tensorwise_scale's division folded into float8_tensorwise_f. */
+int qcc_fp8_tensorwise_from_amax(const void *x, int64_t n, const float *amax, int fmt, void *q, float *scale_out,
+                                 void *stream);
 
 /* One scale per row: scale[r] = max(amax_r, bf16(1e-12)) / fp8_max, q = fp8(x * (1 / scale[r])).
  * rowwise_fp8_f, G:301-307.  q may be NULL to get the scales only (rowwise_precalc_scale,
@@ -198,6 +269,16 @@ int qcc_amax_block128x128(const void *x, int64_t M, int64_t N, int mode, float *
  */
 int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
               void *stream);
+
+/* The rowwise cast of qcc_mxfp8 (flags: QCC_ROWWISE, optionally QCC_SWIZZLE / QCC_FLOOR) that also delivers
+ * amax_out[0] = max |x| (raw fp32) from the same read of x -- for a tensor that is cast to mxfp8 and to nvfp4
+ * (nvfp4_gs_scale G:1243-1246 needs the amax) this saves the separate amax pass.  workspace: as for qcc_amax_bf16
+ * with QCC_AMAX_ONE_LAUNCH.  The _xchg form is a producer of the rank's amax exchange instead: the amax goes into
+ * `state`, and its CTAs wait for nothing (the form above takes a ticket per CTA so that the last one can write
+ * amax_out). */
+int qcc_mxfp8_amax(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, float *amax_out,
+                   void *workspace, size_t workspace_bytes, void *stream);
+int qcc_mxfp8_amax_xchg(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *state, void *stream);
 
 /*
  * E independent (M, N) matrices stacked in x, e.g. per-expert weights (the 3-D branch of quantize_tensor,
@@ -277,6 +358,12 @@ int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const 
  */
 int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
               const uint64_t *philox_key, void *q, void *s, void *stream);
+
+/* qcc_nvfp4 (one outer scale for the tensor, round to nearest; flags: QCC_SWIZZLE or 0) from a raw amax (device
+ * fp32): outer = amax / 2688 (nvfp4_gs_scale G:1243-1246) is formed in the kernel's prologue and also written to
+ * outer_out (device, may be NULL). */
+int qcc_nvfp4_from_amax(const void *x, int64_t M, int64_t N, const float *amax, int flags, void *q, void *s,
+                        float *outer_out, void *stream);
 
 /*
  * Transposed: the outputs that the rowwise cast gives on x.t().contiguous() (the call of

@@ -6,6 +6,7 @@
 // rowwise_fp8_f G:301-307, rowwise_precalc_f G:396-399, nvfp4_gs_scale G:1243-1246.
 #include "common.cuh"
 #include "host_util.h"
+#include "xchg.cuh"
 
 #ifndef QCC_AMAX_LD
 #define QCC_AMAX_LD ld_nc_v4
@@ -17,7 +18,6 @@ namespace qcc {
 // amax: per-CTA partial maxima, then a one-CTA finish
 // ---------------------------------------------------------------------------------------------
 constexpr int AMAX_THREADS = 256;
-constexpr int AMAX_MAX_CTAS = 2048;
 
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v)
 {
@@ -107,6 +107,51 @@ __global__ void scale_from_amax_kernel(const float *__restrict__ amax, int mode,
     out[0] = amax_finish(amax[0], mode, fmt);
 }
 
+// One launch.  A one-shot grid: every CTA reduces its own AMAX1_U x 4 KB piece of x and merges the result into one
+// word (atomic max on the bits of a non-negative float, skipped when the word already holds as much).
+// XCHG false: the CTAs also take a ticket and the one that draws the last ticket writes out[0] and leaves the two
+// control words (ctl[0] = ticket, ctl[1] = running maximum) zero for the next call.
+// XCHG true: the word is the accumulator of this rank's amax exchange (ctl = the exchange state); the first
+// consumer publishes it, so the CTAs wait for nothing.
+#ifndef QCC_AMAX1_U
+#define QCC_AMAX1_U 8
+#endif
+constexpr int AMAX1_U = QCC_AMAX1_U;
+
+template <bool XCHG>
+__global__ void __launch_bounds__(AMAX_THREADS) amax_oneshot_kernel(const uint16_t *__restrict__ x, int64_t n,
+                                                                   uint32_t *__restrict__ ctl, int mode, int fmt,
+                                                                   float *__restrict__ out)
+{
+    uint32_t seen = 0;
+    if (XCHG) seen = xchg_producer_begin(ctl);
+    const int64_t nvec = n >> 3;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    const int64_t base = (int64_t)blockIdx.x * (AMAX_THREADS * AMAX1_U) + threadIdx.x;
+    uint4 v[AMAX1_U];
+#pragma unroll
+    for (int u = 0; u < AMAX1_U; u++) {
+        const int64_t i = base + (int64_t)u * AMAX_THREADS;
+        v[u] = i < nvec ? QCC_AMAX_LD(xv + i) : make_uint4(0, 0, 0, 0);
+    }
+    uint32_t acc0 = 0, acc1 = 0;
+#pragma unroll
+    for (int u = 0; u < AMAX1_U; u++) {
+        acc0 = absmax2_acc(absmax2_acc(acc0, v[u].x), v[u].y);
+        acc1 = absmax2_acc(absmax2_acc(acc1, v[u].z), v[u].w);
+    }
+    uint32_t m = f2u(hmax_halves_f32(absmax2(acc0, acc1)));
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (int64_t t = nvec << 3; t < n; t++) m = max(m, ((uint32_t)x[t] & 0x7FFFu) << 16);
+    __shared__ uint32_t s[AMAX_THREADS / 32];
+    if (XCHG) {
+        xchg_producer_merge(ctl, m, seen, s);
+        return;
+    }
+    if (!cta_max_ticket(m, ctl, s)) return;
+    if (threadIdx.x == 0 && out) out[0] = amax_finish(u2f(m), mode, fmt);
+}
+
 // ---------------------------------------------------------------------------------------------
 // tensorwise cast: 16 elements per thread per step (two 16-byte loads, one 16-byte store)
 // ---------------------------------------------------------------------------------------------
@@ -132,12 +177,13 @@ __device__ __forceinline__ uint2 cast8(uint4 a, float inv)
 constexpr int TW_THREADS = 256;
 constexpr int TW_UNROLL = 1;  // 16-element groups per thread (1 measured best: 7.0 TB/s)
 
-template <int FMT>
+// SRC: where the scale comes from.  QCC_SRC_SCALE: scale[0] is the scale; QCC_SRC_AMAX: scale[0] is a raw amax, the
+// kernel forms max(amax, bf16(1e-12)) / fp8_max itself and its first CTA writes the scale to scale_out.
+template <int FMT, int SRC>
 __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16_t *__restrict__ x, int64_t n,
                                                                    const float *__restrict__ scale,
-                                                                   uint8_t *__restrict__ q)
+                                                                   float *__restrict__ scale_out, uint8_t *__restrict__ q)
 {
-    const float inv = __fdiv_rn(1.0f, __ldg(scale));
     const int64_t ngrp = n >> 4;  // groups of 16 elements
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint4 *qv = reinterpret_cast<uint4 *>(q);
@@ -148,6 +194,12 @@ __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16
         int64_t g = base + (int64_t)u * TW_THREADS;
         if (g < ngrp) { a[u] = ld_nc_v4(xv + 2 * g); b[u] = ld_nc_v4(xv + 2 * g + 1); }
     }
+    float sc = __ldg(scale);
+    if (SRC == QCC_SRC_AMAX) {
+        sc = fp8_scale_from_amax<FMT>(sc);
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) scale_out[0] = sc;
+    }
+    const float inv = __fdiv_rn(1.0f, sc);
 #pragma unroll
     for (int u = 0; u < TW_UNROLL; u++) {
         int64_t g = base + (int64_t)u * TW_THREADS;
@@ -491,6 +543,7 @@ extern "C" int qcc_mxfp8_device_error(unsigned int *out);
 extern "C" int qcc_nvfp4_device_error(unsigned int *out);
 extern "C" int qcc_block128_device_error(unsigned int *out);
 extern "C" int qcc_colwise_device_error(unsigned int *out);
+extern "C" int qcc_xchg_device_error(unsigned int *out);
 
 extern "C" {
 
@@ -508,6 +561,8 @@ int qcc_device_error(unsigned int *out)
     c = c > d ? c : d;
     if ((e = qcc_colwise_device_error(&d)) != 0) return e;
     c = c > d ? c : d;
+    if ((e = qcc_xchg_device_error(&d)) != 0) return e;
+    c = c > d ? c : d;
     if (out) *out = a > b ? (a > c ? a : c) : (b > c ? b : c);
     return 0;
 }
@@ -523,17 +578,43 @@ int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pi
                                   to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice, (cudaStream_t)stream);
 }
 
-size_t qcc_amax_workspace_bytes(void) { return (size_t)AMAX_MAX_CTAS * sizeof(uint32_t); }
+size_t qcc_amax_workspace_bytes(void) { return (size_t)(AMAX_MAX_CTAS + 64) * sizeof(uint32_t); }
+
+int qcc_amax_workspace_init(void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!workspace) return QCC_ERR_ARG;
+    if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
+    return (int)cudaMemsetAsync(workspace, 0, qcc_amax_workspace_bytes(), (cudaStream_t)stream);
+}
+
+static int amax_oneshot_grid(int64_t n, unsigned *grid)
+{
+    const int64_t per_cta = (int64_t)AMAX_THREADS * AMAX1_U;
+    const int64_t want = ((n >> 3) + per_cta - 1) / per_cta;
+    if (want > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    *grid = (unsigned)(want < 1 ? 1 : want);
+    return 0;
+}
 
 int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void *workspace, size_t workspace_bytes,
                   void *stream)
 {
+    const bool one_launch = (mode & QCC_AMAX_ONE_LAUNCH) != 0;
+    mode &= ~QCC_AMAX_ONE_LAUNCH;
     if (!x || !out || !workspace || n < 0) return QCC_ERR_ARG;
     if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
         return QCC_ERR_ARG;
     if (!aligned16(x)) return QCC_ERR_ALIGN;
     if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
+    if (one_launch) {
+        unsigned grid1 = 0;
+        int rc = amax_oneshot_grid(n, &grid1);
+        if (rc) return rc;
+        amax_oneshot_kernel<false><<<grid1, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, (uint32_t *)workspace + AMAX_MAX_CTAS,
+                                                                  mode, fmt, out);
+        return (int)cudaGetLastError();
+    }
     int64_t want = ((n >> 3) + AMAX_THREADS * AMAX_U - 1) / (AMAX_THREADS * AMAX_U);
     int64_t cap = (int64_t)sm_count() * AMAX_CTAS_PER_SM;
     if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
@@ -542,6 +623,18 @@ int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>((const uint32_t *)workspace, grid, mode, fmt, out);
+    return (int)cudaGetLastError();
+}
+
+int qcc_amax_bf16_xchg(const void *x, int64_t n, void *state, void *stream)
+{
+    if (!x || !state || n < 0) return QCC_ERR_ARG;
+    if (!aligned16(x)) return QCC_ERR_ALIGN;
+    unsigned grid1 = 0;
+    int rc = amax_oneshot_grid(n, &grid1);
+    if (rc) return rc;
+    amax_oneshot_kernel<true><<<grid1, AMAX_THREADS, 0, (cudaStream_t)stream>>>((const uint16_t *)x, n, static_cast<uint32_t *>(state),
+                                                                                QCC_AMAX_RAW, QCC_FMT_E4M3, nullptr);
     return (int)cudaGetLastError();
 }
 
@@ -587,21 +680,40 @@ int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *
     return (int)cudaGetLastError();
 }
 
-int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream)
+static int fp8_tensorwise_entry(const void *x, int64_t n, const float *src, int src_kind, int fmt, void *q, float *scale_out,
+                               void *stream)
 {
-    if (n == 0) return 0;
-    if (!x || !scale || !q || n < 0) return QCC_ERR_ARG;
+    if (!src) return QCC_ERR_ARG;
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
+    if (n == 0 && src_kind == QCC_SRC_SCALE) return 0;
+    if (!x || !q || n < 0) return QCC_ERR_ARG;
     if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t per_cta = (int64_t)TW_THREADS * TW_UNROLL * 16;
     int64_t grid = (n + per_cta - 1) / per_cta;
     if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    if (fmt == QCC_FMT_E5M2)
-        fp8_tensorwise_kernel<QCC_FMT_E5M2><<<(unsigned)grid, TW_THREADS, 0, st>>>((const uint16_t *)x, n, scale, (uint8_t *)q);
-    else
-        fp8_tensorwise_kernel<QCC_FMT_E4M3><<<(unsigned)grid, TW_THREADS, 0, st>>>((const uint16_t *)x, n, scale, (uint8_t *)q);
+    if (grid < 1) grid = 1;
+    const uint16_t *xp = (const uint16_t *)x;
+#define QCC_TW(FMT_, SRC_) fp8_tensorwise_kernel<FMT_, SRC_><<<(unsigned)grid, TW_THREADS, 0, st>>>(xp, n, src, scale_out, (uint8_t *)q)
+    if (fmt == QCC_FMT_E5M2) {
+        if (src_kind == QCC_SRC_SCALE) QCC_TW(QCC_FMT_E5M2, QCC_SRC_SCALE); else QCC_TW(QCC_FMT_E5M2, QCC_SRC_AMAX);
+    } else {
+        if (src_kind == QCC_SRC_SCALE) QCC_TW(QCC_FMT_E4M3, QCC_SRC_SCALE); else QCC_TW(QCC_FMT_E4M3, QCC_SRC_AMAX);
+    }
+#undef QCC_TW
     return (int)cudaGetLastError();
+}
+
+int qcc_fp8_tensorwise_from_amax(const void *x, int64_t n, const float *amax, int fmt, void *q, float *scale_out, void *stream)
+{
+    return fp8_tensorwise_entry(x, n, amax, QCC_SRC_AMAX, fmt, q, scale_out, stream);
+}
+
+int qcc_fp8_tensorwise(const void *x, int64_t n, const float *scale, int fmt, void *q, void *stream)
+{
+    if (n == 0) return 0;
+    if (!scale) return QCC_ERR_ARG;
+    return fp8_tensorwise_entry(x, n, scale, QCC_SRC_SCALE, fmt, q, nullptr, stream);
 }
 
 int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale, void *stream)

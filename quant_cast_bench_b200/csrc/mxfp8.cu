@@ -26,6 +26,7 @@
 // G:1000-1037 (swizzled variants G:1051-1053, G:1092-1094, G:1134-1139), e8m0 math G:494-558.
 #include "common.cuh"
 #include "host_util.h"
+#include "xchg.cuh"
 
 namespace qcc {
 
@@ -83,15 +84,26 @@ __device__ __forceinline__ void stream_scale_store(uint8_t *__restrict__ s, uint
     }
 }
 
-template <bool SWZ, bool FLOOR>
+// Where the cast also delivers max |x| (every block maximum is in registers anyway).  AMAX 1: ctl = two zeroed
+// control words (ticket, running maximum) and out receives the raw amax from the CTA that finishes last.  AMAX 2:
+// ctl = this rank's amax-exchange state, whose accumulator the CTAs merge into; the first consumer publishes it.
+struct AmaxSink {
+    uint32_t *ctl;
+    float *out;
+};
+
+// AMAX: 0 the cast alone; 1 / 2 also the tensor's amax (see AmaxSink).
+template <bool SWZ, bool FLOOR, int AMAX = 0>
 __global__ void __launch_bounds__(RS_THREADS)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
-                            uint8_t *__restrict__ q, uint8_t *__restrict__ s, GroupTables g)
+                            uint8_t *__restrict__ q, uint8_t *__restrict__ s, GroupTables g, AmaxSink sink)
 {
     const int32_t *__restrict__ row_map = g.row_map;
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint4 *qv = reinterpret_cast<uint4 *>(q);
     const uint32_t base = blockIdx.x * (RS_THREADS * RS_UNROLL) + threadIdx.x;
+    uint32_t seen = 0;
+    if (AMAX == 2) seen = xchg_producer_begin(sink.ctl);
     uint4 c[RS_UNROLL][4];
 #pragma unroll
     for (int u = 0; u < RS_UNROLL; u++) {
@@ -112,11 +124,14 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             for (int i = 0; i < 4; i++) c[u][i] = make_uint4(0, 0, 0, 0);
         }
     }
+    uint32_t mx = 0;
 #pragma unroll
     for (int u = 0; u < RS_UNROLL; u++) {
         const uint32_t bi = base + u * RS_THREADS;
         const bool ok = bi < nblocks;
-        const uint32_t e = e8m0_from_amax<FLOOR>(amax_of_block(c[u]));
+        const float am = amax_of_block(c[u]);
+        if (AMAX) mx = max(mx, f2u(am));          // non-negative floats order like their bits
+        const uint32_t e = e8m0_from_amax<FLOOR>(am);
         const float rcp = e8m0_recip<FLOOR>(e);
         uint4 o0, o1;
         quant_row_block(c[u], rcp, o0, o1);
@@ -125,6 +140,14 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             __stcs(qv + 2 * (size_t)bi + 1, o1);
         }
         stream_scale_store<SWZ>(s, bi, ok, e, nb, div_nb, row_map);
+    }
+    if (AMAX) {
+        __shared__ uint32_t red[RS_THREADS / 32];
+        if (AMAX == 2) {
+            xchg_producer_merge(sink.ctl, mx, seen, red);
+        } else if (cta_max_ticket(mx, sink.ctl, red)) {
+            if (threadIdx.x == 0 && sink.out) sink.out[0] = u2f(mx);
+        }
     }
 }
 
@@ -486,8 +509,10 @@ using namespace qcc;
 extern "C" int qcc_mxfp8_device_error(unsigned int *out) { return read_clear_device_error(out); }
 
 static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *qm, void *sm,
-                       void *stream, GroupTables g)
+                       void *stream, GroupTables g, int amax_mode = 0, const AmaxSink *sink_p = nullptr)
 {
+    AmaxSink sink{};
+    if (amax_mode) sink = *sink_p;
     const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
     if (M == 0 || N == 0) return 0;
     if (!x || (!row && !col) || (flags & ~(QCC_ROWWISE | QCC_COLWISE | QCC_SWIZZLE | QCC_FLOOR | QCC_BLOCK32))) return QCC_ERR_ARG;
@@ -534,13 +559,17 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
         const unsigned grid = (nblocks + RS_THREADS * RS_UNROLL - 1) / (RS_THREADS * RS_UNROLL);
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
+#define QCC_RS(SWZ_, FL_, AM_) \
+    mxfp8_rowwise_stream_kernel<SWZ_, FL_, AM_><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g, sink)
+#define QCC_RS_AM(SWZ_, FL_) \
+    do { if (amax_mode == 0) QCC_RS(SWZ_, FL_, 0); else if (amax_mode == 1) QCC_RS(SWZ_, FL_, 1); else QCC_RS(SWZ_, FL_, 2); } while (0)
         if (swz) {
-            if (fl) mxfp8_rowwise_stream_kernel<true, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
-            else mxfp8_rowwise_stream_kernel<true, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
+            if (fl) QCC_RS_AM(true, true); else QCC_RS_AM(true, false);
         } else {
-            if (fl) mxfp8_rowwise_stream_kernel<false, true><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
-            else mxfp8_rowwise_stream_kernel<false, false><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g);
+            if (fl) QCC_RS_AM(false, true); else QCC_RS_AM(false, false);
         }
+#undef QCC_RS_AM
+#undef QCC_RS
         return (int)cudaGetLastError();
     }
 
@@ -580,6 +609,32 @@ extern "C" int qcc_mxfp8(const void *x, int64_t M, int64_t N, int flags, void *q
                          void *stream)
 {
     return mxfp8_entry(x, M, N, flags, qk, sk, qm, sm, stream, GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0});
+}
+
+// The rowwise cast that also delivers max |x| (raw, fp32): x is read once for both.  workspace: as for qcc_amax_bf16
+// with QCC_AMAX_ONE_LAUNCH (prepared by qcc_amax_workspace_init).
+extern "C" int qcc_mxfp8_amax(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, float *amax_out,
+                              void *workspace, size_t workspace_bytes, void *stream)
+{
+    if ((flags & (QCC_COLWISE | QCC_BLOCK32)) || !(flags & QCC_ROWWISE) || !amax_out || !workspace) return QCC_ERR_ARG;
+    if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
+    if (M <= 0 || N <= 0) return QCC_ERR_SHAPE;
+    AmaxSink sink{};
+    sink.ctl = static_cast<uint32_t *>(workspace) + AMAX_MAX_CTAS;
+    sink.out = amax_out;
+    return mxfp8_entry(x, M, N, flags, qk, sk, nullptr, nullptr, stream,
+                       GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0}, 1, &sink);
+}
+
+// The same as a producer of this rank's amax exchange: the amax goes into the exchange state's accumulator.
+extern "C" int qcc_mxfp8_amax_xchg(const void *x, int64_t M, int64_t N, int flags, void *qk, void *sk, void *state, void *stream)
+{
+    if ((flags & (QCC_COLWISE | QCC_BLOCK32)) || !(flags & QCC_ROWWISE) || !state) return QCC_ERR_ARG;
+    if (M <= 0 || N <= 0) return QCC_ERR_SHAPE;
+    AmaxSink sink{};
+    sink.ctl = static_cast<uint32_t *>(state);
+    return mxfp8_entry(x, M, N, flags, qk, sk, nullptr, nullptr, stream,
+                       GroupTables{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0}, 2, &sink);
 }
 
 // E independent (M, N) matrices stacked in x (per-expert weights): one launch per matrix, issued from here so that

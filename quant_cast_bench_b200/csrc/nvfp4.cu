@@ -57,13 +57,25 @@ __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer,
 constexpr int NV_THREADS = 256;
 constexpr int NV_UNROLL = 2;
 
+// The per-tensor outer scale.  SRC QCC_SRC_SCALE: outer[0] is the scale; QCC_SRC_AMAX: outer[0] is the raw amax and
+// the scale is amax / 2688 (nvfp4_gs_scale G:1243-1246, folded into the cast), which the first CTA also writes to
+// outer_out.
+template <int SRC>
+__device__ __forceinline__ float nvfp4_outer_of_cta(const float *__restrict__ outer, float *__restrict__ outer_out)
+{
+    if (SRC == QCC_SRC_SCALE) return __ldg(outer);
+    const float o = __fdiv_rn(__ldg(outer), 2688.0f);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && outer_out) outer_out[0] = o;
+    return o;
+}
+
 // OUTER: 0 one outer scale for the tensor, 1 one per row (per token, G:1567-1571), 2 one per 128x128 block
-// (nvfp4_blocked_outer_f G:1609-1634; outer is then the (M/128, N/128) grid)
-template <bool SWZ, bool SR, int OUTER>
+// (nvfp4_blocked_outer_f G:1609-1634; outer is then the (M/128, N/128) grid); SRC (OUTER 0 only): see above
+template <bool SWZ, bool SR, int OUTER, int SRC = QCC_SRC_SCALE>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                      const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
-                     uint8_t *__restrict__ s)
+                     uint8_t *__restrict__ s, float *__restrict__ outer_out)
 {
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint2 *qv = reinterpret_cast<uint2 *>(q);
@@ -73,10 +85,6 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
     // (a shared-memory table of the second division, as the transposed kernel uses, measured slower here:
     // its loads compete with the scale shuffles for the same issue queue)
     const float *lut = nullptr;
-    if (OUTER == 0) {
-        o_all = __ldg(outer);
-        inv_all = __fdiv_rn(1.0f, o_all);
-    }
     const uint32_t base = blockIdx.x * (NV_THREADS * NV_UNROLL) + threadIdx.x;
     uint4 a[NV_UNROLL], b[NV_UNROLL];
 #pragma unroll
@@ -88,6 +96,10 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         } else {
             a[u] = b[u] = make_uint4(0, 0, 0, 0);
         }
+    }
+    if (OUTER == 0) {
+        o_all = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+        inv_all = __fdiv_rn(1.0f, o_all);
     }
     // every lane runs the whole body (the shuffles below need the full warp); stores are predicated
 #pragma unroll
@@ -121,20 +133,22 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
 // contiguous input bytes (four 16-byte loads that share sectors through L1), one 16-byte store of packed nibbles,
 // and one blocked-offset computation per four scale bytes (a lane pair) instead of per byte.  (Four blocks per
 // thread measured 33 % slower: 128-byte strides between lanes defeat coalescing.)
+template <int SRC>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint32_t nb, FastDiv32 div_np,
-                          const float *__restrict__ outer, uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+                          const float *__restrict__ outer, uint8_t *__restrict__ q, uint8_t *__restrict__ s,
+                          float *__restrict__ outer_out)
 {
     const uint32_t pi = blockIdx.x * NV_THREADS + threadIdx.x;   // blocks 2 pi and 2 pi + 1 of the flat stream
     const bool ok = pi < npairs;
-    const float o = __ldg(outer);
-    const float inv = __fdiv_rn(1.0f, o);
     uint4 c[4] = {};
     if (ok) {
         const uint4 *p = reinterpret_cast<const uint4 *>(x) + 4 * (size_t)pi;
 #pragma unroll
         for (int i = 0; i < 4; i++) c[i] = ld_v4(p + i);
     }
+    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+    const float inv = __fdiv_rn(1.0f, o);
     uint2 p0, p1;
     const uint32_t b0 = nvfp4_quant16<false>(c[0], c[1], o, inv, nullptr, 0, 0, 0, p0);
     const uint32_t b1 = nvfp4_quant16<false>(c[2], c[3], o, inv, nullptr, 0, 0, 0, p1);
@@ -425,15 +439,15 @@ using namespace qcc;
 
 extern "C" int qcc_nvfp4_device_error(unsigned int *out) { return read_clear_device_error(out); }
 
-extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
-                         const uint64_t *philox_key, void *q, void *s, void *stream)
+// outer_kind: 0..2 as `outer_per_row` of qcc_nvfp4; 3 = outer points at a raw amax
+static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *outer_src, int outer_kind, int flags,
+                               const uint64_t *philox_key, void *q, void *s, float *outer_out, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !outer || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if (!x || !outer_src || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || N % 16 != 0) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
-    if (M == 0 || N == 0) return 0;
     const int64_t nb = N / 16;
     if (M * nb >= (1ll << 32) - 2 * NV_THREADS * NV_UNROLL || nb > 0x7FFFFFFF || M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -441,11 +455,15 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
     FastDiv32 dv;
     dv.init((uint32_t)nb);
     const unsigned grid = (nblocks + NV_THREADS * NV_UNROLL - 1) / (NV_THREADS * NV_UNROLL);
+    if (outer_kind < 0 || outer_kind > 3) return QCC_ERR_ARG;
+    const int src = outer_kind == 3 ? QCC_SRC_AMAX : QCC_SRC_SCALE;
+    const int outer_per_row = outer_kind <= 2 ? outer_kind : 0;
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row == 1;
-    if (outer_per_row < 0 || outer_per_row > 2) return QCC_ERR_ARG;
+    if (src != QCC_SRC_SCALE && sr) return QCC_ERR_ARG;
     if (outer_per_row == 2 && (sr || M % 128 != 0 || N % 128 != 0)) return sr ? QCC_ERR_ARG : QCC_ERR_SHAPE;
     const uint16_t *xp = (const uint16_t *)x;
     uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
+    const float *outer = (const float *)outer_src;
     if (swz && ((M & 127) != 0 || (nb & 3) != 0)) {
         blocked_zero_pad_kernel<<<sm_count() * 4, 256, 0, st>>>(sp, (uint32_t)M, (uint32_t)nb);
         cudaError_t e = cudaGetLastError();
@@ -456,22 +474,42 @@ extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer
         FastDiv32 dp;
         dp.init((uint32_t)(nb >> 1));
         const unsigned pgrid = (npairs + NV_THREADS - 1) / NV_THREADS;
-        nvfp4_rowwise_pair_kernel<<<pgrid, NV_THREADS, 0, st>>>(xp, npairs, (uint32_t)nb, dp, outer, qp, sp);
+#define QCC_NVP(SRC_) \
+    nvfp4_rowwise_pair_kernel<SRC_><<<pgrid, NV_THREADS, 0, st>>>(xp, npairs, (uint32_t)nb, dp, outer, qp, sp, outer_out)
+        if (src == QCC_SRC_SCALE) QCC_NVP(QCC_SRC_SCALE);
+        else QCC_NVP(QCC_SRC_AMAX);
+#undef QCC_NVP
         return (int)cudaGetLastError();
     }
-#define QCC_NV(SWZ_, SR_, PR_) \
-    nvfp4_rowwise_kernel<SWZ_, SR_, PR_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp)
-    if (outer_per_row == 2) {
-        if (swz) QCC_NV(true, false, 2); else QCC_NV(false, false, 2);
+#define QCC_NV(SWZ_, SR_, PR_, SRC_) \
+    nvfp4_rowwise_kernel<SWZ_, SR_, PR_, SRC_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp, \
+                                                                            outer_out)
+    if (src != QCC_SRC_SCALE) {
+        if (swz) QCC_NV(true, false, 0, QCC_SRC_AMAX); else QCC_NV(false, false, 0, QCC_SRC_AMAX);
+    } else if (outer_per_row == 2) {
+        if (swz) QCC_NV(true, false, 2, QCC_SRC_SCALE); else QCC_NV(false, false, 2, QCC_SRC_SCALE);
     } else if (swz) {
-        if (sr) { if (pr) QCC_NV(true, true, 1); else QCC_NV(true, true, 0); }
-        else    { if (pr) QCC_NV(true, false, 1); else QCC_NV(true, false, 0); }
+        if (sr) { if (pr) QCC_NV(true, true, 1, QCC_SRC_SCALE); else QCC_NV(true, true, 0, QCC_SRC_SCALE); }
+        else    { if (pr) QCC_NV(true, false, 1, QCC_SRC_SCALE); else QCC_NV(true, false, 0, QCC_SRC_SCALE); }
     } else {
-        if (sr) { if (pr) QCC_NV(false, true, 1); else QCC_NV(false, true, 0); }
-        else    { if (pr) QCC_NV(false, false, 1); else QCC_NV(false, false, 0); }
+        if (sr) { if (pr) QCC_NV(false, true, 1, QCC_SRC_SCALE); else QCC_NV(false, true, 0, QCC_SRC_SCALE); }
+        else    { if (pr) QCC_NV(false, false, 1, QCC_SRC_SCALE); else QCC_NV(false, false, 0, QCC_SRC_SCALE); }
     }
 #undef QCC_NV
     return (int)cudaGetLastError();
+}
+
+extern "C" int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
+                         const uint64_t *philox_key, void *q, void *s, void *stream)
+{
+    if (outer_per_row < 0 || outer_per_row > 2) return (M == 0 || N == 0) ? 0 : QCC_ERR_ARG;
+    return nvfp4_rowwise_entry(x, M, N, outer, outer_per_row, flags, philox_key, q, s, nullptr, stream);
+}
+
+extern "C" int qcc_nvfp4_from_amax(const void *x, int64_t M, int64_t N, const float *amax, int flags, void *q, void *s,
+                                   float *outer_out, void *stream)
+{
+    return nvfp4_rowwise_entry(x, M, N, amax, 3, flags, nullptr, q, s, outer_out, stream);
 }
 
 struct NvtArgs {

@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libquant_cast_cuda.so")
 FMT_E4M3, FMT_E5M2 = 0, 1
 ROWWISE, COLWISE, SWIZZLE, FLOOR, SR, BLOCK32 = 1, 2, 4, 8, 16, 32
 AMAX_RAW, AMAX_FP8_SCALE, AMAX_NVFP4_SCALE = 0, 1, 2
+AMAX_ONE_LAUNCH = 0x100
+XCHG_MAX_RANKS, XCHG_STATE_BYTES, XCHG_HANDLE_BYTES = 16, 1024, 64
 ERRORS = {
     -1: "shape: a dimension violates the divisibility this cast needs",
     -2: "alignment: a tensor is not 16-byte aligned",
@@ -29,7 +31,21 @@ SIGNATURES = {
     "qcc_sm_count": (_int, []),
     "qcc_copy2d_async": (_int, [_vp, _sz, _vp, _sz, _sz, _sz, _int, _vp]),
     "qcc_amax_workspace_bytes": (_sz, []),
+    "qcc_amax_workspace_init": (_int, [_vp, _sz, _vp]),
     "qcc_amax_bf16": (_int, [_vp, _i64, _int, _int, _vp, _vp, _sz, _vp]),
+    "qcc_xchg_alloc": (_int, [ctypes.POINTER(_vp)]),
+    "qcc_xchg_free": (_int, [_vp]),
+    "qcc_xchg_state_init": (_int, [_vp, ctypes.c_uint, _vp]),
+    "qcc_xchg_ipc_export": (_int, [_vp, _vp]),
+    "qcc_xchg_ipc_open": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "qcc_xchg_ipc_close": (_int, [_vp]),
+    "qcc_amax_bf16_xchg": (_int, [_vp, _i64, _vp, _vp]),
+    "qcc_xchg_publish": (_int, [_vp, _vp]),
+    "qcc_xchg_resolve": (_int, [_vp, _int, _int, _vp, _vp]),
+    "qcc_fp8_tensorwise_from_amax": (_int, [_vp, _i64, _vp, _int, _vp, _vp, _vp]),
+    "qcc_mxfp8_amax": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "qcc_mxfp8_amax_xchg": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
+    "qcc_nvfp4_from_amax": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
     "qcc_amax_bf16_noalloc": (_int, [_vp, _i64, _int, _int, _vp, _vp]),
     "qcc_scale_from_amax": (_int, [_vp, _int, _int, _vp, _vp]),
     "qcc_fp8_tensorwise": (_int, [_vp, _i64, _vp, _int, _vp, _vp]),
@@ -59,6 +75,16 @@ SIGNATURES = {
     "qcc_nvfp4_rht": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
 }
 
+CHECK_DEVICE = os.environ.get("QCC_CHECK_DEVICE", "0") not in ("", "0")   # see raise_on_device_error
+
+
+
+class XchgRef(ctypes.Structure):
+    """qcc_xchg_ref of include/quant_cast_cuda.h"""
+    _fields_ = [("states", ctypes.POINTER(ctypes.c_void_p)), ("world", ctypes.c_int), ("rank", ctypes.c_int),
+                ("publish", ctypes.c_int)]
+
+
 _lib = None
 launch_count = 0  # kernels launched through this binding (the benchmark resets and reads it)
 
@@ -83,17 +109,37 @@ def load():
 
 def check(rc, what):
     if rc == 0:
+        if CHECK_DEVICE:
+            raise_on_device_error(what)
         return
     if rc < 0:
         raise ValueError(f"{what}: {ERRORS.get(rc, rc)}")
     raise RuntimeError(f"{what}: CUDA error {rc}")
 
 
+DEVICE_ERRORS = {
+    16: "token-group offsets are not ascending multiples of 32 ending at M",
+    17: "the transform matrix is not diag(+-1) @ H16 / 4",
+    18: "a colwise fp8 cast gave up waiting for the column maxima of a panel",
+    19: "a wait for another rank's amax (amax exchange) ran out",
+}
+
+
 def device_error():
     """Reads and clears the device-side error word of the current CUDA device (synchronises): 0 when no kernel
     reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets, 17 an unsupported transform matrix, 18 a colwise cast
-    that gave up waiting for the column maxima of a panel."""
+    that gave up waiting for the column maxima of a panel, 19 a wait for another rank's amax that ran out."""
     v = ctypes.c_uint(0)
     check(load().qcc_device_error(ctypes.byref(v)), "device_error")
     return int(v.value)
+
+
+def raise_on_device_error(what="quant_cast_cuda"):
+    """Opt-in check after a cast (synchronises the device): raises RuntimeError when a kernel of this library
+    recorded an error -- a bounded wait that ran out leaves wrong bytes in the outputs without failing the launch.
+    `QCC_CHECK_DEVICE=1` in the environment makes every recipe call do this."""
+    code = device_error()
+    if code:
+        raise RuntimeError(f"{what}: device error {code}: {DEVICE_ERRORS.get(code, 'a TMA barrier wait ran out')}")
+
 

@@ -95,3 +95,89 @@ class HostMxfp8Caster:
                     out_free[b] = ev
             self.s_d2h.synchronize()
         return tuple(h.view(dt) for h, dt in zip(self.host, self.dtypes))
+
+
+class HostShardCaster:
+    """mxfp8_swizzle + nvfp4_swizzle (tensor-wide outer scale) of one rank's (rows, N) bf16 row shard that lives in
+    pinned host memory; outputs come back to pinned host memory.  The MoE-activation flow of a row-sharded tensor.
+
+    One call: the shard travels host -> device in row chunks; each chunk is cast to mxfp8 as it arrives by the kernel
+    that also accumulates the shard's amax, and its mxfp8 outputs leave device -> host while the next chunk arrives.
+    After the last chunk one warp exchanges the amax with the other ranks (`AmaxExchange`, peer memory) and forms the
+    outer scale; the nvfp4 cast then runs chunk by chunk over the shard, which stayed on the device, with its outputs
+    leaving behind it.  Chunks are multiples of 128 rows, so the result equals the one-shot casts bit for bit."""
+
+    def __init__(self, rows, N, device, exchange, chunk_rows=8192):
+        assert rows % 128 == 0 and N % 64 == 0, "host shard caster wants rows % 128 == 0 and N % 64 == 0"
+        self.rows, self.N, self.device, self.xchg = rows, N, torch.device(device), exchange
+        rc = min(chunk_rows, rows)
+        while rows % rc or rc % 128:
+            rc -= 128
+        self.rc = rc
+        dev, u8 = self.device, torch.uint8
+        self.x_dev = torch.empty((rows, N), dtype=torch.bfloat16, device=dev)
+        shapes = ((rows, N), blocked_shape(rows, N // 32), (rows, N // 2), blocked_shape(rows, N // 16))
+        self.out_dev = [torch.empty(s, dtype=u8, device=dev) for s in shapes]
+        self.outer_dev = torch.empty((), dtype=torch.float32, device=dev)
+        self.host = [torch.empty(s, dtype=u8, pin_memory=True) for s in shapes]
+        self.outer_host = torch.empty((), dtype=torch.float32, pin_memory=True)
+        self.dtypes = [torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float4_e2m1fn_x2, torch.float8_e4m3fn]
+        with torch.cuda.device(dev):
+            self.s_h2d, self.s_cmp, self.s_d2h = (torch.cuda.Stream() for _ in range(3))
+        self.bytes_in = rows * N * 2
+        self.bytes_out = sum(h.numel() for h in self.host) + 4
+
+    def cast(self, x_host):
+        """x_host: contiguous (rows, N) bf16 host tensor (pinned for full copy speed).  Returns (mx_q, mx_scales, nv_q,
+        nv_scales, outer_scale) as views of this object's pinned host buffers; complete on return."""
+        lib = L.load()
+        rows, N, rc = self.rows, self.N, self.rc
+        assert x_host.shape == (rows, N) and x_host.dtype == torch.bfloat16 and x_host.is_contiguous()
+        mq_d, ms_d, nq_d, ns_d = self.out_dev
+        mq_h, ms_h, nq_h, ns_h = self.host
+        n_chunks = rows // rc
+        ab = rc // 128                       # 128-row scale atoms rows per chunk
+        flags = L.ROWWISE | L.SWIZZLE
+        with torch.cuda.device(self.device):
+            cur = torch.cuda.current_stream()
+            for s in (self.s_h2d, self.s_cmp, self.s_d2h):
+                s.wait_stream(cur)
+            for i in range(n_chunks):
+                r0 = i * rc
+                with torch.cuda.stream(self.s_h2d):
+                    self.x_dev[r0:r0 + rc].copy_(x_host[r0:r0 + rc], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(self.s_h2d)
+                with torch.cuda.stream(self.s_cmp):
+                    self.s_cmp.wait_event(arrived)
+                    L.check(lib.qcc_mxfp8_amax_xchg(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, flags, mq_d[r0:r0 + rc].data_ptr(),
+                                                    ms_d[i * ab:(i + 1) * ab].data_ptr(), self.xchg.own, self.s_cmp.cuda_stream),
+                            "mxfp8_amax_xchg")
+                    L.launch_count += 1
+                    done = torch.cuda.Event()
+                    done.record(self.s_cmp)
+                with torch.cuda.stream(self.s_d2h):
+                    self.s_d2h.wait_event(done)
+                    mq_h[r0:r0 + rc].copy_(mq_d[r0:r0 + rc], non_blocking=True)
+                    ms_h[i * ab:(i + 1) * ab].copy_(ms_d[i * ab:(i + 1) * ab], non_blocking=True)
+            with torch.cuda.stream(self.s_cmp):
+                self.xchg._pending = True
+                L.check(lib.qcc_xchg_resolve(self.xchg._ref(), L.AMAX_NVFP4_SCALE, L.FMT_E4M3, self.outer_dev.data_ptr(),
+                                             self.s_cmp.cuda_stream), "xchg_resolve")
+                L.launch_count += 1
+                for i in range(n_chunks):
+                    r0 = i * rc
+                    L.check(lib.qcc_nvfp4(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, self.outer_dev.data_ptr(), 0, L.SWIZZLE, None,
+                                          nq_d[r0:r0 + rc].data_ptr(), ns_d[i * ab:(i + 1) * ab].data_ptr(), self.s_cmp.cuda_stream),
+                            "nvfp4")
+                    L.launch_count += 1
+                    done = torch.cuda.Event()
+                    done.record(self.s_cmp)
+                    with torch.cuda.stream(self.s_d2h):
+                        self.s_d2h.wait_event(done)
+                        nq_h[r0:r0 + rc].copy_(nq_d[r0:r0 + rc], non_blocking=True)
+                        ns_h[i * ab:(i + 1) * ab].copy_(ns_d[i * ab:(i + 1) * ab], non_blocking=True)
+                        if i == 0:
+                            self.outer_host.copy_(self.outer_dev, non_blocking=True)
+            self.s_d2h.synchronize()
+        return tuple(h.view(dt) for h, dt in zip(self.host, self.dtypes)) + (self.outer_host,)

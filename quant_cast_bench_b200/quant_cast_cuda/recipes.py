@@ -84,21 +84,52 @@ def philox_key(seed, offset=0, device="cuda"):
 # --------------------------------------------------------------------------------------------
 # amax and per-tensor scales
 # --------------------------------------------------------------------------------------------
-def _amax(x, mode, fmt=L.FMT_E4M3):
+_amax_ws_cache = {}   # (device index, stream handle) -> prepared workspace
+
+
+def new_amax_workspace(device, stream=None):
+    """A workspace for the one-launch amax (`workspace=` of the amax functions and of `mxfp8_*_amax_cuda`): cleared once
+    here, left cleared by every call that uses it.  Calls that share one must not overlap on the GPU."""
+    lib = L.load()
+    device = torch.device(device)
+    n = lib.qcc_amax_workspace_bytes()
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    st = stream if stream is not None else torch.cuda.current_stream(device).cuda_stream
+    with _on_device(device):
+        L.check(lib.qcc_amax_workspace_init(_p(ws), n, st), "amax_workspace_init")
+    return ws
+
+
+def _amax_workspace(x):
+    """The cached workspace of (device, current stream), or None while the stream is being captured into a CUDA
+    graph and nothing is cached for it (memory allocated during a capture belongs to that graph)."""
+    key = (x.device.index, _stream(x))
+    ws = _amax_ws_cache.get(key)
+    if ws is None and not torch.cuda.is_current_stream_capturing():
+        ws = _amax_ws_cache[key] = new_amax_workspace(x.device)
+    return ws
+
+
+def _amax(x, mode, fmt=L.FMT_E4M3, workspace=None):
     lib = L.load()
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
     out = torch.empty((), dtype=torch.float32, device=x.device)
+    ws = workspace if workspace is not None else _amax_workspace(x)
     ws_bytes = lib.qcc_amax_workspace_bytes()
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
-    L.launch_count += 2
+        if ws is not None:     # one launch
+            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode | L.AMAX_ONE_LAUNCH, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
+            L.launch_count += 1
+        else:                  # two launches, any workspace contents
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
+            L.launch_count += 2
     return out
 
 
-def amax_cuda(x):
+def amax_cuda(x, workspace=None):
     """max |x| as a 0-dim fp32 tensor (exact: a bf16 magnitude)."""
-    return _amax(x, L.AMAX_RAW)
+    return _amax(x, L.AMAX_RAW, workspace=workspace)
 
 
 def scale_from_amax_cuda(amax, kind, fmt="e4m3"):
@@ -114,14 +145,14 @@ def scale_from_amax_cuda(amax, kind, fmt="e4m3"):
     return out
 
 
-def float8_tensorwise_scale_cuda(x, fmt="e4m3"):
+def float8_tensorwise_scale_cuda(x, fmt="e4m3", workspace=None):
     """gold float8_tensorwise_scale (G:1179-1183): 0-dim fp32 scale = max(amax, bf16(1e-12)) / fp8_max."""
-    return _amax(x, L.AMAX_FP8_SCALE, _fmt(fmt))
+    return _amax(x, L.AMAX_FP8_SCALE, _fmt(fmt), workspace=workspace)
 
 
-def nvfp4_gs_scale_cuda(x):
+def nvfp4_gs_scale_cuda(x, workspace=None):
     """gold nvfp4_gs_scale (G:1243-1246): 0-dim fp32 outer scale = amax / (448 * 6)."""
-    return _amax(x, L.AMAX_NVFP4_SCALE)
+    return _amax(x, L.AMAX_NVFP4_SCALE, workspace=workspace)
 
 
 # --------------------------------------------------------------------------------------------
@@ -138,6 +169,22 @@ def float8_tensorwise_cuda(x, scale, fmt="e4m3", **kwargs):
         L.check(lib.qcc_fp8_tensorwise(_p(x), x.numel(), _p(scale), f, _p(q), _stream(x)), "fp8_tensorwise")
     L.launch_count += 1
     return (q.view(_FP8_DTYPE[f]),)
+
+
+def float8_tensorwise_from_amax_cuda(x, amax, fmt="e4m3"):
+    """float8_tensorwise_scale + float8_tensorwise_f (G:1179-1191) for an amax that is already known (e.g. reduced over
+    shards): the division amax -> scale happens in the cast's prologue.  Returns (qdata, scale)."""
+    lib = L.load()
+    _check_x(x)
+    f = _fmt(fmt)
+    assert amax.is_cuda and amax.dtype == torch.float32 and amax.numel() == 1
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scale = torch.empty((), dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_fp8_tensorwise_from_amax(_p(x), x.numel(), _p(amax), f, _p(q), _p(scale), _stream(x)),
+                "fp8_tensorwise_from_amax")
+    L.launch_count += 1
+    return q.view(_FP8_DTYPE[f]), scale
 
 
 def rowwise_fp8_cuda(x, fmt="e4m3", **kwargs):
@@ -245,6 +292,27 @@ def _mxfp8(x, flags):
     if flags & L.COLWISE:
         outs += [qm.view(torch.float8_e4m3fn), sm.view(torch.float8_e8m0fnu)]
     return tuple(outs)
+
+
+def mxfp8_with_amax_cuda(x, swizzle=True, mode="rceil", workspace=None):
+    """mxfp8_f / mxfp8_swizzle_f (G:561-568, G:1051-1053) and max |x| from ONE read of x: (qdata, scale, amax) with amax
+    the raw 0-dim fp32 maximum that nvfp4_gs_scale (G:1243-1246) or float8_tensorwise_scale would reduce again."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 32 == 0, f"mxfp8 needs N % 32 == 0, got N={N}"
+    flags = L.ROWWISE | (L.SWIZZLE if swizzle else 0) | _mode(mode)
+    dev = x.device
+    ws = workspace if workspace is not None else _amax_workspace(x)
+    if ws is None:
+        raise RuntimeError("mxfp8_with_amax_cuda needs workspace=new_amax_workspace(device) when called during a CUDA graph capture")
+    qk = torch.empty((M, N), dtype=torch.uint8, device=dev)
+    sk = torch.empty(blocked_shape(M, N // 32) if swizzle else (M, N // 32), dtype=torch.uint8, device=dev)
+    amax = torch.empty((), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        L.check(lib.qcc_mxfp8_amax(_p(x), M, N, flags, _p(qk), _p(sk), _p(amax), _p(ws), ws.numel(), _stream(x)), "mxfp8_amax")
+    L.launch_count += 1
+    return qk.view(torch.float8_e4m3fn), sk.view(torch.float8_e8m0fnu), amax
 
 
 def mxfp4_cuda(x, swizzle=False, **kwargs):
@@ -427,6 +495,25 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
             L.check(lib.qcc_nvfp4(_p(x), M, N, _p(o), per_row, flags, _p(key), _p(q), _p(s), _stream(x)), "nvfp4")
     L.launch_count += 1
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
+
+
+def nvfp4_from_amax_cuda(x, amax, swizzle=True):
+    """nvfp4_gs_scale + nvfp4_gs_f / nvfp4_gs_swizzle_f (G:1243-1266, G:1494-1517) for an amax that is already known:
+    outer = amax / 2688 is formed in the cast's prologue.  Returns (qdata, inner scales, outer scale)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 16 == 0, f"nvfp4 needs N % 16 == 0, got N={N}"
+    assert amax.is_cuda and amax.dtype == torch.float32 and amax.numel() == 1
+    dev = x.device
+    q = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
+    s_ = torch.empty(blocked_shape(M, N // 16) if swizzle else (M, N // 16), dtype=torch.uint8, device=dev)
+    outer = torch.empty((), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        L.check(lib.qcc_nvfp4_from_amax(_p(x), M, N, _p(amax), L.SWIZZLE if swizzle else 0, _p(q), _p(s_), _p(outer),
+                                        _stream(x)), "nvfp4_from_amax")
+    L.launch_count += 1
+    return q.view(torch.float4_e2m1fn_x2), s_.view(torch.float8_e4m3fn), outer
 
 
 def nvfp4_blocked_outer_scale_cuda(x, blk=128):
@@ -753,4 +840,5 @@ def _build_recipes():
 # Order follows quant_cast_gold.ALL_RECIPES (G:1929-1973), restricted to the recipes this backend implements.
 ALL_RECIPES = _build_recipes()
 
-__all__ = [n for n in dir() if n.endswith("_cuda")] + ["ALL_RECIPES", "QuantCastCudaRecipe", "blocked_shape", "philox_key"]
+__all__ = [n for n in dir() if n.endswith("_cuda")] + ["ALL_RECIPES", "QuantCastCudaRecipe", "blocked_shape", "philox_key",
+                                                          "new_amax_workspace"]

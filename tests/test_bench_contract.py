@@ -23,11 +23,17 @@ def _run(args, timeout):
 
 
 def test_reference_arm_prints_one_json_line():
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import ref_gold
     line = _run(["--impl", "reference", "--steps", "1", "--warmup", "0"], 600)
-    assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port"
+    # the reference's own gold recipes when they are installed under oracle/_ref, else the C restatement
+    assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == ("reference" if ref_gold.available() else "port")
     for k in REQUIRED:
         assert k in line, k
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
+    assert line["config"] == bench.CONFIG and line["metric"] == bench.METRIC      # the same workload as the GPU arm
+    assert line["cpu_baseline"]["cores"] >= 1 and "rows" in line["cpu_baseline"]["sample"]
 
 
 def test_reference_arm_under_torchrun_prints_once():
@@ -49,6 +55,12 @@ def test_default_arm_prints_one_json_line():
     line = _run(["--steps", "3", "--warmup", "3"], 900)
     for k in REQUIRED + ["roofline", "gpu_launches", "clocks"]:
         assert k in line, k
-    assert line["gpu_launches"] == 3 and line["n_gpus"] == 1
+    sys.path.insert(0, ROOT)
+    import bench
+    assert line["gpu_launches"] == 9 and line["n_gpus"] == 1          # mxfp8 (+ amax), exchange warp, nvfp4 per step
+    assert line["config"] == bench.CONFIG and line["scaling"] == "strong"
     assert line["roofline"]["bound"] == "hbm" and 0.3 < line["roofline"]["frac"] < 1.2
+    assert line["roofline"]["launch_ms_avg"] <= line["ms_per_step"]
+    assert line["roofline"]["step"]["bit_identical"] is True
     assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
+    assert line["cpu_baseline"]["kind"] in ("reference", "port")

@@ -5,7 +5,8 @@ qcc_amax_bf16_noalloc exists for hosts that cannot allocate device memory where 
 buffers): its scratch is an 8 KB buffer inside the library image.  Here it is called through the C
 ABI on buffers that exist before the call, twice in a row on different inputs -- the second input is
 smaller and quieter, so partial maxima left over from the first call would show -- and every result
-must equal bit for bit what qcc_amax_bf16 gives with a caller-supplied workspace.
+must equal bit for bit what qcc_amax_bf16 gives with a caller-supplied workspace, and what the CPU oracle computes
+from the same bytes (max |x|, float8_tensorwise_scale G:1179-1183, nvfp4_gs_scale G:1243-1246).
 
 The file name sorts last so that a run that stops at the first failure has already run everything else.
 """
@@ -26,11 +27,21 @@ def _reference(lib, x, mode, fmt, stream):
     return out
 
 
+def _oracle(x_cpu, mode, fmt):
+    from oracle import gold_port as O
+    if mode == L.AMAX_RAW:
+        return O.amax_bf16(x_cpu)
+    if mode == L.AMAX_FP8_SCALE:
+        return O.float8_tensorwise_scale(x_cpu, "e5m2" if fmt == L.FMT_E5M2 else "e4m3")
+    return O.nvfp4_gs_scale(x_cpu)
+
+
 def test_noalloc_amax_matches_regular_entry_point_twice_in_a_row():
     lib = L.load()
     stream = torch.cuda.current_stream().cuda_stream
-    big = make_input(2048, 4096, seed=31, spread=8.0).cuda()             # many CTAs, large values
-    small = (make_input(64, 256, seed=32, spread=0.0, outlier_p=0.0, zero_row_p=0.0) * 1e-3).to(torch.bfloat16).cuda()
+    big_cpu = make_input(2048, 4096, seed=31, spread=8.0)                # many CTAs, large values
+    small_cpu = (make_input(64, 256, seed=32, spread=0.0, outlier_p=0.0, zero_row_p=0.0) * 1e-3).to(torch.bfloat16)
+    big, small = big_cpu.cuda(), small_cpu.cuda()
     outs = torch.empty(2, dtype=torch.float32, device="cuda")            # allocated before the calls under test
     for mode, fmt in ((L.AMAX_RAW, L.FMT_E4M3), (L.AMAX_FP8_SCALE, L.FMT_E4M3), (L.AMAX_FP8_SCALE, L.FMT_E5M2),
                       (L.AMAX_NVFP4_SCALE, L.FMT_E4M3)):
@@ -41,6 +52,9 @@ def test_noalloc_amax_matches_regular_entry_point_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(outs[0:1].view(torch.int32), want[0].view(torch.int32)), f"first call, mode {mode}"
         assert torch.equal(outs[1:2].view(torch.int32), want[1].view(torch.int32)), f"second call, mode {mode}"
+        for i, t in enumerate((big_cpu, small_cpu)):
+            assert torch.equal(outs[i:i + 1].cpu().view(torch.int32), _oracle(t, mode, fmt).reshape(1).view(torch.int32)), (
+                f"call {i} against the CPU oracle, mode {mode}")
     assert float(outs[1]) > 0
 
 
