@@ -57,7 +57,8 @@ WORKLOAD = ("config 4: bf16[131072,7168], N(0,1)*2^U(-6,6) per token, row-sharde
 # the same dict in both arms (ours and --impl reference)
 CONFIG = {"workload": WORKLOAD, "rows": M4, "cols": N4, "sharding": "contiguous row shards, rows / n_gpus each",
           "bytes_per_step": STEP_BYTES,
-          "l2": "every launch streams a shard of >= 235 MB in and >= 120 MB out (L2: 126 MB); no flush between iterations"}
+          "l2": "every launch streams a shard of >= 235 MB in and >= 120 MB out (L2: 126 MB); two input tensors alternate between "
+                "steps; no flush between iterations"}
 METRIC = "achieved_GBps_c4_mxfp8_swizzle+nvfp4_swizzle"
 DTYPE = "bf16 -> e4m3 + e8m0, e2m1 + e4m3 (fp32 scale math)"
 
@@ -347,7 +348,9 @@ def run_ours(args):
     peak, peak_kind = measured_peak()
     r0, r1 = sharded.shard_rows(M4, world, rank, multiple=2048)
     rows = r1 - r0
-    x = chunk_seeded_input(rows, N4, r0, seed=4, device=dev, spread=6.0)
+    # two tensors alternate between steps, so that no step finds its input in L2 because the step before touched it
+    xs = [chunk_seeded_input(rows, N4, r0, seed=4 + i, device=dev, spread=6.0) for i in range(2)]
+    x = xs[0]
 
     # the headline path: mxfp8 cast that also delivers the amax -> exchange over peer memory -> nvfp4
     notes = []
@@ -359,8 +362,11 @@ def run_ours(args):
         caster = sharded.ShardedCaster(exchange="nccl")
         path = "nccl all-reduce, separate amax kernel"
 
+    calls = [0]
+
     def step():
-        return caster.mxfp8_then_nvfp4(x)
+        calls[0] += 1
+        return caster.mxfp8_then_nvfp4(xs[calls[0] & 1])
 
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
@@ -423,6 +429,9 @@ def run_ours(args):
     if caster.xchg is not None:
         variants["peer_exchange_amax_from_mxfp8_kernel"] = variant(caster)
         variants["peer_exchange_separate_amax_kernel"] = variant(caster, fuse_amax=False)
+        caster.pdl = False
+        variants["peer_exchange_amax_from_mxfp8_kernel_no_dependent_launch"] = variant(caster)
+        caster.pdl = True
     try:
         c_nccl = sharded.ShardedCaster(exchange="nccl")
         variants["nccl_all_reduce_separate_amax_kernel"] = variant(c_nccl)
@@ -450,14 +459,15 @@ def run_ours(args):
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
 
     # ---- bit identity: every rank's outputs, gathered, against ONE GPU casting the whole tensor by the plain recipes
-    bit_identical, identity_how = check_identity(outs, x, rows, world, rank, dev, barrier)
+    last = calls[0] & 1                      # which tensor the last step cast
+    bit_identical, identity_how = check_identity(outs, xs[last], 4 + last, world, rank, dev, barrier)
 
     # ---- end to end through the host-buffer API: pinned host shard in, pinned host outputs back, every step
     e2e = None
     if caster.xchg is not None:
         hc = HostShardCaster(rows, N4, dev, caster.xchg)
         x_host = torch.empty((rows, N4), dtype=torch.bfloat16, pin_memory=True)
-        x_host.copy_(x)
+        x_host.copy_(xs[last])
         for _ in range(2):
             hc.cast(x_host)
         torch.cuda.synchronize()
@@ -483,7 +493,7 @@ def run_ours(args):
     if rank == 0:
         clocks = sampler.stop()
     if world == 1:
-        del x
+        del x, xs
         torch.cuda.empty_cache()
         x2 = device_input(M_STEP, N_STEP, seed=1000, device=dev)
         casts = bench_other_casts(Q, x2, dev, peak)
@@ -532,7 +542,7 @@ def run_ours(args):
     emit(json.dumps(line))
 
 
-def check_identity(outs, x, rows, world, rank, dev, barrier):
+def check_identity(outs, x, seed, world, rank, dev, barrier):
     """Byte-for-byte comparison of the step's outputs with ONE GPU casting the whole tensor through the plain recipes
     (mxfp8_swizzle_cuda, nvfp4_gs_scale_cuda, nvfp4_gs_swizzle_cuda).  N > 1: the shards' outputs are gathered on rank 0
     (rowwise outputs and blocked grids of rowwise scales concatenate on their first axis), which regenerates the whole
@@ -558,7 +568,7 @@ def check_identity(outs, x, rows, world, rank, dev, barrier):
             gathered.append(torch.cat(parts, dim=0))
             del parts
     if rank == 0:
-        full = chunk_seeded_input(M4, N4, 0, seed=4, device=dev, spread=6.0)
+        full = chunk_seeded_input(M4, N4, 0, seed=seed, device=dev, spread=6.0)
         gs = Q.nvfp4_gs_scale_cuda(full)
         ok = all(torch.equal(o.view(torch.int32), gs.view(torch.int32)) for o in outers)
         wq, ws = Q.mxfp8_swizzle_cuda(full)

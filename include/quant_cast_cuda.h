@@ -40,6 +40,13 @@ extern "C" {
 #define QCC_FLOOR 8    /* mxfp8: FLOOR scale mode (OCP MX v1.0) instead of RCEIL                     */
 #define QCC_SR 16      /* nvfp4: stochastic rounding of the fp4 values, Philox4x32-10 keyed          */
 #define QCC_BLOCK32 32 /* mxfp8: one scale per 32x32 block instead of per 1x32 / 32x1 block        */
+#define QCC_REVERSE 0x400 /* qcc_nvfp4 / qcc_nvfp4_from_amax: walk the tensor from its end.  Results do not change; a cast
+                             that follows another pass over the same tensor (its amax, its mxfp8 cast) then begins with
+                             the rows that pass touched last, which are still in L2.                                   */
+#define QCC_PDL 0x200  /* qcc_nvfp4 (blocked scales, one outer scale, round to nearest): programmatic dependent launch --
+                          the cast may start, and load x, while the kernel before it on the stream (the one that writes
+                          the outer scale, i.e. qcc_xchg_resolve) is still running; it waits for that kernel before it
+                          reads the scale.  Only for a launch directly behind the kernel that writes `outer`.        */
 
 /* what qcc_amax_finalize writes */
 #define QCC_AMAX_RAW 0        /* the amax itself, fp32                                   */
@@ -165,9 +172,13 @@ typedef struct qcc_xchg_ref {
     void *const *states; /* [world] device addresses of the ranks' states as seen from this GPU */
     int world;           /* 1..QCC_XCHG_MAX_RANKS                                             */
     int rank;            /* this rank                                                         */
-    int publish;         /* qcc_xchg_resolve: 1 = hand this rank's amax to all ranks first (the normal call);
-                            0 = only read an exchange that was published before                */
+    int publish;         /* qcc_xchg_resolve: bit flags.  QCC_XCHG_PUBLISH: hand this rank's amax to all ranks first (the
+                            normal call); without it only read an exchange that was published before.  QCC_XCHG_PDL:
+                            launch directly behind the producing kernel as a programmatic dependent launch (the warp
+                            starts while that kernel drains and waits for its completion on the device) */
 } qcc_xchg_ref;
+#define QCC_XCHG_PUBLISH 1
+#define QCC_XCHG_PDL 2
 
 int qcc_xchg_alloc(void **state);   /* cudaMalloc + clear, timeout 1 s; set-up path, the only allocating call */
 int qcc_xchg_free(void *state);

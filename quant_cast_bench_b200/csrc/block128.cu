@@ -54,8 +54,8 @@ fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t 
     quant_row_block(c, inv, o0, o1);
     if (ok) {
         uint4 *dst = reinterpret_cast<uint4 *>(q) + (size_t)si * 2;
-        __stcs(dst, o0);
-        __stcs(dst + 1, o1);
+        st_out(dst, o0);
+        st_out(dst + 1, o1);
         if ((threadIdx.x & 3) == 0) scale[si >> 2] = s;
     }
 }
@@ -100,7 +100,7 @@ fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *
         uint2 o;
         o.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(v[i].x), bf16hi(v[i].x), bf16lo(v[i].y), bf16hi(v[i].y), inv);
         o.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(v[i].z), bf16hi(v[i].z), bf16lo(v[i].w), bf16hi(v[i].w), inv);
-        __stcs(reinterpret_cast<uint2 *>(qo + (size_t)(i * 8 + r0) * N), o);
+        st_out(reinterpret_cast<uint2 *>(qo + (size_t)(i * 8 + r0) * N), o);
     }
     if (t == 0) scale[blockIdx.x] = s;
 }

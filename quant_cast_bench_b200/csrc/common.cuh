@@ -454,6 +454,31 @@ __device__ __forceinline__ void named_barrier(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Programmatic dependent launch (a launch flagged QCC_PDL may begin while the kernel before it on the stream is still
+// draining; it must not touch that kernel's results before pdl_wait()).  pdl_trigger() in the earlier kernel lets the
+// flagged launch begin as soon as every CTA of the earlier kernel has started.  Both are no-ops in launches that are
+// not part of such a pair.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// a per-tensor scalar that an overlapped predecessor wrote: read past L1 (which may hold what an earlier kernel saw)
+__device__ __forceinline__ float ld_cg_f32(const float *p)
+{
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Output stores of the streaming kernels: evict-first (st.global.cs) unless built with QCC_PLAIN_STORES
+template <class T>
+__device__ __forceinline__ void st_out(T *p, T v)
+{
+#ifdef QCC_PLAIN_STORES
+    *p = v;
+#else
+    __stcs(p, v);
+#endif
+}
+
 // 16-byte vector access
 __device__ __forceinline__ uint4 ld_nc_v4(const void *p)
 {

@@ -124,7 +124,10 @@ __global__ void __launch_bounds__(AMAX_THREADS) amax_oneshot_kernel(const uint16
                                                                    float *__restrict__ out)
 {
     uint32_t seen = 0;
-    if (XCHG) seen = xchg_producer_begin(ctl);
+    if (XCHG) {
+        pdl_trigger();
+        seen = xchg_producer_begin(ctl);
+    }
     const int64_t nvec = n >> 3;
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     const int64_t base = (int64_t)blockIdx.x * (AMAX_THREADS * AMAX1_U) + threadIdx.x;
@@ -174,8 +177,14 @@ __device__ __forceinline__ uint2 cast8(uint4 a, float inv)
     return o;
 }
 
-constexpr int TW_THREADS = 256;
-constexpr int TW_UNROLL = 1;  // 16-element groups per thread (1 measured best: 7.0 TB/s)
+#ifndef QCC_TW_THREADS
+#define QCC_TW_THREADS 256
+#endif
+#ifndef QCC_TW_UNROLL
+#define QCC_TW_UNROLL 1
+#endif
+constexpr int TW_THREADS = QCC_TW_THREADS;
+constexpr int TW_UNROLL = QCC_TW_UNROLL;  // 16-element groups per thread (1 measured best: 7.0 TB/s)
 
 // SRC: where the scale comes from.  QCC_SRC_SCALE: scale[0] is the scale; QCC_SRC_AMAX: scale[0] is a raw amax, the
 // kernel forms max(amax, bf16(1e-12)) / fp8_max itself and its first CTA writes the scale to scale_out.
@@ -203,7 +212,7 @@ __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16
 #pragma unroll
     for (int u = 0; u < TW_UNROLL; u++) {
         int64_t g = base + (int64_t)u * TW_THREADS;
-        if (g < ngrp) __stcs(qv + g, cast16<FMT>(a[u], b[u], inv));
+        if (g < ngrp) st_out(qv + g, cast16<FMT>(a[u], b[u], inv));
     }
     // scalar tail: the last n % 16 elements
     if (blockIdx.x == 0 && threadIdx.x < (n & 15)) {
@@ -272,7 +281,7 @@ __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_kernel(const uint16_t 
                                      __fdiv_rn(bf16hi(a.y), s));
                 o.y = cvt_fp8x4<FMT>(__fdiv_rn(bf16lo(a.z), s), __fdiv_rn(bf16hi(a.z), s), __fdiv_rn(bf16lo(a.w), s),
                                      __fdiv_rn(bf16hi(a.w), s));
-                __stcs(qr + k, o);
+                st_out(qr + k, o);
             }
         }
     } else {
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_kernel(const uint16_t 
 #pragma unroll
         for (int c = 0; c < CH; c++) {
             int64_t k = tr + (int64_t)c * TPR;
-            if (k < nchunk) __stcs(qr + k, cast8<FMT>(v[c], inv));
+            if (k < nchunk) st_out(qr + k, cast8<FMT>(v[c], inv));
         }
     }
 }

@@ -60,6 +60,24 @@ inline int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dt, int rank, c
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// Kernel launch with the programmatic-stream-serialization attribute when `pdl` is set (the kernel may then start while
+// its predecessor on the stream drains and must call pdl_wait() before reading that predecessor's results).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_maybe_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // Launches the one-CTA check that `rht` (device, 16x16 bf16) is diag(+-1) @ H16 / 4; a matrix of another form
 // sets code 17 in the device error word (defined with the nvfp4 kernels).
 int launch_rht_check(const void *rht, cudaStream_t st);

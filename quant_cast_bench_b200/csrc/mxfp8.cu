@@ -33,8 +33,14 @@ namespace qcc {
 // ---------------------------------------------------------------------------------------------
 // rowwise stream
 // ---------------------------------------------------------------------------------------------
-constexpr int RS_THREADS = 256;
-constexpr int RS_UNROLL = 2;
+#ifndef QCC_RS_THREADS
+#define QCC_RS_THREADS 256
+#endif
+#ifndef QCC_RS_UNROLL
+#define QCC_RS_UNROLL 2
+#endif
+constexpr int RS_THREADS = QCC_RS_THREADS;
+constexpr int RS_UNROLL = QCC_RS_UNROLL;
 
 // Tables of the token-group casts (all null for the plain casts).  Rows are rows of the OUTPUT frame.
 //   row_map[r]  row -> row inside the 128-padded, stacked groups (-1: not in any group)
@@ -103,7 +109,10 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
     uint4 *qv = reinterpret_cast<uint4 *>(q);
     const uint32_t base = blockIdx.x * (RS_THREADS * RS_UNROLL) + threadIdx.x;
     uint32_t seen = 0;
-    if (AMAX == 2) seen = xchg_producer_begin(sink.ctl);
+    if (AMAX == 2) {
+        pdl_trigger();      // the exchange warp (and the cast behind it) may be launched once every CTA has got this far
+        seen = xchg_producer_begin(sink.ctl);
+    }
     uint4 c[RS_UNROLL][4];
 #pragma unroll
     for (int u = 0; u < RS_UNROLL; u++) {
@@ -136,8 +145,8 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
         uint4 o0, o1;
         quant_row_block(c[u], rcp, o0, o1);
         if (ok) {
-            __stcs(qv + 2 * (size_t)bi, o0);
-            __stcs(qv + 2 * (size_t)bi + 1, o1);
+            st_out(qv + 2 * (size_t)bi, o0);
+            st_out(qv + 2 * (size_t)bi + 1, o1);
         }
         stream_scale_store<SWZ>(s, bi, ok, e, nb, div_nb, row_map);
     }
@@ -147,6 +156,57 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
             xchg_producer_merge(sink.ctl, mx, seen, red);
         } else if (cta_max_ticket(mx, sink.ctl, red)) {
             if (threadIdx.x == 0 && sink.out) sink.out[0] = u2f(mx);
+        }
+    }
+}
+
+// The same cast with the four 16-byte pieces of a 1x32 block spread over four adjacent lanes: every load instruction of a
+// warp covers 512 contiguous bytes and every store instruction 256, the block maximum takes two shuffles, and four
+// neighbouring blocks' scale bytes leave as one 4-byte store (plain layout: four consecutive bytes; blocked layout: the
+// four columns of one row of an atom).  N % 128 == 0 (four blocks never straddle a row).
+#ifndef QCC_RC_UNROLL
+#define QCC_RC_UNROLL 4
+#endif
+constexpr int RC_UNROLL = QCC_RC_UNROLL;
+
+template <bool SWZ, bool FLOOR>
+__global__ void __launch_bounds__(RS_THREADS)
+mxfp8_rowwise_coal_kernel(const uint16_t *__restrict__ x, uint32_t nchunks, uint32_t nb, FastDiv32 div_nb,
+                          uint8_t *__restrict__ q, uint8_t *__restrict__ s)
+{
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+    uint2 *qv = reinterpret_cast<uint2 *>(q);
+    const uint32_t base = blockIdx.x * (RS_THREADS * RC_UNROLL) + threadIdx.x;
+    uint4 c[RC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < RC_UNROLL; u++) {
+        const uint32_t ci = base + u * RS_THREADS;
+        c[u] = ci < nchunks ? ld_nc_v4(xv + ci) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < RC_UNROLL; u++) {
+        const uint32_t ci = base + u * RS_THREADS;
+        const bool ok = ci < nchunks;
+        uint32_t a = absmax2(absmax2(0u, c[u].x), absmax2(c[u].y, c[u].z));
+        a = absmax2_acc(a, c[u].w);
+        a = absmax2_acc(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
+        a = absmax2_acc(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
+        const uint32_t e = e8m0_from_amax<FLOOR>(hmax_halves_f32(a));
+        const float rcp = e8m0_recip<FLOOR>(e);
+        uint2 o;
+        o.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[u].x), bf16hi(c[u].x), bf16lo(c[u].y), bf16hi(c[u].y), rcp);
+        o.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[u].z), bf16hi(c[u].z), bf16lo(c[u].w), bf16hi(c[u].w), rcp);
+        if (ok) st_out(qv + ci, o);
+        uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 4) << 8);
+        v |= __shfl_down_sync(0xFFFFFFFFu, v, 8) << 16;
+        if (ok && (threadIdx.x & 15) == 0) {
+            const uint32_t bi = ci >> 2;
+            if (SWZ) {
+                const uint32_t row = div_nb.div(bi);
+                *reinterpret_cast<uint32_t *>(s + blocked_offset(row, bi - row * nb, nb >> 2)) = v;
+            } else {
+                *reinterpret_cast<uint32_t *>(s + bi) = v;
+            }
         }
     }
 }
@@ -176,7 +236,7 @@ mxfp4_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
                       bf16lo(c[i].z) * rcp, bf16hi(c[i].z) * rcp, bf16lo(c[i].w) * rcp, bf16hi(c[i].w) * rcp};
         o[i] = cvt_e2m1x8(v);
     }
-    if (ok) __stcs(qv + bi, make_uint4(o[0], o[1], o[2], o[3]));
+    if (ok) st_out(qv + bi, make_uint4(o[0], o[1], o[2], o[3]));
     stream_scale_store<SWZ>(s, bi, ok, e, nb, div_nb, nullptr);
 }
 
@@ -559,6 +619,20 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
         const unsigned grid = (nblocks + RS_THREADS * RS_UNROLL - 1) / (RS_THREADS * RS_UNROLL);
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
+#ifdef QCC_RS_COAL
+        if (!amax_mode && !g.row_map && !g.blk_src && (nb & 3) == 0 && nblocks < (1u << 30)) {
+            const uint32_t nchunks = nblocks * 4;
+            const unsigned cgrid = (nchunks + RS_THREADS * RC_UNROLL - 1) / (RS_THREADS * RC_UNROLL);
+            if (swz) {
+                if (fl) mxfp8_rowwise_coal_kernel<true, true><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
+                else mxfp8_rowwise_coal_kernel<true, false><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
+            } else {
+                if (fl) mxfp8_rowwise_coal_kernel<false, true><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
+                else mxfp8_rowwise_coal_kernel<false, false><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
+            }
+            return (int)cudaGetLastError();
+        }
+#endif
 #define QCC_RS(SWZ_, FL_, AM_) \
     mxfp8_rowwise_stream_kernel<SWZ_, FL_, AM_><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g, sink)
 #define QCC_RS_AM(SWZ_, FL_) \
@@ -782,9 +856,9 @@ __global__ void __launch_bounds__(256) pad_rows_kernel(const uint4 *__restrict__
         if (PAD) {
             uint4 val = make_uint4(0, 0, 0, 0);
             if (real) val = ld_nc_v4(x + other);
-            __stcs(out + i, val);
+            st_out(out + i, val);
         } else if (real) {
-            __stcs(out + other, ld_nc_v4(x + i));
+            st_out(out + other, ld_nc_v4(x + i));
         }
     }
 }

@@ -54,16 +54,34 @@ __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer,
     return byte;
 }
 
-constexpr int NV_THREADS = 256;
-constexpr int NV_UNROLL = 2;
+#ifndef QCC_NV_THREADS
+#define QCC_NV_THREADS 256
+#endif
+#ifndef QCC_NV_UNROLL
+#define QCC_NV_UNROLL 2
+#endif
+constexpr int NV_THREADS = QCC_NV_THREADS;
+constexpr int NV_UNROLL = QCC_NV_UNROLL;
 
 // The per-tensor outer scale.  SRC QCC_SRC_SCALE: outer[0] is the scale; QCC_SRC_AMAX: outer[0] is the raw amax and
 // the scale is amax / 2688 (nvfp4_gs_scale G:1243-1246, folded into the cast), which the first CTA also writes to
-// outer_out.
+// outer_out.  QCC_SRC_SCALE_PDL: as QCC_SRC_SCALE in a launch that overlaps the kernel that writes outer[0]: call after
+// the thread has issued its loads of x; one thread waits for that kernel, reads the value past L1 and hands it to the
+// CTA through shared memory (one barrier).  Called by all threads.
+#define QCC_SRC_SCALE_PDL 2
 template <int SRC>
 __device__ __forceinline__ float nvfp4_outer_of_cta(const float *__restrict__ outer, float *__restrict__ outer_out)
 {
     if (SRC == QCC_SRC_SCALE) return __ldg(outer);
+    if (SRC == QCC_SRC_SCALE_PDL) {
+        __shared__ float sh;
+        if (threadIdx.x == 0) {
+            pdl_wait();
+            sh = ld_cg_f32(outer);
+        }
+        __syncthreads();
+        return sh;
+    }
     const float o = __fdiv_rn(__ldg(outer), 2688.0f);
     if (blockIdx.x == 0 && threadIdx.x == 0 && outer_out) outer_out[0] = o;
     return o;
@@ -75,7 +93,7 @@ template <bool SWZ, bool SR, int OUTER, int SRC = QCC_SRC_SCALE>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                      const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
-                     uint8_t *__restrict__ s, float *__restrict__ outer_out)
+                     uint8_t *__restrict__ s, float *__restrict__ outer_out, int rev)
 {
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint2 *qv = reinterpret_cast<uint2 *>(q);
@@ -85,7 +103,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
     // (a shared-memory table of the second division, as the transposed kernel uses, measured slower here:
     // its loads compete with the scale shuffles for the same issue queue)
     const float *lut = nullptr;
-    const uint32_t base = blockIdx.x * (NV_THREADS * NV_UNROLL) + threadIdx.x;
+    const uint32_t base = (rev ? gridDim.x - 1u - blockIdx.x : blockIdx.x) * (NV_THREADS * NV_UNROLL) + threadIdx.x;
     uint4 a[NV_UNROLL], b[NV_UNROLL];
 #pragma unroll
     for (int u = 0; u < NV_UNROLL; u++) {
@@ -113,7 +131,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         if (OUTER == 2) { o = __ldg(outer + (size_t)(row >> 7) * (nb >> 3) + (cb >> 3)); inv = __fdiv_rn(1.0f, o); }
         uint2 packed;
         const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, lut, (uint64_t)bi * 16u, seed, offset, packed);
-        if (ok) __stcs(qv + bi, packed);
+        if (ok) st_out(qv + bi, packed);
         if (SWZ) {
             // four consecutive lanes hold the four scale columns of one (row, column block)
             uint32_t v = byte | (__shfl_down_sync(0xFFFFFFFFu, byte, 1) << 8);
@@ -137,9 +155,12 @@ template <int SRC>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint32_t nb, FastDiv32 div_np,
                           const float *__restrict__ outer, uint8_t *__restrict__ q, uint8_t *__restrict__ s,
-                          float *__restrict__ outer_out)
+                          float *__restrict__ outer_out, int rev)
 {
-    const uint32_t pi = blockIdx.x * NV_THREADS + threadIdx.x;   // blocks 2 pi and 2 pi + 1 of the flat stream
+    // rev: CTAs walk the tensor from its end (CTAs are dispatched in index order), so a cast that follows another pass
+    // over the same tensor starts with the part that pass left in L2
+    const uint32_t cta = rev ? gridDim.x - 1u - blockIdx.x : blockIdx.x;
+    const uint32_t pi = cta * NV_THREADS + threadIdx.x;   // blocks 2 pi and 2 pi + 1 of the flat stream
     const bool ok = pi < npairs;
     uint4 c[4] = {};
     if (ok) {
@@ -152,7 +173,7 @@ nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint3
     uint2 p0, p1;
     const uint32_t b0 = nvfp4_quant16<false>(c[0], c[1], o, inv, nullptr, 0, 0, 0, p0);
     const uint32_t b1 = nvfp4_quant16<false>(c[2], c[3], o, inv, nullptr, 0, 0, 0, p1);
-    if (ok) __stcs(reinterpret_cast<uint4 *>(q) + pi, make_uint4(p0.x, p0.y, p1.x, p1.y));
+    if (ok) st_out(reinterpret_cast<uint4 *>(q) + pi, make_uint4(p0.x, p0.y, p1.x, p1.y));
     // an even lane and its neighbour hold the four scale columns of one (row, column block)
     const uint32_t b01 = b0 | (b1 << 8);
     const uint32_t v = b01 | (__shfl_down_sync(0xFFFFFFFFu, b01, 1) << 16);
@@ -444,7 +465,7 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
                                const uint64_t *philox_key, void *q, void *s, float *outer_out, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !outer_src || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR))) return QCC_ERR_ARG;
+    if (!x || !outer_src || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR | QCC_PDL | QCC_REVERSE))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || N % 16 != 0) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
@@ -460,6 +481,9 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
     const int outer_per_row = outer_kind <= 2 ? outer_kind : 0;
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row == 1;
     if (src != QCC_SRC_SCALE && sr) return QCC_ERR_ARG;
+    // the overlapped form exists for the common case only: blocked scales, one outer scale, round to nearest
+    const int rev = (flags & QCC_REVERSE) ? 1 : 0;
+    const bool pdl = (flags & QCC_PDL) && swz && !sr && outer_kind == 0 && (nb & 3) == 0;
     if (outer_per_row == 2 && (sr || M % 128 != 0 || N % 128 != 0)) return sr ? QCC_ERR_ARG : QCC_ERR_SHAPE;
     const uint16_t *xp = (const uint16_t *)x;
     uint8_t *qp = (uint8_t *)q, *sp = (uint8_t *)s;
@@ -469,13 +493,21 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
-    if (swz && !sr && outer_per_row == 0 && (nb & 3) == 0) {   // (the plain layout gains nothing from pairing)
+#ifndef QCC_NV_PAIR_MIN_BLOCKS
+#define QCC_NV_PAIR_MIN_BLOCKS 0
+#endif
+    if (swz && !sr && outer_per_row == 0 && (nb & 3) == 0 && nblocks >= (uint32_t)QCC_NV_PAIR_MIN_BLOCKS) {   // (the plain layout gains nothing from pairing)
         const uint32_t npairs = nblocks >> 1;
         FastDiv32 dp;
         dp.init((uint32_t)(nb >> 1));
         const unsigned pgrid = (npairs + NV_THREADS - 1) / NV_THREADS;
 #define QCC_NVP(SRC_) \
-    nvfp4_rowwise_pair_kernel<SRC_><<<pgrid, NV_THREADS, 0, st>>>(xp, npairs, (uint32_t)nb, dp, outer, qp, sp, outer_out)
+    nvfp4_rowwise_pair_kernel<SRC_><<<pgrid, NV_THREADS, 0, st>>>(xp, npairs, (uint32_t)nb, dp, outer, qp, sp, outer_out, rev)
+        if (pdl) {
+            cudaError_t le = launch_maybe_pdl(nvfp4_rowwise_pair_kernel<QCC_SRC_SCALE_PDL>, dim3(pgrid), dim3(NV_THREADS), 0, st, true, xp,
+                                              npairs, (uint32_t)nb, dp, outer, qp, sp, outer_out, rev);
+            return (int)le;
+        }
         if (src == QCC_SRC_SCALE) QCC_NVP(QCC_SRC_SCALE);
         else QCC_NVP(QCC_SRC_AMAX);
 #undef QCC_NVP
@@ -483,7 +515,7 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
     }
 #define QCC_NV(SWZ_, SR_, PR_, SRC_) \
     nvfp4_rowwise_kernel<SWZ_, SR_, PR_, SRC_><<<grid, NV_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, outer, philox_key, qp, sp, \
-                                                                            outer_out)
+                                                                            outer_out, rev)
     if (src != QCC_SRC_SCALE) {
         if (swz) QCC_NV(true, false, 0, QCC_SRC_AMAX); else QCC_NV(false, false, 0, QCC_SRC_AMAX);
     } else if (outer_per_row == 2) {

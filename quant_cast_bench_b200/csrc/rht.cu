@@ -21,8 +21,8 @@ hadamard_rht_rows_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, uin
     const uint4 a = ld_nc_v4(x + 2 * (size_t)bi), b = ld_nc_v4(x + 2 * (size_t)bi + 1);
     uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     rht16_bf16_row(w, sgn);
-    __stcs(y + 2 * (size_t)bi, make_uint4(w[0], w[1], w[2], w[3]));
-    __stcs(y + 2 * (size_t)bi + 1, make_uint4(w[4], w[5], w[6], w[7]));
+    st_out(y + 2 * (size_t)bi, make_uint4(w[0], w[1], w[2], w[3]));
+    st_out(y + 2 * (size_t)bi + 1, make_uint4(w[4], w[5], w[6], w[7]));
 }
 
 // max |RHT(x.t())|: a warp takes 16 rows x 128 columns (lane = four adjacent columns), transforms down the rows

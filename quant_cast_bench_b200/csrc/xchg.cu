@@ -10,7 +10,9 @@ namespace qcc {
 // out[0] = f(maximum over the ranks of the last exchange), f as in qcc_amax_bf16
 __global__ void xchg_resolve_kernel(uint32_t *state, XchgPeers peers, int publish, int mode, int fmt, float *__restrict__ out)
 {
-    const uint32_t e = publish ? xchg_publish(state, peers) : xchg_current(state);
+    pdl_trigger();          // a cast flagged QCC_PDL may start loading its input now; it waits for this kernel's result
+    pdl_wait();             // launched with QCC_XCHG_PDL: the producing kernel may still be draining
+    const uint32_t e = (publish & QCC_XCHG_PUBLISH) ? xchg_publish(state, peers) : xchg_current(state);
     const float am = xchg_resolve(state, peers.world, e);
     if (threadIdx.x != 0) return;
     float r = am;
@@ -106,9 +108,8 @@ int qcc_xchg_resolve(const qcc_xchg_ref *ref, int mode, int fmt, float *out, voi
     XchgPeers peers;
     int rc = make_xchg_peers(&peers, ref->states, ref->world, ref->rank);
     if (rc) return rc;
-    xchg_resolve_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(static_cast<uint32_t *>(ref->states[ref->rank]), peers, ref->publish, mode,
-                                                            fmt, out);
-    return (int)cudaGetLastError();
+    return (int)launch_maybe_pdl(xchg_resolve_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (ref->publish & QCC_XCHG_PDL) != 0,
+                                 static_cast<uint32_t *>(ref->states[ref->rank]), peers, ref->publish, mode, fmt, out);
 }
 
 }  // extern "C"

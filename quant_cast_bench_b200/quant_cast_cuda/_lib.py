@@ -12,6 +12,8 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libquant_cast_cuda.so")
 # constants of include/quant_cast_cuda.h
 FMT_E4M3, FMT_E5M2 = 0, 1
 ROWWISE, COLWISE, SWIZZLE, FLOOR, SR, BLOCK32 = 1, 2, 4, 8, 16, 32
+PDL, REVERSE = 0x200, 0x400
+XCHG_PUBLISH, XCHG_PDL = 1, 2
 AMAX_RAW, AMAX_FP8_SCALE, AMAX_NVFP4_SCALE = 0, 1, 2
 AMAX_ONE_LAUNCH = 0x100
 XCHG_MAX_RANKS, XCHG_STATE_BYTES, XCHG_HANDLE_BYTES = 16, 1024, 64

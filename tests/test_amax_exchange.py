@@ -209,6 +209,40 @@ def test_sharded_caster_with_peer_exchange_on_one_rank():
     c.xchg.close()
 
 
+@pytest.mark.parametrize("pdl", [True, False])
+def test_overlapped_launches_see_each_steps_own_scale(pdl):
+    """The exchange warp and the nvfp4 cast start while the kernel before them drains (programmatic dependent launch)
+    and pick the scale up on the device: consecutive steps on tensors of very different magnitude, issued eagerly
+    and replayed from one CUDA graph, must each be cast under their own outer scale."""
+    from oracle import gold_port as O
+    from quant_cast_bench_b200.quant_cast_cuda import sharded
+    base = make_input(1024, 2048, seed=21, spread=4.0)
+    xs = [(base * k).to(torch.bfloat16) for k in (1.0, 64.0, 1.0 / 128.0, 8.0)]
+    xc = [x.cuda() for x in xs]
+    want = []
+    for x in xs:
+        outer = O.nvfp4_gs_scale(x)
+        want.append((*O.mxfp8_swizzle_f(x), *O.nvfp4_gs_swizzle_f(x, outer), outer))
+    c = sharded.ShardedCaster(exchange="peer", pdl=pdl)
+
+    def check(outs, what):
+        for (mx, nv), w in zip(outs, want):
+            for got, ref in zip((*mx, *nv), w):
+                assert_same_bits(got, ref, what)
+
+    check([c.mxfp8_then_nvfp4(x) for x in xc], "eager")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        outs = [c.mxfp8_then_nvfp4(x) for x in xc]
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    check(outs, "graph replay")
+    c.xchg.close()
+
+
 def test_a_rank_that_never_publishes_runs_the_wait_out():
     ranks = _Ranks(2, timeout_us=20_000)
     x = make_input(128, 256, seed=2).cuda()
