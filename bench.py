@@ -480,11 +480,39 @@ def run_ours(args):
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e_same = all(torch.equal(h.view(torch.uint8), d.view(torch.uint8).cpu()) for h, d in
                        zip(outs_host[:4], (outs[0][0], outs[0][1], outs[1][0], outs[1][1]))) if rows <= 32768 else None
+        # what the link gives with the same buffers: host -> device alone, device -> host alone, both at once (all
+        # ranks at the same time, slowest rank counts).  The step cannot beat input / h2d + nvfp4 outputs / d2h: the nvfp4
+        # cast needs the amax of the whole tensor, so its outputs only start to leave once the last input byte is in.
+        def link_s(fn, reps=3):
+            best = None
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                barrier()
+                t0 = time.perf_counter()
+                fn()
+                torch.cuda.synchronize()
+                dt = max_over_ranks(time.perf_counter() - t0)
+                best = dt if best is None else min(best, dt)
+            return best
+        s2 = torch.cuda.Stream()
+        def d2h_all(stream=None):
+            with torch.cuda.stream(stream or torch.cuda.current_stream()):
+                for h, d in zip(hc.host, hc.out_dev):
+                    h.copy_(d, non_blocking=True)
+        t_h2d = link_s(lambda: hc.x_dev.copy_(x_host, non_blocking=True))
+        t_d2h = link_s(d2h_all)
+        t_dup = link_s(lambda: (hc.x_dev.copy_(x_host, non_blocking=True), d2h_all(s2)))
+        nv_out = hc.host[2].numel() + hc.host[3].numel()
+        bound_s = hc.bytes_in / (hc.bytes_in / t_h2d) + nv_out / (hc.bytes_out / t_d2h)
+        link = {"h2d_GBps_per_gpu": hc.bytes_in / t_h2d / 1e9, "d2h_GBps_per_gpu": hc.bytes_out / t_d2h / 1e9,
+                "duplex_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) / t_dup / 1e9,
+                "step_lower_bound_ms": bound_s * 1e3, "frac_of_bound": bound_s / (e2e_s / e2e_steps),
+                "bound": "input / h2d rate + nvfp4 outputs / d2h rate (the nvfp4 outputs cannot leave before the whole input is in)"}
         e2e = {"value": STEP_BYTES * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": hc.bytes_in * world, "d2h_bytes_per_step": hc.bytes_out * world, "steps": e2e_steps,
                "ms_per_step": e2e_s / e2e_steps * 1e3, "chunk_rows": hc.rc,
                "pcie_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) * e2e_steps / e2e_s / 1e9,
-               "outputs_equal_device_path": e2e_same}
+               "outputs_equal_device_path": e2e_same, "link": link}
         del hc, x_host, outs_host
     del outs
     torch.cuda.empty_cache()

@@ -277,15 +277,15 @@ static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, u
 {
     auto kern = fp8_block128_tile_kernel<DO_K, CLAMP_F32>;
     constexpr int ALLOC = BT_ALLOC;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceFlag configured;
+    const int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    if (!configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ALLOC);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        configured.set(dev);
     }
     const int tiles_n = (N + 127) / 128, tiles_m = M / 128;
     const long long num_tiles = (long long)tiles_n * tiles_m;

@@ -149,9 +149,12 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
     }
     __syncthreads();
     // one thread: loads of panel p into buffer b (0, 1: maxima stream; 2, 3: cast stream) on barrier b
+    uint32_t issued[CWR_NBUF] = {};           // (thread 32) loads posted per buffer
     auto issue = [&](int p, int b) {
         const int col0 = (p * strips + strip) * 64;
         if (col0 >= N || nt == 0) return;
+        if (*(volatile uint32_t *)abort_word != 0) return;      // a wait of this launch has given up: post nothing more
+        issued[b]++;
         mbar_expect_tx(bar + b, (uint32_t)nt * CWR_TILE_BYTES);
         // L2: keep what the maxima stream brings in, let go of what the cast stream has re-read (measured: 192 -> 172 us
         // at 16384^2; with the outputs written evict-first as well 167 us)
@@ -298,6 +301,26 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
             if (p + 2 >= 0 && p + 2 < np) issue(p + 2, 2 + (p & 1));
         }
     }
+    // After a wait has given up the consumers no longer wait for their loads, so copies may still be in flight into this
+    // CTA's shared memory: the issuing thread waits (bounded) for the last phase of every buffer before the CTA ends.
+    if (tid == 32 && *(volatile uint32_t *)abort_word != 0) {
+        for (int b = 0; b < CWR_NBUF; b++) {
+            if (issued[b] == 0) continue;
+            const uint32_t a = smem_u32(bar + b), parity = (issued[b] - 1u) & 1u;
+            const uint64_t start = global_timer_ns();
+            for (;;) {
+                uint32_t ok;
+                asm volatile(
+                    "{\n.reg .pred p;\n"
+                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                    "selp.u32 %0, 1, 0, p;\n}\n"
+                    : "=r"(ok)
+                    : "r"(a), "r"(parity)
+                    : "memory");
+                if (ok || global_timer_ns() - start > CWR_WAIT_NS) break;
+            }
+        }
+    }
 }
 
 // Largest number of 64-column strips per panel (<= 16) for which a CTA's run of row tiles fits its buffers; 0: none.
@@ -315,23 +338,25 @@ static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t 
                            int64_t N, int strips, int np, int grid, cudaStream_t st)
 {
     auto kern = fp8_colwise_resident_kernel<FMT>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return QCC_ERR_DRIVER;
-    if (!configured[dev]) {
+    static PerDeviceFlag configured, cooperative;
+    const int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    if (!configured.get(dev)) {
+        int coop = 0;
+        if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop) cooperative.set(dev);
         cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CWR_ALLOC);
         if (ce != cudaSuccess) return (int)ce;
-        configured[dev] = true;
+        configured.set(dev);
     }
+    if (!cooperative.get(dev)) return 1;                      // no cooperative launches here: two-launch form
     uint8_t *qp = (uint8_t *)q;
     int Mi = (int)M, Ni = (int)N;
     int lag = np >= 40 ? CWR_LAG : CWR_LAG - 1;               // few panels: the steps that only drain the pipeline weigh more
     void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np, &lag};
     const cudaError_t ce = cudaLaunchCooperativeKernel((const void *)kern, dim3((unsigned)grid), dim3(CWR_THREADS), args, CWR_ALLOC, st);
-    if (ce == cudaErrorCooperativeLaunchTooLarge) {         // fewer SMs available than the device reports: two-launch form
-        cudaGetLastError();
-        return 1;
+    if (ce == cudaErrorCooperativeLaunchTooLarge || ce == cudaErrorNotSupported || ce == cudaErrorLaunchOutOfResources) {
+        cudaGetLastError();                                   // fewer SMs available than the device reports, or the context
+        return 1;                                             // refuses the launch form: the two-launch form works there
     }
     return (int)ce;
 }

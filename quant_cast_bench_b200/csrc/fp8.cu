@@ -405,6 +405,14 @@ __global__ void __launch_bounds__(CW_AMAX_THREADS) fp8_colwise_amax_kernel(const
     }
 }
 
+// scale[c] = max(amax_c, bf16(1e-12)) / fp8_max from the finished column maxima
+template <int FMT>
+__global__ void colwise_scale_kernel(const uint32_t *__restrict__ amax_bits, float *__restrict__ scale, int N)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < N) scale[c] = fp8_scale_from_amax<FMT>(u2f(amax_bits[c]));
+}
+
 constexpr int CW_PANEL = 64 * 128;                // one 64-column panel of a 64-row tile
 constexpr int CW_Q_OFF = 2 * CW_PANEL;            // staging: 4 sub-tiles x 32 rows x 64 B
 constexpr int CW_BAR_OFF = CW_Q_OFF + 4 * 32 * 64;
@@ -512,7 +520,7 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
     uint32_t box[2] = {64, 64};
     int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (e) return e;
-    if (!PRECALC) {
+    if (!PRECALC && q != nullptr) {
         // one launch with the panel resident in shared memory where the shape allows it (colwise.cu)
         const int rc = qcc_colwise_resident(x, M, N, FMT, q, scale_out, amax_bits, st);
         if (rc != 1) return rc;
@@ -524,17 +532,21 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
         fp8_colwise_amax_kernel<<<grid, CW_AMAX_THREADS, 0, st>>>((const uint16_t *)x, (int)M, (int)N, amax_bits);
         ce = cudaGetLastError();
         if (ce != cudaSuccess) return (int)ce;
+        if (q == nullptr) {     // the scales alone (colwise_precalc_scale G:438-442): one read of x, no cast
+            colwise_scale_kernel<FMT><<<(unsigned)((N + 255) / 256), 256, 0, st>>>(amax_bits, scale_out, (int)N);
+            return (int)cudaGetLastError();
+        }
     }
     auto kern = fp8_colwise_cast_kernel<FMT, PRECALC>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceFlag configured;
+    const int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    if (!configured.get(dev)) {
         cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CW_ALLOC);
         if (ce != cudaSuccess) return (int)ce;
         ce = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (ce != cudaSuccess) return (int)ce;
-        configured[dev] = true;
+        configured.set(dev);
     }
     const int tiles_n = (int)((N + 127) / 128), tiles_m = (int)((M + 63) / 64);
     const long long num_tiles = (long long)tiles_n * tiles_m;
@@ -656,16 +668,19 @@ int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *ou
     if (n > QCC_AMAX_NOALLOC_MAX_ELEMS) return QCC_ERR_TOO_LARGE;
     // In host code the array's name is only a handle: the device address has to be asked for, once per
     // device, with that device current.  The first call on a device does it here.
-    static uint32_t *scratch[64] = {nullptr};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return QCC_ERR_ARG;
-    if (!scratch[dev]) {
+    // The address stays valid for the life of the device's primary context.  Host threads that make their first call
+    // on a device at the same time all store the same address (the slots are atomics), so the race is harmless.
+    static std::atomic<uint32_t *> scratch[QCC_MAX_DEVICES];
+    const int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    cudaError_t e;
+    uint32_t *scratch_dev = scratch[dev].load(std::memory_order_acquire);
+    if (!scratch_dev) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_amax_noalloc_scratch);
         if (e != cudaSuccess) return (int)e;
-        scratch[dev] = static_cast<uint32_t *>(p);
+        scratch_dev = static_cast<uint32_t *>(p);
+        scratch[dev].store(scratch_dev, std::memory_order_release);
     }
     cudaStream_t st = (cudaStream_t)stream;
     int64_t want = ((n >> 3) + AMAX_THREADS * AMAX_U - 1) / (AMAX_THREADS * AMAX_U);
@@ -673,10 +688,10 @@ int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *ou
     if (cap > AMAX_MAX_CTAS) cap = AMAX_MAX_CTAS;
     int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
     // every slot the finish reads is written by this launch, so nothing has to be cleared
-    amax_partial_kernel<<<grid, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, scratch[dev]);
+    amax_partial_kernel<<<grid, AMAX_THREADS, 0, st>>>((const uint16_t *)x, n, scratch_dev);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>(scratch[dev], grid, mode, fmt, out);
+    amax_finish_kernel<<<1, AMAX_THREADS, 0, st>>>(scratch_dev, grid, mode, fmt, out);
     return (int)cudaGetLastError();
 }
 
@@ -760,11 +775,11 @@ int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
                     size_t workspace_bytes, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !q || !scale || !workspace || M < 0 || N < 0) return QCC_ERR_ARG;
+    if (!x || !scale || !workspace || M < 0 || N < 0) return QCC_ERR_ARG;
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00 || (M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS > 65535)
         return QCC_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(q) || !aligned16(workspace)) return QCC_ERR_ALIGN;
+    if (!aligned16(x) || (q && !aligned16(q)) || !aligned16(workspace)) return QCC_ERR_ALIGN;
     if (workspace_bytes < qcc_fp8_colwise_workspace_bytes(M, N)) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st)

@@ -5,22 +5,42 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace qcc {
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Per-device host-side caches ("this kernel's attributes are set on device d", "the address of this symbol on device
+// d").  Host threads may make their first call on a device at the same time: every writer stores the same value, and
+// the flags are atomics, so the only cost of that race is doing the set-up twice.  Devices 0..63; current_device_slot()
+// returns -1 for any other ordinal and the entry points then reject the call.
+constexpr int QCC_MAX_DEVICES = 64;
+struct PerDeviceFlag {
+    std::atomic<unsigned char> v[QCC_MAX_DEVICES];
+    PerDeviceFlag() { for (auto &e : v) e.store(0, std::memory_order_relaxed); }
+    bool get(int dev) const { return v[dev].load(std::memory_order_acquire) != 0; }
+    void set(int dev) { v[dev].store(1, std::memory_order_release); }
+};
+inline int current_device_slot()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= QCC_MAX_DEVICES) return -1;
+    return dev;
+}
+
 // SM count of the current device, cached per device ordinal.
 inline int sm_count()
 {
-    static int cache[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cache[dev] == 0) {
-        int n = 0;
+    static std::atomic<int> cache[QCC_MAX_DEVICES];
+    const int dev = current_device_slot();
+    if (dev < 0) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cache[dev] = n;
+        cache[dev].store(n, std::memory_order_relaxed);
     }
-    return cache[dev];
+    return n;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

@@ -541,15 +541,15 @@ static int launch_t64(const CUtensorMap &tx, uint8_t *qk, uint8_t *sk, uint8_t *
 {
     using L = T64<DO_K, DO_M>;
     auto kern = mxfp8_tile64_kernel<DO_K, DO_M, SWZ, FLOOR, B32, PAD, BATCHED>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceFlag configured;          // one per template instance
+    int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    if (!configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        configured.set(dev);
     }
     // With blocked scales the tiles must cover whole 128-row atoms so that the padding gets its zeros:
     // a tile that lies entirely below the matrix loads zero-filled data and stores nothing but scales.
@@ -986,6 +986,15 @@ extern "C" int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int fl
     cudaError_t ce;
     if (row && sk && (ce = cudaMemsetAsync(sk, 0, (size_t)(R + G * 128) * nb, st)) != cudaSuccess) return (int)ce;
     if (col && sm && (ce = cudaMemsetAsync(sm, 0, (size_t)padded_c * (mb + G * 4), st)) != cudaSuccess) return (int)ce;
+    if (M == 0) {
+        // a rank that received no tokens (expert parallelism): the padded frame is all padding -- zero elements, zero
+        // scales, every padded group empty -- as the pad-then-cast route gives for an empty input
+        if (row && qk && (ce = cudaMemsetAsync(qk, 0, (size_t)R * N, st)) != cudaSuccess) return (int)ce;
+        if (col && qm && (ce = cudaMemsetAsync(qm, 0, (size_t)R * N, st)) != cudaSuccess) return (int)ce;
+        if (padded_offs && (ce = cudaMemsetAsync(padded_offs, 0, (size_t)G * sizeof(int32_t), st)) != cudaSuccess) return (int)ce;
+        return 0;
+    }
+    if (!x) return QCC_ERR_ARG;
     PadTables t;
     int e = build_pad_tables(offs, G, M, R, padded_c, padded_offs, workspace, st, t);
     if (e) return e;

@@ -555,15 +555,15 @@ template <bool DO_K, bool SWZ, bool SR, bool RHT>
 static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cudaStream_t st)
 {
     auto kern = nvfp4_transposed_kernel<DO_K, SWZ, SR, RHT>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    static PerDeviceFlag configured;
+    const int dev = current_device_slot();
+    if (dev < 0) return QCC_ERR_ARG;
+    if (!configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, NVT_ALLOC);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        configured.set(dev);
     }
     const int tiles_n = (N + 127) / 128, tiles_m = (M + NVT_TILE_M - 1) / NVT_TILE_M;
     const long long num_tiles = (long long)tiles_n * tiles_m;

@@ -245,8 +245,19 @@ def colwise_fp8_cuda(x, fmt="e4m3", **kwargs):
 
 
 def colwise_precalc_scale_cuda(x, fmt="e4m3"):
-    """gold colwise_precalc_scale (G:438-442): (1, N) fp32 per-column scale."""
-    return colwise_fp8_cuda(x, fmt)[1].reshape(1, -1)
+    """gold colwise_precalc_scale (G:438-442): (1, N) fp32 per-column scale -- the column maxima pass alone (one read
+    of x, no cast)."""
+    lib = L.load()
+    _check_x(x)
+    M, N = x.shape
+    assert N % 8 == 0 and M % 16 == 0, f"colwise fp8 needs N % 8 == 0 and M % 16 == 0, got {M}x{N}"
+    s = torch.empty((1, N), dtype=torch.float32, device=x.device)
+    ws_bytes = int(lib.qcc_fp8_colwise_workspace_bytes(M, N))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_fp8_colwise(_p(x), M, N, _fmt(fmt), None, _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise_scale")
+    L.launch_count += 2
+    return s
 
 
 def colwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):

@@ -1,7 +1,8 @@
 """Generate tests/golden/gold_vectors.npz by running the REFERENCE's gold recipes on CPU.
 
-Run in a checkout where the reference project is available:
+Run where a checkout of the reference project is available:
     python tests/golden/make_golden.py --reference /path/to/quant_cast_bench_checkout
+(default: $QCC_REFERENCE_ROOT, else a checkout named `reference` beside this repository)
 The reference imports `torch.func._random` (a module of newer PyTorch builds) at import time; it is
 only used by the stochastic-rounding recipes, which are not part of the stored vectors, so an empty
 stand-in module is registered before the import.  Nothing from the reference is copied: only the
@@ -21,6 +22,15 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def default_reference():
+    """$QCC_REFERENCE_ROOT, else a checkout named `reference` beside this repository, else None."""
+    repo = os.path.dirname(os.path.dirname(HERE))
+    for c in (os.environ.get("QCC_REFERENCE_ROOT"), os.path.join(os.path.dirname(repo), "reference")):
+        if c and os.path.isfile(os.path.join(c, "quant_cast_bench", "quant_cast_gold", "recipes.py")):
+            return c
+    return None
 
 
 def import_gold(ref_root):
@@ -56,9 +66,11 @@ def raw(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference())
     ap.add_argument("--out", default=os.path.join(HERE, "gold_vectors.npz"))
     args = ap.parse_args()
+    if not args.reference:
+        raise SystemExit("no reference checkout: pass --reference or set QCC_REFERENCE_ROOT")
     G, GU = import_gold(args.reference)
     out = {}
 

@@ -206,13 +206,18 @@ def test_floor_mode_definition():
     assert q.view(torch.uint8)[0, :2].tolist() == [0x7E, 0xC4]
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/quant_cast_bench"), reason="reference checkout not present")
-def test_against_live_reference():
-    """Where the reference checkout is present, run its gold recipes directly on fresh inputs."""
+def _reference_checkout():
     import sys
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
     import make_golden
-    G, _ = make_golden.import_gold("/root/reference")
+    return make_golden.default_reference()
+
+
+@pytest.mark.skipif(_reference_checkout() is None, reason="reference checkout not present ($QCC_REFERENCE_ROOT)")
+def test_against_live_reference():
+    """Where the reference checkout is present, run its gold recipes directly on fresh inputs."""
+    import make_golden
+    G, _ = make_golden.import_gold(_reference_checkout())
     for (M, N, seed) in [(256, 256, 11), (384, 128, 12), (32, 2048, 13)]:
         x = make_golden.make_input(M, N, seed, spread=8.0)
         for fn in ONE_INPUT:

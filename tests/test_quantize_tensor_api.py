@@ -158,6 +158,7 @@ def test_token_groups_errors():
 
 PAD_CASES = [
     (100, 128, [7, 7, 40, 100]),          # ragged groups, an empty one
+    (0, 128, [0, 0, 0]),                  # a rank that received no tokens (expert parallelism)
     (64, 256, [64]),                      # one aligned group
     (131, 128, [1, 33, 131]),             # a one-row group
     (1000, 384, [0, 250, 250, 777, 1000]),

@@ -8,14 +8,14 @@ import sys
 
 import pytest
 
-REFERENCE = "/root/reference"
-pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "quant_cast_bench")),
-                                reason="reference checkout not present")
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import make_golden  # noqa: E402
+
+REFERENCE = make_golden.default_reference()      # $QCC_REFERENCE_ROOT, or a checkout named `reference` beside the repository
+pytestmark = pytest.mark.skipif(REFERENCE is None, reason="reference checkout not present ($QCC_REFERENCE_ROOT)")
 
 
 def test_names_order_and_gold_fields():
-    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
-    import make_golden
     G, _ = make_golden.import_gold(REFERENCE)           # stubs torch.func._random, puts the reference on sys.path
     from quant_cast_bench_b200.quant_cast_cuda import recipes as R
     R = importlib.reload(R)                             # now quant_cast_gold is importable: records come from gold
