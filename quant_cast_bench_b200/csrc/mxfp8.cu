@@ -931,6 +931,15 @@ int build_pad_tables(const int32_t *offs, int64_t G, int64_t M, int64_t R, int64
 static int pad_or_unpad(const void *x, int64_t M, int64_t row_bytes, const int32_t *offs, int64_t G, void *out,
                         int32_t *padded_offs, void *workspace, size_t workspace_bytes, void *stream, bool unpad)
 {
+    if (M == 0) {
+        // no tokens at all: the padded frame (32 G rows) is all padding, the unpadded one is empty
+        if (!offs || G <= 0 || row_bytes <= 0 || (!unpad && !out)) return QCC_ERR_ARG;
+        if (G > GROUPS_MAX_PAD || row_bytes % 16 != 0) return QCC_ERR_SHAPE;
+        cudaError_t ce = cudaSuccess;
+        if (!unpad) ce = cudaMemsetAsync(out, 0, (size_t)qcc_padded_token_rows(0, G) * row_bytes, (cudaStream_t)stream);
+        if (ce == cudaSuccess && padded_offs) ce = cudaMemsetAsync(padded_offs, 0, (size_t)G * sizeof(int32_t), (cudaStream_t)stream);
+        return (int)ce;
+    }
     if (!x || !offs || !out || !workspace || G <= 0 || M < 0 || row_bytes <= 0) return QCC_ERR_ARG;
     if (G > GROUPS_MAX_PAD || row_bytes % 16 != 0 || M > 0x7FFFF000) return QCC_ERR_SHAPE;
     const int64_t R = qcc_padded_token_rows(M, G);
