@@ -346,7 +346,9 @@ def run_ours(args):
 
     warmup = max(args.warmup, 3)
     peak, peak_kind = measured_peak()
-    r0, r1 = sharded.shard_rows(M4, world, rank, multiple=2048)
+    total_rows = args.rows
+    step_bytes = STEP_BYTES * total_rows // M4
+    r0, r1 = sharded.shard_rows(total_rows, world, rank, multiple=2048)
     rows = r1 - r0
     # two tensors alternate between steps, so that no step finds its input in L2 because the step before touched it
     xs = [chunk_seeded_input(rows, N4, r0, seed=4 + i, device=dev, spread=6.0) for i in range(2)]
@@ -407,7 +409,7 @@ def run_ours(args):
     barrier()
     launches = L.launch_count
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    value = STEP_BYTES * args.steps / (ms_total * 1e-3) / 1e9
+    value = step_bytes * args.steps / (ms_total * 1e-3) / 1e9
     ms_step = ms_total / args.steps
     err = L.device_error()
     if err:
@@ -460,11 +462,11 @@ def run_ours(args):
 
     # ---- bit identity: every rank's outputs, gathered, against ONE GPU casting the whole tensor by the plain recipes
     last = calls[0] & 1                      # which tensor the last step cast
-    bit_identical, identity_how = check_identity(outs, xs[last], 4 + last, world, rank, dev, barrier)
+    bit_identical, identity_how = check_identity(outs, xs[last], 4 + last, world, rank, dev, barrier, total_rows)
 
     # ---- end to end through the host-buffer API: pinned host shard in, pinned host outputs back, every step
     e2e = None
-    if caster.xchg is not None:
+    if caster.xchg is not None and not args.only_step:
         hc = HostShardCaster(rows, N4, dev, caster.xchg)
         x_host = torch.empty((rows, N4), dtype=torch.bfloat16, pin_memory=True)
         x_host.copy_(xs[last])
@@ -508,7 +510,7 @@ def run_ours(args):
                 "duplex_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) / t_dup / 1e9,
                 "step_lower_bound_ms": bound_s * 1e3, "frac_of_bound": bound_s / (e2e_s / e2e_steps),
                 "bound": "input / h2d rate + nvfp4 outputs / d2h rate (the nvfp4 outputs cannot leave before the whole input is in)"}
-        e2e = {"value": STEP_BYTES * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
+        e2e = {"value": step_bytes * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": hc.bytes_in * world, "d2h_bytes_per_step": hc.bytes_out * world, "steps": e2e_steps,
                "ms_per_step": e2e_s / e2e_steps * 1e3, "chunk_rows": hc.rc,
                "pcie_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) * e2e_steps / e2e_s / 1e9,
@@ -520,7 +522,7 @@ def run_ours(args):
     casts, moe, cpu, ref_gpu, clocks = {}, None, None, None, None
     if rank == 0:
         clocks = sampler.stop()
-    if world == 1:
+    if world == 1 and not args.only_step:
         del x, xs
         torch.cuda.empty_cache()
         x2 = device_input(M_STEP, N_STEP, seed=1000, device=dev)
@@ -546,7 +548,8 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": DTYPE, "data": "synthetic",
         "timed_region": "one CUDA graph of K steps" if graph is not None else "K eager launches",
-        "config": CONFIG,
+        "config": CONFIG if total_rows == M4 else dict(CONFIG, rows=total_rows, bytes_per_step=step_bytes,
+                                                        note="NOT the benchmark configuration: --rows given (profiling case)"),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * rows) if NCU_TRAFFIC_BYTES_PER_ROW else None,
                      "traffic_note": "ncu capture of a 16384-row shard, scaled by rows per launch",
@@ -554,9 +557,9 @@ def run_ours(args):
                      "launch_ms_avg": k_ms, "launch_timing": "10 launches replayed from one CUDA graph / 10",
                      "frac_of_8TBps": achieved / 8000.0,
                      "step": {"path": path, "launches_per_step": launches // max(args.steps, 1),
-                              "bytes_algorithmic": STEP_BYTES, "bytes_min_traffic": STEP_BYTES_MIN,
-                              "GBps_min_traffic": STEP_BYTES_MIN / (ms_step * 1e-3) / 1e9,
-                              "frac_measured_peak_min_traffic_per_gpu": STEP_BYTES_MIN / (ms_step * 1e-3) / 1e9 / world / peak,
+                              "bytes_algorithmic": step_bytes, "bytes_min_traffic": STEP_BYTES_MIN * total_rows // M4,
+                              "GBps_min_traffic": STEP_BYTES_MIN * total_rows // M4 / (ms_step * 1e-3) / 1e9,
+                              "frac_measured_peak_min_traffic_per_gpu": STEP_BYTES_MIN * total_rows // M4 / (ms_step * 1e-3) / 1e9 / world / peak,
                               "ms_per_iter_by_path": variants, "bit_identical": bit_identical, "identity_check": identity_how,
                               "notes": notes}},
         "cpu_baseline": cpu,
@@ -570,7 +573,7 @@ def run_ours(args):
     emit(json.dumps(line))
 
 
-def check_identity(outs, x, seed, world, rank, dev, barrier):
+def check_identity(outs, x, seed, world, rank, dev, barrier, total_rows=M4):
     """Byte-for-byte comparison of the step's outputs with ONE GPU casting the whole tensor through the plain recipes
     (mxfp8_swizzle_cuda, nvfp4_gs_scale_cuda, nvfp4_gs_swizzle_cuda).  N > 1: the shards' outputs are gathered on rank 0
     (rowwise outputs and blocked grids of rowwise scales concatenate on their first axis), which regenerates the whole
@@ -596,7 +599,7 @@ def check_identity(outs, x, seed, world, rank, dev, barrier):
             gathered.append(torch.cat(parts, dim=0))
             del parts
     if rank == 0:
-        full = chunk_seeded_input(M4, N4, 0, seed=seed, device=dev, spread=6.0)
+        full = chunk_seeded_input(total_rows, N4, 0, seed=seed, device=dev, spread=6.0)
         gs = Q.nvfp4_gs_scale_cuda(full)
         ok = all(torch.equal(o.view(torch.int32), gs.view(torch.int32)) for o in outers)
         wq, ws = Q.mxfp8_swizzle_cuda(full)
@@ -621,8 +624,9 @@ def bench_reference_gpu(dev, budget_s):
     in order until `budget_s` seconds are spent; the CuTe kernels are tried last and their exception recorded if the
     installed nvidia-cutlass-dsl refuses them."""
     import torch
+    from quant_cast_bench_b200 import quant_cast_cuda as Q
     t_start = time.perf_counter()
-    out = {"shape": [M_STEP, N_STEP], "method": "median of 10 x [256 MB L2 flush, kernel] minus 10 x flush, replayed from CUDA graphs",
+    out = {"shape": [M_STEP, N_STEP], "method": "10 x [256 MB L2 flush, kernel] minus 10 x flush, replayed from CUDA graphs",
            "recipes": {}}
     try:
         from oracle import ref_gold
@@ -639,16 +643,27 @@ def bench_reference_gpu(dev, budget_s):
     side = torch.cuda.Stream()
 
     def cold_ms(fn):
+        """(cold-L2 kernel time, back-to-back time per launch) in ms"""
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
         gk, _ = graph_of(lambda: (flush.zero_(), fn()), 10, side)
         gf, _ = graph_of(lambda: flush.zero_(), 10, side)
+        gb, _ = graph_of(fn, 10, side)
         t = (replay_ms(gk) - replay_ms(gf)) / 10
-        del gk, gf
-        return t
+        tb = replay_ms(gb) / 10
+        del gk, gf, gb
+        return t, tb
 
-    from quant_cast_bench_b200 import quant_cast_cuda as Q
+    def same_as_ours(name, inputs, outs):
+        """The reference kernel's outputs against this backend's for the same inputs (raw bytes)."""
+        ours = dict(Q.ALL_RECIPES).get(name)
+        if ours is None:
+            return None
+        mine = ours.cuda_fn(*inputs)
+        return bool(len(mine) == len(outs) and all(a.shape == b.shape and torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
+                                                   for a, b in zip(mine, outs)))
+
     s8 = Q.float8_tensorwise_scale_cuda(x)
     gs = Q.nvfp4_gs_scale_cuda(x)
     order = [("mxfp8_dim_km_swizzle", (x,)), ("nvfp4_swizzle", (x, gs)), ("fp8_tensorwise_precalc_scale", (x, s8)),
@@ -668,9 +683,11 @@ def bench_reference_gpu(dev, budget_s):
             torch.cuda.synchronize()
             nbytes = sum(t.numel() * t.element_size() for t in inputs) + sum(t.numel() * t.element_size() for t in outs)
             first_call_s = time.perf_counter() - t0
-            ms = cold_ms(lambda: rec.triton_fn(*inputs))
+            same = same_as_ours(name, inputs, outs)
+            ms, ms_b2b = cold_ms(lambda: rec.triton_fn(*inputs))
             out["recipes"][name] = {"ms_cold_in_graph": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_8TBps": nbytes / (ms * 1e-3) / 8e12,
-                                    "bytes": nbytes, "compile_and_autotune_s": first_call_s}
+                                    "ms_sustained": ms_b2b, "GBps_sustained": nbytes / (ms_b2b * 1e-3) / 1e9,
+                                    "bytes": nbytes, "compile_and_autotune_s": first_call_s, "outputs_equal_ours": same}
         except Exception as exc:
             out["recipes"][name] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
             torch.cuda.synchronize()
@@ -682,8 +699,15 @@ def bench_reference_gpu(dev, budget_s):
         outs = crec.cute_fn(x)
         torch.cuda.synchronize()
         nbytes = x.numel() * 2 + sum(t.numel() * t.element_size() for t in outs)
-        ms = cold_ms(lambda: crec.cute_fn(x))
-        out["cute_mxfp8_dim_km_swizzle"] = {"ms_cold_in_graph": ms, "GBps": nbytes / (ms * 1e-3) / 1e9}
+        same = same_as_ours("mxfp8_dim_km_swizzle", (x,), outs)
+        ms, ms_b2b = cold_ms(lambda: crec.cute_fn(x))
+        if nbytes / (ms * 1e-3) / 1e9 > 10000.0:
+            # the kernel did not run inside the captured graph (the CuTe DSL launches on a stream of its own): no timing
+            out["cute_mxfp8_dim_km_swizzle"] = {"unavailable": "launch not captured by the CUDA graph (implausible %.4f ms); "
+                                                "nvidia-cutlass-dsl here is older than the 4.5.2 the reference was written for" % ms,
+                                                "outputs_equal_ours": same}
+        else:
+            out["cute_mxfp8_dim_km_swizzle"] = {"ms_cold_in_graph": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "outputs_equal_ours": same}
     except Exception as exc:
         out["cute_mxfp8_dim_km_swizzle"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     del x, flush
@@ -911,6 +935,9 @@ def main():
     ap.add_argument("--reference-gpu", action="store_true",
                     help="also time the reference's own Triton kernels on this GPU (their autotuning takes minutes)")
     ap.add_argument("--reference-gpu-budget", type=float, default=600.0, help="seconds after which no further reference recipe is started")
+    ap.add_argument("--rows", type=int, default=M4, help="rows of the whole tensor (default: configuration 4's 131072); a smaller "
+                    "value gives the small case that profiler captures want -- not the benchmark configuration")
+    ap.add_argument("--only-step", action="store_true", help="time the step only: no per-cast table, no CPU or end-to-end leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

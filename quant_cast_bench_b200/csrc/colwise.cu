@@ -149,12 +149,13 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
     }
     __syncthreads();
     // one thread: loads of panel p into buffer b (0, 1: maxima stream; 2, 3: cast stream) on barrier b
-    uint32_t issued[CWR_NBUF] = {};           // (thread 32) loads posted per buffer
+    uint32_t issued0 = 0, issued1 = 0, issued2 = 0, issued3 = 0;   // (thread 32) loads posted per buffer
+    uint32_t abort_seen = 0;                  // (thread 32) the launch's abort word as read at the top of the step
     auto issue = [&](int p, int b) {
         const int col0 = (p * strips + strip) * 64;
         if (col0 >= N || nt == 0) return;
-        if (*(volatile uint32_t *)abort_word != 0) return;      // a wait of this launch has given up: post nothing more
-        issued[b]++;
+        if (abort_seen != 0) return;                             // a wait of this launch has given up: post nothing more
+        if (b == 0) issued0++; else if (b == 1) issued1++; else if (b == 2) issued2++; else issued3++;
         mbar_expect_tx(bar + b, (uint32_t)nt * CWR_TILE_BYTES);
         // L2: keep what the maxima stream brings in, let go of what the cast stream has re-read (measured: 192 -> 172 us
         // at 16384^2; with the outputs written evict-first as well 167 us)
@@ -167,6 +168,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
 
     for (int i = 0; i < np + lag; i++) {
         const int p = i - lag;                                              // the panel cast in this step
+        if (tid == 32) abort_seen = *(volatile uint32_t *)abort_word;       // read now, used at the end of the step
         const int col0_x = (i * strips + strip) * 64, col0_c = (p * strips + strip) * 64;
         const bool have_x = i < np && col0_x < N && nt > 0;
         const bool have_c = p >= 0 && col0_c < N && nt > 0;
@@ -304,6 +306,9 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
     // After a wait has given up the consumers no longer wait for their loads, so copies may still be in flight into this
     // CTA's shared memory: the issuing thread waits (bounded) for the last phase of every buffer before the CTA ends.
     if (tid == 32 && *(volatile uint32_t *)abort_word != 0) {
+        const uint32_t issued[CWR_NBUF] = {issued0, issued1, issued2, issued3};
+        static_assert(CWR_NBUF == 4, "four buffers");
+#pragma unroll
         for (int b = 0; b < CWR_NBUF; b++) {
             if (issued[b] == 0) continue;
             const uint32_t a = smem_u32(bar + b), parity = (issued[b] - 1u) & 1u;

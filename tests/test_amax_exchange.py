@@ -243,6 +243,28 @@ def test_overlapped_launches_see_each_steps_own_scale(pdl):
     c.xchg.close()
 
 
+@pytest.mark.parametrize("rows,chunk", [(512, 128), (1024, 384), (256, 8192)])
+def test_host_shard_caster_matches_the_one_shot_casts(rows, chunk):
+    """Pinned host shard in, pinned host outputs back, cast in row chunks with the amax accumulating over the chunks:
+    the same bytes as the one-shot casts of the oracle."""
+    from oracle import gold_port as O
+    from quant_cast_bench_b200.quant_cast_cuda import sharded
+    from quant_cast_bench_b200.quant_cast_cuda.host_api import HostShardCaster
+    N = 1024
+    x = make_input(rows, N, seed=rows, spread=6.0)
+    x[rows - 3, 11] = 7.0e3                                   # the maximum sits in the last chunk
+    xh = x.pin_memory()
+    xchg = sharded.AmaxExchange()
+    hc = HostShardCaster(rows, N, "cuda", xchg, chunk_rows=chunk)
+    outer = O.nvfp4_gs_scale(x)
+    want = (*O.mxfp8_swizzle_f(x), *O.nvfp4_gs_swizzle_f(x, outer), outer)
+    for _ in range(2):                                        # buffers and exchange state are reused
+        got = hc.cast(xh)
+        for g, w in zip(got, want):
+            assert_same_bits(g, w, "host shard caster")
+    xchg.close()
+
+
 def test_a_rank_that_never_publishes_runs_the_wait_out():
     ranks = _Ranks(2, timeout_us=20_000)
     x = make_input(128, 256, seed=2).cuda()
