@@ -50,8 +50,9 @@ BYTES_NVFP4 = 2 * E4 + 4 + E4 // 2 + E4 // 16          # nvfp4_gs_swizzle_f(x, o
 STEP_BYTES = BYTES_MXFP8 + BYTES_AMAX + BYTES_NVFP4
 STEP_BYTES_MIN = BYTES_MXFP8 + BYTES_NVFP4             # x read twice: what the fused path moves
 # dram__bytes_read.sum + dram__bytes_write.sum of mxfp8_rowwise_stream_kernel<blocked scales, RCEIL, amax> from one ncu
-# capture of a 16384 x 7168 shard (235 MB read, 242 MB written); traffic grows in proportion to the rows of a launch.
-NCU_TRAFFIC_BYTES_PER_ROW = None   # filled in from the capture; None -> the line says null
+# capture of a 16384 x 7168 shard (234.9 MB read, 80.3 MB written: about 40 MB of the 121 MB the launch writes are still
+# in L2 when it ends); traffic grows in proportion to the rows of a launch.
+NCU_TRAFFIC_BYTES_PER_ROW = (234_911_488 + 80_282_624) / 16384
 WORKLOAD = ("config 4: bf16[131072,7168], N(0,1)*2^U(-6,6) per token, row-sharded over the GPUs; per step: mxfp8_swizzle "
             "+ nvfp4 outer scale from the tensor-wide amax (one exchange between the GPUs) + nvfp4_swizzle")
 # the same dict in both arms (ours and --impl reference)
@@ -551,7 +552,7 @@ def run_ours(args):
         "config": CONFIG if total_rows == M4 else dict(CONFIG, rows=total_rows, bytes_per_step=step_bytes,
                                                         note="NOT the benchmark configuration: --rows given (profiling case)"),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * rows) if NCU_TRAFFIC_BYTES_PER_ROW else None,
+                     "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * rows) if NCU_TRAFFIC_BYTES_PER_ROW else None,
                      "traffic_note": "ncu capture of a 16384-row shard, scaled by rows per launch",
                      "peak_kind": peak_kind, "kernel": kname, "bytes_per_launch": k_bytes, "rows_per_launch": rows,
                      "launch_ms_avg": k_ms, "launch_timing": "10 launches replayed from one CUDA graph / 10",
