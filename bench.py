@@ -857,10 +857,10 @@ def bench_other_casts(Q, x, dev, peak):
     ws = Q.new_amax_workspace(dev)            # the one-launch amax inside graph captures needs its workspace up front
     s = Q.float8_tensorwise_scale_cuda(x)
     gs = Q.nvfp4_gs_scale_cuda(x)
-    # same-size plain copies (torch's bf16 -> bf16 copy kernel, timed the same way): what a streaming kernel reaches at
-    # each size on this GPU
+    # same-size plain copies (this library's copy kernel, the streaming casts' access pattern, timed the same way): what a
+    # kernel that only moves data reaches at each size on this GPU
     y = torch.empty_like(x)
-    out["copy_16384"] = timed(lambda: y.copy_(x), algorithmic_bytes(M, N, "copy"))
+    out["copy_16384"] = timed(lambda: Q.stream_copy_cuda(x, y), algorithmic_bytes(M, N, "copy"))
     del y
     out["amax_16384"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x, workspace=ws), algorithmic_bytes(M, N, "amax"))
     out["fp8_tensorwise_16384"] = timed(lambda: Q.float8_tensorwise_cuda(x, s), algorithmic_bytes(M, N, "fp8_tensorwise"))
@@ -886,7 +886,7 @@ def bench_other_casts(Q, x, dev, peak):
     x1 = x[:4096, :4096].contiguous()          # config 1 shape (fits L2: flush between iterations)
     s1 = Q.float8_tensorwise_scale_cuda(x1)
     y1 = torch.empty_like(x1)
-    out["c1_copy_4096"] = timed(lambda: y1.copy_(x1), algorithmic_bytes(4096, 4096, "copy"), True)
+    out["c1_copy_4096"] = timed(lambda: Q.stream_copy_cuda(x1, y1), algorithmic_bytes(4096, 4096, "copy"), True)
     out["c1_fp8_tensorwise_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
     out["c1_fp8_tensorwise_e5m2_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1, "e5m2"), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
     out["c1_fp8_rowwise_4096"] = timed(lambda: Q.rowwise_fp8_cuda(x1), algorithmic_bytes(4096, 4096, "fp8_rowwise"), True)
@@ -894,7 +894,7 @@ def bench_other_casts(Q, x, dev, peak):
     x3 = x[:8192, :8192].contiguous()          # config 3 shape (128 MiB input)
     gs3 = Q.nvfp4_gs_scale_cuda(x3)
     y3 = torch.empty_like(x3)
-    out["c3_copy_8192"] = timed(lambda: y3.copy_(x3), algorithmic_bytes(8192, 8192, "copy"), True)
+    out["c3_copy_8192"] = timed(lambda: Q.stream_copy_cuda(x3, y3), algorithmic_bytes(8192, 8192, "copy"), True)
     del y3
     out["c3_nvfp4_amax_8192"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x3, workspace=ws), algorithmic_bytes(8192, 8192, "amax"), True)
     out["c3_nvfp4_8192"] = timed(lambda: Q.nvfp4_gs_cuda(x3, gs3), algorithmic_bytes(8192, 8192, "nvfp4"), True)

@@ -95,6 +95,11 @@ int qcc_sm_count(void);
 int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
                      size_t rows, int to_host, void *stream);
 
+/* dst[0..bytes) = src[0..bytes) by a kernel with the access pattern of the streaming casts (bytes % 16 == 0): the
+ * bandwidth yardstick of the benchmarks -- what a kernel that only moves data reaches at a given size on this GPU.
+ * (No counterpart in the reference, whose yardstick is an eager relu, benchmarks/benchmark.py:41-60.) */
+int qcc_stream_copy(const void *src, void *dst, size_t bytes, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * amax and per-tensor scales
  * ------------------------------------------------------------------------------------------- */

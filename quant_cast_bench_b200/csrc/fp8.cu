@@ -221,6 +221,18 @@ __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16
     }
 }
 
+// A plain copy with the access pattern of the streaming casts (one-shot grid, two 16-byte loads in flight per thread,
+// evict-first stores): the yardstick the benchmarks hold the casts against at each size.
+__global__ void __launch_bounds__(TW_THREADS) stream_copy_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, int64_t nvec)
+{
+    const int64_t i = (int64_t)blockIdx.x * (TW_THREADS * 2) + threadIdx.x;
+    uint4 a = make_uint4(0, 0, 0, 0), b = a;
+    if (i < nvec) a = ld_nc_v4(src + i);
+    if (i + TW_THREADS < nvec) b = ld_nc_v4(src + i + TW_THREADS);
+    if (i < nvec) st_out(dst + i, a);
+    if (i + TW_THREADS < nvec) st_out(dst + i + TW_THREADS, b);
+}
+
 // ---------------------------------------------------------------------------------------------
 // rowwise cast: TPR threads share a row and keep it in registers (CH 16-byte chunks each), so x is
 // read from HBM exactly once.  PRECALC: per-row scale supplied, true division.
@@ -597,6 +609,19 @@ int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pi
     if (width_bytes == 0 || rows == 0) return 0;
     return (int)cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
                                   to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice, (cudaStream_t)stream);
+}
+
+int qcc_stream_copy(const void *src, void *dst, size_t bytes, void *stream)
+{
+    if (bytes == 0) return 0;
+    if (!src || !dst) return QCC_ERR_ARG;
+    if (bytes % 16 != 0) return QCC_ERR_SHAPE;
+    if (!aligned16(src) || !aligned16(dst)) return QCC_ERR_ALIGN;
+    const int64_t nvec = (int64_t)(bytes / 16);
+    const int64_t grid = (nvec + TW_THREADS * 2 - 1) / (TW_THREADS * 2);
+    if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    stream_copy_kernel<<<(unsigned)grid, TW_THREADS, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, nvec);
+    return (int)cudaGetLastError();
 }
 
 size_t qcc_amax_workspace_bytes(void) { return (size_t)(AMAX_MAX_CTAS + 64) * sizeof(uint32_t); }

@@ -160,57 +160,6 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
     }
 }
 
-// The same cast with the four 16-byte pieces of a 1x32 block spread over four adjacent lanes: every load instruction of a
-// warp covers 512 contiguous bytes and every store instruction 256, the block maximum takes two shuffles, and four
-// neighbouring blocks' scale bytes leave as one 4-byte store (plain layout: four consecutive bytes; blocked layout: the
-// four columns of one row of an atom).  N % 128 == 0 (four blocks never straddle a row).
-#ifndef QCC_RC_UNROLL
-#define QCC_RC_UNROLL 4
-#endif
-constexpr int RC_UNROLL = QCC_RC_UNROLL;
-
-template <bool SWZ, bool FLOOR>
-__global__ void __launch_bounds__(RS_THREADS)
-mxfp8_rowwise_coal_kernel(const uint16_t *__restrict__ x, uint32_t nchunks, uint32_t nb, FastDiv32 div_nb,
-                          uint8_t *__restrict__ q, uint8_t *__restrict__ s)
-{
-    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
-    uint2 *qv = reinterpret_cast<uint2 *>(q);
-    const uint32_t base = blockIdx.x * (RS_THREADS * RC_UNROLL) + threadIdx.x;
-    uint4 c[RC_UNROLL];
-#pragma unroll
-    for (int u = 0; u < RC_UNROLL; u++) {
-        const uint32_t ci = base + u * RS_THREADS;
-        c[u] = ci < nchunks ? ld_nc_v4(xv + ci) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int u = 0; u < RC_UNROLL; u++) {
-        const uint32_t ci = base + u * RS_THREADS;
-        const bool ok = ci < nchunks;
-        uint32_t a = absmax2(absmax2(0u, c[u].x), absmax2(c[u].y, c[u].z));
-        a = absmax2_acc(a, c[u].w);
-        a = absmax2_acc(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
-        a = absmax2_acc(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
-        const uint32_t e = e8m0_from_amax<FLOOR>(hmax_halves_f32(a));
-        const float rcp = e8m0_recip<FLOOR>(e);
-        uint2 o;
-        o.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[u].x), bf16hi(c[u].x), bf16lo(c[u].y), bf16hi(c[u].y), rcp);
-        o.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[u].z), bf16hi(c[u].z), bf16lo(c[u].w), bf16hi(c[u].w), rcp);
-        if (ok) st_out(qv + ci, o);
-        uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 4) << 8);
-        v |= __shfl_down_sync(0xFFFFFFFFu, v, 8) << 16;
-        if (ok && (threadIdx.x & 15) == 0) {
-            const uint32_t bi = ci >> 2;
-            if (SWZ) {
-                const uint32_t row = div_nb.div(bi);
-                *reinterpret_cast<uint32_t *>(s + blocked_offset(row, bi - row * nb, nb >> 2)) = v;
-            } else {
-                *reinterpret_cast<uint32_t *>(s + bi) = v;
-            }
-        }
-    }
-}
-
 // mxfp4 (gold mxfp4_f G:607-617): the same 1x32 blocks and RCEIL e8m0 scale, descaled by 6 instead of 448,
 // elements as e2m1 packed two per byte (even element in the low nibble).
 template <bool SWZ>
@@ -619,20 +568,6 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
         const unsigned grid = (nblocks + RS_THREADS * RS_UNROLL - 1) / (RS_THREADS * RS_UNROLL);
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
-#ifdef QCC_RS_COAL
-        if (!amax_mode && !g.row_map && !g.blk_src && (nb & 3) == 0 && nblocks < (1u << 30)) {
-            const uint32_t nchunks = nblocks * 4;
-            const unsigned cgrid = (nchunks + RS_THREADS * RC_UNROLL - 1) / (RS_THREADS * RC_UNROLL);
-            if (swz) {
-                if (fl) mxfp8_rowwise_coal_kernel<true, true><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
-                else mxfp8_rowwise_coal_kernel<true, false><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
-            } else {
-                if (fl) mxfp8_rowwise_coal_kernel<false, true><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
-                else mxfp8_rowwise_coal_kernel<false, false><<<cgrid, RS_THREADS, 0, st>>>(xp, nchunks, (uint32_t)nb, dv, qp, skp);
-            }
-            return (int)cudaGetLastError();
-        }
-#endif
 #define QCC_RS(SWZ_, FL_, AM_) \
     mxfp8_rowwise_stream_kernel<SWZ_, FL_, AM_><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g, sink)
 #define QCC_RS_AM(SWZ_, FL_) \

@@ -185,6 +185,53 @@ nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint3
     }
 }
 
+// The same cast for M % 128 == 0, N % 128 == 0 with the CTAs laid over 128-row x 128-column tiles instead of the flat
+// stream: a tile is two whole 512-byte atoms of the blocked scale layout, so the scale bytes go through 1 KB of shared
+// memory and leave as 64 contiguous 16-byte stores per CTA.  In the flat form every lane pair's 4-byte store lands in an
+// atom of its own (the four bytes of a row, 512 bytes from the next pair's): four times as many store transactions as
+// the packed data itself needs.  Thread = (row of the upper or lower 64-row half, 32-column pair of blocks); a warp
+// reads 256 contiguous bytes of each of 8 rows.
+#ifndef QCC_NV_ATOM_MIN_BLOCKS
+#define QCC_NV_ATOM_MIN_BLOCKS 0
+#endif
+template <int SRC>
+__global__ void __launch_bounds__(NV_THREADS)
+nvfp4_rowwise_atom_kernel(const uint16_t *__restrict__ x, uint32_t tiles_n, uint32_t N, const float *__restrict__ outer,
+                          uint8_t *__restrict__ q, uint8_t *__restrict__ s, float *__restrict__ outer_out, int rev)
+{
+    __shared__ __align__(16) uint8_t stage[2 * 512];
+    const uint32_t cta = rev ? gridDim.x - 1u - blockIdx.x : blockIdx.x;
+    const uint32_t tile_m = cta / tiles_n, tile_n = cta - tile_m * tiles_n;
+    const uint32_t pr = threadIdx.x & 3u, rr = threadIdx.x >> 2;
+    uint4 c[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const size_t row = (size_t)tile_m * 128u + rr + 64u * u;
+        const uint4 *p = reinterpret_cast<const uint4 *>(x + row * N + tile_n * 128u + pr * 32u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[u][i] = ld_v4(p + i);
+    }
+    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+    const float inv = __fdiv_rn(1.0f, o);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const uint32_t r = rr + 64u * u;                       // row inside the tile
+        const size_t row = (size_t)tile_m * 128u + r;
+        uint2 p0, p1;
+        const uint32_t b0 = nvfp4_quant16<false>(c[u][0], c[u][1], o, inv, nullptr, 0, 0, 0, p0);
+        const uint32_t b1 = nvfp4_quant16<false>(c[u][2], c[u][3], o, inv, nullptr, 0, 0, 0, p1);
+        st_out(reinterpret_cast<uint4 *>(q + row * (N >> 1) + tile_n * 64u + pr * 16u), make_uint4(p0.x, p0.y, p1.x, p1.y));
+        *reinterpret_cast<uint16_t *>(stage + (pr >> 1) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (pr & 1u) * 2u) =
+            (uint16_t)(b0 | (b1 << 8));
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        const uint32_t a = threadIdx.x >> 5, i = threadIdx.x & 31u;
+        const size_t off = ((size_t)tile_m * (N >> 6) + tile_n * 2u + a) * 512u + i * 16u;
+        *reinterpret_cast<uint4 *>(s + off) = *reinterpret_cast<const uint4 *>(stage + a * 512u + i * 16u);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // transposed cast: one-shot tile kernel
 // ---------------------------------------------------------------------------------------------
@@ -495,6 +542,17 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
     }
 #ifndef QCC_NV_PAIR_MIN_BLOCKS
 #define QCC_NV_PAIR_MIN_BLOCKS 0
+#endif
+#ifndef QCC_NV_NO_ATOM
+    if (swz && !sr && outer_per_row == 0 && !pdl && (M & 127) == 0 && (N & 127) == 0 && nblocks >= (uint32_t)QCC_NV_ATOM_MIN_BLOCKS) {
+        const uint32_t tiles_n = (uint32_t)(N >> 7);
+        const unsigned agrid = (unsigned)((M >> 7) * tiles_n);
+        if (src == QCC_SRC_SCALE)
+            nvfp4_rowwise_atom_kernel<QCC_SRC_SCALE><<<agrid, NV_THREADS, 0, st>>>(xp, tiles_n, (uint32_t)N, outer, qp, sp, outer_out, rev);
+        else
+            nvfp4_rowwise_atom_kernel<QCC_SRC_AMAX><<<agrid, NV_THREADS, 0, st>>>(xp, tiles_n, (uint32_t)N, outer, qp, sp, outer_out, rev);
+        return (int)cudaGetLastError();
+    }
 #endif
     if (swz && !sr && outer_per_row == 0 && (nb & 3) == 0 && nblocks >= (uint32_t)QCC_NV_PAIR_MIN_BLOCKS) {   // (the plain layout gains nothing from pairing)
         const uint32_t npairs = nblocks >> 1;

@@ -81,6 +81,19 @@ def philox_key(seed, offset=0, device="cuda"):
     return t.view(torch.uint64)
 
 
+def stream_copy_cuda(src, dst):
+    """dst = src by this library's plain copy kernel (same access pattern as the streaming casts): the yardstick the
+    benchmarks hold the casts against.  Tensors of equal byte size, contiguous, a multiple of 16 bytes."""
+    lib = L.load()
+    assert src.is_cuda and dst.is_cuda and src.is_contiguous() and dst.is_contiguous()
+    nbytes = src.numel() * src.element_size()
+    assert nbytes == dst.numel() * dst.element_size(), "source and destination differ in size"
+    with _on_device(src.device):
+        L.check(lib.qcc_stream_copy(_p(src), _p(dst), nbytes, _stream(src)), "stream_copy")
+    L.launch_count += 1
+    return dst
+
+
 # --------------------------------------------------------------------------------------------
 # amax and per-tensor scales
 # --------------------------------------------------------------------------------------------

@@ -513,3 +513,14 @@ def test_recipe_index_mirrors_reference_backends():
         inputs = r.example_input_fn(256, 256)
         outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
         assert isinstance(outs, tuple) and all(o.is_cuda for o in outs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [16, 4096 + 16, 1 << 20, (1 << 22) + 48])
+def test_stream_copy_yardstick(n):
+    """The benchmarks' plain-copy kernel copies exactly (sizes around the 8 KB per-CTA step)."""
+    src = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(n + 32, dtype=torch.uint8, device="cuda")
+    Q.stream_copy_cuda(src, dst[:n])
+    assert torch.equal(dst[:n], src) and int(dst[n:].sum()) == 0
+    assert L.load().qcc_stream_copy(src.data_ptr(), dst.data_ptr(), 24, None) == -1
