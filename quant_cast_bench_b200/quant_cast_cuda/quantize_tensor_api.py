@@ -115,7 +115,9 @@ def quantize_tensor(input: Tensor, *, qdata_dtype: torch.dtype = torch.float8_e4
                     orientation: QuantOrientation = QuantOrientation.NATURAL,
                     swizzle_type=SwizzleType.SWIZZLE_32_4_4, rounding_mode: RoundingMode = RoundingMode.RTNE,
                     random_key: Tensor | None = None, outer_scale: Tensor | None = None) -> tuple[Tensor, Tensor]:
-    """One-orientation block-scaled cast: returns (qdata, scale).  See the module docstring for the table."""
+    """One-orientation block-scaled cast: returns (qdata, scale).  See the module docstring for the table.
+    `input` must be bfloat16 (the reference's API documents bf16 or fp32 input; this backend's kernels read bf16 only --
+    cast fp32 activations with `.to(torch.bfloat16)` first, which is also what the gold recipes' bf16 amax assumes)."""
     assert input.dim() in (2, 3), f"only 2D or 3D input supported, got {input.dim()}D"
     swz = _is_swz(swizzle_type)
     sr = rounding_mode == RoundingMode.STOCHASTIC
