@@ -200,7 +200,12 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax)
 // inner = e4m3(clamp((amax / 6) / outer, 2^-6, 448)); recip = (1 / outer) / fp32(inner).
 __device__ __forceinline__ uint32_t nvfp4_inner(float amax, float outer, float inv_outer, float &recip)
 {
-    float f = __fdiv_rn(__fdiv_rn(amax, 6.0f), outer);   // the streaming cast hides the slow path behind its loads
+    // A zero dividend sends the IEEE division down its slow path, and a warp whose lanes hold blocks of different rows
+    // pays for it whenever ONE of them is an all-zero block.  0 / 6 / outer is 0 for any finite outer > 0, so there a
+    // stand-in is divided and its quotient replaced by 0; for any other outer the division runs as written.
+    const bool shortcut = !(amax > 0.0f) && outer > 0.0f && outer < __int_as_float(0x7F800000);
+    float f = __fdiv_rn(__fdiv_rn(shortcut ? 1.0f : amax, 6.0f), outer);
+    f = shortcut ? 0.0f : f;
     f = fminf(fmaxf(f, 0.015625f), 448.0f);
     uint32_t byte = cvt_fp8x2<QCC_FMT_E4M3>(f, 0.0f) & 0xFFu;
     recip = __fdiv_rn(inv_outer, e4m3_to_f32(byte));

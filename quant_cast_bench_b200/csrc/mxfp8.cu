@@ -100,7 +100,10 @@ struct AmaxSink {
 
 // AMAX: 0 the cast alone; 1 / 2 also the tensor's amax (see AmaxSink).
 template <bool SWZ, bool FLOOR, int AMAX = 0>
-__global__ void __launch_bounds__(RS_THREADS, AMAX ? 5 : 1)      // the amax forms would take 52 registers: 4 CTAs per SM instead of 5
+#ifndef QCC_RS_MINCTAS
+#define QCC_RS_MINCTAS 5
+#endif
+__global__ void __launch_bounds__(RS_THREADS, QCC_RS_MINCTAS)    // (the amax forms would take 52 registers: 4 CTAs per SM instead of 5)
 mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                             uint8_t *__restrict__ q, uint8_t *__restrict__ s, GroupTables g, AmaxSink sink)
 {

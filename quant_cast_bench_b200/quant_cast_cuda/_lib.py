@@ -133,7 +133,9 @@ def device_error():
     reported anything, 1..15 a TMA barrier wait that ran out, 16 invalid token-group offsets, 17 an unsupported transform matrix, 18 a colwise cast
     that gave up waiting for the column maxima of a panel, 19 a wait for another rank's amax that ran out."""
     v = ctypes.c_uint(0)
-    check(load().qcc_device_error(ctypes.byref(v)), "device_error")
+    rc = load().qcc_device_error(ctypes.byref(v))       # (not through check(): that is what calls this under QCC_CHECK_DEVICE)
+    if rc:
+        raise RuntimeError(f"device_error: CUDA error {rc}")
     return int(v.value)
 
 

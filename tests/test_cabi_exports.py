@@ -43,3 +43,23 @@ def test_no_cpu_path():
     x = torch.zeros(32, 32, dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         Q.mxfp8_cuda(x)
+
+
+def test_opt_in_device_check_raises_on_a_recorded_error(monkeypatch):
+    """QCC_CHECK_DEVICE=1: after every call the recipe layer reads the device error word and raises when a kernel gave
+    up a bounded wait (host logic only: the library is replaced by a stand-in that reports code 19)."""
+    import pytest
+
+    class Recorded:
+        def qcc_device_error(self, ref):
+            ref._obj.value = 19
+            return 0
+
+    monkeypatch.setattr(L, "_lib", Recorded())
+    monkeypatch.setattr(L, "CHECK_DEVICE", True)
+    with pytest.raises(RuntimeError, match="device error 19"):
+        L.check(0, "some cast")
+    monkeypatch.setattr(L, "CHECK_DEVICE", False)
+    L.check(0, "some cast")                      # off by default: no synchronisation, no raise
+    with pytest.raises(ValueError):
+        L.check(-1, "some cast")
