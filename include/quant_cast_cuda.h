@@ -48,7 +48,18 @@ extern "C" {
                           the outer scale, i.e. qcc_xchg_resolve) is still running; it waits for that kernel before it
                           reads the scale.  Only for a launch directly behind the kernel that writes `outer`.        */
 
-/* what qcc_amax_finalize writes */
+/* How a tensor is divided by a constant (amax / 448, amax / 57344, amax / 2688, block amax / 6).  The gold recipes
+ * write `tensor / python_scalar`: PyTorch's CPU kernels compute that as one IEEE division, its CUDA kernels as a
+ * multiplication with the fp32 reciprocal of the scalar (aten/src/ATen/native/cuda/BinaryDivTrueKernel.cu), and the two
+ * differ in the last bit for about half of all operands.  Default: the IEEE division (the gold recipes on the CPU).
+ * With QCC_RECIP_DIV: a * fl(1 / c), bit-identical to the gold recipes run eagerly on a CUDA device.  Accepted in the
+ * `mode` of the amax entry points (qcc_amax_bf16, qcc_amax_bf16_noalloc, qcc_scale_from_amax, qcc_xchg_resolve,
+ * qcc_amax_block128x128, qcc_nvfp4_rht_amax), in the `fmt` of qcc_fp8_tensorwise_from_amax, qcc_fp8_rowwise and
+ * qcc_fp8_colwise, and in the `flags` of qcc_fp8_block128, qcc_fp8_block128x128 and every qcc_nvfp4* cast.  Casts that
+ * only multiply (mxfp8, mxfp4, a cast by a given scale) have no such division and do not take it. */
+#define QCC_RECIP_DIV 0x800
+
+/* what the amax entry points write (their `mode`) */
 #define QCC_AMAX_RAW 0        /* the amax itself, fp32                                   */
 #define QCC_AMAX_FP8_SCALE 1  /* max(amax, bf16(1e-12)) / fp8_max     G:1179-1183        */
 #define QCC_AMAX_NVFP4_SCALE 2 /* amax / (448 * 6)                    G:1243-1246        */
@@ -254,7 +265,8 @@ int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, void *qk, f
                      void *stream);
 
 /* 128x128 blocks: q (M, N), scale (M/128, N/128) fp32 (deepseek_128x128_f G:141-161).  M % 128 == 0, N % 128 == 0. */
-int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, void *q, float *scale, void *stream);
+int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, int flags /* 0 or QCC_RECIP_DIV */, void *q, float *scale,
+                         void *stream);
 
 /* out (M/128, N/128) fp32 = max |x| of every 128x128 block (QCC_AMAX_RAW) or that maximum / 2688
  * (QCC_AMAX_NVFP4_SCALE: nvfp4_blocked_outer_scale G:1601-1606).  M % 128 == 0, N % 128 == 0. */

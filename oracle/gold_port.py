@@ -42,7 +42,40 @@ def lib():
         _lib.qco_fp8_blockwise.restype = ctypes.c_int
         _lib.qco_amax_block128x128.restype = ctypes.c_int
         _lib.qco_hadamard_rht_t.restype = ctypes.c_int
+        _lib.qco_get_recip_div.restype = ctypes.c_int
     return _lib
+
+
+def set_scalar_division(mode: str) -> str:
+    """How `tensor / python_scalar` of the gold recipes is restated: "ieee" (default; eager PyTorch on the CPU) or
+    "cuda_eager" (eager PyTorch on a CUDA device multiplies by the fp32 reciprocal of the scalar).  Returns the
+    previous setting."""
+    assert mode in ("ieee", "cuda_eager"), mode
+    prev = "cuda_eager" if lib().qco_get_recip_div() else "ieee"
+    lib().qco_set_recip_div(int(mode == "cuda_eager"))
+    return prev
+
+
+class scalar_division:
+    """`with scalar_division("cuda_eager"): ...`"""
+
+    def __init__(self, mode):
+        self.mode = mode
+
+    def __enter__(self):
+        self.prev = set_scalar_division(self.mode)
+        return self
+
+    def __exit__(self, *exc):
+        set_scalar_division(self.prev)
+        return False
+
+
+def _div_const(t, c):
+    """t / c for a fp32 tensor t and a Python scalar c, under the current setting."""
+    if lib().qco_get_recip_div():
+        return t * (torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(c), dtype=torch.float32))
+    return t / c
 
 
 def num_threads() -> int:
@@ -488,7 +521,7 @@ def hadamard_rht_t(x, rht):
 
 def nvfp4_rht_outer_scale_m(x, rht):
     """The dim-m outer scale of _nvfp4_gs_swizzle_dim_k_dim_m_rht_inputs (G:1364-1365)."""
-    return hadamard_rht_t(x, rht).abs().to(torch.float32).amax() / (448.0 * 6.0)
+    return _div_const(hadamard_rht_t(x, rht).abs().to(torch.float32).amax(), 448.0 * 6.0)
 
 
 def nvfp4_gs_swizzle_dim_k_dim_m_rht_f(x, outer_scale_k, outer_scale_m, rht, **kwargs):

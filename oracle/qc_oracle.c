@@ -90,6 +90,22 @@ static inline uint8_t f32_to_fp8_fmt(float f, int fmt)
 
 static inline float fp8_max_fmt(int fmt) { return fmt == QC_FMT_E5M2 ? 57344.0f : 448.0f; }
 
+/* `tensor / python_scalar` of the gold recipes.  Eager PyTorch computes it as one IEEE division on the CPU, and as a
+ * multiplication with the fp32 reciprocal of the scalar on a CUDA device (aten/src/ATen/native/cuda/
+ * BinaryDivTrueKernel.cu: "a * (1 / b)" when b is a host scalar).  qco_set_recip_div(1) selects the second form for
+ * every such division below (amax / 448, amax / 57344, amax / 2688, block amax / 6); the default is the first. */
+static int g_recip_div = 0;
+void qco_set_recip_div(int on) { g_recip_div = on != 0; }
+int qco_get_recip_div(void) { return g_recip_div; }
+static inline float div_by_const(float a, float c)
+{
+    if (g_recip_div) {
+        volatile float inv = 1.0f / c;   /* rounded to fp32 before the product */
+        return a * inv;
+    }
+    return a / c;
+}
+
 /* e4m3fn byte -> fp32 (exact).  Inverse of the cast at G:1259 as read back at G:1261. */
 static inline float e4m3_to_f32(uint8_t b)
 {
@@ -289,7 +305,7 @@ void qco_fp8_scale_from_amax(float amax, int fmt, float *scale)
 {
     const float tiny = u2f(0x2B8D0000u);                    /* bf16(1e-12) widened */
     float a = amax < tiny ? tiny : amax;
-    *scale = a / fp8_max_fmt(fmt);
+    *scale = div_by_const(a, fp8_max_fmt(fmt));
 }
 
 void qco_fp8_tensorwise_scale(const uint16_t *x, int64_t n, int fmt, float *scale)
@@ -313,13 +329,13 @@ int qco_amax_block128x128(const uint16_t *x, int64_t M, int64_t N, float div, fl
                 uint16_t a = bf16_abs(x[(br * 128 + r) * N + bc * 128 + c]);
                 if (a > best) best = a;
             }
-        out[bi] = bf16_to_f32(best) / div;
+        out[bi] = div_by_const(bf16_to_f32(best), div);
     }
     return 0;
 }
 
 /* amax -> nvfp4 per-tensor outer scale = amax / (448 * 6), no clamp.  G:1243-1246. */
-void qco_nvfp4_scale_from_amax(float amax, float *scale) { *scale = amax / 2688.0f; }
+void qco_nvfp4_scale_from_amax(float amax, float *scale) { *scale = div_by_const(amax, 2688.0f); }
 
 void qco_nvfp4_gs_scale(const uint16_t *x, int64_t n, float *scale)
 {
@@ -452,7 +468,7 @@ int qco_fp8_blockwise(const uint16_t *x, int64_t M, int64_t N, int64_t bm, int64
                 if (a > best) best = a;
             }
         float amax = bf16_to_f32(best);
-        float s = (amax < tiny ? tiny : amax) / 448.0f;
+        float s = div_by_const(amax < tiny ? tiny : amax, 448.0f);
         float inv = 1.0f / s;
         scale[transposed ? bc * nbr + br : br * nbc + bc] = s;
         for (int64_t r = 0; r < bm; r++)
@@ -612,7 +628,7 @@ static inline uint8_t nvfp4_block(const float v[16], float amax, float outer, ui
                                   int sr, uint64_t flat0, int64_t flat_stride, uint64_t seed,
                                   uint64_t offset)
 {
-    float inner_f = (amax / 6.0f) / outer;
+    float inner_f = div_by_const(amax, 6.0f) / outer;
     if (inner_f < 0.015625f) inner_f = 0.015625f;
     if (inner_f > 448.0f) inner_f = 448.0f;
     uint8_t inner = f32_to_fp8(inner_f, 3, 7, 0x7E);

@@ -13,7 +13,8 @@
 //
 // Numerics: G = quant_cast_bench/quant_cast_gold/recipes.py of vkuzo/quant_cast_bench.  deepseek_1x128_f
 // G:103-110, deepseek_128x128_f G:141-161, deepseek_1x128_dim_m_f G:194-214, deepseek_1x128_dim_km_f G:251-277:
-// scale = clamp(amax, 1e-12) / 448 (IEEE division), q = e4m3(x * (1 / scale)).  The clamp happens in bf16 in the
+// scale = clamp(amax, 1e-12) / 448 (IEEE division; with QCC_RECIP_DIV the product with fl(1 / 448) that CUDA eager
+// computes), q = e4m3(x * (1 / scale)).  The clamp happens in bf16 in the
 // first three (bf16(1e-12) = 0x2B8D) and in fp32 in the fused recipe (G:264, G:268), which only shows in the
 // scale of an all-zero block.
 #include "common.cuh"
@@ -22,10 +23,10 @@
 namespace qcc {
 
 template <bool CLAMP_F32>
-__device__ __forceinline__ float block_scale(float amax)
+__device__ __forceinline__ float block_scale(float amax, bool recip_div)
 {
     const float a = fmaxf(amax, CLAMP_F32 ? 1e-12f : u2f(0x2B8D0000u));
-    return __fdiv_rn(a, 448.0f);
+    return div_by_const(a, 448.0f, recip_div);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -35,7 +36,8 @@ constexpr int B1_THREADS = 256;
 
 template <bool CLAMP_F32>
 __global__ void __launch_bounds__(B1_THREADS)
-fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t *__restrict__ q, float *__restrict__ scale)
+fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t *__restrict__ q, float *__restrict__ scale,
+                        int recip_div)
 {
     const uint32_t si = blockIdx.x * B1_THREADS + threadIdx.x;   // 32-element segment; four per block
     const bool ok = si < n_seg;
@@ -48,7 +50,7 @@ fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t 
     uint32_t m = f2u(amax_of_block(c));                          // non-negative floats order like integers
     m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-    const float s = block_scale<CLAMP_F32>(u2f(m));
+    const float s = block_scale<CLAMP_F32>(u2f(m), recip_div != 0);
     const float inv = __fdiv_rn(1.0f, s);
     uint4 o0, o1;
     quant_row_block(c, inv, o0, o1);
@@ -68,7 +70,7 @@ fp8_1x128_stream_kernel(const uint16_t *__restrict__ x, uint32_t n_seg, uint8_t 
 template <bool AMAX_ONLY>
 __global__ void __launch_bounds__(128, 4)
 fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *__restrict__ q, float *__restrict__ scale,
-                   float amax_div)
+                   float amax_div, int recip_div)
 {
     __shared__ uint32_t s_max[4];
     const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
@@ -89,10 +91,10 @@ fp8_128x128_kernel(const uint16_t *__restrict__ x, int N, int tiles_n, uint8_t *
     __syncthreads();
     m = max(max(s_max[0], s_max[1]), max(s_max[2], s_max[3]));
     if (AMAX_ONLY) {
-        if (t == 0) scale[blockIdx.x] = __fdiv_rn(u2f(m), amax_div);
+        if (t == 0) scale[blockIdx.x] = div_by_const(u2f(m), amax_div, recip_div != 0);
         return;
     }
-    const float s = block_scale<false>(u2f(m));
+    const float s = block_scale<false>(u2f(m), recip_div != 0);
     const float inv = __fdiv_rn(1.0f, s);
     uint8_t *qo = q + origin;
 #pragma unroll
@@ -127,11 +129,13 @@ __device__ __forceinline__ uint4 quant16(uint4 a, uint4 b, float inv)
     return o;
 }
 
-template <bool DO_K, bool CLAMP_F32>
+// RECIP: QCC_RECIP_DIV, as a template parameter because the kernel sits at its register limit.
+template <bool DO_K, bool CLAMP_F32, bool RECIP>
 __global__ void __launch_bounds__(128, 4)
 fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__restrict__ qk, float *__restrict__ sk,
                          uint8_t *__restrict__ qm, float *__restrict__ sm, int M, int N, int tiles_n)
 {
+    constexpr bool recip_div = RECIP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
@@ -164,7 +168,7 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
             a0 = absmax2_acc(absmax2_acc(a0, v.x), v.y);
             a1 = absmax2_acc(absmax2_acc(a1, v.z), v.w);
         }
-        const float s = block_scale<CLAMP_F32>(hmax_halves_f32(absmax2(a0, a1)));
+        const float s = block_scale<CLAMP_F32>(hmax_halves_f32(absmax2(a0, a1)), recip_div);
         const float inv = __fdiv_rn(1.0f, s);
         const uint32_t qrow = base + BT_QK_OFF + row_t * 128;
 #pragma unroll
@@ -216,7 +220,7 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
         const float am[4] = {u2f(a0 << 16), u2f(a0 & 0xFFFF0000u), u2f(a1 << 16), u2f(a1 & 0xFFFF0000u)};
 #pragma unroll
         for (int kk = 0; kk < 4; kk++) {
-            s[kk] = block_scale<CLAMP_F32>(am[kk]);
+            s[kk] = block_scale<CLAMP_F32>(am[kk], recip_div);
             inv[kk] = __fdiv_rn(1.0f, s[kk]);
         }
     }
@@ -272,10 +276,10 @@ fp8_block128_tile_kernel(const __grid_constant__ CUtensorMap tm_x, uint8_t *__re
     }
 }
 
-template <bool DO_K, bool CLAMP_F32>
-static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, uint8_t *qm, float *sm, int M, int N, cudaStream_t st)
+template <bool DO_K, bool CLAMP_F32, bool RECIP>
+static int launch_block128_tile_r(const CUtensorMap &tx, uint8_t *qk, float *sk, uint8_t *qm, float *sm, int M, int N, cudaStream_t st)
 {
-    auto kern = fp8_block128_tile_kernel<DO_K, CLAMP_F32>;
+    auto kern = fp8_block128_tile_kernel<DO_K, CLAMP_F32, RECIP>;
     constexpr int ALLOC = BT_ALLOC;
     static PerDeviceFlag configured;
     const int dev = current_device_slot();
@@ -294,6 +298,14 @@ static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, u
     return (int)cudaGetLastError();
 }
 
+template <bool DO_K, bool CLAMP_F32>
+static int launch_block128_tile(const CUtensorMap &tx, uint8_t *qk, float *sk, uint8_t *qm, float *sm, int M, int N, int recip_div,
+                                cudaStream_t st)
+{
+    return recip_div ? launch_block128_tile_r<DO_K, CLAMP_F32, true>(tx, qk, sk, qm, sm, M, N, st)
+                     : launch_block128_tile_r<DO_K, CLAMP_F32, false>(tx, qk, sk, qm, sm, M, N, st);
+}
+
 }  // namespace qcc
 
 using namespace qcc;
@@ -303,6 +315,7 @@ extern "C" int qcc_block128_device_error(unsigned int *out) { return read_clear_
 extern "C" int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, void *qk, float *sk, void *qm, float *sm,
                                 void *stream)
 {
+    const int recip_div = take_recip_div(flags);
     const bool row = flags & QCC_ROWWISE, col = flags & QCC_COLWISE;
     if (M == 0 || N == 0) return 0;
     if (!x || (!row && !col) || (flags & ~(QCC_ROWWISE | QCC_COLWISE))) return QCC_ERR_ARG;
@@ -315,7 +328,7 @@ extern "C" int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, 
         if (M * (N / 32) >= (1ll << 32) - B1_THREADS) return QCC_ERR_SHAPE;
         const uint32_t n_seg = (uint32_t)(M * (N / 32));
         fp8_1x128_stream_kernel<false><<<(n_seg + B1_THREADS - 1) / B1_THREADS, B1_THREADS, 0, st>>>(
-            (const uint16_t *)x, n_seg, (uint8_t *)qk, sk);
+            (const uint16_t *)x, n_seg, (uint8_t *)qk, sk, recip_div);
         return (int)cudaGetLastError();
     }
     CUtensorMap tx;
@@ -324,30 +337,31 @@ extern "C" int qcc_fp8_block128(const void *x, int64_t M, int64_t N, int flags, 
     uint32_t box[2] = {64, 128};
     int e = make_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (e) return e;
-    if (row) return launch_block128_tile<true, true>(tx, (uint8_t *)qk, sk, (uint8_t *)qm, sm, (int)M, (int)N, st);
-    return launch_block128_tile<false, false>(tx, nullptr, nullptr, (uint8_t *)qm, sm, (int)M, (int)N, st);
+    if (row) return launch_block128_tile<true, true>(tx, (uint8_t *)qk, sk, (uint8_t *)qm, sm, (int)M, (int)N, recip_div, st);
+    return launch_block128_tile<false, false>(tx, nullptr, nullptr, (uint8_t *)qm, sm, (int)M, (int)N, recip_div, st);
 }
 
-extern "C" int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, void *q, float *scale, void *stream)
+extern "C" int qcc_fp8_block128x128(const void *x, int64_t M, int64_t N, int flags, void *q, float *scale, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !q || !scale) return QCC_ERR_ARG;
+    if (!x || !q || !scale || (flags & ~QCC_RECIP_DIV)) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M % 128 != 0 || N % 128 != 0 || N > 0x7FFFFF00 || (M / 128) * (N / 128) > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
     const int tiles_n = (int)(N / 128);
     fp8_128x128_kernel<false><<<(unsigned)((M / 128) * tiles_n), 128, 0, (cudaStream_t)stream>>>(
-        (const uint16_t *)x, (int)N, tiles_n, (uint8_t *)q, scale, 1.0f);
+        (const uint16_t *)x, (int)N, tiles_n, (uint8_t *)q, scale, 1.0f, (flags & QCC_RECIP_DIV) ? 1 : 0);
     return (int)cudaGetLastError();
 }
 
 extern "C" int qcc_amax_block128x128(const void *x, int64_t M, int64_t N, int mode, float *out, void *stream)
 {
     if (M == 0 || N == 0) return 0;
+    const int recip_div = take_recip_div(mode);
     if (!x || !out || (mode != QCC_AMAX_RAW && mode != QCC_AMAX_NVFP4_SCALE)) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M % 128 != 0 || N % 128 != 0 || N > 0x7FFFFF00 || (M / 128) * (N / 128) > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     if (!aligned16(x)) return QCC_ERR_ALIGN;
     const int tiles_n = (int)(N / 128);
     fp8_128x128_kernel<true><<<(unsigned)((M / 128) * tiles_n), 128, 0, (cudaStream_t)stream>>>(
-        (const uint16_t *)x, (int)N, tiles_n, nullptr, out, mode == QCC_AMAX_NVFP4_SCALE ? 2688.0f : 1.0f);
+        (const uint16_t *)x, (int)N, tiles_n, nullptr, out, mode == QCC_AMAX_NVFP4_SCALE ? 2688.0f : 1.0f, recip_div);
     return (int)cudaGetLastError();
 }

@@ -123,7 +123,8 @@ __device__ __forceinline__ void fence_proxy_async_smem()
 template <int FMT>
 __global__ void __launch_bounds__(CWR_THREADS, 1)
 fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *amax_bits, uint32_t *done,
-                            uint8_t *__restrict__ q, float *__restrict__ scale_out, int M, int N, int strips, int np, int lag)
+                            uint8_t *__restrict__ q, float *__restrict__ scale_out, int M, int N, int strips, int np, int lag,
+                            int recip_div)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -248,7 +249,7 @@ fp8_colwise_resident_kernel(const __grid_constant__ CUtensorMap tm_x, uint32_t *
                     const int c = lane + 32 * h, Cn = col0_n + c;
                     float s = 1.0f;
                     if (Cn < N) {
-                        s = fp8_scale_from_amax<FMT>(u2f(__ldcg(amax_bits + Cn)));
+                        s = fp8_scale_from_amax<FMT>(u2f(__ldcg(amax_bits + Cn)), recip_div != 0);
                         if (t0 == 0) scale_out[Cn] = s;                         // the owner of row tile 0
                     }
                     s_rcp[(pn & 1) * 64 + c] = __fdiv_rn(1.0f, s);
@@ -340,7 +341,7 @@ static int resident_strips(int64_t M, int64_t N, int grid)
 
 template <int FMT>
 static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t *done, void *q, float *scale_out, int64_t M,
-                           int64_t N, int strips, int np, int grid, cudaStream_t st)
+                           int64_t N, int strips, int np, int grid, int recip_div, cudaStream_t st)
 {
     auto kern = fp8_colwise_resident_kernel<FMT>;
     static PerDeviceFlag configured, cooperative;
@@ -357,7 +358,7 @@ static int launch_resident(const CUtensorMap &tx, uint32_t *amax_bits, uint32_t 
     uint8_t *qp = (uint8_t *)q;
     int Mi = (int)M, Ni = (int)N;
     int lag = np >= 40 ? CWR_LAG : CWR_LAG - 1;               // few panels: the steps that only drain the pipeline weigh more
-    void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np, &lag};
+    void *args[] = {(void *)&tx, &amax_bits, &done, &qp, &scale_out, &Mi, &Ni, &strips, &np, &lag, &recip_div};
     const cudaError_t ce = cudaLaunchCooperativeKernel((const void *)kern, dim3((unsigned)grid), dim3(CWR_THREADS), args, CWR_ALLOC, st);
     if (ce == cudaErrorCooperativeLaunchTooLarge || ce == cudaErrorNotSupported || ce == cudaErrorLaunchOutOfResources) {
         cudaGetLastError();                                   // fewer SMs available than the device reports, or the context
@@ -376,6 +377,7 @@ using namespace qcc;
 int qcc_colwise_resident(const void *x, int64_t M, int64_t N, int fmt, void *q, float *scale_out, uint32_t *amax_bits,
                          cudaStream_t st)
 {
+    const int recip_div = take_recip_div(fmt);   // the caller passes QCC_RECIP_DIV inside fmt
     const int grid = sm_count();
     const int strips = resident_strips(M, N, grid);
     if (strips == 0) return 1;
@@ -389,8 +391,8 @@ int qcc_colwise_resident(const void *x, int64_t M, int64_t N, int fmt, void *q, 
     uint32_t *done = (uint32_t *)(((uintptr_t)(amax_bits + N) + 127) & ~(uintptr_t)127);
     cudaError_t ce = cudaMemsetAsync(amax_bits, 0, (size_t)((uint8_t *)(done + 32 * (np + 1)) - (uint8_t *)amax_bits), st);
     if (ce != cudaSuccess) return (int)ce;
-    return fmt == QCC_FMT_E5M2 ? launch_resident<QCC_FMT_E5M2>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, st)
-                               : launch_resident<QCC_FMT_E4M3>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, st);
+    return fmt == QCC_FMT_E5M2 ? launch_resident<QCC_FMT_E5M2>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, recip_div, st)
+                               : launch_resident<QCC_FMT_E4M3>(tx, amax_bits, done, q, scale_out, M, N, strips, np, grid, recip_div, st);
 }
 
 extern "C" int qcc_colwise_device_error(unsigned int *out) { return read_clear_device_error(out); }

@@ -187,24 +187,33 @@ __device__ __forceinline__ uint32_t e8m0_from_amax(float amax)
     return FLOOR ? e8m0_floor(amax) : e8m0_rceil(amax);
 }
 
+// a / c for a constant c, the way the gold recipes get `tensor / python_scalar`: one IEEE division when they run on
+// the CPU; under CUDA eager PyTorch multiplies by the fp32 reciprocal of the scalar instead (aten's
+// BinaryDivTrueKernel.cu: "a * (1 / b)" when b is a host scalar), which differs in the last bit for about half of
+// all operands.  `recip` (QCC_RECIP_DIV) selects the second form.
+__device__ __forceinline__ float div_by_const(float a, float c, bool recip)
+{
+    return recip ? __fmul_rn(a, __fdiv_rn(1.0f, c)) : __fdiv_rn(a, c);
+}
+
 // fp8 per-tensor / per-row scale from an amax: clamp at bf16(1e-12) (the clamp happens in bf16 in
-// the reference, G:304, G:1182), then an IEEE division by the format maximum.
+// the reference, G:304, G:1182), then the division by the format maximum.
 template <int FMT>
-__device__ __forceinline__ float fp8_scale_from_amax(float amax)
+__device__ __forceinline__ float fp8_scale_from_amax(float amax, bool recip)
 {
     float a = fmaxf(amax, u2f(0x2B8D0000u));
-    return __fdiv_rn(a, FMT == QCC_FMT_E5M2 ? 57344.0f : 448.0f);
+    return div_by_const(a, FMT == QCC_FMT_E5M2 ? 57344.0f : 448.0f, recip);
 }
 
 // nvfp4 inner (per-16) scale byte and the data multiplier.  G:1505-1513:
 // inner = e4m3(clamp((amax / 6) / outer, 2^-6, 448)); recip = (1 / outer) / fp32(inner).
-__device__ __forceinline__ uint32_t nvfp4_inner(float amax, float outer, float inv_outer, float &recip)
+__device__ __forceinline__ uint32_t nvfp4_inner(float amax, float outer, float inv_outer, float &recip, bool recip_div)
 {
     // A zero dividend sends the IEEE division down its slow path, and a warp whose lanes hold blocks of different rows
     // pays for it whenever ONE of them is an all-zero block.  0 / 6 / outer is 0 for any finite outer > 0, so there a
     // stand-in is divided and its quotient replaced by 0; for any other outer the division runs as written.
     const bool shortcut = !(amax > 0.0f) && outer > 0.0f && outer < __int_as_float(0x7F800000);
-    float f = __fdiv_rn(__fdiv_rn(shortcut ? 1.0f : amax, 6.0f), outer);
+    float f = __fdiv_rn(div_by_const(shortcut ? 1.0f : amax, 6.0f, recip_div), outer);
     f = shortcut ? 0.0f : f;
     f = fminf(fmaxf(f, 0.015625f), 448.0f);
     uint32_t byte = cvt_fp8x2<QCC_FMT_E4M3>(f, 0.0f) & 0xFFu;
@@ -220,12 +229,12 @@ __device__ __forceinline__ void nvfp4_fill_recip_lut(float *lut, float inv_outer
 {
     if (threadIdx.x < 128) lut[threadIdx.x] = __fdiv_rn(inv_outer, e4m3_to_f32(threadIdx.x));
 }
-__device__ __forceinline__ uint32_t nvfp4_inner_lut(float amax, float outer, const float *lut, float &recip)
+__device__ __forceinline__ uint32_t nvfp4_inner_lut(float amax, float outer, const float *lut, float &recip, bool recip_div)
 {
     // A zero dividend sends the IEEE division down its slow path (measured: 1 % all-zero rows cost the fused
     // two-orientation cast 20 %); 0 / 6 / outer is 0 for any finite outer > 0, so a stand-in is divided and its
     // quotient replaced by 0.
-    float f = __fdiv_rn(__fdiv_rn(amax > 0.0f ? amax : 1.0f, 6.0f), outer);
+    float f = __fdiv_rn(div_by_const(amax > 0.0f ? amax : 1.0f, 6.0f, recip_div), outer);
     f = amax > 0.0f ? f : 0.0f;
     f = fminf(fmaxf(f, 0.015625f), 448.0f);
     uint32_t byte = cvt_fp8x2<QCC_FMT_E4M3>(f, 0.0f) & 0xFFu;

@@ -78,11 +78,14 @@ __global__ void __launch_bounds__(AMAX_THREADS, AMAX_CTAS_PER_SM) amax_partial_k
 // the library image, so every GPU that loads the library keeps these 8 KB until the process exits.
 static __device__ __align__(256) uint32_t g_amax_noalloc_scratch[AMAX_MAX_CTAS];
 
+// mode: QCC_AMAX_*, with QCC_RECIP_DIV or-ed in when given
 __device__ __forceinline__ float amax_finish(float amax, int mode, int fmt)
 {
+    const bool recip = mode & QCC_RECIP_DIV;
+    mode &= ~QCC_RECIP_DIV;
     if (mode == QCC_AMAX_FP8_SCALE)
-        return fmt == QCC_FMT_E5M2 ? fp8_scale_from_amax<QCC_FMT_E5M2>(amax) : fp8_scale_from_amax<QCC_FMT_E4M3>(amax);
-    if (mode == QCC_AMAX_NVFP4_SCALE) return __fdiv_rn(amax, 2688.0f);
+        return fmt == QCC_FMT_E5M2 ? fp8_scale_from_amax<QCC_FMT_E5M2>(amax, recip) : fp8_scale_from_amax<QCC_FMT_E4M3>(amax, recip);
+    if (mode == QCC_AMAX_NVFP4_SCALE) return div_by_const(amax, 2688.0f, recip);
     return amax;
 }
 
@@ -191,7 +194,7 @@ constexpr int TW_UNROLL = QCC_TW_UNROLL;  // 16-element groups per thread (1 mea
 template <int FMT, int SRC>
 __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16_t *__restrict__ x, int64_t n,
                                                                    const float *__restrict__ scale,
-                                                                   float *__restrict__ scale_out, uint8_t *__restrict__ q)
+                                                                   float *__restrict__ scale_out, uint8_t *__restrict__ q, int recip_div)
 {
     const int64_t ngrp = n >> 4;  // groups of 16 elements
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(TW_THREADS) fp8_tensorwise_kernel(const uint16
     }
     float sc = __ldg(scale);
     if (SRC == QCC_SRC_AMAX) {
-        sc = fp8_scale_from_amax<FMT>(sc);
+        sc = fp8_scale_from_amax<FMT>(sc, recip_div != 0);
         if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) scale_out[0] = sc;
     }
     const float inv = __fdiv_rn(1.0f, sc);
@@ -240,9 +243,9 @@ __global__ void __launch_bounds__(TW_THREADS) stream_copy_kernel(const uint4 *__
 constexpr int RW_THREADS = 256;
 
 template <int FMT, int TPR, int CH, bool PRECALC>
-__global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_kernel(const uint16_t *__restrict__ x, int64_t M, int64_t N,
+__global__ void __launch_bounds__(RW_THREADS, (TPR == 256 && CH == 8) ? 5 : 1) fp8_rowwise_kernel(const uint16_t *__restrict__ x, int64_t M, int64_t N,
                                                                 const float *__restrict__ scale_in,
-                                                                uint8_t *__restrict__ q, float *__restrict__ scale_out)
+                                                                uint8_t *__restrict__ q, float *__restrict__ scale_out, int recip_div)
 {
     constexpr int ROWS = RW_THREADS / TPR;
     const int tr = threadIdx.x % TPR;
@@ -277,7 +280,7 @@ __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_kernel(const uint16_t 
 #pragma unroll
             for (int w = 0; w < WPR; w++) m = max(m, sm[lr * WPR + w]);
         }
-        s = fp8_scale_from_amax<FMT>(u2f(m));
+        s = fp8_scale_from_amax<FMT>(u2f(m), recip_div != 0);
         if (row_ok && tr == 0) scale_out[row] = s;
     }
     if (q == nullptr || !row_ok) return;
@@ -312,7 +315,7 @@ template <int FMT, bool PRECALC>
 __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_generic_kernel(const uint16_t *__restrict__ x, int64_t M,
                                                                         int64_t N, const float *__restrict__ scale_in,
                                                                         uint8_t *__restrict__ q,
-                                                                        float *__restrict__ scale_out)
+                                                                        float *__restrict__ scale_out, int recip_div)
 {
     const int64_t row = blockIdx.x;
     const uint16_t *xr = x + row * N;
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_generic_kernel(const u
         m = 0;
 #pragma unroll
         for (int w = 0; w < RW_THREADS / 32; w++) m = max(m, sm[w]);
-        s = fp8_scale_from_amax<FMT>(u2f(m));
+        s = fp8_scale_from_amax<FMT>(u2f(m), recip_div != 0);
         if (threadIdx.x == 0) scale_out[row] = s;
     }
     if (q == nullptr) return;
@@ -343,7 +346,7 @@ __global__ void __launch_bounds__(RW_THREADS) fp8_rowwise_generic_kernel(const u
 
 template <int FMT, bool PRECALC>
 static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scale_in, void *q, float *scale_out,
-                          cudaStream_t st)
+                          int recip_div, cudaStream_t st)
 {
     const uint16_t *xp = (const uint16_t *)x;
     uint8_t *qp = (uint8_t *)q;
@@ -351,7 +354,7 @@ static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scal
     do {                                                                                                     \
         constexpr int ROWS = RW_THREADS / (TPR);                                                             \
         unsigned grid = (unsigned)((M + ROWS - 1) / ROWS);                                                   \
-        fp8_rowwise_kernel<FMT, TPR, CH, PRECALC><<<grid, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out); \
+        fp8_rowwise_kernel<FMT, TPR, CH, PRECALC><<<grid, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out, recip_div); \
         return (int)cudaGetLastError();                                                                      \
     } while (0)
     if (N % 8 == 0 && N <= 16384 && M <= 0x7FFFFFFF) {
@@ -366,7 +369,7 @@ static int launch_rowwise(const void *x, int64_t M, int64_t N, const float *scal
     }
 #undef QCC_RW
     if (M > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    fp8_rowwise_generic_kernel<FMT, PRECALC><<<(unsigned)M, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out);
+    fp8_rowwise_generic_kernel<FMT, PRECALC><<<(unsigned)M, RW_THREADS, 0, st>>>(xp, M, N, scale_in, qp, scale_out, recip_div);
     return (int)cudaGetLastError();
 }
 
@@ -419,10 +422,10 @@ __global__ void __launch_bounds__(CW_AMAX_THREADS) fp8_colwise_amax_kernel(const
 
 // scale[c] = max(amax_c, bf16(1e-12)) / fp8_max from the finished column maxima
 template <int FMT>
-__global__ void colwise_scale_kernel(const uint32_t *__restrict__ amax_bits, float *__restrict__ scale, int N)
+__global__ void colwise_scale_kernel(const uint32_t *__restrict__ amax_bits, float *__restrict__ scale, int N, int recip_div)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c < N) scale[c] = fp8_scale_from_amax<FMT>(u2f(amax_bits[c]));
+    if (c < N) scale[c] = fp8_scale_from_amax<FMT>(u2f(amax_bits[c]), recip_div != 0);
 }
 
 constexpr int CW_PANEL = 64 * 128;                // one 64-column panel of a 64-row tile
@@ -436,7 +439,8 @@ constexpr int CW_ALLOC = CW_BAR_OFF + 32 + 1024;     // four barriers
 template <int FMT, bool PRECALC>
 __device__ __forceinline__ void colwise_cast_tile(uint32_t base, uint64_t *bar, uint32_t parity, const uint32_t *amax_bits,
                                                   const float *__restrict__ scale_in, uint8_t *__restrict__ q,
-                                                  float *__restrict__ scale_out, int M, int N, int tile_m, int tile_n)
+                                                  float *__restrict__ scale_out, int M, int N, int tile_m, int tile_n,
+                                                  bool recip_div)
 {
     const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float sc[4];   // multiplier (or divisor when PRECALC) of the four columns
@@ -448,7 +452,7 @@ __device__ __forceinline__ void colwise_cast_tile(uint32_t base, uint64_t *bar, 
             if (PRECALC) {
                 s = __ldg(scale_in + Cn);
             } else {
-                s = fp8_scale_from_amax<FMT>(u2f(__ldcg(amax_bits + Cn)));
+                s = fp8_scale_from_amax<FMT>(u2f(__ldcg(amax_bits + Cn)), recip_div);
                 if (tile_m == 0 && b == 0) scale_out[Cn] = s;
             }
         }
@@ -502,7 +506,7 @@ template <int FMT, bool PRECALC>
 __global__ void __launch_bounds__(64, 8)
 fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t *__restrict__ amax_bits,
                         const float *__restrict__ scale_in, uint8_t *__restrict__ q, float *__restrict__ scale_out, int M,
-                        int N, int tiles_n)
+                        int N, int tiles_n, int recip_div)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -519,12 +523,12 @@ fp8_colwise_cast_kernel(const __grid_constant__ CUtensorMap tm_x, const uint32_t
         tma_load_2d(sbase, &tm_x, bar, tile_n * 128, tile_m * 64);
         tma_load_2d(sbase + CW_PANEL, &tm_x, bar, tile_n * 128 + 64, tile_m * 64);
     }
-    colwise_cast_tile<FMT, PRECALC>(base, bar, 0, amax_bits, scale_in, q, scale_out, M, N, tile_m, tile_n);
+    colwise_cast_tile<FMT, PRECALC>(base, bar, 0, amax_bits, scale_in, q, scale_out, M, N, tile_m, tile_n, recip_div != 0);
 }
 
 template <int FMT, bool PRECALC>
 static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scale_in, void *q, float *scale_out,
-                          uint32_t *amax_bits, cudaStream_t st)
+                          uint32_t *amax_bits, int recip_div, cudaStream_t st)
 {
     CUtensorMap tx;
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
@@ -534,7 +538,7 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
     if (e) return e;
     if (!PRECALC && q != nullptr) {
         // one launch with the panel resident in shared memory where the shape allows it (colwise.cu)
-        const int rc = qcc_colwise_resident(x, M, N, FMT, q, scale_out, amax_bits, st);
+        const int rc = qcc_colwise_resident(x, M, N, FMT | (recip_div ? QCC_RECIP_DIV : 0), q, scale_out, amax_bits, st);
         if (rc != 1) return rc;
     }
     if (!PRECALC) {
@@ -545,7 +549,7 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
         ce = cudaGetLastError();
         if (ce != cudaSuccess) return (int)ce;
         if (q == nullptr) {     // the scales alone (colwise_precalc_scale G:438-442): one read of x, no cast
-            colwise_scale_kernel<FMT><<<(unsigned)((N + 255) / 256), 256, 0, st>>>(amax_bits, scale_out, (int)N);
+            colwise_scale_kernel<FMT><<<(unsigned)((N + 255) / 256), 256, 0, st>>>(amax_bits, scale_out, (int)N, recip_div);
             return (int)cudaGetLastError();
         }
     }
@@ -563,7 +567,7 @@ static int launch_colwise(const void *x, int64_t M, int64_t N, const float *scal
     const int tiles_n = (int)((N + 127) / 128), tiles_m = (int)((M + 63) / 64);
     const long long num_tiles = (long long)tiles_n * tiles_m;
     if (num_tiles > 0x7FFFFFFF) return QCC_ERR_SHAPE;
-    kern<<<(unsigned)num_tiles, 64, CW_ALLOC, st>>>(tx, amax_bits, scale_in, (uint8_t *)q, scale_out, (int)M, (int)N, tiles_n);
+    kern<<<(unsigned)num_tiles, 64, CW_ALLOC, st>>>(tx, amax_bits, scale_in, (uint8_t *)q, scale_out, (int)M, (int)N, tiles_n, recip_div);
     return (int)cudaGetLastError();
 }
 
@@ -648,8 +652,7 @@ int qcc_amax_bf16(const void *x, int64_t n, int mode, int fmt, float *out, void 
     const bool one_launch = (mode & QCC_AMAX_ONE_LAUNCH) != 0;
     mode &= ~QCC_AMAX_ONE_LAUNCH;
     if (!x || !out || !workspace || n < 0) return QCC_ERR_ARG;
-    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
-        return QCC_ERR_ARG;
+    if (!amax_mode_ok(mode) || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2)) return QCC_ERR_ARG;
     if (!aligned16(x)) return QCC_ERR_ALIGN;
     if (workspace_bytes < qcc_amax_workspace_bytes()) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -687,8 +690,7 @@ int qcc_amax_bf16_xchg(const void *x, int64_t n, void *state, void *stream)
 int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *out, void *stream)
 {
     if (!x || !out || n < 0) return QCC_ERR_ARG;
-    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
-        return QCC_ERR_ARG;
+    if (!amax_mode_ok(mode) || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2)) return QCC_ERR_ARG;
     if (!aligned16(x)) return QCC_ERR_ALIGN;
     if (n > QCC_AMAX_NOALLOC_MAX_ELEMS) return QCC_ERR_TOO_LARGE;
     // In host code the array's name is only a handle: the device address has to be asked for, once per
@@ -723,8 +725,7 @@ int qcc_amax_bf16_noalloc(const void *x, int64_t n, int mode, int fmt, float *ou
 int qcc_scale_from_amax(const float *amax, int mode, int fmt, float *out, void *stream)
 {
     if (!amax || !out) return QCC_ERR_ARG;
-    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
-        return QCC_ERR_ARG;
+    if (!amax_mode_ok(mode) || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2)) return QCC_ERR_ARG;
     scale_from_amax_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(amax, mode, fmt, out);
     return (int)cudaGetLastError();
 }
@@ -733,6 +734,7 @@ static int fp8_tensorwise_entry(const void *x, int64_t n, const float *src, int 
                                void *stream)
 {
     if (!src) return QCC_ERR_ARG;
+    const int recip_div = take_recip_div(fmt);
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (n == 0 && src_kind == QCC_SRC_SCALE) return 0;
     if (!x || !q || n < 0) return QCC_ERR_ARG;
@@ -743,7 +745,7 @@ static int fp8_tensorwise_entry(const void *x, int64_t n, const float *src, int 
     if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     if (grid < 1) grid = 1;
     const uint16_t *xp = (const uint16_t *)x;
-#define QCC_TW(FMT_, SRC_) fp8_tensorwise_kernel<FMT_, SRC_><<<(unsigned)grid, TW_THREADS, 0, st>>>(xp, n, src, scale_out, (uint8_t *)q)
+#define QCC_TW(FMT_, SRC_) fp8_tensorwise_kernel<FMT_, SRC_><<<(unsigned)grid, TW_THREADS, 0, st>>>(xp, n, src, scale_out, (uint8_t *)q, recip_div)
     if (fmt == QCC_FMT_E5M2) {
         if (src_kind == QCC_SRC_SCALE) QCC_TW(QCC_FMT_E5M2, QCC_SRC_SCALE); else QCC_TW(QCC_FMT_E5M2, QCC_SRC_AMAX);
     } else {
@@ -769,12 +771,13 @@ int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
 {
     if (M == 0 || N == 0) return 0;
     if (!x || !scale || M < 0 || N < 0) return QCC_ERR_ARG;
+    const int recip_div = take_recip_div(fmt);
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (N % 8 == 0 && (!aligned16(x) || (q && !aligned16(q)))) return QCC_ERR_ALIGN;
     if (M == 0 || N == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, st)
-                               : launch_rowwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, st);
+    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, recip_div, st)
+                               : launch_rowwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, recip_div, st);
 }
 
 int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
@@ -785,8 +788,8 @@ int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
     if (N % 8 == 0 && (!aligned16(x) || !aligned16(q))) return QCC_ERR_ALIGN;
     if (M == 0 || N == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, st)
-                               : launch_rowwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, st);
+    return fmt == QCC_FMT_E5M2 ? launch_rowwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, 0, st)
+                               : launch_rowwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, 0, st);
 }
 
 size_t qcc_fp8_colwise_workspace_bytes(int64_t M, int64_t N)
@@ -801,14 +804,15 @@ int qcc_fp8_colwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
 {
     if (M == 0 || N == 0) return 0;
     if (!x || !scale || !workspace || M < 0 || N < 0) return QCC_ERR_ARG;
+    const int recip_div = take_recip_div(fmt);
     if (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2) return QCC_ERR_ARG;
     if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00 || (M + CW_AMAX_ROWS - 1) / CW_AMAX_ROWS > 65535)
         return QCC_ERR_SHAPE;
     if (!aligned16(x) || (q && !aligned16(q)) || !aligned16(workspace)) return QCC_ERR_ALIGN;
     if (workspace_bytes < qcc_fp8_colwise_workspace_bytes(M, N)) return QCC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
-    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st)
-                               : launch_colwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, st);
+    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, recip_div, st)
+                               : launch_colwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, (uint32_t *)workspace, recip_div, st);
 }
 
 int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
@@ -819,8 +823,8 @@ int qcc_fp8_colwise_precalc(const void *x, int64_t M, int64_t N, const float *sc
     if (N % 8 != 0 || M % 16 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q)) return QCC_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
-    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, nullptr, st)
-                               : launch_colwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, nullptr, st);
+    return fmt == QCC_FMT_E5M2 ? launch_colwise<QCC_FMT_E5M2, true>(x, M, N, scale, q, nullptr, nullptr, 0, st)
+                               : launch_colwise<QCC_FMT_E4M3, true>(x, M, N, scale, q, nullptr, nullptr, 0, st);
 }
 
 }  // extern "C"

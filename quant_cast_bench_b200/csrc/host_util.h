@@ -11,6 +11,20 @@ namespace qcc {
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// QCC_RECIP_DIV rides in the `fmt`, `mode` or `flags` argument of an entry point: take_recip_div strips it from the
+// argument and returns 1 when it was set; amax_mode_ok checks an amax `mode` that may still carry it.
+inline int take_recip_div(int &arg)
+{
+    const int r = (arg & QCC_RECIP_DIV) ? 1 : 0;
+    arg &= ~QCC_RECIP_DIV;
+    return r;
+}
+inline bool amax_mode_ok(int mode)
+{
+    mode &= ~QCC_RECIP_DIV;
+    return mode >= QCC_AMAX_RAW && mode <= QCC_AMAX_NVFP4_SCALE;
+}
+
 // Per-device host-side caches ("this kernel's attributes are set on device d", "the address of this symbol on device
 // d").  Host threads may make their first call on a device at the same time: every writer stores the same value, and
 // the flags are atomics, so the only cost of that race is doing the set-up twice.  Devices 0..63; current_device_slot()

@@ -24,13 +24,13 @@ namespace qcc {
 // One block: 16 bf16 in two uint4 -> 8 packed bytes and the inner scale byte.
 template <bool SR>
 __device__ __forceinline__ uint32_t nvfp4_quant16(uint4 a, uint4 b, float outer, float inv_outer, const float *lut,
-                                                 uint64_t flat0, uint64_t seed, uint64_t offset, uint2 &packed)
+                                                 uint64_t flat0, uint64_t seed, uint64_t offset, uint2 &packed, bool recip_div)
 {
     uint32_t acc = absmax2(absmax2(absmax2(absmax2(0u, a.x), a.y), absmax2(a.z, a.w)),
                            absmax2(absmax2(b.x, b.y), absmax2(b.z, b.w)));
     float recip;
-    const uint32_t byte = lut ? nvfp4_inner_lut(hmax_halves_f32(acc), outer, lut, recip)
-                              : nvfp4_inner(hmax_halves_f32(acc), outer, inv_outer, recip);
+    const uint32_t byte = lut ? nvfp4_inner_lut(hmax_halves_f32(acc), outer, lut, recip, recip_div)
+                              : nvfp4_inner(hmax_halves_f32(acc), outer, inv_outer, recip, recip_div);
     float v[16] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w),
                    bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
 #pragma unroll
@@ -68,9 +68,12 @@ constexpr int NV_UNROLL = QCC_NV_UNROLL;
 // outer_out.  QCC_SRC_SCALE_PDL: as QCC_SRC_SCALE in a launch that overlaps the kernel that writes outer[0]: call after
 // the thread has issued its loads of x; one thread waits for that kernel, reads the value past L1 and hands it to the
 // CTA through shared memory (one barrier).  Called by all threads.
+// Kernel option word `opts`: bit 0 walk the tensor from its end (QCC_REVERSE), bit 1 divisions by a constant as
+// multiplications with its reciprocal (QCC_RECIP_DIV).
 #define QCC_SRC_SCALE_PDL 2
+constexpr int NV_OPT_REV = 1, NV_OPT_RECIP = 2;
 template <int SRC>
-__device__ __forceinline__ float nvfp4_outer_of_cta(const float *__restrict__ outer, float *__restrict__ outer_out)
+__device__ __forceinline__ float nvfp4_outer_of_cta(const float *__restrict__ outer, float *__restrict__ outer_out, bool recip_div)
 {
     if (SRC == QCC_SRC_SCALE) return __ldg(outer);
     if (SRC == QCC_SRC_SCALE_PDL) {
@@ -82,7 +85,7 @@ __device__ __forceinline__ float nvfp4_outer_of_cta(const float *__restrict__ ou
         __syncthreads();
         return sh;
     }
-    const float o = __fdiv_rn(__ldg(outer), 2688.0f);
+    const float o = div_by_const(__ldg(outer), 2688.0f, recip_div);
     if (blockIdx.x == 0 && threadIdx.x == 0 && outer_out) outer_out[0] = o;
     return o;
 }
@@ -93,8 +96,9 @@ template <bool SWZ, bool SR, int OUTER, int SRC = QCC_SRC_SCALE>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
                      const float *__restrict__ outer, const uint64_t *__restrict__ key, uint8_t *__restrict__ q,
-                     uint8_t *__restrict__ s, float *__restrict__ outer_out, int rev)
+                     uint8_t *__restrict__ s, float *__restrict__ outer_out, int opts)
 {
+    const bool rev = opts & NV_OPT_REV, recip_div = opts & NV_OPT_RECIP;
     const uint4 *xv = reinterpret_cast<const uint4 *>(x);
     uint2 *qv = reinterpret_cast<uint2 *>(q);
     uint64_t seed = 0, offset = 0;
@@ -116,7 +120,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         }
     }
     if (OUTER == 0) {
-        o_all = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+        o_all = nvfp4_outer_of_cta<SRC>(outer, outer_out, recip_div);
         inv_all = __fdiv_rn(1.0f, o_all);
     }
     // every lane runs the whole body (the shuffles below need the full warp); stores are predicated
@@ -130,7 +134,7 @@ nvfp4_rowwise_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t 
         if (OUTER == 1) { o = __ldg(outer + row); inv = __fdiv_rn(1.0f, o); }
         if (OUTER == 2) { o = __ldg(outer + (size_t)(row >> 7) * (nb >> 3) + (cb >> 3)); inv = __fdiv_rn(1.0f, o); }
         uint2 packed;
-        const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, lut, (uint64_t)bi * 16u, seed, offset, packed);
+        const uint32_t byte = nvfp4_quant16<SR>(a[u], b[u], o, inv, lut, (uint64_t)bi * 16u, seed, offset, packed, recip_div);
         if (ok) st_out(qv + bi, packed);
         if (SWZ) {
             // four consecutive lanes hold the four scale columns of one (row, column block)
@@ -155,8 +159,9 @@ template <int SRC>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint32_t nb, FastDiv32 div_np,
                           const float *__restrict__ outer, uint8_t *__restrict__ q, uint8_t *__restrict__ s,
-                          float *__restrict__ outer_out, int rev)
+                          float *__restrict__ outer_out, int opts)
 {
+    const bool rev = opts & NV_OPT_REV, recip_div = opts & NV_OPT_RECIP;
     // rev: CTAs walk the tensor from its end (CTAs are dispatched in index order), so a cast that follows another pass
     // over the same tensor starts with the part that pass left in L2
     const uint32_t cta = rev ? gridDim.x - 1u - blockIdx.x : blockIdx.x;
@@ -168,11 +173,11 @@ nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint3
 #pragma unroll
         for (int i = 0; i < 4; i++) c[i] = ld_v4(p + i);
     }
-    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out, recip_div);
     const float inv = __fdiv_rn(1.0f, o);
     uint2 p0, p1;
-    const uint32_t b0 = nvfp4_quant16<false>(c[0], c[1], o, inv, nullptr, 0, 0, 0, p0);
-    const uint32_t b1 = nvfp4_quant16<false>(c[2], c[3], o, inv, nullptr, 0, 0, 0, p1);
+    const uint32_t b0 = nvfp4_quant16<false>(c[0], c[1], o, inv, nullptr, 0, 0, 0, p0, recip_div);
+    const uint32_t b1 = nvfp4_quant16<false>(c[2], c[3], o, inv, nullptr, 0, 0, 0, p1, recip_div);
     if (ok) st_out(reinterpret_cast<uint4 *>(q) + pi, make_uint4(p0.x, p0.y, p1.x, p1.y));
     // an even lane and its neighbour hold the four scale columns of one (row, column block)
     const uint32_t b01 = b0 | (b1 << 8);
@@ -197,8 +202,9 @@ nvfp4_rowwise_pair_kernel(const uint16_t *__restrict__ x, uint32_t npairs, uint3
 template <int SRC>
 __global__ void __launch_bounds__(NV_THREADS)
 nvfp4_rowwise_atom_kernel(const uint16_t *__restrict__ x, uint32_t tiles_n, uint32_t N, const float *__restrict__ outer,
-                          uint8_t *__restrict__ q, uint8_t *__restrict__ s, float *__restrict__ outer_out, int rev)
+                          uint8_t *__restrict__ q, uint8_t *__restrict__ s, float *__restrict__ outer_out, int opts)
 {
+    const bool rev = opts & NV_OPT_REV, recip_div = opts & NV_OPT_RECIP;
     __shared__ __align__(16) uint8_t stage[2 * 512];
     const uint32_t cta = rev ? gridDim.x - 1u - blockIdx.x : blockIdx.x;
     const uint32_t tile_m = cta / tiles_n, tile_n = cta - tile_m * tiles_n;
@@ -211,15 +217,15 @@ nvfp4_rowwise_atom_kernel(const uint16_t *__restrict__ x, uint32_t tiles_n, uint
 #pragma unroll
         for (int i = 0; i < 4; i++) c[u][i] = ld_v4(p + i);
     }
-    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out);
+    const float o = nvfp4_outer_of_cta<SRC>(outer, outer_out, recip_div);
     const float inv = __fdiv_rn(1.0f, o);
 #pragma unroll
     for (int u = 0; u < 2; u++) {
         const uint32_t r = rr + 64u * u;                       // row inside the tile
         const size_t row = (size_t)tile_m * 128u + r;
         uint2 p0, p1;
-        const uint32_t b0 = nvfp4_quant16<false>(c[u][0], c[u][1], o, inv, nullptr, 0, 0, 0, p0);
-        const uint32_t b1 = nvfp4_quant16<false>(c[u][2], c[u][3], o, inv, nullptr, 0, 0, 0, p1);
+        const uint32_t b0 = nvfp4_quant16<false>(c[u][0], c[u][1], o, inv, nullptr, 0, 0, 0, p0, recip_div);
+        const uint32_t b1 = nvfp4_quant16<false>(c[u][2], c[u][3], o, inv, nullptr, 0, 0, 0, p1, recip_div);
         st_out(reinterpret_cast<uint4 *>(q + row * (N >> 1) + tile_n * 64u + pr * 16u), make_uint4(p0.x, p0.y, p1.x, p1.y));
         *reinterpret_cast<uint16_t *>(stage + (pr >> 1) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (pr & 1u) * 2u) =
             (uint16_t)(b0 | (b1 << 8));
@@ -252,7 +258,8 @@ constexpr int NVT_ALLOC = NVT_BAR_OFF + 512 + 1024;
 // are quantised -- the dim-m half of nvfp4_gs_swizzle_dim_k_dim_m_rht_f (G:1324-1333) and of its stochastic form
 // (G:1429-1438); the rowwise half is not transformed and has its own outer scale and Philox key.
 
-template <bool DO_K, bool SWZ, bool SR, bool RHT>
+// RECIP: QCC_RECIP_DIV, as a template parameter because the kernel sits at its register limit.
+template <bool DO_K, bool SWZ, bool SR, bool RHT, bool RECIP>
 __global__ void __launch_bounds__(128, (RHT && SR) ? 4 : 5)
 nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *__restrict__ outer_p,
                         const float *__restrict__ outer_k_p, const uint64_t *__restrict__ key,
@@ -260,6 +267,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
                         uint8_t *__restrict__ s, uint8_t *__restrict__ qk, uint8_t *__restrict__ sk, int M, int N,
                         int tiles_n)
 {
+    constexpr bool recip_div = RECIP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sbase = smem_raw + (base - smem_u32(smem_raw));
@@ -309,7 +317,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
             const uint4 b4 = lds_v4(prow + (((j0 + 1) ^ key7) << 4));
             uint2 packed;
             const uint64_t flat0 = (uint64_t)R * (uint64_t)N + (uint64_t)(tile_n * 128 + kb * 16);
-            uint32_t byte = nvfp4_quant16<SR>(a4, b4, outer_k, inv_outer_k, lut, flat0, seed_k, offset_k, packed);
+            uint32_t byte = nvfp4_quant16<SR>(a4, b4, outer_k, inv_outer_k, lut, flat0, seed_k, offset_k, packed, recip_div);
             const bool ok = R < M && (tile_n * 8 + kb) < nb16;
             sb[kb >> 2] |= (ok ? byte : 0u) << (8 * (kb & 3));
             asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(qrow + ((kb ^ key2) << 3)), "r"(packed.x), "r"(packed.y) : "memory");
@@ -385,7 +393,7 @@ nvfp4_transposed_kernel(const __grid_constant__ CUtensorMap tm_x, const float *_
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             float recip;
-            sc[k][h] = nvfp4_inner_lut(am[k], outer, lut, recip);
+            sc[k][h] = nvfp4_inner_lut(am[k], outer, lut, recip, recip_div);
             float v[16];
 #pragma unroll
             for (int r = 0; r < 16; r += 2) {
@@ -512,7 +520,7 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
                                const uint64_t *philox_key, void *q, void *s, float *outer_out, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !outer_src || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR | QCC_PDL | QCC_REVERSE))) return QCC_ERR_ARG;
+    if (!x || !outer_src || !q || !s || (flags & ~(QCC_SWIZZLE | QCC_SR | QCC_PDL | QCC_REVERSE | QCC_RECIP_DIV))) return QCC_ERR_ARG;
     if ((flags & QCC_SR) && !philox_key) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || N % 16 != 0) return QCC_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(q) || !aligned16(s)) return QCC_ERR_ALIGN;
@@ -529,7 +537,7 @@ static int nvfp4_rowwise_entry(const void *x, int64_t M, int64_t N, const void *
     const bool swz = flags & QCC_SWIZZLE, sr = flags & QCC_SR, pr = outer_per_row == 1;
     if (src != QCC_SRC_SCALE && sr) return QCC_ERR_ARG;
     // the overlapped form exists for the common case only: blocked scales, one outer scale, round to nearest
-    const int rev = (flags & QCC_REVERSE) ? 1 : 0;
+    const int rev = ((flags & QCC_REVERSE) ? NV_OPT_REV : 0) | ((flags & QCC_RECIP_DIV) ? NV_OPT_RECIP : 0);   // the kernels' option word
     const bool pdl = (flags & QCC_PDL) && swz && !sr && outer_kind == 0 && (nb & 3) == 0;
     if (outer_per_row == 2 && (sr || M % 128 != 0 || N % 128 != 0)) return sr ? QCC_ERR_ARG : QCC_ERR_SHAPE;
     const uint16_t *xp = (const uint16_t *)x;
@@ -607,12 +615,13 @@ struct NvtArgs {
     const uint64_t *key, *key_k;
     const uint16_t *rht;                   // non-null: transform down the rows
     uint8_t *q, *s, *qk, *sk;
+    int recip_div = 0;                     // QCC_RECIP_DIV given
 };
 
-template <bool DO_K, bool SWZ, bool SR, bool RHT>
-static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cudaStream_t st)
+template <bool DO_K, bool SWZ, bool SR, bool RHT, bool RECIP>
+static int launch_nvt_r(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cudaStream_t st)
 {
-    auto kern = nvfp4_transposed_kernel<DO_K, SWZ, SR, RHT>;
+    auto kern = nvfp4_transposed_kernel<DO_K, SWZ, SR, RHT, RECIP>;
     static PerDeviceFlag configured;
     const int dev = current_device_slot();
     if (dev < 0) return QCC_ERR_ARG;
@@ -631,6 +640,12 @@ static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cud
     return (int)cudaGetLastError();
 }
 
+template <bool DO_K, bool SWZ, bool SR, bool RHT>
+static int launch_nvt(const CUtensorMap &tx, const NvtArgs &a, int M, int N, cudaStream_t st)
+{
+    return a.recip_div ? launch_nvt_r<DO_K, SWZ, SR, RHT, true>(tx, a, M, N, st) : launch_nvt_r<DO_K, SWZ, SR, RHT, false>(tx, a, M, N, st);
+}
+
 template <bool DO_K, bool RHT>
 static int launch_nvt_flags(const CUtensorMap &tx, const NvtArgs &a, bool swz, bool sr, int M, int N, cudaStream_t st)
 {
@@ -640,10 +655,12 @@ static int launch_nvt_flags(const CUtensorMap &tx, const NvtArgs &a, bool swz, b
     return (sr && SR_OK) ? launch_nvt<DO_K, false, SR_OK, RHT>(tx, a, M, N, st) : launch_nvt<DO_K, false, false, RHT>(tx, a, M, N, st);
 }
 
-static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &a, int flags, bool both, void *stream)
+static int nvfp4_tile_entry(const void *x, int64_t M, int64_t N, const NvtArgs &args, int flags, bool both, void *stream)
 {
     if (M == 0 || N == 0) return 0;
-    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || !a.outer_k)) || (flags & ~(QCC_SWIZZLE | QCC_SR)))
+    NvtArgs a = args;
+    a.recip_div = (flags & QCC_RECIP_DIV) ? 1 : 0;
+    if (!x || !a.outer || !a.q || !a.s || (both && (!a.qk || !a.sk || !a.outer_k)) || (flags & ~(QCC_SWIZZLE | QCC_SR | QCC_RECIP_DIV)))
         return QCC_ERR_ARG;
     if ((flags & QCC_SR) && (!a.key || (both && !a.key_k))) return QCC_ERR_ARG;
     if (M < 0 || N < 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;

@@ -72,7 +72,7 @@ rht_t_amax_kernel(const uint16_t *__restrict__ x, int M, int N, const uint16_t *
 
 __global__ void rht_amax_finish_kernel(float *out, int mode)
 {
-    if (mode == QCC_AMAX_NVFP4_SCALE) out[0] = __fdiv_rn(out[0], 2688.0f);   // 448 * 6, no clamp (G:1365)
+    if ((mode & ~QCC_RECIP_DIV) == QCC_AMAX_NVFP4_SCALE) out[0] = div_by_const(out[0], 2688.0f, mode & QCC_RECIP_DIV);   // 448 * 6, no clamp (G:1365)
 }
 
 }  // namespace qcc
@@ -96,7 +96,7 @@ extern "C" int qcc_hadamard_rht(const void *x, int64_t M, int64_t N, const void 
 
 extern "C" int qcc_nvfp4_rht_amax(const void *x, int64_t M, int64_t N, const void *rht, int mode, float *out, void *stream)
 {
-    if (!x || !rht || !out || (mode != QCC_AMAX_RAW && mode != QCC_AMAX_NVFP4_SCALE)) return QCC_ERR_ARG;
+    if (!x || !rht || !out || ((mode & ~QCC_RECIP_DIV) != QCC_AMAX_RAW && (mode & ~QCC_RECIP_DIV) != QCC_AMAX_NVFP4_SCALE)) return QCC_ERR_ARG;
     if (M <= 0 || N <= 0 || M % 16 != 0 || N % 4 != 0 || M > 0x7FFFFF00 || N > 0x7FFFFF00) return QCC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(x) & 7u) != 0) return QCC_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;

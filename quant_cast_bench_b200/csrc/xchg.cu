@@ -16,10 +16,11 @@ __global__ void xchg_resolve_kernel(uint32_t *state, XchgPeers peers, int publis
     const float am = xchg_resolve(state, peers.world, e);
     if (threadIdx.x != 0) return;
     float r = am;
-    if (mode == QCC_AMAX_FP8_SCALE)
-        r = fmt == QCC_FMT_E5M2 ? fp8_scale_from_amax<QCC_FMT_E5M2>(am) : fp8_scale_from_amax<QCC_FMT_E4M3>(am);
-    else if (mode == QCC_AMAX_NVFP4_SCALE)
-        r = __fdiv_rn(am, 2688.0f);
+    const bool recip = mode & QCC_RECIP_DIV;   // mode: QCC_AMAX_*, with QCC_RECIP_DIV or-ed in when given
+    if ((mode & ~QCC_RECIP_DIV) == QCC_AMAX_FP8_SCALE)
+        r = fmt == QCC_FMT_E5M2 ? fp8_scale_from_amax<QCC_FMT_E5M2>(am, recip) : fp8_scale_from_amax<QCC_FMT_E4M3>(am, recip);
+    else if ((mode & ~QCC_RECIP_DIV) == QCC_AMAX_NVFP4_SCALE)
+        r = div_by_const(am, 2688.0f, recip);
     out[0] = r;
 }
 
@@ -103,7 +104,7 @@ int qcc_xchg_publish(const qcc_xchg_ref *ref, void *stream)
 int qcc_xchg_resolve(const qcc_xchg_ref *ref, int mode, int fmt, float *out, void *stream)
 {
     if (!ref || !out) return QCC_ERR_ARG;
-    if (mode < QCC_AMAX_RAW || mode > QCC_AMAX_NVFP4_SCALE || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
+    if (!amax_mode_ok(mode) || (fmt != QCC_FMT_E4M3 && fmt != QCC_FMT_E5M2))
         return QCC_ERR_ARG;
     XchgPeers peers;
     int rc = make_xchg_peers(&peers, ref->states, ref->world, ref->rank);

@@ -16,6 +16,7 @@ PDL, REVERSE = 0x200, 0x400
 XCHG_PUBLISH, XCHG_PDL = 1, 2
 AMAX_RAW, AMAX_FP8_SCALE, AMAX_NVFP4_SCALE = 0, 1, 2
 AMAX_ONE_LAUNCH = 0x100
+RECIP_DIV = 0x800   # QCC_RECIP_DIV: `tensor / constant` as PyTorch's CUDA kernels compute it, tensor * fl(1 / constant)
 XCHG_MAX_RANKS, XCHG_STATE_BYTES, XCHG_HANDLE_BYTES = 16, 1024, 64
 ERRORS = {
     -1: "shape: a dimension violates the divisibility this cast needs",
@@ -71,7 +72,7 @@ SIGNATURES = {
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_both": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp, _vp]),
     "qcc_fp8_block128": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
-    "qcc_fp8_block128x128": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "qcc_fp8_block128x128": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_amax_block128x128": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
     "qcc_hadamard_rht": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     "qcc_nvfp4_rht_amax": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp]),
@@ -108,6 +109,51 @@ def load():
             fn.argtypes = args
         _lib = lib
     return _lib
+
+
+# ---- how the casts divide by a constant ------------------------------------------------------------------------
+# The gold recipes write `amax / 448.0`, `amax / 2688.0`, `block_amax / 6.0`.  Run eagerly on the CPU PyTorch computes
+# an IEEE division there; run eagerly on a CUDA device it multiplies by the fp32 reciprocal of the scalar (aten's
+# BinaryDivTrueKernel.cu), and the two results differ in the last bit for about half of all operands.  "ieee" (default)
+# makes the casts bit-identical to the gold recipes on the CPU, "cuda_eager" to the gold recipes on a CUDA device.
+_SCALAR_DIVISIONS = ("ieee", "cuda_eager")
+_scalar_division = os.environ.get("QCC_SCALAR_DIVISION", "ieee")
+if _scalar_division not in _SCALAR_DIVISIONS:
+    raise ValueError(f"QCC_SCALAR_DIVISION must be one of {_SCALAR_DIVISIONS}, not {_scalar_division!r}")
+
+
+def set_scalar_division(mode):
+    """Process-wide choice of how `amax / constant` is computed by every cast that follows: "ieee" or "cuda_eager"
+    (see above).  Returns the previous setting."""
+    global _scalar_division
+    if mode not in _SCALAR_DIVISIONS:
+        raise ValueError(f"scalar division must be one of {_SCALAR_DIVISIONS}, not {mode!r}")
+    prev, _scalar_division = _scalar_division, mode
+    return prev
+
+
+def get_scalar_division():
+    return _scalar_division
+
+
+class scalar_division:
+    """Context manager: `with scalar_division("cuda_eager"): ...`."""
+
+    def __init__(self, mode):
+        self.mode = mode
+
+    def __enter__(self):
+        self.prev = set_scalar_division(self.mode)
+        return self
+
+    def __exit__(self, *exc):
+        set_scalar_division(self.prev)
+        return False
+
+
+def div_flag():
+    """The bit the C entry points take for the current setting (0 or RECIP_DIV)."""
+    return RECIP_DIV if _scalar_division == "cuda_eager" else 0
 
 
 def check(rc, what):

@@ -162,12 +162,12 @@ class HostShardCaster:
                     ms_h[i * ab:(i + 1) * ab].copy_(ms_d[i * ab:(i + 1) * ab], non_blocking=True)
             with torch.cuda.stream(self.s_cmp):
                 self.xchg._pending = True
-                L.check(lib.qcc_xchg_resolve(self.xchg._ref(), L.AMAX_NVFP4_SCALE, L.FMT_E4M3, self.outer_dev.data_ptr(),
+                L.check(lib.qcc_xchg_resolve(self.xchg._ref(), L.AMAX_NVFP4_SCALE | L.div_flag(), L.FMT_E4M3, self.outer_dev.data_ptr(),
                                              self.s_cmp.cuda_stream), "xchg_resolve")
                 L.launch_count += 1
                 for i in range(n_chunks):
                     r0 = i * rc
-                    L.check(lib.qcc_nvfp4(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, self.outer_dev.data_ptr(), 0, L.SWIZZLE, None,
+                    L.check(lib.qcc_nvfp4(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, self.outer_dev.data_ptr(), 0, L.SWIZZLE | L.div_flag(), None,
                                           nq_d[r0:r0 + rc].data_ptr(), ns_d[i * ab:(i + 1) * ab].data_ptr(), self.s_cmp.cuda_stream),
                             "nvfp4")
                     L.launch_count += 1

@@ -131,11 +131,11 @@ def _amax(x, mode, fmt=L.FMT_E4M3, workspace=None):
     ws_bytes = lib.qcc_amax_workspace_bytes()
     with _on_device(x.device):
         if ws is not None:     # one launch
-            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode | L.AMAX_ONE_LAUNCH, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
+            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode | L.AMAX_ONE_LAUNCH | L.div_flag(), fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
             L.launch_count += 1
         else:                  # two launches, any workspace contents
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode, fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
+            L.check(lib.qcc_amax_bf16(_p(x), x.numel(), mode | L.div_flag(), fmt, _p(out), _p(ws), ws_bytes, _stream(x)), "amax")
             L.launch_count += 2
     return out
 
@@ -153,7 +153,7 @@ def scale_from_amax_cuda(amax, kind, fmt="e4m3"):
     a = amax.reshape(-1)[:1].contiguous().float()
     out = torch.empty((), dtype=torch.float32, device=amax.device)
     with _on_device(amax.device):
-        L.check(lib.qcc_scale_from_amax(_p(a), mode, _fmt(fmt), _p(out), _stream(amax)), "scale_from_amax")
+        L.check(lib.qcc_scale_from_amax(_p(a), mode | L.div_flag(), _fmt(fmt), _p(out), _stream(amax)), "scale_from_amax")
     L.launch_count += 1
     return out
 
@@ -194,7 +194,7 @@ def float8_tensorwise_from_amax_cuda(x, amax, fmt="e4m3"):
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     scale = torch.empty((), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_tensorwise_from_amax(_p(x), x.numel(), _p(amax), f, _p(q), _p(scale), _stream(x)),
+        L.check(lib.qcc_fp8_tensorwise_from_amax(_p(x), x.numel(), _p(amax), f | L.div_flag(), _p(q), _p(scale), _stream(x)),
                 "fp8_tensorwise_from_amax")
     L.launch_count += 1
     return q.view(_FP8_DTYPE[f]), scale
@@ -209,7 +209,7 @@ def rowwise_fp8_cuda(x, fmt="e4m3", **kwargs):
     q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
     s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, f, _p(q), _p(s), _stream(x)), "fp8_rowwise")
+        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, f | L.div_flag(), _p(q), _p(s), _stream(x)), "fp8_rowwise")
     L.launch_count += 1
     return q.view(_FP8_DTYPE[f]), s
 
@@ -221,7 +221,7 @@ def rowwise_precalc_scale_cuda(x, fmt="e4m3"):
     M, N = x.shape
     s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, _fmt(fmt), None, _p(s), _stream(x)), "fp8_rowwise_scale")
+        L.check(lib.qcc_fp8_rowwise(_p(x), M, N, _fmt(fmt) | L.div_flag(), None, _p(s), _stream(x)), "fp8_rowwise_scale")
     L.launch_count += 1
     return s
 
@@ -252,7 +252,7 @@ def colwise_fp8_cuda(x, fmt="e4m3", **kwargs):
     ws_bytes = int(lib.qcc_fp8_colwise_workspace_bytes(M, N))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_colwise(_p(x), M, N, f, _p(q), _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise")
+        L.check(lib.qcc_fp8_colwise(_p(x), M, N, f | L.div_flag(), _p(q), _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise")
     L.launch_count += 2
     return q.view(_FP8_DTYPE[f]), s
 
@@ -268,7 +268,7 @@ def colwise_precalc_scale_cuda(x, fmt="e4m3"):
     ws_bytes = int(lib.qcc_fp8_colwise_workspace_bytes(M, N))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_colwise(_p(x), M, N, _fmt(fmt), None, _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise_scale")
+        L.check(lib.qcc_fp8_colwise(_p(x), M, N, _fmt(fmt) | L.div_flag(), None, _p(s), _p(ws), ws_bytes, _stream(x)), "fp8_colwise_scale")
     L.launch_count += 2
     return s
 
@@ -369,7 +369,7 @@ def _fp8_block128(x, row, col):
     sm = torch.empty((N, M // 128), dtype=torch.float32, device=dev) if col else None
     flags = (L.ROWWISE if row else 0) | (L.COLWISE if col else 0)
     with _on_device(dev):
-        L.check(lib.qcc_fp8_block128(_p(x), M, N, flags, _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "fp8_block128")
+        L.check(lib.qcc_fp8_block128(_p(x), M, N, flags | L.div_flag(), _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "fp8_block128")
     L.launch_count += 1
     outs = []
     if row:
@@ -403,7 +403,7 @@ def deepseek_128x128_cuda(x, **kwargs):
     q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
     s = torch.empty((M // 128, N // 128), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_fp8_block128x128(_p(x), M, N, _p(q), _p(s), _stream(x)), "fp8_block128x128")
+        L.check(lib.qcc_fp8_block128x128(_p(x), M, N, L.div_flag(), _p(q), _p(s), _stream(x)), "fp8_block128x128")
     L.launch_count += 1
     return q.view(torch.float8_e4m3fn), s
 
@@ -511,12 +511,12 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
             assert M % 32 == 0 and N % 8 == 0, f"transposed nvfp4 needs M % 32 == 0 and N % 8 == 0, got {M}x{N}"
             q = torch.empty((N, M // 2), dtype=torch.uint8, device=dev)
             s = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=torch.uint8, device=dev)
-            L.check(lib.qcc_nvfp4_transposed(_p(x), M, N, _p(o), flags, _p(key), _p(q), _p(s), _stream(x)), "nvfp4_t")
+            L.check(lib.qcc_nvfp4_transposed(_p(x), M, N, _p(o), flags | L.div_flag(), _p(key), _p(q), _p(s), _stream(x)), "nvfp4_t")
         else:
             assert N % 16 == 0, f"nvfp4 needs N % 16 == 0, got N={N}"
             q = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
             s = torch.empty(blocked_shape(M, N // 16) if swz else (M, N // 16), dtype=torch.uint8, device=dev)
-            L.check(lib.qcc_nvfp4(_p(x), M, N, _p(o), per_row, flags, _p(key), _p(q), _p(s), _stream(x)), "nvfp4")
+            L.check(lib.qcc_nvfp4(_p(x), M, N, _p(o), per_row, flags | L.div_flag(), _p(key), _p(q), _p(s), _stream(x)), "nvfp4")
     L.launch_count += 1
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
 
@@ -534,7 +534,7 @@ def nvfp4_from_amax_cuda(x, amax, swizzle=True):
     s_ = torch.empty(blocked_shape(M, N // 16) if swizzle else (M, N // 16), dtype=torch.uint8, device=dev)
     outer = torch.empty((), dtype=torch.float32, device=dev)
     with _on_device(dev):
-        L.check(lib.qcc_nvfp4_from_amax(_p(x), M, N, _p(amax), L.SWIZZLE if swizzle else 0, _p(q), _p(s_), _p(outer),
+        L.check(lib.qcc_nvfp4_from_amax(_p(x), M, N, _p(amax), (L.SWIZZLE if swizzle else 0) | L.div_flag(), _p(q), _p(s_), _p(outer),
                                         _stream(x)), "nvfp4_from_amax")
     L.launch_count += 1
     return q.view(torch.float4_e2m1fn_x2), s_.view(torch.float8_e4m3fn), outer
@@ -548,7 +548,7 @@ def nvfp4_blocked_outer_scale_cuda(x, blk=128):
     assert blk == 128 and M % 128 == 0 and N % 128 == 0, f"needs 128x128 blocks tiling the input, got {M}x{N}"
     out = torch.empty((M // 128, N // 128), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_amax_block128x128(_p(x), M, N, L.AMAX_NVFP4_SCALE, _p(out), _stream(x)), "amax_block128x128")
+        L.check(lib.qcc_amax_block128x128(_p(x), M, N, L.AMAX_NVFP4_SCALE | L.div_flag(), _p(out), _stream(x)), "amax_block128x128")
     L.launch_count += 1
     return out
 
@@ -564,7 +564,7 @@ def nvfp4_blocked_outer_cuda(x, outer_blocked, **kwargs):
     q = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
     s = torch.empty(blocked_shape(M, N // 16), dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_nvfp4(_p(x), M, N, _p(outer_blocked.contiguous()), 2, L.SWIZZLE, None, _p(q), _p(s), _stream(x)),
+        L.check(lib.qcc_nvfp4(_p(x), M, N, _p(outer_blocked.contiguous()), 2, L.SWIZZLE | L.div_flag(), None, _p(q), _p(s), _stream(x)),
                 "nvfp4 blocked outer")
     L.launch_count += 1
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
@@ -617,7 +617,7 @@ def _nvfp4_both(x, outer_scale, flags):
     qm = torch.empty((N, M // 2), dtype=torch.uint8, device=dev)
     sm = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=torch.uint8, device=dev)
     with _on_device(dev):
-        L.check(lib.qcc_nvfp4_both(_p(x), M, N, _p(outer_scale.contiguous()), flags, _p(qk), _p(sk), _p(qm), _p(sm),
+        L.check(lib.qcc_nvfp4_both(_p(x), M, N, _p(outer_scale.contiguous()), flags | L.div_flag(), _p(qk), _p(sk), _p(qm), _p(sm),
                                    _stream(x)), "nvfp4_both")
     L.launch_count += 1
     f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
@@ -678,7 +678,7 @@ def nvfp4_rht_outer_scale_m_cuda(x, rht):
     rht = _check_rht(rht, x)
     out = torch.empty((), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
-        L.check(lib.qcc_nvfp4_rht_amax(_p(x), M, N, _p(rht), L.AMAX_NVFP4_SCALE, _p(out), _stream(x)), "nvfp4_rht_amax")
+        L.check(lib.qcc_nvfp4_rht_amax(_p(x), M, N, _p(rht), L.AMAX_NVFP4_SCALE | L.div_flag(), _p(out), _stream(x)), "nvfp4_rht_amax")
     L.launch_count += 3
     return out
 
@@ -703,7 +703,7 @@ def _nvfp4_rht(x, outer_scale_k, outer_scale_m, rht, flags, key_k=None, key_m=No
     sm = torch.empty(blocked_shape(N, M // 16) if swz else (N, M // 16), dtype=u8, device=dev)
     with _on_device(dev):
         L.check(lib.qcc_nvfp4_rht(_p(x), M, N, _p(outer_scale_k.contiguous()) if both else None, _p(outer_scale_m.contiguous()),
-                                  _p(rht), flags, _p(key_k), _p(key_m), _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "nvfp4_rht")
+                                  _p(rht), flags | L.div_flag(), _p(key_k), _p(key_m), _p(qk), _p(sk), _p(qm), _p(sm), _stream(x)), "nvfp4_rht")
     L.launch_count += 3 if (both and flags & L.SR) else 2
     f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
     if both:

@@ -142,7 +142,7 @@ class AmaxExchange:
         resident when the producer's last CTA retires."""
         mode = {"raw": L.AMAX_RAW, "fp8": L.AMAX_FP8_SCALE, "nvfp4": L.AMAX_NVFP4_SCALE}[kind]
         out = torch.empty((), dtype=torch.float32, device=self.device)
-        L.check(self.lib.qcc_xchg_resolve(self._ref(pdl), mode, _FMT[fmt], out.data_ptr(),
+        L.check(self.lib.qcc_xchg_resolve(self._ref(pdl), mode | L.div_flag(), _FMT[fmt], out.data_ptr(),
                                          torch.cuda.current_stream(self.device).cuda_stream), "xchg_resolve")
         L.launch_count += 1
         return out

@@ -8,6 +8,14 @@ only used by the stochastic-rounding recipes, which are not part of the stored v
 stand-in module is registered before the import.  Nothing from the reference is copied: only the
 inputs fed to it and the bytes it returned are stored.
 
+With `--device cuda` (on a machine with a GPU) the same recipes run eagerly on the CUDA device instead and the
+result goes to tests/golden/gold_vectors_cuda.npz:
+    python tests/golden/make_golden.py --reference oracle/_ref --device cuda
+Eager PyTorch computes `tensor / python_scalar` as an IEEE division on the CPU and as a multiplication with the
+fp32 reciprocal of the scalar on a CUDA device, so the recipes that divide an amax by 448, 2688 or 6 give slightly
+different bytes there.  That file stores only the outputs that differ from the CPU file (same keys), and under
+`same_as_cpu` the names of those that do not.
+
 Stored per case `<shape>_<seed>`: the bf16 input bits and, for every gold recipe on the hot path,
 the raw bytes of each output (fp8 / e8m0 / packed fp4 as uint8, fp32 scales as their int32 bits).
 Also stored: scalar known-answer tables for PyTorch's fp32->e4m3/e5m2 casts, the reference's fp4
@@ -57,6 +65,7 @@ def make_input(M, N, seed, spread=10.0, outlier_p=1e-3, outlier_mul=100.0, zero_
 
 
 def raw(t):
+    t = t.detach().cpu()
     if t.dtype == torch.float32:
         return t.contiguous().view(torch.int32).numpy()
     if t.dtype == torch.bfloat16:
@@ -67,8 +76,12 @@ def raw(t):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=default_reference())
-    ap.add_argument("--out", default=os.path.join(HERE, "gold_vectors.npz"))
+    ap.add_argument("--device", default="cpu", choices=("cpu", "cuda"))
+    ap.add_argument("--out", default=None)
     args = ap.parse_args()
+    dev = args.device
+    if args.out is None:
+        args.out = os.path.join(HERE, "gold_vectors.npz" if dev == "cpu" else "gold_vectors_cuda.npz")
     if not args.reference:
         raise SystemExit("no reference checkout: pass --reference or set QCC_REFERENCE_ROOT")
     G, GU = import_gold(args.reference)
@@ -77,7 +90,7 @@ def main():
     cases = [(128, 128, 0), (96, 160, 1), (128, 160, 2), (160, 320, 4), (256, 256, 5)]
     names = []
     for M, N, seed in cases:
-        x = make_input(M, N, seed)
+        x = make_input(M, N, seed).to(dev)
         tag = f"{M}x{N}_s{seed}"
         names.append(tag)
         out[f"{tag}/x"] = raw(x)
@@ -123,7 +136,7 @@ def main():
         # randomised Hadamard transform and the two-orientation nvfp4 cast built on it (G:1324-1372, G:1778-1810)
         sign = torch.tensor([1, -1] * 8 if seed % 2 == 0 else [1, 1, -1, 1, -1, -1, -1, 1, 1, -1, 1, 1, -1, 1, -1, -1],
                             dtype=torch.bfloat16)
-        rht = G.hadamard_rht_matrix(sign, "cpu", torch.bfloat16)
+        rht = G.hadamard_rht_matrix(sign, dev, torch.bfloat16)
         out[f"{tag}/rht"] = raw(rht)
         out[f"{tag}/hadamard_rht_f/0"] = raw(G.hadamard_rht_f(x, rht)[0])
         (x_t_rht,) = G.hadamard_rht_f(x.t().contiguous(), rht)
@@ -136,6 +149,26 @@ def main():
         for i, o in enumerate(G.nvfp4_gs_f(x, pt)):
             out[f"{tag}/nvfp4_gs_f_per_token/{i}"] = raw(o)
     out["cases"] = np.array(names)
+    if dev != "cpu":
+        # keep what the device computes differently, name the rest
+        cpu = np.load(os.path.join(HERE, "gold_vectors.npz"))
+        same, kept = [], {"cases": out["cases"]}
+        for k, v in out.items():
+            if k == "cases" or k.endswith("/x") or k.endswith("/rht"):
+                assert k == "cases" or np.array_equal(v, cpu[k]), k   # same inputs as the CPU file
+                continue
+            if v.shape == cpu[k].shape and np.array_equal(v, cpu[k]):
+                same.append(k)
+            else:
+                kept[k] = v
+        kept["same_as_cpu"] = np.array(same)
+        np.savez_compressed(args.out, **kept)
+        print(f"wrote {args.out}: {len(kept) - 2} outputs differ from the CPU file, {len(same)} do not; "
+              f"{os.path.getsize(args.out)/1e6:.2f} MB, torch {torch.__version__}, {torch.cuda.get_device_name(0)}")
+        for k in sorted(kept):
+            if k not in ("cases", "same_as_cpu"):
+                print("  differs:", k, int((kept[k] != cpu[k]).sum()) if kept[k].shape == cpu[k].shape else "shape", "of", kept[k].size)
+        return
 
     # ---- scalar known-answer tables -------------------------------------------------------------
     g = torch.Generator().manual_seed(1234)

@@ -465,7 +465,8 @@ def test_rejected_arguments_of_the_block_and_transform_entries():
     assert lib.qcc_fp8_block128(p, 96, 128, L.COLWISE, None, None, p, p, None) == -1              # M % 128
     assert lib.qcc_fp8_block128(p, 128, 128, 0, p, p, p, p, None) == -3
     assert lib.qcc_fp8_block128(p, 128, 128, L.ROWWISE, p + 4, p, None, None, None) == -2
-    assert lib.qcc_fp8_block128x128(p, 128, 192, p, p, None) == -1
+    assert lib.qcc_fp8_block128x128(p, 128, 192, 0, p, p, None) == -1
+    assert lib.qcc_fp8_block128x128(p, 128, 128, L.SWIZZLE, p, p, None) == -3                      # only QCC_RECIP_DIV is a valid flag
     assert lib.qcc_amax_block128x128(p, 128, 128, 1, p, None) == -3                                # FP8_SCALE is not a mode here
     assert lib.qcc_nvfp4(p, 128, 128, p, 3, 0, None, p, p, None) == -3                             # outer mode 0..2
     assert lib.qcc_nvfp4(p, 96, 128, p, 2, L.SWIZZLE, None, p, p, None) == -1                      # blocked outer needs M % 128
