@@ -679,6 +679,31 @@ def bench_reference_gpu(dev, budget_s):
         with QL.scalar_division("cuda_eager"):
             return "cuda_eager" if equal() else False
 
+    def bytes_off_gold(name, inputs, outs):
+        """The arbiter: the reference's gold recipe run eagerly on this GPU for the same inputs.  Number of differing
+        bytes per output, for the reference's kernel and for this backend (set to divide as eager PyTorch does on a
+        CUDA device, and as it does on the CPU, which is the default)."""
+        from quant_cast_bench_b200.quant_cast_cuda import _lib as QL
+        try:
+            gold = dict(ref_gold.gold().ALL_RECIPES)[name].pt_ref_fn(*inputs)
+            ours = dict(Q.ALL_RECIPES)[name]
+
+            def count(got):
+                if len(got) != len(gold):
+                    return "different number of outputs"
+                def flat(t):      # (a (N, 1) scale may come with strides (1, N): flatten before viewing it as bytes)
+                    return t.contiguous().reshape(-1).contiguous().view(torch.uint8)
+                return [int((flat(a) != flat(b)).sum()) if a.shape == b.shape else "shape" for a, b in zip(got, gold)]
+            res = {"reference_kernel": count(outs)}
+            with QL.scalar_division("cuda_eager"):
+                res["ours_cuda_eager"] = count(ours.cuda_fn(*inputs))
+            res["ours_default_ieee"] = count(ours.cuda_fn(*inputs))
+            res["of_bytes"] = [int(b.numel() * b.element_size()) for b in gold]
+            return res
+        except Exception as exc:
+            torch.cuda.synchronize()
+            return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+
     s8 = Q.float8_tensorwise_scale_cuda(x)
     gs = Q.nvfp4_gs_scale_cuda(x)
     order = [("mxfp8_dim_km_swizzle", (x,)), ("nvfp4_swizzle", (x, gs)), ("fp8_tensorwise_precalc_scale", (x, s8)),
@@ -701,10 +726,18 @@ def bench_reference_gpu(dev, budget_s):
             nbytes = sum(t.numel() * t.element_size() for t in inputs) + sum(t.numel() * t.element_size() for t in outs)
             first_call_s = time.perf_counter() - t0
             same = same_as_ours(name, inputs, outs)
+            off_gold = bytes_off_gold(name, inputs, outs)
             ms, ms_b2b = cold_ms(lambda: rec.triton_fn(*inputs))
             out["recipes"][name] = {"ms_cold_in_graph": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_8TBps": nbytes / (ms * 1e-3) / 8e12,
                                     "ms_sustained": ms_b2b, "GBps_sustained": nbytes / (ms_b2b * 1e-3) / 1e9,
-                                    "bytes": nbytes, "compile_and_autotune_s": first_call_s, "outputs_equal_ours": same}
+                                    "bytes": nbytes, "compile_and_autotune_s": first_call_s, "outputs_equal_ours": same,
+                                    "bytes_differing_from_gold_on_this_gpu": off_gold}
+            ours = dict(Q.ALL_RECIPES).get(name)
+            if ours is not None:      # this backend on the very same input, by the very same function, right behind it
+                del outs
+                oms, oms_b2b = cold_ms(lambda: ours.cuda_fn(*inputs))
+                out["recipes"][name].update({"ours_ms_cold_in_graph": oms, "ours_GBps": nbytes / (oms * 1e-3) / 1e9,
+                                             "ours_ms_sustained": oms_b2b, "ours_GBps_sustained": nbytes / (oms_b2b * 1e-3) / 1e9})
         except Exception as exc:
             out["recipes"][name] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
             torch.cuda.synchronize()

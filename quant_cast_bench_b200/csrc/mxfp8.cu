@@ -163,60 +163,6 @@ mxfp8_rowwise_stream_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, ui
     }
 }
 
-#ifdef QCC_RS_QUAD
-// experiment: four lanes per block, 16-byte loads that a warp issues over 512 contiguous bytes, 8-byte stores
-#ifndef QCC_RQ_THREADS
-#define QCC_RQ_THREADS 128
-#endif
-#ifndef QCC_RQ_PASSES
-#define QCC_RQ_PASSES 4
-#endif
-template <bool SWZ, bool FLOOR>
-__global__ void __launch_bounds__(QCC_RQ_THREADS)
-mxfp8_rowwise_quad_kernel(const uint16_t *__restrict__ x, uint32_t nblocks, uint32_t nb, FastDiv32 div_nb,
-                          uint8_t *__restrict__ q, uint8_t *__restrict__ s)
-{
-    constexpr int BPP = QCC_RQ_THREADS / 4;            // blocks per pass
-    const uint4 *xv = reinterpret_cast<const uint4 *>(x);
-    uint2 *qv = reinterpret_cast<uint2 *>(q);
-    const uint32_t qd = threadIdx.x & 3u, slot = threadIdx.x >> 2;
-    const uint32_t base = blockIdx.x * (BPP * QCC_RQ_PASSES) + slot;
-    uint4 c[QCC_RQ_PASSES];
-#pragma unroll
-    for (int p = 0; p < QCC_RQ_PASSES; p++) {
-        const uint32_t bi = base + p * BPP;
-        c[p] = bi < nblocks ? ld_v4(xv + 4 * (size_t)bi + qd) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int p = 0; p < QCC_RQ_PASSES; p++) {
-        const uint32_t bi = base + p * BPP;
-        const bool ok = bi < nblocks;
-        uint32_t a = absmax2(absmax2(c[p].x, c[p].y), absmax2(c[p].z, c[p].w));
-        uint32_t m = f2u(hmax_halves_f32(a));
-        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
-        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-        const uint32_t e = e8m0_from_amax<FLOOR>(u2f(m));
-        const float rcp = e8m0_recip<FLOOR>(e);
-        uint2 o;
-        o.x = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[p].x), bf16hi(c[p].x), bf16lo(c[p].y), bf16hi(c[p].y), rcp);
-        o.y = scale_cvt_fp8x4<QCC_FMT_E4M3>(bf16lo(c[p].z), bf16hi(c[p].z), bf16lo(c[p].w), bf16hi(c[p].w), rcp);
-        if (ok) st_out(qv + 4 * (size_t)bi + qd, o);
-        if (!SWZ) {
-            if (ok && qd == 0) s[bi] = (uint8_t)e;
-        } else {
-            // lanes 0, 4, 8, 12 (and 16, ...) hold four consecutive blocks
-            uint32_t v = e | (__shfl_down_sync(0xFFFFFFFFu, e, 4) << 8);
-            v |= __shfl_down_sync(0xFFFFFFFFu, v, 8) << 16;
-            if (ok && (threadIdx.x & 15u) == 0) {
-                const uint32_t row = div_nb.div(bi);
-                const uint32_t cb = bi - row * nb;
-                *reinterpret_cast<uint32_t *>(s + blocked_offset(row, cb, nb >> 2)) = v;
-            }
-        }
-    }
-}
-#endif
-
 // mxfp4 (gold mxfp4_f G:607-617): the same 1x32 blocks and RCEIL e8m0 scale, descaled by 6 instead of 448,
 // elements as e2m1 packed two per byte (even element in the low nibble).
 template <bool SWZ>
@@ -625,15 +571,6 @@ static int mxfp8_entry(const void *x, int64_t M, int64_t N, int flags, void *qk,
         const unsigned grid = (nblocks + RS_THREADS * RS_UNROLL - 1) / (RS_THREADS * RS_UNROLL);
         const uint16_t *xp = (const uint16_t *)x;
         uint8_t *qp = (uint8_t *)qk;
-#ifdef QCC_RS_QUAD
-        if (amax_mode == 0 && !g.row_map && !g.blk_src && (nb & 3) == 0 && !fl) {
-            const unsigned per = (QCC_RQ_THREADS / 4) * QCC_RQ_PASSES;
-            const unsigned qgrid = (nblocks + per - 1) / per;
-            if (swz) mxfp8_rowwise_quad_kernel<true, false><<<qgrid, QCC_RQ_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
-            else mxfp8_rowwise_quad_kernel<false, false><<<qgrid, QCC_RQ_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp);
-            return (int)cudaGetLastError();
-        }
-#endif
 #define QCC_RS(SWZ_, FL_, AM_) \
     mxfp8_rowwise_stream_kernel<SWZ_, FL_, AM_><<<grid, RS_THREADS, 0, st>>>(xp, nblocks, (uint32_t)nb, dv, qp, skp, g, sink)
 #define QCC_RS_AM(SWZ_, FL_) \
