@@ -80,7 +80,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--extensions", action="store_true")
     ap.add_argument("--include_skipped", action="store_true", help="also run the recipes the reference sweep skips")
+    ap.add_argument("--scalar_division", default=None, choices=("ieee", "cuda_eager"),
+                    help="how amax / 448 and the like are computed: as the gold recipes do on the CPU (default) or on a CUDA device")
     args = ap.parse_args()
+    if args.scalar_division:
+        Q.set_scalar_division(args.scalar_division)
     assert args.mode == "cuda", "this harness drives the CUDA backend only (--mode cuda)"
     assert torch.cuda.is_available(), "no CUDA device"
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
