@@ -387,6 +387,10 @@ int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const 
 int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
               const uint64_t *philox_key, void *q, void *s, void *stream);
 
+/* scale (M, 1) fp32 = max |x| of every row / 2688, no clamp: the per-token outer scale that qcc_nvfp4 takes with
+ * outer_per_row = 1 (nvfp4_gs_per_token_scale, G:1569-1573).  flags: 0 or QCC_RECIP_DIV.  One read of x. */
+int qcc_nvfp4_per_token_scale(const void *x, int64_t M, int64_t N, int flags, float *scale, void *stream);
+
 /* qcc_nvfp4 (one outer scale for the tensor, round to nearest; flags: QCC_SWIZZLE or 0) from a raw amax (device
  * fp32): outer = amax / 2688 (nvfp4_gs_scale G:1243-1246) is formed in the kernel's prologue and also written to
  * outer_out (device, may be NULL). */

@@ -209,6 +209,12 @@ def nvfp4_gs_scale(x):
     return out
 
 
+def nvfp4_gs_per_token_scale(x):
+    """(M, 1) fp32: row amax / (448 * 6), no clamp.  nvfp4_gs_per_token_scale, G:1569-1573."""
+    _check_x(x)
+    return _div_const(x.abs().to(torch.float32).amax(dim=-1, keepdim=True), 448.0 * 6.0)
+
+
 def nvfp4_scale_from_amax(amax):
     out = torch.empty((), dtype=torch.float32)
     lib().qco_nvfp4_scale_from_amax(ctypes.c_float(float(amax)), _p(out))

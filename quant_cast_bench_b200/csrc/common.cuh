@@ -198,9 +198,13 @@ __device__ __forceinline__ float div_by_const(float a, float c, bool recip)
 
 // fp8 per-tensor / per-row scale from an amax: clamp at bf16(1e-12) (the clamp happens in bf16 in
 // the reference, G:304, G:1182), then the division by the format maximum.
+// FMT_NVFP4_OUTER (library internal): not an fp8 format -- the row kernels then deliver the nvfp4 per-token outer scale,
+// amax / (448 * 6) without a clamp (nvfp4_gs_per_token_scale G:1569-1573), and are launched without a cast.
+constexpr int FMT_NVFP4_OUTER = 2;
 template <int FMT>
 __device__ __forceinline__ float fp8_scale_from_amax(float amax, bool recip)
 {
+    if (FMT == FMT_NVFP4_OUTER) return div_by_const(amax, 2688.0f, recip);
     float a = fmaxf(amax, u2f(0x2B8D0000u));
     return div_by_const(a, FMT == QCC_FMT_E5M2 ? 57344.0f : 448.0f, recip);
 }

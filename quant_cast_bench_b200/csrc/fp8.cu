@@ -780,6 +780,14 @@ int qcc_fp8_rowwise(const void *x, int64_t M, int64_t N, int fmt, void *q, float
                                : launch_rowwise<QCC_FMT_E4M3, false>(x, M, N, nullptr, q, scale, recip_div, st);
 }
 
+int qcc_nvfp4_per_token_scale(const void *x, int64_t M, int64_t N, int flags, float *scale, void *stream)
+{
+    if (M == 0 || N == 0) return 0;
+    if (!x || !scale || M < 0 || N < 0 || (flags & ~QCC_RECIP_DIV)) return QCC_ERR_ARG;
+    if (N % 8 == 0 && !aligned16(x)) return QCC_ERR_ALIGN;
+    return launch_rowwise<FMT_NVFP4_OUTER, false>(x, M, N, nullptr, nullptr, scale, (flags & QCC_RECIP_DIV) ? 1 : 0, (cudaStream_t)stream);
+}
+
 int qcc_fp8_rowwise_precalc(const void *x, int64_t M, int64_t N, const float *scale, int fmt, void *q, void *stream)
 {
     if (M == 0 || N == 0) return 0;

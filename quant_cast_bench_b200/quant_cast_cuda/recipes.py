@@ -521,6 +521,20 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
 
 
+def nvfp4_gs_per_token_scale_cuda(x):
+    """Per-token fp32 outer scale, (M, 1): row amax / (448 * 6) without a clamp (nvfp4_gs_per_token_scale, G:1569-1573).
+    `nvfp4_gs_cuda(x, scale)` / `nvfp4_gs_swizzle_cuda(x, scale)` take it as the outer scale.  (An all-zero row gets
+    scale 0, which the cast divides by, as in the reference.)"""
+    lib = L.load()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    M, N = x.shape
+    s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_nvfp4_per_token_scale(_p(x), M, N, L.div_flag(), _p(s), _stream(x)), "nvfp4_per_token_scale")
+    L.launch_count += 1
+    return s
+
+
 def nvfp4_from_amax_cuda(x, amax, swizzle=True):
     """nvfp4_gs_scale + nvfp4_gs_f / nvfp4_gs_swizzle_f (G:1243-1266, G:1494-1517) for an amax that is already known:
     outer = amax / 2688 is formed in the cast's prologue.  Returns (qdata, inner scales, outer scale)."""

@@ -101,6 +101,7 @@ def test_nvfp4(tag):
         for i, o in enumerate(getattr(O, fn)(x, gs)):
             assert_same_bits(o, golden_out(tag, fn, i), f"{fn}[{i}] {tag}")
     pt = golden_out(tag, "nvfp4_per_token_scale", 0).view(torch.float32)
+    assert_same_bits(O.nvfp4_gs_per_token_scale(x).clamp(min=2.0 ** -100), pt, "per-token outer scale")   # (the stored one is clamped)
     for i, o in enumerate(O.nvfp4_gs_f(x, pt)):
         assert_same_bits(o, golden_out(tag, "nvfp4_gs_f_per_token", i), f"per-token[{i}] {tag}")
 

@@ -178,6 +178,9 @@ def test_golden_nvfp4(tag):
         for i, o in enumerate(outs):
             assert_same_bits(o, golden_out(tag, fn + "_f", i), f"{fn}[{i}] {tag}")
     pt = golden_out(tag, "nvfp4_per_token_scale", 0).view(torch.float32).cuda()
+    mine = Q.nvfp4_gs_per_token_scale_cuda(x)
+    assert mine.shape == (x.shape[0], 1) and mine.dtype == torch.float32
+    assert_same_bits(mine.clamp(min=2.0 ** -100), pt, "per-token outer scale")      # (the stored one is clamped)
     for i, o in enumerate(Q.nvfp4_gs_cuda(x, pt)):
         assert_same_bits(o, golden_out(tag, "nvfp4_gs_f_per_token", i), f"per-token[{i}] {tag}")
 

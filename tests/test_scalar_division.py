@@ -82,6 +82,7 @@ def chain(ns, suffix, x, tag, rht, per_token, dev):
         out[f"nvfp4_gs_swizzle_dim_k_dim_m_rht_f/{i}"] = o
     for i, o in enumerate(g("nvfp4_gs_f")(x, per_token.to(dev))):
         out[f"nvfp4_gs_f_per_token/{i}"] = o
+    out["nvfp4_per_token_scale/0"] = f("nvfp4_gs_per_token_scale")(x).clamp(min=2.0 ** -100)   # the files store it clamped
     return out
 
 
@@ -221,6 +222,7 @@ def test_kernels_cuda_eager_match_the_reference_gold_on_this_gpu():
             assert_same_bits(Q.rowwise_precalc_scale_cuda(x), G.rowwise_precalc_scale(x), "row scales")
             assert_same_bits(Q.colwise_precalc_scale_cuda(x).reshape(-1), G.colwise_precalc_scale(x).reshape(-1), "column scales")
             assert_same_bits(Q.nvfp4_blocked_outer_scale_cuda(x), G.nvfp4_blocked_outer_scale(x), "blocked outer scales")
+            assert_same_bits(Q.nvfp4_gs_per_token_scale_cuda(x), G.nvfp4_gs_per_token_scale(x), "per-token outer scales")
             rht = R._rht_matrix(x)
             # The gold transform is a bf16 matmul, which on the GPU runs on the tensor cores: their accumulation aligns
             # the 16 addends to the largest exponent and drops bits below it, so where the sum nearly cancels the gold
