@@ -59,7 +59,9 @@ WORKLOAD = ("config 4: bf16[131072,7168], N(0,1)*2^U(-6,6) per token, row-sharde
 CONFIG = {"workload": WORKLOAD, "rows": M4, "cols": N4, "sharding": "contiguous row shards, rows / n_gpus each",
           "bytes_per_step": STEP_BYTES,
           "l2": "every launch streams a shard of >= 235 MB in and >= 120 MB out (L2: 126 MB); two input tensors alternate between "
-                "steps; no flush between iterations"}
+                "steps; no flush between iterations",
+          "timed_region": "K steps replayed from one CUDA graph; with more than one rank, one untimed step directly in front of "
+                          "it lines the ranks up on the device"}
 METRIC = "achieved_GBps_c4_mxfp8_swizzle+nvfp4_swizzle"
 DTYPE = "bf16 -> e4m3 + e8m0, e2m1 + e4m3 (fp32 scale math)"
 
@@ -382,9 +384,16 @@ def run_ours(args):
     # allocated per step from the graph's pool) and replayed once: the device then runs K back-to-back steps whatever the
     # host is doing -- with 8 ranks on one box, host scheduling jitter between launches otherwise shows up as idle gaps on
     # the slowest rank.  If capture is not possible the steps are issued eagerly.
-    graph = None
+    # One more untimed step, replayed directly in front of the timed region, lines the ranks up ON THE DEVICE: its
+    # exchange lets no rank past before every rank has arrived, so the K timed steps start within microseconds of each
+    # other on all GPUs.  Without it the ranks start as far apart as their hosts left the barrier (tens of microseconds
+    # with 8 processes), and the early ranks' first exchange waits that long inside the timed region.
+    graph = galign = None
     L.launch_count = 0
     try:
+        if world > 1:
+            galign, _ = graph_of(step, 1)
+            L.launch_count = 0
         graph, outs = graph_of(step, args.steps)
         captured_launches = L.launch_count
     except Exception as exc:   # pragma: no cover
@@ -398,6 +407,8 @@ def run_ours(args):
     # device-timed region holds K back-to-back steps and not the host's launch latency for the first one.
     if hasattr(torch.cuda, "_sleep"):
         torch.cuda._sleep(400_000)
+    if galign is not None and graph is not None:
+        galign.replay()
     e0.record()
     if graph is not None:
         graph.replay()
@@ -418,11 +429,16 @@ def run_ours(args):
 
     # ---- the other ways to run the step, same shard, 10 iterations each in one graph (max over ranks)
     def variant(c, **kw):
+        it = [0]
+
+        def one():                      # the two inputs alternate here too
+            it[0] += 1
+            return c.mxfp8_then_nvfp4(xs[it[0] & 1], **kw)
         for _ in range(3):
-            c.mxfp8_then_nvfp4(x, **kw)
+            one()
         torch.cuda.synchronize()
         barrier()
-        g, _ = graph_of(lambda: c.mxfp8_then_nvfp4(x, **kw), 10)
+        g, _ = graph_of(one, 10)
         barrier()
         t = max_over_ranks(replay_ms(g) / 10)
         del g
