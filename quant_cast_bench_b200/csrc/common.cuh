@@ -424,8 +424,8 @@ static inline int read_clear_device_error(unsigned int *out)
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA load / mbarrier wrappers (cluster size 1, no multicast; outputs leave by plain coalesced stores, which
-// measured faster than TMA stores on B200)
+// TMA load / mbarrier wrappers (cluster size 1, every CTA fetches its own tile; outputs leave by plain coalesced
+// stores, which measured faster than TMA stores on B200)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
