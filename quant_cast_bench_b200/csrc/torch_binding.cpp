@@ -1,0 +1,228 @@
+// The casts as native PyTorch operators: TORCH_LIBRARY(quant_cast_cuda_native, ...) over the C ABI.
+//
+// A thin layer: every operator checks its tensors, allocates the outputs with the gold shapes and dtype views, and
+// calls the entry point of include/quant_cast_cuda.h on the current CUDA stream of x's device.  Meta implementations
+// give the same shapes without touching a device, so the operators trace (torch.compile, torch.export) and can be
+// called from C++ (torch::Dispatcher / the generated torch.ops handles) without Python.  The reference's counterpart is
+// the recipe layer of its Triton backend (quant_cast_triton/recipes.py:48-65 of vkuzo/quant_cast_bench).
+//
+//   amax(x, kind, fmt, recip_div)                           -> fp32 scalar   kind: "raw" | "fp8" | "nvfp4"
+//   fp8_tensorwise(x, scale, fmt)                           -> q
+//   fp8_rowwise(x, fmt, recip_div)                          -> (q, scale (M, 1))
+//   fp8_colwise(x, fmt, recip_div)                          -> (q (N, M), scale (N, 1))
+//   mxfp8(x, rowwise, colwise, swizzle, mode)               -> [qk, sk][qm, sm]   mode: "rceil" | "floor"
+//   nvfp4(x, outer_scale, swizzle, transposed, recip_div)   -> (q, inner scales)
+//
+// recip_div: QCC_RECIP_DIV (divisions by a constant as eager PyTorch computes them on a CUDA device).
+// Built by quant_cast_bench_b200/build.py into lib/libquant_cast_torch.so, which links against libquant_cast_cuda.so.
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../../include/quant_cast_cuda.h"
+
+namespace {
+
+void check_x(const at::Tensor &x)
+{
+    TORCH_CHECK(x.dim() == 2, "quant_cast_cuda: x must be 2-D");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16, "quant_cast_cuda: x must be bfloat16");
+}
+void check_x_cuda(const at::Tensor &x)
+{
+    check_x(x);
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "quant_cast_cuda: x must be a contiguous CUDA tensor (there is no CPU implementation)");
+}
+void *stream_of(const at::Tensor &x) { return c10::cuda::getCurrentCUDAStream(x.get_device()).stream(); }
+void ok(int rc, const char *what) { TORCH_CHECK(rc == 0, "quant_cast_cuda: ", what, " failed with code ", rc); }
+int fmt_of(const std::string &fmt)
+{
+    TORCH_CHECK(fmt == "e4m3" || fmt == "e5m2", "quant_cast_cuda: fmt must be 'e4m3' or 'e5m2'");
+    return fmt == "e5m2" ? QCC_FMT_E5M2 : QCC_FMT_E4M3;
+}
+at::ScalarType fp8_dtype(const std::string &fmt) { return fmt_of(fmt) == QCC_FMT_E5M2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn; }
+int amax_mode(const std::string &kind)
+{
+    TORCH_CHECK(kind == "raw" || kind == "fp8" || kind == "nvfp4", "quant_cast_cuda: kind must be 'raw', 'fp8' or 'nvfp4'");
+    return kind == "raw" ? QCC_AMAX_RAW : kind == "fp8" ? QCC_AMAX_FP8_SCALE : QCC_AMAX_NVFP4_SCALE;
+}
+int mx_mode(const std::string &mode)
+{
+    TORCH_CHECK(mode == "rceil" || mode == "floor", "quant_cast_cuda: mode must be 'rceil' or 'floor'");
+    return mode == "floor" ? QCC_FLOOR : 0;
+}
+std::vector<int64_t> blocked_shape(int64_t rows, int64_t cols) { return {(rows + 127) / 128, (cols + 3) / 4, 32, 16}; }
+std::vector<int64_t> scale_shape(int64_t rows, int64_t cols, bool swizzle)
+{
+    return swizzle ? blocked_shape(rows, cols) : std::vector<int64_t>{rows, cols};
+}
+at::Tensor bytes(at::IntArrayRef shape, const at::Tensor &like) { return at::empty(shape, like.options().dtype(at::kByte)); }
+
+// ---------------------------------------------------------------------------------------- CUDA implementations
+at::Tensor amax_cuda(const at::Tensor &x, std::string kind, std::string fmt, bool recip_div)
+{
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "quant_cast_cuda: x must be contiguous CUDA bfloat16");
+    const c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor out = at::empty({}, x.options().dtype(at::kFloat));
+    const size_t ws_bytes = qcc_amax_workspace_bytes();
+    at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));   // two launches: any contents will do
+    ok(qcc_amax_bf16(x.data_ptr(), x.numel(), amax_mode(kind) | (recip_div ? QCC_RECIP_DIV : 0), fmt_of(fmt), out.data_ptr<float>(),
+                     ws.data_ptr(), ws_bytes, stream_of(x)),
+       "amax");
+    return out;
+}
+
+at::Tensor fp8_tensorwise_cuda(const at::Tensor &x, const at::Tensor &scale, std::string fmt)
+{
+    check_x_cuda(x);
+    TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1, "quant_cast_cuda: scale must be one CUDA fp32 value");
+    const c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor q = bytes(x.sizes(), x);
+    ok(qcc_fp8_tensorwise(x.data_ptr(), x.numel(), scale.data_ptr<float>(), fmt_of(fmt), q.data_ptr(), stream_of(x)), "fp8_tensorwise");
+    return q.view(fp8_dtype(fmt));
+}
+
+std::tuple<at::Tensor, at::Tensor> fp8_rowwise_cuda(const at::Tensor &x, std::string fmt, bool recip_div)
+{
+    check_x_cuda(x);
+    const c10::cuda::CUDAGuard guard(x.device());
+    const int64_t M = x.size(0), N = x.size(1);
+    at::Tensor q = bytes({M, N}, x), s = at::empty({M, 1}, x.options().dtype(at::kFloat));
+    ok(qcc_fp8_rowwise(x.data_ptr(), M, N, fmt_of(fmt) | (recip_div ? QCC_RECIP_DIV : 0), q.data_ptr(), s.data_ptr<float>(), stream_of(x)),
+       "fp8_rowwise");
+    return {q.view(fp8_dtype(fmt)), s};
+}
+
+std::tuple<at::Tensor, at::Tensor> fp8_colwise_cuda(const at::Tensor &x, std::string fmt, bool recip_div)
+{
+    check_x_cuda(x);
+    const c10::cuda::CUDAGuard guard(x.device());
+    const int64_t M = x.size(0), N = x.size(1);
+    TORCH_CHECK(M % 16 == 0 && N % 8 == 0, "quant_cast_cuda: colwise fp8 needs M % 16 == 0 and N % 8 == 0");
+    at::Tensor q = bytes({N, M}, x), s = at::empty({N, 1}, x.options().dtype(at::kFloat));
+    const size_t ws_bytes = qcc_fp8_colwise_workspace_bytes(M, N);
+    at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+    ok(qcc_fp8_colwise(x.data_ptr(), M, N, fmt_of(fmt) | (recip_div ? QCC_RECIP_DIV : 0), q.data_ptr(), s.data_ptr<float>(), ws.data_ptr(),
+                       ws_bytes, stream_of(x)),
+       "fp8_colwise");
+    return {q.view(fp8_dtype(fmt)), s};
+}
+
+std::vector<at::Tensor> mxfp8_cuda(const at::Tensor &x, bool rowwise, bool colwise, bool swizzle, std::string mode)
+{
+    check_x_cuda(x);
+    TORCH_CHECK(rowwise || colwise, "quant_cast_cuda: mxfp8 needs at least one direction");
+    const c10::cuda::CUDAGuard guard(x.device());
+    const int64_t M = x.size(0), N = x.size(1);
+    TORCH_CHECK((!rowwise || N % 32 == 0) && (!colwise || (M % 32 == 0 && N % 8 == 0)), "quant_cast_cuda: mxfp8 blocks need N % 32 == 0 (rowwise) / M % 32 == 0 (colwise)");
+    at::Tensor qk, sk, qm, sm;
+    if (rowwise) { qk = bytes({M, N}, x); sk = bytes(scale_shape(M, N / 32, swizzle), x); }
+    if (colwise) { qm = bytes({N, M}, x); sm = bytes(scale_shape(N, M / 32, swizzle), x); }
+    const int flags = (rowwise ? QCC_ROWWISE : 0) | (colwise ? QCC_COLWISE : 0) | (swizzle ? QCC_SWIZZLE : 0) | mx_mode(mode);
+    ok(qcc_mxfp8(x.data_ptr(), M, N, flags, rowwise ? qk.data_ptr() : nullptr, rowwise ? sk.data_ptr() : nullptr,
+                 colwise ? qm.data_ptr() : nullptr, colwise ? sm.data_ptr() : nullptr, stream_of(x)),
+       "mxfp8");
+    std::vector<at::Tensor> outs;
+    if (rowwise) { outs.push_back(qk.view(at::kFloat8_e4m3fn)); outs.push_back(sk.view(at::kFloat8_e8m0fnu)); }
+    if (colwise) { outs.push_back(qm.view(at::kFloat8_e4m3fn)); outs.push_back(sm.view(at::kFloat8_e8m0fnu)); }
+    return outs;
+}
+
+std::tuple<at::Tensor, at::Tensor> nvfp4_cuda(const at::Tensor &x, const at::Tensor &outer_scale, bool swizzle, bool transposed,
+                                              bool recip_div)
+{
+    check_x_cuda(x);
+    TORCH_CHECK(outer_scale.is_cuda() && outer_scale.scalar_type() == at::kFloat && outer_scale.numel() == 1,
+                "quant_cast_cuda: outer_scale must be one CUDA fp32 value");
+    const c10::cuda::CUDAGuard guard(x.device());
+    const int64_t M = x.size(0), N = x.size(1);
+    const int flags = (swizzle ? QCC_SWIZZLE : 0) | (recip_div ? QCC_RECIP_DIV : 0);
+    at::Tensor q, s;
+    if (transposed) {
+        TORCH_CHECK(M % 32 == 0 && N % 8 == 0, "quant_cast_cuda: transposed nvfp4 needs M % 32 == 0 and N % 8 == 0");
+        q = bytes({N, M / 2}, x);
+        s = bytes(scale_shape(N, M / 16, swizzle), x);
+        ok(qcc_nvfp4_transposed(x.data_ptr(), M, N, outer_scale.data_ptr<float>(), flags, nullptr, q.data_ptr(), s.data_ptr(), stream_of(x)),
+           "nvfp4 transposed");
+    } else {
+        TORCH_CHECK(N % 16 == 0, "quant_cast_cuda: nvfp4 needs N % 16 == 0");
+        q = bytes({M, N / 2}, x);
+        s = bytes(scale_shape(M, N / 16, swizzle), x);
+        ok(qcc_nvfp4(x.data_ptr(), M, N, outer_scale.data_ptr<float>(), 0, flags, nullptr, q.data_ptr(), s.data_ptr(), stream_of(x)), "nvfp4");
+    }
+    return {q.view(at::kFloat4_e2m1fn_x2), s.view(at::kFloat8_e4m3fn)};
+}
+
+// ---------------------------------------------------------------------------------------- Meta (shape) implementations
+at::Tensor like(const at::Tensor &x, std::vector<int64_t> shape, at::ScalarType dt) { return at::empty(shape, x.options().dtype(dt)); }
+
+at::Tensor amax_meta(const at::Tensor &x, std::string kind, std::string fmt, bool)
+{
+    amax_mode(kind);
+    fmt_of(fmt);
+    return like(x, {}, at::kFloat);
+}
+at::Tensor fp8_tensorwise_meta(const at::Tensor &x, const at::Tensor &, std::string fmt) { return like(x, x.sizes().vec(), fp8_dtype(fmt)); }
+std::tuple<at::Tensor, at::Tensor> fp8_rowwise_meta(const at::Tensor &x, std::string fmt, bool)
+{
+    check_x(x);
+    return {like(x, {x.size(0), x.size(1)}, fp8_dtype(fmt)), like(x, {x.size(0), 1}, at::kFloat)};
+}
+std::tuple<at::Tensor, at::Tensor> fp8_colwise_meta(const at::Tensor &x, std::string fmt, bool)
+{
+    check_x(x);
+    return {like(x, {x.size(1), x.size(0)}, fp8_dtype(fmt)), like(x, {x.size(1), 1}, at::kFloat)};
+}
+std::vector<at::Tensor> mxfp8_meta(const at::Tensor &x, bool rowwise, bool colwise, bool swizzle, std::string mode)
+{
+    check_x(x);
+    mx_mode(mode);
+    const int64_t M = x.size(0), N = x.size(1);
+    std::vector<at::Tensor> outs;
+    if (rowwise) { outs.push_back(like(x, {M, N}, at::kFloat8_e4m3fn)); outs.push_back(like(x, scale_shape(M, N / 32, swizzle), at::kFloat8_e8m0fnu)); }
+    if (colwise) { outs.push_back(like(x, {N, M}, at::kFloat8_e4m3fn)); outs.push_back(like(x, scale_shape(N, M / 32, swizzle), at::kFloat8_e8m0fnu)); }
+    return outs;
+}
+std::tuple<at::Tensor, at::Tensor> nvfp4_meta(const at::Tensor &x, const at::Tensor &, bool swizzle, bool transposed, bool)
+{
+    check_x(x);
+    const int64_t rows = transposed ? x.size(1) : x.size(0), cols = transposed ? x.size(0) : x.size(1);
+    return {like(x, {rows, cols / 2}, at::kFloat4_e2m1fn_x2), like(x, scale_shape(rows, cols / 16, swizzle), at::kFloat8_e4m3fn)};
+}
+
+}  // namespace
+
+TORCH_LIBRARY(quant_cast_cuda_native, m)
+{
+    m.def("amax(Tensor x, str kind, str fmt, bool recip_div=False) -> Tensor");
+    m.def("fp8_tensorwise(Tensor x, Tensor scale, str fmt) -> Tensor");
+    m.def("fp8_rowwise(Tensor x, str fmt, bool recip_div=False) -> (Tensor, Tensor)");
+    m.def("fp8_colwise(Tensor x, str fmt, bool recip_div=False) -> (Tensor, Tensor)");
+    m.def("mxfp8(Tensor x, bool rowwise, bool colwise, bool swizzle, str mode) -> Tensor[]");
+    m.def("nvfp4(Tensor x, Tensor outer_scale, bool swizzle, bool transposed, bool recip_div=False) -> (Tensor, Tensor)");
+}
+
+TORCH_LIBRARY_IMPL(quant_cast_cuda_native, CUDA, m)
+{
+    m.impl("amax", amax_cuda);
+    m.impl("fp8_tensorwise", fp8_tensorwise_cuda);
+    m.impl("fp8_rowwise", fp8_rowwise_cuda);
+    m.impl("fp8_colwise", fp8_colwise_cuda);
+    m.impl("mxfp8", mxfp8_cuda);
+    m.impl("nvfp4", nvfp4_cuda);
+}
+
+TORCH_LIBRARY_IMPL(quant_cast_cuda_native, Meta, m)
+{
+    m.impl("amax", amax_meta);
+    m.impl("fp8_tensorwise", fp8_tensorwise_meta);
+    m.impl("fp8_rowwise", fp8_rowwise_meta);
+    m.impl("fp8_colwise", fp8_colwise_meta);
+    m.impl("mxfp8", mxfp8_meta);
+    m.impl("nvfp4", nvfp4_meta);
+}
