@@ -24,7 +24,8 @@ Printed: ONE JSON line (rank 0).  Besides the base keys it carries
                 byte with one GPU casting the whole tensor through the plain three-call recipes
   cpu_baseline  the reference's own gold recipes run eagerly on the host cores on a bounded row sample (oracle/_ref),
                 with the C restatement (oracle/qc_oracle.c, OpenMP) beside it
-  e2e           the same step through the host-buffer API (pinned host shard in, pinned host outputs back)
+  e2e           the same step through the host-buffer API (pinned host shard in, pinned host outputs back): a stream of
+                steps with two in flight (`HostShardCaster.submit` / `result`), and one step at a time beside it
   casts         per-cast GB/s of every cast of the benchmark configurations, same run, next to a same-size copy
   reference_gpu the reference's own Triton kernels timed with the same method on this GPU (N=1; --no-reference-gpu skips it)
   clocks        SM clock / throttle reasons sampled while the GPU was under load
@@ -484,17 +485,29 @@ def run_ours(args):
     # ---- end to end through the host-buffer API: pinned host shard in, pinned host outputs back, every step
     e2e = None
     if caster.xchg is not None and not args.only_step:
-        hc = HostShardCaster(rows, N4, dev, caster.xchg)
+        hc = HostShardCaster(rows, N4, dev, caster.xchg, slots=2)
         x_host = torch.empty((rows, N4), dtype=torch.bfloat16, pin_memory=True)
         x_host.copy_(xs[last])
         for _ in range(2):
             hc.cast(x_host)
         torch.cuda.synchronize()
         barrier()
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(4, min(args.steps, 30))
+        # one shard at a time: submit, wait, next (the latency of a step)
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             outs_host = hc.cast(x_host)
+        torch.cuda.synchronize()
+        e2e_serial_s = max_over_ranks(time.perf_counter() - t0)
+        barrier()
+        # a stream of shards, two in flight: the input of step k + 1 arrives while the nvfp4 outputs of step k leave
+        t0 = time.perf_counter()
+        for k in range(e2e_steps):
+            if k >= 2:
+                hc.result(k & 1)
+            hc.submit(x_host, k & 1)
+        for k in range(max(0, e2e_steps - 2), e2e_steps):
+            outs_host = hc.result(k & 1)
         torch.cuda.synchronize()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e_same = all(torch.equal(h.view(torch.uint8), d.view(torch.uint8).cpu()) for h, d in
@@ -525,11 +538,15 @@ def run_ours(args):
         bound_s = hc.bytes_in / (hc.bytes_in / t_h2d) + nv_out / (hc.bytes_out / t_d2h)
         link = {"h2d_GBps_per_gpu": hc.bytes_in / t_h2d / 1e9, "d2h_GBps_per_gpu": hc.bytes_out / t_d2h / 1e9,
                 "duplex_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) / t_dup / 1e9,
-                "step_lower_bound_ms": bound_s * 1e3, "frac_of_bound": bound_s / (e2e_s / e2e_steps),
-                "bound": "input / h2d rate + nvfp4 outputs / d2h rate (the nvfp4 outputs cannot leave before the whole input is in)"}
+                "step_lower_bound_ms": bound_s * 1e3, "frac_of_bound": bound_s / (e2e_serial_s / e2e_steps),
+                "bound": "one step alone: input / h2d rate + nvfp4 outputs / d2h rate (the nvfp4 outputs cannot leave before the "
+                         "whole input is in)",
+                "stream_lower_bound_ms": t_dup * 1e3, "frac_of_stream_bound": t_dup / (e2e_s / e2e_steps),
+                "stream_bound": "a stream of steps: all bytes of a step in both directions at the measured duplex rate"}
         e2e = {"value": step_bytes * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": hc.bytes_in * world, "d2h_bytes_per_step": hc.bytes_out * world, "steps": e2e_steps,
-               "ms_per_step": e2e_s / e2e_steps * 1e3, "chunk_rows": hc.rc,
+               "ms_per_step": e2e_s / e2e_steps * 1e3, "chunk_rows": hc.rc, "steps_in_flight": 2,
+               "one_step_at_a_time": {"value": step_bytes * e2e_steps / e2e_serial_s / 1e9, "ms_per_step": e2e_serial_s / e2e_steps * 1e3},
                "pcie_GBps_per_gpu": (hc.bytes_in + hc.bytes_out) * e2e_steps / e2e_s / 1e9,
                "outputs_equal_device_path": e2e_same, "link": link}
         del hc, x_host, outs_host

@@ -107,20 +107,27 @@ class HostShardCaster:
     outer scale; the nvfp4 cast then runs chunk by chunk over the shard, which stayed on the device, with its outputs
     leaving behind it.  Chunks are multiples of 128 rows, so the result equals the one-shot casts bit for bit."""
 
-    def __init__(self, rows, N, device, exchange, chunk_rows=8192):
+    def __init__(self, rows, N, device, exchange, chunk_rows=8192, slots=1):
         assert rows % 128 == 0 and N % 64 == 0, "host shard caster wants rows % 128 == 0 and N % 64 == 0"
+        assert slots >= 1
         self.rows, self.N, self.device, self.xchg = rows, N, torch.device(device), exchange
         rc = min(chunk_rows, rows)
         while rows % rc or rc % 128:
             rc -= 128
         self.rc = rc
         dev, u8 = self.device, torch.uint8
-        self.x_dev = torch.empty((rows, N), dtype=torch.bfloat16, device=dev)
         shapes = ((rows, N), blocked_shape(rows, N // 32), (rows, N // 2), blocked_shape(rows, N // 16))
-        self.out_dev = [torch.empty(s, dtype=u8, device=dev) for s in shapes]
-        self.outer_dev = torch.empty((), dtype=torch.float32, device=dev)
-        self.host = [torch.empty(s, dtype=u8, pin_memory=True) for s in shapes]
-        self.outer_host = torch.empty((), dtype=torch.float32, pin_memory=True)
+        # One slot = the device and pinned host buffers of one shard in flight.  With two slots `submit` can take the
+        # next shard while the nvfp4 outputs of the one before are still leaving (see submit / result).
+        self.slot = [{"x_dev": torch.empty((rows, N), dtype=torch.bfloat16, device=dev),
+                      "out_dev": [torch.empty(sh, dtype=u8, device=dev) for sh in shapes],
+                      "outer_dev": torch.empty((), dtype=torch.float32, device=dev),
+                      "host": [torch.empty(sh, dtype=u8, pin_memory=True) for sh in shapes],
+                      "outer_host": torch.empty((), dtype=torch.float32, pin_memory=True),
+                      "read_done": None, "done": None} for _ in range(slots)]
+        s0 = self.slot[0]
+        self.x_dev, self.out_dev, self.outer_dev, self.host, self.outer_host = (s0["x_dev"], s0["out_dev"], s0["outer_dev"], s0["host"],
+                                                                               s0["outer_host"])
         self.dtypes = [torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float4_e2m1fn_x2, torch.float8_e4m3fn]
         with torch.cuda.device(dev):
             self.s_h2d, self.s_cmp, self.s_d2h = (torch.cuda.Stream() for _ in range(3))
@@ -130,11 +137,30 @@ class HostShardCaster:
     def cast(self, x_host):
         """x_host: contiguous (rows, N) bf16 host tensor (pinned for full copy speed).  Returns (mx_q, mx_scales, nv_q,
         nv_scales, outer_scale) as views of this object's pinned host buffers; complete on return."""
+        self.submit(x_host, 0)
+        return self.result(0)
+
+    def result(self, slot=0):
+        """Waits for the shard submitted into `slot` and returns its five outputs (views of the slot's pinned buffers,
+        valid until the slot is submitted to again)."""
+        sl = self.slot[slot]
+        assert sl["done"] is not None, "nothing was submitted into this slot"
+        sl["done"].synchronize()
+        return tuple(h.view(dt) for h, dt in zip(sl["host"], self.dtypes)) + (sl["outer_host"],)
+
+    def submit(self, x_host, slot=0):
+        """Queues the whole flow for one shard into `slot` and returns without waiting.  With two slots used in turn
+        (submit(a, 0); submit(b, 1); result(0); submit(c, 0); ...) the input copy of a shard overlaps the departure of the
+        nvfp4 outputs of the shard before it, which a single shard cannot overlap with anything because they need the
+        amax of ALL its rows.  Every rank of the exchange must submit in the same order.  The caller must have taken
+        `result(slot)` of the slot's previous shard (its pinned output buffers are overwritten)."""
         lib = L.load()
         rows, N, rc = self.rows, self.N, self.rc
         assert x_host.shape == (rows, N) and x_host.dtype == torch.bfloat16 and x_host.is_contiguous()
-        mq_d, ms_d, nq_d, ns_d = self.out_dev
-        mq_h, ms_h, nq_h, ns_h = self.host
+        sl = self.slot[slot]
+        x_dev, outer_dev, outer_host = sl["x_dev"], sl["outer_dev"], sl["outer_host"]
+        mq_d, ms_d, nq_d, ns_d = sl["out_dev"]
+        mq_h, ms_h, nq_h, ns_h = sl["host"]
         n_chunks = rows // rc
         ab = rc // 128                       # 128-row scale atoms rows per chunk
         flags = L.ROWWISE | L.SWIZZLE
@@ -142,15 +168,19 @@ class HostShardCaster:
             cur = torch.cuda.current_stream()
             for s in (self.s_h2d, self.s_cmp, self.s_d2h):
                 s.wait_stream(cur)
+            if sl["read_done"] is not None:      # the slot's previous shard: its last cast has read x_dev ...
+                self.s_h2d.wait_event(sl["read_done"])
+            if sl["done"] is not None:           # ... and its outputs have left the device buffers
+                self.s_cmp.wait_event(sl["done"])
             for i in range(n_chunks):
                 r0 = i * rc
                 with torch.cuda.stream(self.s_h2d):
-                    self.x_dev[r0:r0 + rc].copy_(x_host[r0:r0 + rc], non_blocking=True)
+                    x_dev[r0:r0 + rc].copy_(x_host[r0:r0 + rc], non_blocking=True)
                     arrived = torch.cuda.Event()
                     arrived.record(self.s_h2d)
                 with torch.cuda.stream(self.s_cmp):
                     self.s_cmp.wait_event(arrived)
-                    L.check(lib.qcc_mxfp8_amax_xchg(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, flags, mq_d[r0:r0 + rc].data_ptr(),
+                    L.check(lib.qcc_mxfp8_amax_xchg(x_dev[r0:r0 + rc].data_ptr(), rc, N, flags, mq_d[r0:r0 + rc].data_ptr(),
                                                     ms_d[i * ab:(i + 1) * ab].data_ptr(), self.xchg.own, self.s_cmp.cuda_stream),
                             "mxfp8_amax_xchg")
                     L.launch_count += 1
@@ -162,12 +192,12 @@ class HostShardCaster:
                     ms_h[i * ab:(i + 1) * ab].copy_(ms_d[i * ab:(i + 1) * ab], non_blocking=True)
             with torch.cuda.stream(self.s_cmp):
                 self.xchg._pending = True
-                L.check(lib.qcc_xchg_resolve(self.xchg._ref(), L.AMAX_NVFP4_SCALE | L.div_flag(), L.FMT_E4M3, self.outer_dev.data_ptr(),
+                L.check(lib.qcc_xchg_resolve(self.xchg._ref(), L.AMAX_NVFP4_SCALE | L.div_flag(), L.FMT_E4M3, outer_dev.data_ptr(),
                                              self.s_cmp.cuda_stream), "xchg_resolve")
                 L.launch_count += 1
                 for i in range(n_chunks):
                     r0 = i * rc
-                    L.check(lib.qcc_nvfp4(self.x_dev[r0:r0 + rc].data_ptr(), rc, N, self.outer_dev.data_ptr(), 0, L.SWIZZLE | L.div_flag(), None,
+                    L.check(lib.qcc_nvfp4(x_dev[r0:r0 + rc].data_ptr(), rc, N, outer_dev.data_ptr(), 0, L.SWIZZLE | L.div_flag(), None,
                                           nq_d[r0:r0 + rc].data_ptr(), ns_d[i * ab:(i + 1) * ab].data_ptr(), self.s_cmp.cuda_stream),
                             "nvfp4")
                     L.launch_count += 1
@@ -178,6 +208,8 @@ class HostShardCaster:
                         nq_h[r0:r0 + rc].copy_(nq_d[r0:r0 + rc], non_blocking=True)
                         ns_h[i * ab:(i + 1) * ab].copy_(ns_d[i * ab:(i + 1) * ab], non_blocking=True)
                         if i == 0:
-                            self.outer_host.copy_(self.outer_dev, non_blocking=True)
-            self.s_d2h.synchronize()
-        return tuple(h.view(dt) for h, dt in zip(self.host, self.dtypes)) + (self.outer_host,)
+                            outer_host.copy_(outer_dev, non_blocking=True)
+                sl["read_done"] = done                      # the last nvfp4 chunk: x_dev may be overwritten after it
+            sl["done"] = torch.cuda.Event()
+            sl["done"].record(self.s_d2h)
+        return slot

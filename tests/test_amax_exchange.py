@@ -265,6 +265,38 @@ def test_host_shard_caster_matches_the_one_shot_casts(rows, chunk):
     xchg.close()
 
 
+def test_host_shard_caster_two_slots_in_flight():
+    """submit / result with two slots: five different shards go through in turn, two in flight at any time; every one
+    comes back with the bytes of its own one-shot casts (its own amax, not a neighbour's)."""
+    from oracle import gold_port as O
+    from quant_cast_bench_b200.quant_cast_cuda import sharded
+    from quant_cast_bench_b200.quant_cast_cuda.host_api import HostShardCaster
+    rows, N = 512, 1024
+    xs = []
+    for k in range(5):
+        x = make_input(rows, N, seed=40 + k, spread=6.0)
+        x[(37 * k) % rows, 5] = 1.0e3 * (k + 1)               # a different maximum, in a different chunk, every time
+        xs.append(x)
+    xh = [x.pin_memory() for x in xs]
+    xchg = sharded.AmaxExchange()
+    hc = HostShardCaster(rows, N, "cuda", xchg, chunk_rows=128, slots=2)
+
+    def check(k, got):
+        outer = O.nvfp4_gs_scale(xs[k])
+        want = (*O.mxfp8_swizzle_f(xs[k]), *O.nvfp4_gs_swizzle_f(xs[k], outer), outer)
+        for g, w in zip(got, want):
+            assert_same_bits(g, w, f"shard {k}")
+    hc.submit(xh[0], 0)
+    hc.submit(xh[1], 1)
+    for k in range(2, 5):
+        check(k - 2, hc.result(k & 1))
+        hc.submit(xh[k], k & 1)
+    check(3, hc.result(1))
+    check(4, hc.result(0))
+    check(0, hc.cast(xh[0]))                                   # the blocking form still works on the same object
+    xchg.close()
+
+
 def test_a_rank_that_never_publishes_runs_the_wait_out():
     ranks = _Ranks(2, timeout_us=20_000)
     x = make_input(128, 256, seed=2).cuda()
