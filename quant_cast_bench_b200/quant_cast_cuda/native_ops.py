@@ -80,6 +80,83 @@ def nvfp4_gs_swizzle_t_native(x, outer_scale, **kwargs):
     return tuple(ops.nvfp4(x, outer_scale, True, True, _recip()))
 
 
+def nvfp4_gs_swizzle_sr_native(x, outer_scale, key, **kwargs):
+    return tuple(ops.nvfp4_sr(x, outer_scale, key, True, False, _recip()))
+
+
+def nvfp4_gs_swizzle_t_sr_native(x, outer_scale, key, **kwargs):
+    return tuple(ops.nvfp4_sr(x, outer_scale, key, True, True, _recip()))
+
+
+def nvfp4_gs_swizzle_both_native(x, outer_scale, **kwargs):
+    return tuple(ops.nvfp4_both(x, outer_scale, True, _recip()))
+
+
+def nvfp4_blocked_outer_native(x, outer_blocked, **kwargs):
+    return tuple(ops.nvfp4(x, outer_blocked, True, False, _recip()))
+
+
+def rowwise_precalc_native(x, scale, fmt="e4m3", **kwargs):
+    return (ops.fp8_rowwise_precalc(x, scale, fmt),)
+
+
+def colwise_precalc_native(x, scale, fmt="e4m3", **kwargs):
+    return (ops.fp8_colwise_precalc(x, scale, fmt),)
+
+
+def deepseek_1x128_native(x, **kwargs):
+    return tuple(ops.fp8_block128(x, True, False, _recip()))
+
+
+def deepseek_1x128_dim_m_native(x, **kwargs):
+    return tuple(ops.fp8_block128(x, False, True, _recip()))
+
+
+def deepseek_1x128_dim_km_native(x, **kwargs):
+    return tuple(ops.fp8_block128(x, True, True, _recip()))
+
+
+def deepseek_128x128_native(x, **kwargs):
+    return tuple(ops.fp8_block128x128(x, _recip()))
+
+
+def mxfp8_32x32_native(x, **kwargs):
+    return tuple(ops.mxfp8_32x32(x, True, False, False, True))
+
+
+def mxfp8_32x32_swizzle_native(x, **kwargs):
+    return tuple(ops.mxfp8_32x32(x, True, False, True, True))
+
+
+def mxfp8_32x32_dim_m_swizzle_native(x, **kwargs):
+    return tuple(ops.mxfp8_32x32(x, False, True, True, True))
+
+
+def mxfp8_32x32_dim_km_swizzle_native(x, **kwargs):
+    return tuple(ops.mxfp8_32x32(x, True, True, True, True))
+
+
+def mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_native(x, **kwargs):
+    return tuple(ops.mxfp8_32x32(x, True, True, True, False))
+
+
+def mxfp4_native(x, swizzle=False, **kwargs):
+    return tuple(ops.mxfp4(x, swizzle))
+
+
+# (gold function name in the golden vectors, operator-backed function, aux input): the other recipe families
+MORE_NATIVE = [
+    ("rowwise_precalc_f", rowwise_precalc_native, "row_scale"), ("colwise_precalc_f", colwise_precalc_native, "col_scale"),
+    ("deepseek_1x128_f", deepseek_1x128_native, None), ("deepseek_1x128_dim_m_f", deepseek_1x128_dim_m_native, None),
+    ("deepseek_1x128_dim_km_f", deepseek_1x128_dim_km_native, None), ("deepseek_128x128_f", deepseek_128x128_native, None),
+    ("mxfp8_32x32_f", mxfp8_32x32_native, None), ("mxfp8_32x32_swizzle_f", mxfp8_32x32_swizzle_native, None),
+    ("mxfp8_32x32_dim_m_swizzle_f", mxfp8_32x32_dim_m_swizzle_native, None),
+    ("mxfp8_32x32_dim_km_swizzle_f", mxfp8_32x32_dim_km_swizzle_native, None),
+    ("mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_f", mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle_native, None),
+    ("mxfp4_f", mxfp4_native, None), ("nvfp4_blocked_outer_f", nvfp4_blocked_outer_native, "blocked_outer"),
+    ("nvfp4_gs_f_per_token", nvfp4_gs_native, "per_token"), ("nvfp4_gs_swizzle_t_f", nvfp4_gs_swizzle_t_native, "outer"),
+]
+
 # (gold recipe name, operator-backed function): the recipes of BASELINE configurations 1-4
 NATIVE_RECIPES = [
     ("fp8_tensorwise_precalc_scale", float8_tensorwise_native), ("fp8_rowwise", rowwise_fp8_native), ("fp8_colwise", colwise_fp8_native),

@@ -41,6 +41,63 @@ def test_meta_implementations_give_the_gold_shapes(name, fn):
             assert o.numel() * o.element_size() == want.numel() * want.element_size(), (name, tag, i)
 
 
+def _more_inputs(tag, aux, device):
+    x = golden_x(tag).to(device)
+    key = {"row_scale": "rowwise_precalc_scale", "col_scale": "colwise_precalc_scale", "blocked_outer": "nvfp4_blocked_outer_scale",
+           "per_token": "nvfp4_per_token_scale", "outer": "nvfp4_gs_scale"}.get(aux)
+    if key is None:
+        return (x,)
+    a = golden_out(tag, key, 0).view(torch.float32)
+    return (x, (a.reshape(()) if aux == "outer" else a).to(device))
+
+
+@pytest.mark.parametrize("gold_fn,fn,aux", N.MORE_NATIVE)
+def test_meta_shapes_of_the_other_families(gold_fn, fn, aux):
+    ran = 0
+    for tag in golden_cases():
+        n = golden_n_outputs(tag, gold_fn)
+        if n == 0:
+            continue
+        outs = fn(*(t.to("meta") for t in _more_inputs(tag, aux, "cpu")))
+        assert len(outs) == n, (gold_fn, tag)
+        for i, o in enumerate(outs):
+            want = golden_out(tag, gold_fn, i)
+            assert tuple(o.shape) == tuple(want.shape) and o.numel() * o.element_size() == want.numel() * want.element_size(), (gold_fn, tag, i)
+        ran += 1
+    assert ran > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("gold_fn,fn,aux", N.MORE_NATIVE)
+def test_the_other_families_match_the_golden_vectors(gold_fn, fn, aux):
+    ran = 0
+    for tag in golden_cases():
+        n = golden_n_outputs(tag, gold_fn)
+        if n == 0:
+            continue
+        outs = fn(*_more_inputs(tag, aux, "cuda"))
+        for i, o in enumerate(outs):
+            assert_same_bits(o, golden_out(tag, gold_fn, i), f"{gold_fn}[{i}] {tag}")
+        ran += 1
+    assert ran > 0
+
+
+@pytest.mark.gpu
+def test_stochastic_and_two_orientation_forms_match_the_ctypes_route():
+    from quant_cast_bench_b200 import quant_cast_cuda as Q
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    gs = Q.nvfp4_gs_scale_cuda(x)
+    key = Q.philox_key(7, device="cuda")
+    for a, b in zip(N.nvfp4_gs_swizzle_sr_native(x, gs, key), Q.nvfp4_gs_swizzle_sr_cuda(x, gs, key)):
+        assert_same_bits(a, b, "nvfp4 sr")
+    for a, b in zip(N.nvfp4_gs_swizzle_t_sr_native(x, gs, key), Q.nvfp4_gs_swizzle_t_sr_cuda(x, gs, key)):
+        assert_same_bits(a, b, "nvfp4 transposed sr")
+    for a, b in zip(N.nvfp4_gs_swizzle_both_native(x, gs), Q.nvfp4_gs_swizzle_both_cuda(x, gs)):
+        assert_same_bits(a, b, "nvfp4 both")
+    for a, b in zip(N.mxfp4_native(x, swizzle=True), Q.mxfp4_cuda(x, swizzle=True)):
+        assert_same_bits(a, b, "mxfp4 blocked")
+
+
 def test_operators_have_no_cpu_implementation_and_check_their_arguments():
     with pytest.raises(NotImplementedError):
         torch.ops.quant_cast_cuda_native.mxfp8(torch.zeros(32, 32, dtype=torch.bfloat16), True, False, False, "rceil")
