@@ -55,7 +55,8 @@ extern "C" {
  * With QCC_RECIP_DIV: a * fl(1 / c), bit-identical to the gold recipes run eagerly on a CUDA device.  Accepted in the
  * `mode` of the amax entry points (qcc_amax_bf16, qcc_amax_bf16_noalloc, qcc_scale_from_amax, qcc_xchg_resolve,
  * qcc_amax_block128x128, qcc_nvfp4_rht_amax), in the `fmt` of qcc_fp8_tensorwise_from_amax, qcc_fp8_rowwise and
- * qcc_fp8_colwise, and in the `flags` of qcc_fp8_block128, qcc_fp8_block128x128 and every qcc_nvfp4* cast.  Casts that
+ * qcc_fp8_colwise, and in the `flags` of qcc_fp8_block128, qcc_fp8_block128x128, qcc_nvfp4_per_token_scale and every
+ * qcc_nvfp4* cast.  Casts that
  * only multiply (mxfp8, mxfp4, a cast by a given scale) have no such division and do not take it. */
 #define QCC_RECIP_DIV 0x800
 
