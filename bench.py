@@ -26,7 +26,8 @@ Printed: ONE JSON line (rank 0).  Besides the base keys it carries
                 with the C restatement (oracle/qc_oracle.c, OpenMP) beside it
   e2e           the same step through the host-buffer API (pinned host shard in, pinned host outputs back): a stream of
                 steps with two in flight (`HostShardCaster.submit` / `result`), and one step at a time beside it
-  casts         per-cast GB/s of every cast of the benchmark configurations, same run, next to a same-size copy
+  casts         per-cast GB/s of every cast of the benchmark configurations, same run, next to a same-size copy and next to
+                a kernel that moves the same bytes in and out without computing (`frac_same_traffic_cold`)
   reference_gpu the reference's own Triton kernels timed with the same method on this GPU (N=1; --no-reference-gpu skips it)
   clocks        SM clock / throttle reasons sampled while the GPU was under load
 `--impl reference` times the reference's gold recipes (PyTorch eager, host CPU, all threads) on the same step.
@@ -943,7 +944,12 @@ def bench_other_casts(Q, x, dev, peak):
     # kernel that only moves data reaches at each size on this GPU
     y = torch.empty_like(x)
     out["copy_16384"] = timed(lambda: Q.stream_copy_cuda(x, y), algorithmic_bytes(M, N, "copy"))
-    del y
+    # ... and the same for casts that write less than they read: the loads and stores of a 2-byte -> 1-byte cast
+    # (fold 2:1) and of a 2-byte -> half-byte cast (fold 4:1) without the arithmetic
+    yb = y.view(torch.uint8).reshape(-1)
+    out["fold2_16384"] = timed(lambda: Q.stream_fold_cuda(x, yb[:M * N], 2), 3 * M * N)
+    out["fold4_16384"] = timed(lambda: Q.stream_fold_cuda(x, yb[:M * N // 2], 4), 2 * M * N + M * N // 2)
+    del y, yb
     out["amax_16384"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x, workspace=ws), algorithmic_bytes(M, N, "amax"))
     out["fp8_tensorwise_16384"] = timed(lambda: Q.float8_tensorwise_cuda(x, s), algorithmic_bytes(M, N, "fp8_tensorwise"))
     out["fp8_rowwise_16384"] = timed(lambda: Q.rowwise_fp8_cuda(x), algorithmic_bytes(M, N, "fp8_rowwise"))
@@ -969,6 +975,7 @@ def bench_other_casts(Q, x, dev, peak):
     s1 = Q.float8_tensorwise_scale_cuda(x1)
     y1 = torch.empty_like(x1)
     out["c1_copy_4096"] = timed(lambda: Q.stream_copy_cuda(x1, y1), algorithmic_bytes(4096, 4096, "copy"), True)
+    out["c1_fold2_4096"] = timed(lambda: Q.stream_fold_cuda(x1, y1.view(torch.uint8).reshape(-1)[:4096 * 4096], 2), 3 * 4096 * 4096, True)
     out["c1_fp8_tensorwise_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
     out["c1_fp8_tensorwise_e5m2_4096"] = timed(lambda: Q.float8_tensorwise_cuda(x1, s1, "e5m2"), algorithmic_bytes(4096, 4096, "fp8_tensorwise"), True)
     out["c1_fp8_rowwise_4096"] = timed(lambda: Q.rowwise_fp8_cuda(x1), algorithmic_bytes(4096, 4096, "fp8_rowwise"), True)
@@ -977,6 +984,7 @@ def bench_other_casts(Q, x, dev, peak):
     gs3 = Q.nvfp4_gs_scale_cuda(x3)
     y3 = torch.empty_like(x3)
     out["c3_copy_8192"] = timed(lambda: Q.stream_copy_cuda(x3, y3), algorithmic_bytes(8192, 8192, "copy"), True)
+    out["c3_fold4_8192"] = timed(lambda: Q.stream_fold_cuda(x3, y3.view(torch.uint8).reshape(-1)[:8192 * 8192 // 2], 4), 2 * 8192 * 8192 + 8192 * 8192 // 2, True)
     del y3
     out["c3_nvfp4_amax_8192"] = timed(lambda: Q.nvfp4_gs_scale_cuda(x3, workspace=ws), algorithmic_bytes(8192, 8192, "amax"), True)
     out["c3_nvfp4_8192"] = timed(lambda: Q.nvfp4_gs_cuda(x3, gs3), algorithmic_bytes(8192, 8192, "nvfp4"), True)
@@ -987,6 +995,21 @@ def bench_other_casts(Q, x, dev, peak):
     for k, v in out.items():                   # each row against the copy of its own size
         ref = out["c1_copy_4096"] if k.startswith("c1_") else out["c3_copy_8192"] if k.startswith("c3_") else out["copy_16384"]
         v["frac_same_size_copy_cold"] = v["GBps_cold_in_graph"] / ref["GBps_cold_in_graph"]
+        # ... and, for the casts that read x once and write one output, against the kernel that moves the same bytes in
+        # and (nearly) the same bytes out and computes nothing: time of that kernel / time of the cast
+        fold = None
+        if k in ("c1_fp8_tensorwise_4096", "c1_fp8_tensorwise_e5m2_4096", "c1_fp8_rowwise_4096"):
+            fold = out["c1_fold2_4096"]
+        elif k in ("c3_nvfp4_8192", "c3_nvfp4_swizzle_8192", "c3_nvfp4_swizzle_t_8192"):
+            fold = out["c3_fold4_8192"]
+        elif k in ("mxfp8", "mxfp8_swizzle", "mxfp8_floor", "mxfp8_swizzle_floor", "mxfp8_dim_m", "mxfp8_dim_m_swizzle", "mxfp8_32x32",
+                   "mxfp8_32x32_swizzle", "fp8_deepseek_1x128", "fp8_deepseek_1x128_dim_m", "fp8_deepseek_128x128", "fp8_tensorwise_16384",
+                   "fp8_rowwise_16384", "fp8_colwise_16384"):
+            fold = out["fold2_16384"]
+        elif k in ("nvfp4_16384", "nvfp4_swizzle_16384", "nvfp4_swizzle_t_16384"):
+            fold = out["fold4_16384"]
+        if fold is not None:
+            v["frac_same_traffic_cold"] = fold["ms_cold_in_graph"] / v["ms_cold_in_graph"]
     return out
 
 

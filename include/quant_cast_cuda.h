@@ -112,6 +112,12 @@ int qcc_copy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pi
  * (No counterpart in the reference, whose yardstick is an eager relu, benchmarks/benchmark.py:41-60.) */
 int qcc_stream_copy(const void *src, void *dst, size_t bytes, void *stream);
 
+/* The yardstick for casts that write fewer bytes than they read: piece i (16 bytes) of dst = XOR of pieces ratio * i ...
+ * ratio * i + ratio - 1 of src; ratio 2 or 4, bytes_in % (16 * ratio) == 0, dst holds bytes_in / ratio bytes.  The loads
+ * and stores of an fp8 / mxfp8 cast (2: two bytes in, one out) or of an nvfp4 cast (4: two bytes in, half a byte out)
+ * without their arithmetic. */
+int qcc_stream_fold(const void *src, void *dst, size_t bytes_in, int ratio, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * amax and per-tensor scales
  * ------------------------------------------------------------------------------------------- */

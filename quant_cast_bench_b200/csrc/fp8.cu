@@ -236,6 +236,31 @@ __global__ void __launch_bounds__(TW_THREADS) stream_copy_kernel(const uint4 *__
     if (i + TW_THREADS < nvec) st_out(dst + i + TW_THREADS, b);
 }
 
+// The same yardstick for casts that write fewer bytes than they read: every 16-byte piece of dst is the XOR of R
+// consecutive 16-byte pieces of src -- the loads and stores of a 2-byte -> 1-byte cast (R = 2: a thread reads 32 contiguous
+// bytes, as the tensorwise cast does) or of a 2-byte -> half-byte cast (R = 4: 64 contiguous bytes, as the nvfp4 stream
+// does), without their arithmetic.
+template <int R, int U>
+__global__ void __launch_bounds__(TW_THREADS) stream_fold_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, int64_t nout)
+{
+    const int64_t base = (int64_t)blockIdx.x * (TW_THREADS * U) + threadIdx.x;
+    uint4 v[U][R];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int64_t o = base + (int64_t)u * TW_THREADS;
+#pragma unroll
+        for (int r = 0; r < R; r++) v[u][r] = o < nout ? ld_v4(src + o * R + r) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int64_t o = base + (int64_t)u * TW_THREADS;
+        uint4 a = v[u][0];
+#pragma unroll
+        for (int r = 1; r < R; r++) { a.x ^= v[u][r].x; a.y ^= v[u][r].y; a.z ^= v[u][r].z; a.w ^= v[u][r].w; }
+        if (o < nout) st_out(dst + o, a);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // rowwise cast: TPR threads share a row and keep it in registers (CH 16-byte chunks each), so x is
 // read from HBM exactly once.  PRECALC: per-row scale supplied, true division.
@@ -625,6 +650,23 @@ int qcc_stream_copy(const void *src, void *dst, size_t bytes, void *stream)
     const int64_t grid = (nvec + TW_THREADS * 2 - 1) / (TW_THREADS * 2);
     if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
     stream_copy_kernel<<<(unsigned)grid, TW_THREADS, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, nvec);
+    return (int)cudaGetLastError();
+}
+
+int qcc_stream_fold(const void *src, void *dst, size_t bytes_in, int ratio, void *stream)
+{
+    if (bytes_in == 0) return 0;
+    if (!src || !dst || (ratio != 2 && ratio != 4)) return QCC_ERR_ARG;
+    if (bytes_in % (16 * (size_t)ratio) != 0) return QCC_ERR_SHAPE;
+    if (!aligned16(src) || !aligned16(dst)) return QCC_ERR_ALIGN;
+    const int64_t nout = (int64_t)(bytes_in / 16 / ratio);
+    const int u = ratio == 2 ? 2 : 1;
+    const int64_t grid = (nout + TW_THREADS * u - 1) / (TW_THREADS * u);
+    if (grid > 0x7FFFFFFF) return QCC_ERR_SHAPE;
+    if (ratio == 2)
+        stream_fold_kernel<2, 2><<<(unsigned)grid, TW_THREADS, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, nout);
+    else
+        stream_fold_kernel<4, 1><<<(unsigned)grid, TW_THREADS, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, nout);
     return (int)cudaGetLastError();
 }
 

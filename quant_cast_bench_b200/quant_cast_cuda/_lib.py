@@ -34,6 +34,7 @@ SIGNATURES = {
     "qcc_sm_count": (_int, []),
     "qcc_copy2d_async": (_int, [_vp, _sz, _vp, _sz, _sz, _sz, _int, _vp]),
     "qcc_stream_copy": (_int, [_vp, _vp, _sz, _vp]),
+    "qcc_stream_fold": (_int, [_vp, _vp, _sz, _int, _vp]),
     "qcc_amax_workspace_bytes": (_sz, []),
     "qcc_amax_workspace_init": (_int, [_vp, _sz, _vp]),
     "qcc_amax_bf16": (_int, [_vp, _i64, _int, _int, _vp, _vp, _sz, _vp]),

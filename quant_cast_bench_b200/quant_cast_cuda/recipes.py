@@ -94,6 +94,19 @@ def stream_copy_cuda(src, dst):
     return dst
 
 
+def stream_fold_cuda(src, dst, ratio):
+    """dst = XOR-fold of src, `ratio` (2 or 4) 16-byte pieces into one: the data movement of a cast that writes
+    1/ratio of what it reads, without the arithmetic -- the yardstick for the fp8 / mxfp8 casts (2) and nvfp4 (4)."""
+    lib = L.load()
+    assert src.is_cuda and dst.is_cuda and src.is_contiguous() and dst.is_contiguous()
+    nbytes = src.numel() * src.element_size()
+    assert nbytes == ratio * dst.numel() * dst.element_size(), "dst must hold 1/ratio of the bytes of src"
+    with _on_device(src.device):
+        L.check(lib.qcc_stream_fold(_p(src), _p(dst), nbytes, ratio, _stream(src)), "stream_fold")
+    L.launch_count += 1
+    return dst
+
+
 # --------------------------------------------------------------------------------------------
 # amax and per-tensor scales
 # --------------------------------------------------------------------------------------------

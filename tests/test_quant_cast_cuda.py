@@ -528,3 +528,20 @@ def test_stream_copy_yardstick(n):
     Q.stream_copy_cuda(src, dst[:n])
     assert torch.equal(dst[:n], src) and int(dst[n:].sum()) == 0
     assert L.load().qcc_stream_copy(src.data_ptr(), dst.data_ptr(), 24, None) == -1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ratio", [2, 4])
+@pytest.mark.parametrize("nout", [1, 511, 512, 1 << 16, (1 << 18) + 3])
+def test_stream_fold_yardstick(ratio, nout):
+    """The benchmarks' fold kernel: piece i of dst is the XOR of `ratio` consecutive 16-byte pieces of src."""
+    src = torch.randint(0, 256, (nout * ratio, 16), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(nout * 16 + 32, dtype=torch.uint8, device="cuda")
+    Q.stream_fold_cuda(src, dst[:nout * 16], ratio)
+    want = src.view(nout, ratio, 16)[:, 0]
+    for r in range(1, ratio):
+        want = want ^ src.view(nout, ratio, 16)[:, r]
+    assert torch.equal(dst[:nout * 16].view(nout, 16), want) and int(dst[nout * 16:].sum()) == 0
+    lib = L.load()
+    assert lib.qcc_stream_fold(src.data_ptr(), dst.data_ptr(), 16 * ratio, 3, None) == -3
+    assert lib.qcc_stream_fold(src.data_ptr(), dst.data_ptr(), 16 * ratio + 16, ratio, None) == -1
