@@ -51,7 +51,14 @@ def _extensions(x):
     key = Q.philox_key(0, device=x.device)
     rht = Q.hadamard_rht_matrix_cuda(torch.tensor([1, -1] * 8), x.device)
     gs_m = Q.nvfp4_rht_outer_scale_m_cuda(x, rht)
+    y = torch.empty_like(x)
+    yb = y.view(torch.uint8).reshape(-1)
+    n = x.numel()
     return [
+        # the yardsticks: kernels that only move data, with the streaming casts' access pattern
+        ("yardstick_copy", (x,), lambda: (Q.stream_copy_cuda(x, y),)),
+        ("yardstick_fold_2_to_1", (x,), lambda: (Q.stream_fold_cuda(x, yb[:n], 2),)),
+        ("yardstick_fold_4_to_1", (x,), lambda: (Q.stream_fold_cuda(x, yb[:n // 2], 4),)),
         ("amax_fp8_scale", (x,), lambda: (Q.float8_tensorwise_scale_cuda(x),)),
         ("amax_nvfp4_scale", (x,), lambda: (Q.nvfp4_gs_scale_cuda(x),)),
         ("fp8_tensorwise_e5m2", (x, s5), lambda: Q.float8_tensorwise_cuda(x, s5, "e5m2")),
