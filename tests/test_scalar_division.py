@@ -182,6 +182,22 @@ def test_kernels_cuda_eager_match_the_oracle(shape, seed):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["ieee", "cuda_eager"])
+def test_e5m2_forms_match_the_oracle_in_both_settings(mode):
+    """The e5m2 extension divides by 57344 the same two ways."""
+    from quant_cast_bench_b200 import quant_cast_cuda as Q
+    x = _c2_like(256, 768, 21)
+    xc = x.cuda()
+    with O.scalar_division(mode), L.scalar_division(mode):
+        assert_same_bits(Q.float8_tensorwise_scale_cuda(xc, "e5m2").reshape(1), O.float8_tensorwise_scale(x, "e5m2").reshape(1), "scale")
+        for name in ("rowwise_fp8", "colwise_fp8"):
+            got = getattr(Q, name + "_cuda")(xc, "e5m2")
+            ref = getattr(O, name + "_f")(x, "e5m2")
+            for i, (a, b) in enumerate(zip(got, ref)):
+                assert_same_bits(a, b, f"{name} e5m2 [{i}] {mode}")
+
+
+@pytest.mark.gpu
 def test_from_amax_and_exchange_forms_follow_the_setting():
     """The casts that form their scale from a raw amax in their prologue take the same flag."""
     from quant_cast_bench_b200 import quant_cast_cuda as Q
