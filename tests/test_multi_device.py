@@ -54,3 +54,4 @@ def test_casts_on_a_second_device():
     for d in (0, 1):
         with torch.cuda.device(d):
             assert L.device_error() == 0
+
