@@ -971,6 +971,10 @@ def bench_other_casts(Q, x, dev, peak):
     out["nvfp4_swizzle_dim_m_rht_16384"] = timed(lambda: Q.nvfp4_gs_swizzle_dim_m_rht_cuda(x, gs_m, rht), algorithmic_bytes(M, N, "nvfp4") + 512)
     out["nvfp4_swizzle_dim_k_sr_dim_m_rht_sr_16384"] = timed(
         lambda: Q.nvfp4_gs_swizzle_dim_k_dim_m_rht_sr_cuda(x, gs, gs_m, rht, key, key_m), both_bytes + 32)
+    # fp32 -> bf16 stochastic rounding (gold fp32_to_bf16_sr / _global_offsets): 4 bytes in, 2 out, one Philox call per 8 elements
+    xf = x.float()
+    out["fp32_to_bf16_sr_16384"] = timed(lambda: Q.sr_bf16_global_cuda(xf, key), 6 * M * N + 16)
+    del xf
     x1 = x[:4096, :4096].contiguous()          # config 1 shape (fits L2: flush between iterations)
     s1 = Q.float8_tensorwise_scale_cuda(x1)
     y1 = torch.empty_like(x1)

@@ -394,6 +394,15 @@ int qcc_mxfp8_grouped_pad(const void *x, int64_t M, int64_t N, int flags, const 
 int qcc_nvfp4(const void *x, int64_t M, int64_t N, const float *outer, int outer_per_row, int flags,
               const uint64_t *philox_key, void *q, void *s, void *stream);
 
+/* fp32 -> bf16 with stochastic rounding: out = bf16((bits(x) + rand16) & 0xFFFF0000), rand16 uniform in [0, 2^16)
+ * (sr_bf16_f G:1841-1851, sr_bf16_global_f G:1887-1914; _sr_bf16_dither G:1828-1838).  x (M, N) fp32, out (M, N) bf16.
+ * Element (i, j) has the flat index g = (global_row + i) * num_col + global_col + j in its parent tensor and takes 16-bit
+ * piece g & 7 (half (g & 1) of word (g & 7) >> 1, low half first) of Philox4x32-10(counter = (g >> 3) + offset, key =
+ * seed), philox_key = device uint64 {seed, offset}: the cast of a tile equals that tile of the cast of the whole tensor.  global_row = global_col = 0,
+ * num_col = N is the plain recipe.  num_col >= global_col + N. */
+int qcc_sr_f32_to_bf16(const void *x, int64_t M, int64_t N, const uint64_t *philox_key, int64_t global_row, int64_t global_col,
+                       int64_t num_col, void *out, void *stream);
+
 /* scale (M, 1) fp32 = max |x| of every row / 2688, no clamp: the per-token outer scale that qcc_nvfp4 takes with
  * outer_per_row = 1 (nvfp4_gs_per_token_scale, G:1569-1573).  flags: 0 or QCC_RECIP_DIV.  One read of x. */
 int qcc_nvfp4_per_token_scale(const void *x, int64_t M, int64_t N, int flags, float *scale, void *stream);

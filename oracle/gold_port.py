@@ -172,6 +172,22 @@ def sr_dither22(first, n, key):
     return out
 
 
+def sr_bf16_global_f(x, key, global_row=0, global_col=0, num_col=None, **kwargs):
+    """fp32 -> bf16 stochastic rounding keyed on the element's position in its parent tensor (sr_bf16_global_f,
+    G:1887-1914); `sr_bf16_f` (G:1841-1851) is the case of a tile that is the whole tensor.  Returns `(out,)`."""
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous()
+    M, N = x.shape
+    seed, off = key_words(key)
+    out = torch.empty((M, N), dtype=torch.bfloat16)
+    lib().qco_sr_f32_to_bf16(_p(x), _i64(M), _i64(N), _u64(seed), _u64(off), _i64(global_row), _i64(global_col),
+                             _i64(N if num_col is None else num_col), _p(out))
+    return (out,)
+
+
+def sr_bf16_f(x, key, **kwargs):
+    return sr_bf16_global_f(x, key)
+
+
 def to_blocked_4d(scale):
     """G:1000-1037: (H, W) one-byte scales -> (ceil(H/128), ceil(W/4), 32, 16), padding 0."""
     H, W = scale.shape

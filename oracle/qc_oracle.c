@@ -262,6 +262,28 @@ void qco_e8m0_to_recip(const uint8_t *in, int64_t n, int floor_mode, float *out)
 {
     for (int64_t i = 0; i < n; i++) out[i] = e8m0_to_recip(in[i], floor_mode);
 }
+/*
+ * fp32 -> bf16 stochastic rounding (sr_bf16_f G:1841-1851, sr_bf16_global_f G:1887-1914, _sr_bf16_dither G:1828-1838):
+ * out = bf16((bits(x) + rand16) & 0xFFFF0000).  rand16 of the element with flat index g in its parent tensor
+ * (g = (global_row + i) * num_col + global_col + j) = 16-bit piece g & 7 of the 128 bits of Philox4x32-10 at counter
+ * (g >> 3) + offset: piece k is half (k & 1), low half first, of word k >> 1 -- eight elements per Philox call (the
+ * reference's own draw comes from a module that the installed PyTorch lacks, so the stream is this backend's).
+ */
+void qco_sr_f32_to_bf16(const uint32_t *xbits, int64_t M, int64_t N, uint64_t seed, uint64_t offset, int64_t global_row,
+                        int64_t global_col, int64_t num_col, uint16_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < M; i++)
+        for (int64_t j = 0; j < N; j++) {
+            uint64_t flat = (uint64_t)(global_row + i) * (uint64_t)num_col + (uint64_t)(global_col + j);
+            uint64_t g = (flat >> 3) + offset;
+            uint32_t c[4] = {(uint32_t)g, (uint32_t)(g >> 32), 0, 0};
+            philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+            uint32_t k = (uint32_t)(flat & 7), rand16 = (c[k >> 1] >> (16 * (k & 1))) & 0xFFFFu;
+            out[i * N + j] = (uint16_t)((xbits[i * N + j] + rand16) >> 16);
+        }
+}
+
 void qco_sr_dither22(int64_t first, int64_t n, uint64_t seed, uint64_t offset, uint32_t *out)
 {
     for (int64_t i = 0; i < n; i++) out[i] = sr_dither22((uint64_t)(first + i), seed, offset);

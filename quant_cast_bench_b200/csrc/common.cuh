@@ -391,12 +391,28 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1
     }
     return c;
 }
+// the same with one 64-bit product per word (IMAD.WIDE): half as many multiplies
+__device__ __forceinline__ uint4 philox4x32_10_wide(uint4 c, uint32_t k0, uint32_t k1)
+{
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        const uint64_t p0 = (uint64_t)0xD2511F53u * c.x, p1 = (uint64_t)0xCD9E8D57u * c.z;
+        c = make_uint4((uint32_t)(p1 >> 32) ^ c.y ^ k0, (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c.w ^ k1, (uint32_t)p0);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return c;
+}
 // the four 32-bit words for elements [4g, 4g+4) of the flat stream (g = flat index >> 2)
 __device__ __forceinline__ uint4 sr_words(uint64_t g, uint64_t seed, uint64_t offset)
 {
     g += offset;
+#ifdef QCC_PHILOX_WIDE
+    return philox4x32_10_wide(make_uint4((uint32_t)g, (uint32_t)(g >> 32), 0u, 0u), (uint32_t)seed, (uint32_t)(seed >> 32));
+#else
     return philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), 0u, 0u), (uint32_t)seed,
                          (uint32_t)(seed >> 32));
+#endif
 }
 // G:1401-1405: add a 22-bit dither into the mantissa bits fp4 discards, then truncate them
 __device__ __forceinline__ float sr_dither(float d, uint32_t word)

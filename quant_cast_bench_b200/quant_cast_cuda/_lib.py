@@ -73,6 +73,7 @@ SIGNATURES = {
     "qcc_nvfp4_transposed": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp]),
     "qcc_nvfp4_both": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _vp, _vp, _vp, _vp]),
     "qcc_fp8_block128": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "qcc_sr_f32_to_bf16": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _vp]),
     "qcc_nvfp4_per_token_scale": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
     "qcc_fp8_block128x128": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "qcc_amax_block128x128": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),

@@ -534,6 +534,28 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     return q.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn)
 
 
+def sr_bf16_global_cuda(x, key, global_row=0, global_col=0, num_col=None, **kwargs):
+    """gold sr_bf16_global_f (G:1887-1914): fp32 -> bf16 with stochastic rounding, the draw keyed on each element's
+    position in the parent tensor (`global_row`, `global_col`, `num_col`, as the reference's tiling framework passes
+    them), so the cast of a tile equals that tile of the cast of the whole tensor.  key: `philox_key(seed)`.  The
+    VALUES of the draw are this backend's Philox4x32-10 stream (the reference's comes from `torch.func._random`)."""
+    lib = L.load()
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "SR bf16 expects a contiguous 2-D CUDA fp32 tensor"
+    assert key is not None and key.is_cuda and key.numel() >= 2 and key.element_size() == 8, "key: philox_key(...) on the device"
+    M, N = x.shape
+    nc = N if num_col is None else int(num_col)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with _on_device(x.device):
+        L.check(lib.qcc_sr_f32_to_bf16(_p(x), M, N, _p(key), int(global_row), int(global_col), nc, _p(out), _stream(x)), "sr_f32_to_bf16")
+    L.launch_count += 1
+    return (out,)
+
+
+def sr_bf16_cuda(x, key, **kwargs):
+    """gold sr_bf16_f (G:1841-1851): the same cast keyed on the layout of the tensor it is given (tile-local)."""
+    return sr_bf16_global_cuda(x, key)
+
+
 def nvfp4_gs_per_token_scale_cuda(x):
     """Per-token fp32 outer scale, (M, 1): row amax / (448 * 6) without a clamp (nvfp4_gs_per_token_scale, G:1569-1573).
     `nvfp4_gs_cuda(x, scale)` / `nvfp4_gs_swizzle_cuda(x, scale)` take it as the outer scale.  (An all-zero row gets
@@ -834,6 +856,11 @@ def _inputs_nvfp4_rht_sr(M, K):
     return _inputs_nvfp4_rht(M, K) + (philox_key(0, device="cuda"), philox_key(1, device="cuda"))
 
 
+def _inputs_sr_bf16(M, K):
+    # a constant strictly between two bf16 grid points, as the reference's unbiasedness check wants (G:1872-1876)
+    return (torch.full((M, K), 1.0 + 0.003, dtype=torch.float32, device="cuda"), philox_key(0, device="cuda"))
+
+
 # (gold recipe name, gold attribute in quant_cast_gold.recipes, cuda fn, input builder, description)
 _TABLE = [
     ("fp8_tensorwise_precalc_scale", "Float8TensorwiseGold", float8_tensorwise_cuda, _inputs_tensorwise, "elementwise"),
@@ -870,6 +897,8 @@ _TABLE = [
     ("nvfp4_blocked_outer", "Nvfp4BlockedOuterGold", nvfp4_blocked_outer_cuda, _inputs_nvfp4_blocked_outer,
      "(1,16) block, fp4 qdata, swizzle, 128x128-blocked outer scale"),
     ("bf16_rht", "HadamardRht", hadamard_rht_cuda, _inputs_rht, "elementwise RHT"),
+    ("fp32_to_bf16_sr", "SrF32ToBf16", sr_bf16_cuda, _inputs_sr_bf16, ""),
+    ("fp32_to_bf16_sr_global_offsets", "SrF32ToBf16Global", sr_bf16_global_cuda, _inputs_sr_bf16, "elementwise SR with stateless RNG"),
 ]
 
 

@@ -512,7 +512,8 @@ def test_recipe_index_mirrors_reference_backends():
                      "mxfp8_32x32", "mxfp8_32x32_swizzle",
                      "mxfp8_32x32_dim_m_swizzle", "mxfp8_32x32_dim_km_swizzle", "mxfp8_32x32_qdata_dim_k_scale_dim_km_swizzle",
                      "fp8_deepseek_128x128", "fp8_rowwise", "fp8_colwise", "nvfp4", "nvfp4_swizzle",
-                     "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "nvfp4_blocked_outer", "bf16_rht"]
+                     "nvfp4_swizzle_dim_k_dim_m_rht", "nvfp4_swizzle_dim_k_sr_dim_m_rht_sr", "nvfp4_blocked_outer", "bf16_rht",
+                     "fp32_to_bf16_sr", "fp32_to_bf16_sr_global_offsets"]
     for name, r in Q.ALL_RECIPES:
         inputs = r.example_input_fn(256, 256)
         outs = r.cuda_fn(*inputs, global_row=0, global_col=0, num_col=256)
