@@ -27,7 +27,13 @@ hadamard_rht_rows_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ y, uin
 
 // max |RHT(x.t())|: a warp takes 16 rows x 128 columns (lane = four adjacent columns), transforms down the rows
 // and keeps the packed bf16 maximum; one atomic max per CTA on the bits of a non-negative fp32.
-__global__ void __launch_bounds__(RHT_THREADS)
+#ifndef QCC_RHTA_MINCTAS
+#define QCC_RHTA_MINCTAS 3   // 80 registers (a few spilled words) and 3 CTAs per SM: 6 % faster than 101 registers and 2
+#endif
+#ifndef QCC_RHTA_CTAS_PER_SM
+#define QCC_RHTA_CTAS_PER_SM 16
+#endif
+__global__ void __launch_bounds__(RHT_THREADS, QCC_RHTA_MINCTAS)
 rht_t_amax_kernel(const uint16_t *__restrict__ x, int M, int N, const uint16_t *__restrict__ rht,
                   unsigned int *__restrict__ out_bits)
 {
@@ -106,7 +112,7 @@ extern "C" int qcc_nvfp4_rht_amax(const void *x, int64_t M, int64_t N, const voi
     if (ce != cudaSuccess) return (int)ce;
     const long long items = (M / 16) * ((N + 127) / 128);
     long long grid = (items + RHT_THREADS / 32 - 1) / (RHT_THREADS / 32);
-    const long long cap = (long long)sm_count() * 16;
+    const long long cap = (long long)sm_count() * QCC_RHTA_CTAS_PER_SM;
     if (grid > cap) grid = cap;
     rht_t_amax_kernel<<<(unsigned)grid, RHT_THREADS, 0, st>>>((const uint16_t *)x, (int)M, (int)N, (const uint16_t *)rht,
                                                             (unsigned int *)out);
