@@ -20,6 +20,8 @@
 //   fp8_block128x128(x, recip_div)                          -> (q, scale (M/128, N/128))
 //   mxfp8_32x32(x, rowwise, colwise, swizzle, transposed_data) -> [qk, sk][qm] [sm] one e8m0 scale per 32x32 block
 //   mxfp4(x, swizzle)                                       -> (q (M, N/2), scale)
+//   nvfp4_per_token_scale(x, recip_div)                     -> (M, 1) fp32 outer scales
+//   sr_f32_to_bf16(x, key, global_row, global_col, num_col) -> bf16       fp32 input, stochastic rounding
 //
 // recip_div: QCC_RECIP_DIV (divisions by a constant as eager PyTorch computes them on a CUDA device).
 // Built by quant_cast_bench_b200/build.py into lib/libquant_cast_torch.so, which links against libquant_cast_cuda.so.
@@ -301,6 +303,30 @@ std::tuple<at::Tensor, at::Tensor> mxfp4_cuda(const at::Tensor &x, bool swizzle)
     return {q.view(at::kFloat4_e2m1fn_x2), s.view(at::kFloat8_e8m0fnu)};
 }
 
+at::Tensor nvfp4_per_token_scale_cuda(const at::Tensor &x, bool recip_div)
+{
+    check_x_cuda(x);
+    const c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor s = at::empty({x.size(0), 1}, x.options().dtype(at::kFloat));
+    ok(qcc_nvfp4_per_token_scale(x.data_ptr(), x.size(0), x.size(1), recip_div ? QCC_RECIP_DIV : 0, s.data_ptr<float>(), stream_of(x)),
+       "nvfp4_per_token_scale");
+    return s;
+}
+
+at::Tensor sr_f32_to_bf16_cuda(const at::Tensor &x, const at::Tensor &key, int64_t global_row, int64_t global_col, int64_t num_col)
+{
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == at::kFloat,
+                "quant_cast_cuda: sr_f32_to_bf16 takes a contiguous 2-D CUDA fp32 tensor");
+    TORCH_CHECK(key.is_cuda() && key.element_size() == 8 && key.numel() >= 2 && key.is_contiguous(),
+                "quant_cast_cuda: key must be a CUDA tensor of two 64-bit words [seed, offset]");
+    const c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor out = at::empty(x.sizes(), x.options().dtype(at::kBFloat16));
+    ok(qcc_sr_f32_to_bf16(x.data_ptr(), x.size(0), x.size(1), static_cast<const uint64_t *>(key.data_ptr()), global_row, global_col,
+                          num_col < 0 ? x.size(1) : num_col, out.data_ptr(), stream_of(x)),
+       "sr_f32_to_bf16");
+    return out;
+}
+
 // ---------------------------------------------------------------------------------------- Meta (shape) implementations
 at::Tensor like(const at::Tensor &x, std::vector<int64_t> shape, at::ScalarType dt) { return at::empty(shape, x.options().dtype(dt)); }
 
@@ -395,6 +421,17 @@ std::tuple<at::Tensor, at::Tensor> mxfp4_meta(const at::Tensor &x, bool swizzle)
     return {like(x, {x.size(0), x.size(1) / 2}, at::kFloat4_e2m1fn_x2), like(x, scale_shape(x.size(0), x.size(1) / 32, swizzle), at::kFloat8_e8m0fnu)};
 }
 
+at::Tensor nvfp4_per_token_scale_meta(const at::Tensor &x, bool)
+{
+    check_x(x);
+    return like(x, {x.size(0), 1}, at::kFloat);
+}
+at::Tensor sr_f32_to_bf16_meta(const at::Tensor &x, const at::Tensor &, int64_t, int64_t, int64_t)
+{
+    TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kFloat, "quant_cast_cuda: sr_f32_to_bf16 takes a 2-D fp32 tensor");
+    return like(x, x.sizes().vec(), at::kBFloat16);
+}
+
 }  // namespace
 
 TORCH_LIBRARY(quant_cast_cuda_native, m)
@@ -413,6 +450,8 @@ TORCH_LIBRARY(quant_cast_cuda_native, m)
     m.def("fp8_block128x128(Tensor x, bool recip_div=False) -> (Tensor, Tensor)");
     m.def("mxfp8_32x32(Tensor x, bool rowwise, bool colwise, bool swizzle, bool transposed_data=True) -> Tensor[]");
     m.def("mxfp4(Tensor x, bool swizzle) -> (Tensor, Tensor)");
+    m.def("nvfp4_per_token_scale(Tensor x, bool recip_div=False) -> Tensor");
+    m.def("sr_f32_to_bf16(Tensor x, Tensor key, int global_row=0, int global_col=0, int num_col=-1) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(quant_cast_cuda_native, CUDA, m)
@@ -431,6 +470,8 @@ TORCH_LIBRARY_IMPL(quant_cast_cuda_native, CUDA, m)
     m.impl("fp8_block128x128", fp8_block128x128_cuda);
     m.impl("mxfp8_32x32", mxfp8_32x32_cuda);
     m.impl("mxfp4", mxfp4_cuda);
+    m.impl("nvfp4_per_token_scale", nvfp4_per_token_scale_cuda);
+    m.impl("sr_f32_to_bf16", sr_f32_to_bf16_cuda);
 }
 
 TORCH_LIBRARY_IMPL(quant_cast_cuda_native, Meta, m)
@@ -449,4 +490,6 @@ TORCH_LIBRARY_IMPL(quant_cast_cuda_native, Meta, m)
     m.impl("fp8_block128x128", fp8_block128x128_meta);
     m.impl("mxfp8_32x32", mxfp8_32x32_meta);
     m.impl("mxfp4", mxfp4_meta);
+    m.impl("nvfp4_per_token_scale", nvfp4_per_token_scale_meta);
+    m.impl("sr_f32_to_bf16", sr_f32_to_bf16_meta);
 }

@@ -144,6 +144,18 @@ def mxfp4_native(x, swizzle=False, **kwargs):
     return tuple(ops.mxfp4(x, swizzle))
 
 
+def nvfp4_gs_per_token_scale_native(x):
+    return ops.nvfp4_per_token_scale(x, _recip())
+
+
+def sr_bf16_global_native(x, key, global_row=0, global_col=0, num_col=None, **kwargs):
+    return (ops.sr_f32_to_bf16(x, key, int(global_row), int(global_col), -1 if num_col is None else int(num_col)),)
+
+
+def sr_bf16_native(x, key, **kwargs):
+    return (ops.sr_f32_to_bf16(x, key, 0, 0, -1),)
+
+
 # (gold function name in the golden vectors, operator-backed function, aux input): the other recipe families
 MORE_NATIVE = [
     ("rowwise_precalc_f", rowwise_precalc_native, "row_scale"), ("colwise_precalc_f", colwise_precalc_native, "col_scale"),

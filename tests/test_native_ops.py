@@ -98,6 +98,20 @@ def test_stochastic_and_two_orientation_forms_match_the_ctypes_route():
         assert_same_bits(a, b, "mxfp4 blocked")
 
 
+@pytest.mark.gpu
+def test_per_token_scale_and_stochastic_bf16_match_the_ctypes_route():
+    from quant_cast_bench_b200 import quant_cast_cuda as Q
+    x = torch.randn(200, 328, device="cuda", dtype=torch.bfloat16)
+    assert_same_bits(N.nvfp4_gs_per_token_scale_native(x), Q.nvfp4_gs_per_token_scale_cuda(x), "per-token scale")
+    xf = torch.randn(96, 200, device="cuda")
+    key = Q.philox_key(3, 9, device="cuda")
+    assert_same_bits(N.sr_bf16_native(xf, key)[0], Q.sr_bf16_cuda(xf, key)[0], "sr bf16")
+    assert_same_bits(N.sr_bf16_global_native(xf, key, global_row=4, global_col=16, num_col=512)[0],
+                     Q.sr_bf16_global_cuda(xf, key, global_row=4, global_col=16, num_col=512)[0], "sr bf16 global")
+    m = N.sr_bf16_native(xf.to("meta"), key.to("meta"))[0]
+    assert m.device.type == "meta" and m.dtype == torch.bfloat16 and tuple(m.shape) == (96, 200)
+
+
 def test_operators_have_no_cpu_implementation_and_check_their_arguments():
     with pytest.raises(NotImplementedError):
         torch.ops.quant_cast_cuda_native.mxfp8(torch.zeros(32, 32, dtype=torch.bfloat16), True, False, False, "rceil")
