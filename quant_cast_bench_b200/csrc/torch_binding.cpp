@@ -48,6 +48,11 @@ void check_x_cuda(const at::Tensor &x)
     check_x(x);
     TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "quant_cast_cuda: x must be a contiguous CUDA tensor (there is no CPU implementation)");
 }
+// an auxiliary tensor (scale, key) must live on x's device: the kernels read it there
+void same_device(const at::Tensor &x, const at::Tensor &aux, const char *what)
+{
+    TORCH_CHECK(aux.device() == x.device(), "quant_cast_cuda: ", what, " is on ", aux.device(), ", x on ", x.device());
+}
 void *stream_of(const at::Tensor &x) { return c10::cuda::getCurrentCUDAStream(x.get_device()).stream(); }
 void ok(int rc, const char *what) { TORCH_CHECK(rc == 0, "quant_cast_cuda: ", what, " failed with code ", rc); }
 int fmt_of(const std::string &fmt)
@@ -91,6 +96,7 @@ at::Tensor fp8_tensorwise_cuda(const at::Tensor &x, const at::Tensor &scale, std
 {
     check_x_cuda(x);
     TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1, "quant_cast_cuda: scale must be one CUDA fp32 value");
+    same_device(x, scale, "scale");
     const c10::cuda::CUDAGuard guard(x.device());
     at::Tensor q = bytes(x.sizes(), x);
     ok(qcc_fp8_tensorwise(x.data_ptr(), x.numel(), scale.data_ptr<float>(), fmt_of(fmt), q.data_ptr(), stream_of(x)), "fp8_tensorwise");
@@ -160,6 +166,7 @@ std::tuple<at::Tensor, at::Tensor> nvfp4_impl(const at::Tensor &x, const at::Ten
 {
     check_x_cuda(x);
     TORCH_CHECK(outer_in.is_cuda() && outer_in.scalar_type() == at::kFloat, "quant_cast_cuda: outer_scale must be a CUDA fp32 tensor");
+    same_device(x, outer_in, "outer_scale");
     const c10::cuda::CUDAGuard guard(x.device());
     const int64_t M = x.size(0), N = x.size(1);
     const at::Tensor outer = outer_in.contiguous();
@@ -194,6 +201,7 @@ std::tuple<at::Tensor, at::Tensor> nvfp4_sr_cuda(const at::Tensor &x, const at::
 {
     TORCH_CHECK(key.is_cuda() && key.element_size() == 8 && key.numel() >= 2 && key.is_contiguous(),
                 "quant_cast_cuda: key must be a CUDA tensor of two 64-bit words [seed, offset]");
+    same_device(x, key, "key");
     return nvfp4_impl(x, outer_scale, static_cast<const uint64_t *>(key.data_ptr()), swizzle, transposed, recip_div);
 }
 
@@ -203,6 +211,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> nvfp4_both_cuda(const
     check_x_cuda(x);
     TORCH_CHECK(outer_scale.is_cuda() && outer_scale.scalar_type() == at::kFloat && outer_scale.numel() == 1,
                 "quant_cast_cuda: outer_scale must be one CUDA fp32 value");
+    same_device(x, outer_scale, "outer_scale");
     const c10::cuda::CUDAGuard guard(x.device());
     const int64_t M = x.size(0), N = x.size(1);
     TORCH_CHECK(M % 32 == 0 && N % 32 == 0, "quant_cast_cuda: nvfp4 in both orientations needs M % 32 == 0 and N % 32 == 0");
@@ -219,6 +228,7 @@ at::Tensor fp8_rowwise_precalc_cuda(const at::Tensor &x, const at::Tensor &scale
     check_x_cuda(x);
     const int64_t M = x.size(0), N = x.size(1);
     TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == M, "quant_cast_cuda: scale must hold one CUDA fp32 value per row");
+    same_device(x, scale, "scale");
     const c10::cuda::CUDAGuard guard(x.device());
     const at::Tensor sc = scale.contiguous();
     at::Tensor q = bytes({M, N}, x);
@@ -231,6 +241,7 @@ at::Tensor fp8_colwise_precalc_cuda(const at::Tensor &x, const at::Tensor &scale
     check_x_cuda(x);
     const int64_t M = x.size(0), N = x.size(1);
     TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == N, "quant_cast_cuda: scale must hold one CUDA fp32 value per column");
+    same_device(x, scale, "scale");
     TORCH_CHECK(M % 16 == 0 && N % 8 == 0, "quant_cast_cuda: colwise fp8 needs M % 16 == 0 and N % 8 == 0");
     const c10::cuda::CUDAGuard guard(x.device());
     const at::Tensor sc = scale.contiguous();
@@ -319,6 +330,7 @@ at::Tensor sr_f32_to_bf16_cuda(const at::Tensor &x, const at::Tensor &key, int64
                 "quant_cast_cuda: sr_f32_to_bf16 takes a contiguous 2-D CUDA fp32 tensor");
     TORCH_CHECK(key.is_cuda() && key.element_size() == 8 && key.numel() >= 2 && key.is_contiguous(),
                 "quant_cast_cuda: key must be a CUDA tensor of two 64-bit words [seed, offset]");
+    same_device(x, key, "key");
     const c10::cuda::CUDAGuard guard(x.device());
     at::Tensor out = at::empty(x.sizes(), x.options().dtype(at::kBFloat16));
     ok(qcc_sr_f32_to_bf16(x.data_ptr(), x.size(0), x.size(1), static_cast<const uint64_t *>(key.data_ptr()), global_row, global_col,

@@ -189,7 +189,7 @@ def float8_tensorwise_cuda(x, scale, fmt="e4m3", **kwargs):
     lib = L.load()
     _check_x(x)
     f = _fmt(fmt)
-    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1
+    assert scale.device == x.device and scale.dtype == torch.float32 and scale.numel() == 1
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
         L.check(lib.qcc_fp8_tensorwise(_p(x), x.numel(), _p(scale), f, _p(q), _stream(x)), "fp8_tensorwise")
@@ -203,7 +203,7 @@ def float8_tensorwise_from_amax_cuda(x, amax, fmt="e4m3"):
     lib = L.load()
     _check_x(x)
     f = _fmt(fmt)
-    assert amax.is_cuda and amax.dtype == torch.float32 and amax.numel() == 1
+    assert amax.device == x.device and amax.dtype == torch.float32 and amax.numel() == 1
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     scale = torch.empty((), dtype=torch.float32, device=x.device)
     with _on_device(x.device):
@@ -245,7 +245,7 @@ def rowwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
     _check_x(x)
     f = _fmt(fmt)
     M, N = x.shape
-    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == M and scale.is_contiguous()
+    assert scale.device == x.device and scale.dtype == torch.float32 and scale.numel() == M and scale.is_contiguous()
     q = torch.empty((M, N), dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
         L.check(lib.qcc_fp8_rowwise_precalc(_p(x), M, N, _p(scale), f, _p(q), _stream(x)), "fp8_rowwise_precalc")
@@ -293,7 +293,7 @@ def colwise_precalc_cuda(x, scale, fmt="e4m3", **kwargs):
     f = _fmt(fmt)
     M, N = x.shape
     assert N % 8 == 0 and M % 16 == 0, f"colwise fp8 needs N % 8 == 0 and M % 16 == 0, got {M}x{N}"
-    assert scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == N and scale.is_contiguous()
+    assert scale.device == x.device and scale.dtype == torch.float32 and scale.numel() == N and scale.is_contiguous()
     q = torch.empty((N, M), dtype=torch.uint8, device=x.device)
     with _on_device(x.device):
         L.check(lib.qcc_fp8_colwise_precalc(_p(x), M, N, _p(scale), f, _p(q), _stream(x)), "fp8_colwise_precalc")
@@ -508,7 +508,7 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     _check_x(x)
     M, N = x.shape
     dev = x.device
-    assert outer_scale.is_cuda and outer_scale.dtype == torch.float32, "outer_scale must be a CUDA fp32 tensor"
+    assert outer_scale.device == x.device and outer_scale.dtype == torch.float32, "outer_scale must be a CUDA fp32 tensor"
     per_row = int(outer_scale.ndim == 2)
     o = outer_scale.contiguous()
     if per_row:
@@ -516,7 +516,7 @@ def _nvfp4(x, outer_scale, flags, key=None, transposed=False):
     else:
         assert o.numel() == 1
     if flags & L.SR:
-        assert key is not None and key.is_cuda and key.numel() >= 2 and key.element_size() == 8, (
+        assert key is not None and key.device == x.device and key.numel() >= 2 and key.element_size() == 8, (
             "stochastic rounding needs a uint64 [seed, offset] key on the device (see philox_key)")
     swz = bool(flags & L.SWIZZLE)
     with _on_device(dev):
@@ -541,7 +541,7 @@ def sr_bf16_global_cuda(x, key, global_row=0, global_col=0, num_col=None, **kwar
     VALUES of the draw are this backend's Philox4x32-10 stream (the reference's comes from `torch.func._random`)."""
     lib = L.load()
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "SR bf16 expects a contiguous 2-D CUDA fp32 tensor"
-    assert key is not None and key.is_cuda and key.numel() >= 2 and key.element_size() == 8, "key: philox_key(...) on the device"
+    assert key is not None and key.device == x.device and key.numel() >= 2 and key.element_size() == 8, "key: philox_key(...) on the device"
     M, N = x.shape
     nc = N if num_col is None else int(num_col)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
@@ -577,7 +577,7 @@ def nvfp4_from_amax_cuda(x, amax, swizzle=True):
     _check_x(x)
     M, N = x.shape
     assert N % 16 == 0, f"nvfp4 needs N % 16 == 0, got N={N}"
-    assert amax.is_cuda and amax.dtype == torch.float32 and amax.numel() == 1
+    assert amax.device == x.device and amax.dtype == torch.float32 and amax.numel() == 1
     dev = x.device
     q = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
     s_ = torch.empty(blocked_shape(M, N // 16) if swizzle else (M, N // 16), dtype=torch.uint8, device=dev)
@@ -608,7 +608,7 @@ def nvfp4_blocked_outer_cuda(x, outer_blocked, **kwargs):
     _check_x(x)
     M, N = x.shape
     assert M % 128 == 0 and N % 128 == 0, f"needs 128x128 blocks tiling the input, got {M}x{N}"
-    assert outer_blocked.is_cuda and outer_blocked.dtype == torch.float32 and outer_blocked.shape == (M // 128, N // 128), (
+    assert outer_blocked.device == x.device and outer_blocked.dtype == torch.float32 and outer_blocked.shape == (M // 128, N // 128), (
         "outer_blocked: (M/128, N/128) fp32 on the device")
     q = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
     s = torch.empty(blocked_shape(M, N // 16), dtype=torch.uint8, device=x.device)
@@ -658,7 +658,7 @@ def _nvfp4_both(x, outer_scale, flags):
     _check_x(x)
     M, N = x.shape
     dev = x.device
-    assert outer_scale.is_cuda and outer_scale.dtype == torch.float32 and outer_scale.numel() == 1
+    assert outer_scale.device == x.device and outer_scale.dtype == torch.float32 and outer_scale.numel() == 1
     assert M % 32 == 0 and N % 32 == 0, f"fused nvfp4 needs M % 32 == 0 and N % 32 == 0, got {M}x{N}"
     swz = bool(flags & L.SWIZZLE)
     qk = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
